@@ -1,0 +1,290 @@
+// pybind11 bindings: torch tensors in, `fb_*` kernel launches out (on the current CUDA stream).
+// No logic lives here beyond argument checking; the kernels are in csrc/kernels and csrc/comm.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <vector>
+
+#include "flodl_b200.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+void* stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+void check(int rc, const char* what) {
+  if (rc == 0) return;
+  if (rc > 0) {
+    TORCH_CHECK(false, what, ": CUDA error ", rc, " (", cudaGetErrorString(static_cast<cudaError_t>(rc)), ")");
+  }
+  TORCH_CHECK(false, what, ": rejected arguments (code ", rc, ")");
+}
+
+bool is_bf16(const Tensor& t) { return t.scalar_type() == at::kBFloat16; }
+void want_cuda(const Tensor& t, const char* name) { TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor"); }
+void want_f32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), name, " must be a contiguous fp32 CUDA tensor");
+}
+void want_float_kind(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && (t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16), name,
+              " must be fp32 or bf16 on CUDA");
+}
+template <typename T = void>
+T* ptr(const OptTensor& t) { return t.has_value() ? static_cast<T*>(t->data_ptr()) : nullptr; }
+
+// one status word per device, shared by every kernel that has bounded waits
+Tensor& status_word(int device) {
+  static std::vector<Tensor> words(64);
+  TORCH_CHECK(device >= 0 && device < 64);
+  if (!words[device].defined())
+    words[device] = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  return words[device];
+}
+
+// ------------------------------------------------------------------------------------------ GEMM
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, const OptTensor& bias, int epi,
+          const OptTensor& aux, const OptTensor& alpha, bool accumulate, int split_k, int config) {
+  want_cuda(a, "a");
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(is_bf16(a) && is_bf16(b), "gemm operands must be bf16");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm takes 2-D tensors");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm needs unit inner strides");
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm K mismatch: ", K, " vs ", Kb);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm output shape mismatch");
+  TORCH_CHECK(out.scalar_type() == at::kFloat || is_bf16(out), "gemm output must be fp32 or bf16");
+  if (bias.has_value()) TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must be [N]");
+  if (aux.has_value()) TORCH_CHECK(is_bf16(*aux) && aux->stride(1) == 1 && aux->size(0) == M && aux->size(1) == N, "aux must be bf16 [M,N]");
+  if (alpha.has_value()) TORCH_CHECK(alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "alpha must be one fp32");
+  Tensor& st = status_word(a.get_device());
+  int rc = fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                        out.stride(0), a_mn, b_mn, out.scalar_type() == at::kFloat, ptr<const void>(bias),
+                        bias.has_value() && bias->scalar_type() == at::kFloat, epi, ptr<void>(aux),
+                        aux.has_value() ? aux->stride(0) : 0, ptr<const float>(alpha), accumulate, split_k, config,
+                        st.data_ptr<int>(), stream_of(a));
+  check(rc, "fb_gemm_bf16");
+}
+
+int gemm_pick_config(int M, int N, int K, int split_k) { return fb_gemm_pick_config(M, N, K, split_k); }
+
+int read_status(int device) {
+  return status_word(device).item<int>();
+}
+void clear_status(int device) { status_word(device).zero_(); }
+
+// ------------------------------------------------------------------------------------- LayerNorm
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const OptTensor& residual, const OptTensor& gamma,
+                                  const OptTensor& beta, double eps, double p_drop, uint64_t seed, bool want_pre) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  const int64_t cols = x.size(-1);
+  const int64_t rows = x.numel() / cols;
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == x.scalar_type() && residual->numel() == x.numel());
+  if (gamma.has_value()) want_f32(*gamma, "gamma");
+  if (beta.has_value()) want_f32(*beta, "beta");
+  Tensor y = torch::empty_like(x);
+  Tensor pre = want_pre ? torch::empty_like(x) : Tensor();
+  auto fopts = torch::dtype(torch::kFloat).device(x.device());
+  Tensor mean = torch::empty({rows}, fopts), rstd = torch::empty({rows}, fopts);
+  int rc = fb_layernorm_fwd(x.data_ptr(), ptr<const void>(residual), ptr<const float>(gamma), ptr<const float>(beta),
+                            y.data_ptr(), want_pre ? pre.data_ptr() : nullptr, mean.data_ptr<float>(),
+                            rstd.data_ptr<float>(), (int)rows, (int)cols, (float)eps, (float)p_drop, seed, is_bf16(x),
+                            stream_of(x));
+  check(rc, "fb_layernorm_fwd");
+  return {y, pre, mean, rstd};
+}
+
+// returns {dpre, dx_drop (or undefined), dgamma, dbeta}
+std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& pre, const Tensor& mean, const Tensor& rstd,
+                                  const OptTensor& gamma, double p_drop, uint64_t seed, bool want_dx_drop,
+                                  bool want_param_grads, const OptTensor& dgamma_acc, const OptTensor& dbeta_acc) {
+  want_float_kind(dy, "dy");
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous() && pre.is_contiguous() && dy.scalar_type() == pre.scalar_type());
+  const int64_t cols = dy.size(-1);
+  const int64_t rows = dy.numel() / cols;
+  Tensor dpre = torch::empty_like(dy);
+  Tensor dxd = want_dx_drop ? torch::empty_like(dy) : Tensor();
+  auto fopts = torch::dtype(torch::kFloat).device(dy.device());
+  Tensor partial, dgamma, dbeta;
+  bool accumulate = false;
+  if (want_param_grads) {
+    const int grid = fb_layernorm_bwd_grid((int)rows);
+    partial = torch::empty({grid, 2, cols}, fopts);
+    if (dgamma_acc.has_value()) {
+      want_f32(*dgamma_acc, "dgamma_acc");
+      want_f32(*dbeta_acc, "dbeta_acc");
+      dgamma = *dgamma_acc;
+      dbeta = *dbeta_acc;
+      accumulate = true;
+    } else {
+      dgamma = torch::empty({cols}, fopts);
+      dbeta = torch::empty({cols}, fopts);
+    }
+  }
+  int rc = fb_layernorm_bwd(dy.data_ptr(), pre.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                            ptr<const float>(gamma), dpre.data_ptr(), want_dx_drop ? dxd.data_ptr() : nullptr,
+                            want_param_grads ? partial.data_ptr<float>() : nullptr,
+                            want_param_grads ? dgamma.data_ptr<float>() : nullptr,
+                            want_param_grads ? dbeta.data_ptr<float>() : nullptr, accumulate, (int)rows, (int)cols,
+                            (float)p_drop, seed, is_bf16(dy), stream_of(dy));
+  check(rc, "fb_layernorm_bwd");
+  return {dpre, dxd, dgamma, dbeta};
+}
+
+// --------------------------------------------------------------------------------- elementwise
+Tensor gelu_fwd(const Tensor& x, bool tanh_approx) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous());
+  Tensor y = torch::empty_like(x);
+  check(fb_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), tanh_approx, is_bf16(x), stream_of(x)), "fb_gelu_fwd");
+  return y;
+}
+Tensor gelu_bwd(const Tensor& dy, const Tensor& x, bool tanh_approx) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dy.scalar_type() == x.scalar_type());
+  Tensor dx = torch::empty_like(x);
+  check(fb_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), tanh_approx, is_bf16(x), stream_of(x)), "fb_gelu_bwd");
+  return dx;
+}
+Tensor dropout(const Tensor& x, double p, uint64_t seed) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous());
+  Tensor y = torch::empty_like(x);
+  check(fb_dropout(x.data_ptr(), y.data_ptr(), x.numel(), (float)p, seed, is_bf16(x), stream_of(x)), "fb_dropout");
+  return y;
+}
+void colsum(const Tensor& x, Tensor& out) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1);
+  want_f32(out, "out");
+  TORCH_CHECK(out.numel() == x.size(1));
+  check(fb_colsum(x.data_ptr(), out.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), is_bf16(x), stream_of(x)), "fb_colsum");
+}
+void cast_into(const Tensor& x, Tensor& y, double scale) {
+  want_float_kind(x, "x");
+  want_float_kind(y, "y");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel());
+  check(fb_cast(x.data_ptr(), y.data_ptr(), x.numel(), (float)scale, is_bf16(x), is_bf16(y), stream_of(x)), "fb_cast");
+}
+
+// ------------------------------------------------------------------------------------------- CE
+// logits [rows, V] (unit inner stride). Returns {loss (0-dim fp32), dlogits, count_inv}.
+// With `inplace` the gradient overwrites the logits.
+std::vector<Tensor> softmax_ce(Tensor& logits, const Tensor& targets, int64_t ignore_index, bool want_grad, bool inplace) {
+  want_float_kind(logits, "logits");
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [rows, V] with unit inner stride");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0));
+  const int64_t rows = logits.size(0), V = logits.size(1);
+  auto fopts = torch::dtype(torch::kFloat).device(logits.device());
+  Tensor count_inv = torch::empty({2}, fopts), row_loss = torch::empty({rows}, fopts), loss = torch::empty({}, fopts);
+  Tensor dl;
+  if (want_grad) {
+    if (inplace) dl = logits;
+    else {
+      // keep the padded leading dimension so rows stay 16-byte aligned
+      const int64_t ld = logits.stride(0);
+      dl = torch::empty({rows, ld}, logits.options()).narrow(1, 0, V);
+    }
+  }
+  int rc = fb_softmax_ce(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), (int)rows, (int)V, ignore_index,
+                         want_grad ? dl.data_ptr() : nullptr, want_grad ? dl.stride(0) : 0, count_inv.data_ptr<float>(),
+                         row_loss.data_ptr<float>(), loss.data_ptr<float>(), is_bf16(logits), stream_of(logits));
+  check(rc, "fb_softmax_ce");
+  return {loss, dl, count_inv};
+}
+void scale_rows(Tensor& x, const Tensor& scalar) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1);
+  TORCH_CHECK(scalar.is_cuda() && scalar.scalar_type() == at::kFloat && scalar.numel() == 1);
+  check(fb_scale_rows(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), scalar.data_ptr<float>(), is_bf16(x), stream_of(x)), "fb_scale_rows");
+}
+
+// ---------------------------------------------------------------------------------- optimizers
+void adam_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor& p16, const Tensor& hyper, double b1,
+               double b2, double eps, const OptTensor& grad_scale) {
+  want_f32(p, "p");
+  want_f32(m, "m");
+  want_f32(v, "v");
+  want_f32(hyper, "hyper");
+  c10::cuda::CUDAGuard guard(p.device());
+  want_float_kind(g, "g");
+  TORCH_CHECK(g.is_contiguous() && g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel() && hyper.numel() >= 4);
+  if (p16.has_value()) TORCH_CHECK(is_bf16(*p16) && p16->is_contiguous() && p16->numel() == p.numel());
+  check(fb_adam_step(p.data_ptr<float>(), g.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), ptr<void>(p16), p.numel(),
+                     hyper.data_ptr<float>(), (float)b1, (float)b2, (float)eps, ptr<const float>(grad_scale), is_bf16(g),
+                     stream_of(p)),
+        "fb_adam_step");
+}
+void sgd_step(Tensor& p, const Tensor& g, const OptTensor& buf, const OptTensor& p16, const Tensor& hyper,
+              const OptTensor& grad_scale) {
+  want_f32(p, "p");
+  want_f32(hyper, "hyper");
+  c10::cuda::CUDAGuard guard(p.device());
+  want_float_kind(g, "g");
+  TORCH_CHECK(g.is_contiguous() && g.numel() == p.numel() && hyper.numel() >= 4);
+  if (buf.has_value()) want_f32(*buf, "buf");
+  check(fb_sgd_step(p.data_ptr<float>(), g.data_ptr(), ptr<float>(buf), ptr<void>(p16), p.numel(), hyper.data_ptr<float>(),
+                    ptr<const float>(grad_scale), is_bf16(g), stream_of(p)),
+        "fb_sgd_step");
+}
+// returns fp32 [2] = {norm * extra_scale, clip coefficient}
+Tensor grad_norm(const Tensor& g, double max_norm, double extra_scale) {
+  want_float_kind(g, "g");
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_contiguous());
+  auto fopts = torch::dtype(torch::kFloat).device(g.device());
+  Tensor partial = torch::empty({fb_grad_norm_parts(g.numel())}, fopts);
+  Tensor out = torch::empty({2}, fopts);
+  check(fb_grad_norm(g.data_ptr(), g.numel(), partial.data_ptr<float>(), (float)max_norm, (float)extra_scale,
+                     out.data_ptr<float>(), is_bf16(g), stream_of(g)),
+        "fb_grad_norm");
+  return out;
+}
+
+}  // namespace
+
+void bind_comm(py::module_& m);     // comm.cpp
+void bind_runtime(py::module_& m);  // runtime.cpp
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("bias") = py::none(), py::arg("epi") = 0, py::arg("aux") = py::none(), py::arg("alpha") = py::none(),
+        py::arg("accumulate") = false, py::arg("split_k") = 1, py::arg("config") = -1);
+  m.def("gemm_pick_config", &gemm_pick_config);
+  m.def("read_status", &read_status);
+  m.def("clear_status", &clear_status);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("gelu_fwd", &gelu_fwd);
+  m.def("gelu_bwd", &gelu_bwd);
+  m.def("dropout", &dropout);
+  m.def("colsum", &colsum);
+  m.def("cast_into", &cast_into);
+  m.def("softmax_ce", &softmax_ce);
+  m.def("scale_rows", &scale_rows);
+  m.def("adam_step", &adam_step, py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p16"), py::arg("hyper"),
+        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none());
+  m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
+        py::arg("grad_scale") = py::none());
+  m.def("grad_norm", &grad_norm);
+  bind_comm(m);
+  bind_runtime(m);
+}

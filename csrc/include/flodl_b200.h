@@ -1,0 +1,121 @@
+/* C ABI of the flodl-b200 native library.
+ *
+ * Plays the role of the reference's C shim header (flodl-sys/shim.h): a flat `extern "C"` surface
+ * that a binding in any language can call. Where the shim forwards to libtorch, these entry points
+ * launch this library's own sm_100a kernels. Conventions:
+ *   - every function returns 0 on success, a cudaError_t (> 0) from the launch, or a negative
+ *     code for a rejected argument (-2 dtype/mode, -3 alignment, -4 unsupported shape, -5 world);
+ *   - pointers are device pointers unless a comment says otherwise;
+ *   - `stream` is a cudaStream_t passed as void*;
+ *   - nothing here allocates device memory unless its comment says so.
+ */
+#ifndef FLODL_B200_H_
+#define FLODL_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype / device tags: same numbering as the reference ABI (flodl-sys/shim.h:920-929). */
+#define FLODL_FLOAT16 5
+#define FLODL_BFLOAT16 15
+#define FLODL_FLOAT32 6
+#define FLODL_FLOAT64 7
+#define FLODL_INT32 3
+#define FLODL_INT64 4
+#define FLODL_CPU 0
+#define FLODL_CUDA 1
+
+/* GEMM epilogues */
+#define FB_EPI_NONE 0
+#define FB_EPI_GELU_ERF 1    /* C = gelu(acc + bias); aux (optional) receives acc + bias   */
+#define FB_EPI_DGELU_ERF 2   /* C = acc * gelu'(aux)                                        */
+#define FB_EPI_GELU_TANH 3
+#define FB_EPI_DGELU_TANH 4
+
+/* symmetric-memory collectives */
+#define FB_MAX_RANKS 16
+#define FB_MAX_BLOCKS 256
+#define FB_SIGNAL_PAD_BYTES (FB_MAX_BLOCKS * FB_MAX_RANKS * 4)
+
+typedef struct fb_symm_ctx {
+  void* data[FB_MAX_RANKS];  /* peer-mapped payload buffers, indexed by rank            */
+  void* sig[FB_MAX_RANKS];   /* peer-mapped signal pads (FB_SIGNAL_PAD_BYTES, zeroed)    */
+  void* epochs;              /* local: FB_MAX_BLOCKS uint32, zeroed                      */
+  const void* abort;         /* optional device-visible int the host may set to 1        */
+  void* status;              /* local int: 0 ok, else the code of the wait that gave up  */
+  long long timeout_ns;      /* bound of every device-side wait; 0 = 2 s                 */
+  int rank, world;
+} fb_symm_ctx;
+
+/* ---- tensor-core GEMM: D[m,n] = sum_k A(m,k) B(n,k) (bf16 in, fp32 accumulate) ------------ */
+/* a_mn = 0: A is [M][lda] (K contiguous); a_mn = 1: A is [K][lda] (M contiguous). Same for B/N.
+ * lda, ldb multiples of 8; A, B 16-byte aligned. config: -1 auto, 0 = CTA pair 256x256,
+ * 1 = 128x256, 2 = 128x128, 3 = 128x64. split_k > 1 needs c_fp32 and adds into C atomically. */
+int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                 long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias, int bias_fp32, int epi,
+                 void* aux, long long ldaux, const float* alpha, int accumulate, int split_k, int config,
+                 int* status, void* stream);
+int fb_gemm_pick_config(int M, int N, int K, int split_k);
+
+/* ---- attention ----------------------------------------------------------------------------- */
+/* q,k,v,o,do,dq,dk,dv: bf16 [B, S, H, 64] with the given element strides for (batch, seq, head);
+ * S a multiple of 128. mask: optional fp32 additive [B, S] key mask. lse: fp32 [B, H, S]. */
+int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* mask, int B, int H,
+                int S, long long stride_b, long long stride_s, long long stride_h, float scale, int causal,
+                float p_drop, unsigned long long seed, int* status, void* stream);
+int fb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                const float* mask, void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int S,
+                long long stride_b, long long stride_s, long long stride_h, float scale, int causal, float p_drop,
+                unsigned long long seed, int* status, void* stream);
+
+/* ---- normalisation / activation / loss ----------------------------------------------------- */
+int fb_layernorm_fwd(const void* x, const void* residual, const float* gamma, const float* beta, void* y,
+                     void* pre_out, float* mean, float* rstd, int rows, int cols, float eps, float p_drop,
+                     unsigned long long seed, int is_bf16, void* stream);
+int fb_layernorm_bwd_grid(int rows);
+int fb_layernorm_bwd(const void* dy, const void* pre, const float* mean, const float* rstd, const float* gamma,
+                     void* dpre, void* dx_drop, float* partial, float* dgamma, float* dbeta, int accumulate,
+                     int rows, int cols, float p_drop, unsigned long long seed, int is_bf16, void* stream);
+int fb_gelu_fwd(const void* x, void* y, long long n, int tanh_approx, int is_bf16, void* stream);
+int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int tanh_approx, int is_bf16, void* stream);
+int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, int is_bf16, void* stream);
+int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream);
+int fb_cast(const void* x, void* y, long long n, float scale, int in_bf16, int out_bf16, void* stream);
+int fb_softmax_ce(const void* logits, long long ld, const long long* targets, int rows, int V,
+                  long long ignore_index, void* dlogits, long long ldd, float* count_inv, float* row_loss,
+                  float* loss, int is_bf16, void* stream);
+int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream);
+
+/* ---- batch norm (NCHW, training), fused ReLU / residual add --------------------------------- */
+int fb_bn_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
+              float* running_var, void* y, float* save_mean, float* save_rstd, int N, int C, int HW, float eps,
+              float momentum, int relu, int training, int is_bf16, void* stream);
+int fb_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
+              const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int N, int C, int HW,
+              int relu, int is_bf16, void* stream);
+
+/* ---- optimizers / gradient norm -------------------------------------------------------------- */
+int fb_adam_step(float* p, const void* g, float* m, float* v, void* p16, long long n, const float* hyper, float b1,
+                 float b2, float eps, const float* grad_scale, int g_bf16, void* stream);
+int fb_sgd_step(float* p, const void* g, float* buf, void* p16, long long n, const float* hyper,
+                const float* grad_scale, int g_bf16, void* stream);
+int fb_grad_norm_parts(long long n);
+int fb_grad_norm(const void* g, long long n, float* partial, float max_norm, float extra_scale, float* out,
+                 int is_bf16, void* stream);
+
+/* ---- collectives over peer-mapped buffers ---------------------------------------------------- */
+int fb_allreduce(const fb_symm_ctx* ctx, long long byte_off, long long n, int is_bf16, const float* weights,
+                 int blocks, void* stream);
+int fb_allreduce_oneshot(const fb_symm_ctx* ctx, long long byte_off, long long n, int in_bf16, void* out,
+                         int out_bf16, const float* weights, int blocks, void* stream);
+int fb_param_average(const fb_symm_ctx* params, const fb_symm_ctx* staging, long long n, const float* weights,
+                     float alpha, void* p16, float* partial, unsigned int* counter, float* out2, int blocks,
+                     void* stream);
+int fb_broadcast(const fb_symm_ctx* ctx, long long byte_off, long long nbytes, int root, int blocks, void* stream);
+int fb_symm_barrier(const fb_symm_ctx* ctx, int blocks, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLODL_B200_H_ */

@@ -1,0 +1,546 @@
+// bf16 GEMM on the 5th-generation tensor cores: D[m,n] = sum_k A(m,k) * B(n,k), fp32 accumulate.
+//
+// Replaces the cuBLAS call behind `torch::linear` that the reference issues for every Linear
+// layer (flodl-sys/ops_training.cpp:306-318) and for the dX / dW products libtorch's autograd
+// derives from it.
+//
+// Shape of the kernel
+//   * persistent: one CTA (or one CTA pair) per SM walks a list of output tiles;
+//   * warp 0 feeds a multi-stage shared-memory ring with TMA (`cp.async.bulk.tensor`, 128-byte
+//     swizzle), warp 1 issues `tcgen05.mma` from one elected thread, warps 2..9 drain the
+//     accumulator from TMEM with `tcgen05.ld` and run the epilogue;
+//   * two accumulator buffers in TMEM, so the epilogue of tile i overlaps the main loop of
+//     tile i+1;
+//   * `kCG == 2` pairs two CTAs of a cluster on one 256-row tile (`cta_group::2`): each CTA loads
+//     its own half of A and B with plain (non-multicast) TMA loads that credit the leader's
+//     mbarrier, the leader issues the MMAs, commits are multicast to both CTAs.
+//   * operands may be K-major (row = M/N index) or MN-major (row = K index); the second form is
+//     what dX = dY * W and dW = dY^T * X need, so no transposes are materialised.
+//   * epilogue: optional alpha (device scalar), bias, GELU (erf or tanh; pre-activation saved to
+//     `aux`), GELU' (multiply by gelu'(aux)), accumulate into C, split-K via fp32 atomics.
+//
+// All waits are bounded (see ptx_sm100.cuh); a give-up is reported through `status`.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../include/flodl_b200.h"
+#include "ptx_sm100.cuh"
+
+namespace fb {
+
+constexpr int BM = 128;  // rows of the tile held by ONE CTA
+constexpr int BK = 64;   // K per stage = one 128-byte swizzle row of bf16
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;
+  void* C;
+  long long ldc;
+  int c_fp32;
+  const void* bias;
+  int bias_fp32;
+  int epi;
+  void* aux;
+  long long ldaux;
+  const float* alpha;
+  int accumulate;
+  int split_k;
+  int* status;
+};
+
+template <int kCG, int kBN>
+struct GemmCfg {
+  static constexpr int BN_CTA = kBN / kCG;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN_CTA * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+  static constexpr int TMEM_COLS = (2 * kBN < 32) ? 32 : 2 * kBN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
+};
+
+__device__ __forceinline__ float gelu_erf_f(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+__device__ __forceinline__ float dgelu_erf_f(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float dgelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Epilogue for 32 consecutive columns of one output row.
+__device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint32_t (&acc)[32],
+                                                 int row, int col0, bool add_bias) {
+  if (row >= p.M || col0 >= p.N) return;
+  float v[32];
+  const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
+  const bool full = (col0 + 32 <= p.N);
+  if (p.bias && add_bias) {
+    if (p.bias_fp32) {
+      const float* b = static_cast<const float*>(p.bias) + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (full || col0 + i < p.N) v[i] += __ldg(b + i);
+    } else {
+      const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (full || col0 + i < p.N) v[i] += __bfloat162float(b[i]);
+    }
+  }
+  if (p.epi == FB_EPI_GELU_ERF || p.epi == FB_EPI_GELU_TANH) {
+    if (p.aux) {  // save the pre-activation for the backward pass
+      __nv_bfloat16* a = static_cast<__nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
+      if (full && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j * 8 + 2 * i], v[j * 8 + 2 * i + 1]);
+          *reinterpret_cast<uint4*>(a + j * 8) = *reinterpret_cast<uint4*>(h);
+        }
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) a[i] = __float2bfloat16(v[i]);
+      }
+    }
+    if (p.epi == FB_EPI_GELU_ERF) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+    }
+  } else if (p.epi == FB_EPI_DGELU_ERF || p.epi == FB_EPI_DGELU_TANH) {
+    const __nv_bfloat16* a =
+        static_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
+    float h[32];
+    if (full && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 raw = *reinterpret_cast<const uint4*>(a + j * 8);
+        const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(hp[i]);
+          h[j * 8 + 2 * i] = f.x;
+          h[j * 8 + 2 * i + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) h[i] = (col0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
+    }
+    if (p.epi == FB_EPI_DGELU_ERF) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf_f(h[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= dgelu_tanh_f(h[i]);
+    }
+  }
+
+  if (p.c_fp32) {
+    float* c = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.split_k > 1) {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) atomicAdd(c + i, v[i]);
+    } else if (full && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        if (p.accumulate) {
+          float4 old = *reinterpret_cast<float4*>(c + 4 * j);
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *reinterpret_cast<float4*>(c + 4 * j) = o;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) c[i] = p.accumulate ? c[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (full && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.accumulate) {
+          uint4 raw = *reinterpret_cast<uint4*>(c + j * 8);
+          const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(op[i]);
+            v[j * 8 + 2 * i] += f.x;
+            v[j * 8 + 2 * i + 1] += f.y;
+          }
+        }
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j * 8 + 2 * i], v[j * 8 + 2 * i + 1]);
+        *reinterpret_cast<uint4*>(c + j * 8) = *reinterpret_cast<uint4*>(h);
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+        float o = v[i];
+        if (p.accumulate) o += __bfloat162float(c[i]);
+        c[i] = __float2bfloat16(o);
+      }
+    }
+  }
+}
+
+template <int kCG, int kBN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<kCG, kBN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* tfull_bar = empty_bar + Cfg::STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (kCG == 2) ? cluster_ctarank() : 0u;
+  const int group = blockIdx.x / kCG;          // CTA (pair) index
+  const int num_groups = gridDim.x / kCG;
+
+  const int num_m = (p.M + BM * kCG - 1) / (BM * kCG);
+  const int num_n = (p.N + kBN - 1) / kBN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int kb_per = (num_kb + p.split_k - 1) / p.split_k;
+  const int num_units = num_m * num_n * p.split_k;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], kEpiWarps * kCG);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<kCG>(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish<kCG>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCG == 2) cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int u = group; u < num_units && ok; u += num_groups) {
+        const int ks = u % p.split_k;
+        const int t = u / p.split_k;
+        const int m0 = (t % num_m) * BM * kCG + static_cast<int>(rank) * BM;
+        const int n0 = (t / num_m) * kBN + static_cast<int>(rank) * Cfg::BN_CTA;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, kStatusWaitEmpty);
+          if (!ok) break;
+          uint8_t* sa = stage_base + s * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          if (kCG == 1 || rank == 0) mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES * kCG);
+          if constexpr (kCG == 1) {
+            if (!p.a_mn) {
+              tma_load_2d(sa, &tmA, &full_bar[s], kb * BK, m0);
+            } else {
+              tma_load_2d(sa, &tmA, &full_bar[s], m0, kb * BK);
+              tma_load_2d(sa + 8192, &tmA, &full_bar[s], m0 + 64, kb * BK);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(sb, &tmB, &full_bar[s], kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int q = 0; q < Cfg::BN_CTA / 64; ++q)
+                tma_load_2d(sb + q * 8192, &tmB, &full_bar[s], n0 + q * 64, kb * BK);
+            }
+          } else {
+            if (!p.a_mn) {
+              tma_load_2d_pair(sa, &tmA, &full_bar[s], kb * BK, m0);
+            } else {
+              tma_load_2d_pair(sa, &tmA, &full_bar[s], m0, kb * BK);
+              tma_load_2d_pair(sa + 8192, &tmA, &full_bar[s], m0 + 64, kb * BK);
+            }
+            if (!p.b_mn) {
+              tma_load_2d_pair(sb, &tmB, &full_bar[s], kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int q = 0; q < Cfg::BN_CTA / 64; ++q)
+                tma_load_2d_pair(sb + q * 8192, &tmB, &full_bar[s], n0 + q * 64, kb * BK);
+            }
+          }
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (rank == 0 && lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM * kCG, kBN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int u = group; u < num_units && ok; u += num_groups, ++it) {
+        const int ks = u % p.split_k;
+        const int kb0 = ks * kb_per;
+        const int kb1 = min(num_kb, kb0 + kb_per);
+        const int acc = it & 1;
+        ok = mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1, abort_flag, p.status, kStatusWaitEpi);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kStatusWaitFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t da = make_smem_desc(sa + k4 * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + k4 * b_kstep, b_lbo, 1024);
+            umma_bf16<kCG>(d_tmem, da, db, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+          }
+          if constexpr (kCG == 1) umma_commit(&empty_bar[s]);
+          else umma_commit_pair(&empty_bar[s], 3);
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        if constexpr (kCG == 1) umma_commit(&tfull_bar[acc]);
+        else umma_commit_pair(&tfull_bar[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;                 // TMEM lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;       // which half of the tile's columns
+    constexpr int COLS_PER_WARP = kBN / 2;
+    int it = 0;
+    bool ok = true;
+    for (int u = group; u < num_units && ok; u += num_groups, ++it) {
+      const int ks = u % p.split_k;
+      const int t = u / p.split_k;
+      const int m0 = (t % num_m) * BM * kCG + static_cast<int>(rank) * BM;
+      const int n0 = (t / num_m) * kBN;
+      const int acc = it & 1;
+      ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, abort_flag, p.status, kStatusWaitAccum);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * COLS_PER_WARP;
+#pragma unroll 1
+      for (int c = 0; c < COLS_PER_WARP; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c, v);
+        tmem_ld_wait();
+        epilogue_store32(p, v, row, n0 + half * COLS_PER_WARP + c, ks == 0);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (kCG == 1 || rank == 0) mbar_arrive(&tempty_bar[acc]);
+        else mbar_arrive_cluster(&tempty_bar[acc], 0);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCG == 2) cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<kCG>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows][ld] matrix with a {box_inner, box_outer} box.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int kCG, int kBN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<kCG, kBN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<kCG, kBN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int num_m = (p.M + BM * kCG - 1) / (BM * kCG);
+  const int num_n = (p.N + kBN - 1) / kBN;
+  const int units = num_m * num_n * p.split_k;
+  int groups = sm_count() / kCG;
+  if (units < groups) groups = units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(groups * kCG, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  return static_cast<int>(e);
+}
+
+}  // namespace fb
+
+extern "C" int fb_gemm_pick_config(int M, int N, int K, int split_k) {
+  // Score = SM occupancy of the last wave x a per-tile efficiency prior (bigger tiles re-use
+  // operands more and are less L2-bound). Configs: 0 = pair 256x256, 1 = 128x256, 2 = 128x128, 3 = 128x64.
+  const int sms = 148;
+  const struct { int cg, bn; float prior; } cand[4] = {{2, 256, 1.00f}, {1, 256, 0.92f}, {1, 128, 0.80f}, {1, 64, 0.55f}};
+  int best = 2;
+  float best_score = -1.f;
+  for (int i = 0; i < 4; ++i) {
+    const int num_m = (M + 128 * cand[i].cg - 1) / (128 * cand[i].cg);
+    const int num_n = (N + cand[i].bn - 1) / cand[i].bn;
+    const long units = 1L * num_m * num_n * split_k;
+    const int slots = sms / cand[i].cg;
+    const long waves = (units + slots - 1) / slots;
+    // useful fraction of the padded tile grid
+    const float useful = (1.f * M * N) / (1.f * num_m * 128 * cand[i].cg * num_n * cand[i].bn);
+    const float score = cand[i].prior * useful * (1.f * units) / (1.f * waves * slots);
+    if (score > best_score) { best_score = score; best = i; }
+  }
+  (void)K;
+  return best;
+}
+
+extern "C" int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                            long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias,
+                            int bias_fp32, int epi, void* aux, long long ldaux, const float* alpha,
+                            int accumulate, int split_k, int config, int* status, void* stream_) {
+  using namespace fb;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (split_k < 1) split_k = 1;
+  if (split_k > 1 && !c_fp32) return -2;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (config < 0) config = fb_gemm_pick_config(M, N, K, split_k);
+  const int cg = (config == 0) ? 2 : 1;
+  const int bn = (config == 0 || config == 1) ? 256 : (config == 2 ? 128 : 64);
+  const int bn_cta = bn / cg;
+
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  else       r = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK);
+  if (r) return r;
+  if (!b_mn) r = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn_cta);
+  else       r = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
+  if (r) return r;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  p.bias = bias; p.bias_fp32 = bias_fp32; p.epi = epi; p.aux = aux; p.ldaux = ldaux; p.alpha = alpha;
+  p.accumulate = accumulate; p.split_k = split_k; p.status = status;
+  switch (config) {
+    case 0: return launch_gemm<2, 256>(ta, tb, p, stream);
+    case 1: return launch_gemm<1, 256>(ta, tb, p, stream);
+    case 2: return launch_gemm<1, 128>(ta, tb, p, stream);
+    default: return launch_gemm<1, 64>(ta, tb, p, stream);
+  }
+}

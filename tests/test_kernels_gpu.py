@@ -1,0 +1,241 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from flodl_b200 import _ext
+    return _ext.require()
+
+
+def _ref_gemm(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float().t() if b_mn else b.float()
+    return A @ B.t()
+
+
+def _gemm_case(C, M, N, K, a_mn, b_mn, config, out_dtype=torch.bfloat16, **kw):
+    torch.manual_seed(M * 7 + N * 3 + K)
+    dev = "cuda"
+    a = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+    out = torch.zeros(M, N, device=dev, dtype=out_dtype)
+    C.clear_status(0)
+    C.gemm(a, b, out, a_mn, b_mn, config=config, **kw)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0, f"kernel status {C.read_status(0)}"
+    ref = _ref_gemm(a, b, a_mn, b_mn)
+    return out.float(), ref
+
+
+@pytest.mark.parametrize("config", [2, 1, 3, 0])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_layouts(C, config, a_mn, b_mn):
+    out, ref = _gemm_case(C, 512, 768, 256, a_mn, b_mn, config)
+    err = (out - ref).abs().max().item()
+    assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
+
+
+@pytest.mark.parametrize("config", [0, 1, 2, 3])
+def test_gemm_ragged_edges(C, config):
+    # M, N not multiples of the tile, K not a multiple of 64 (TMA zero-fills the tails)
+    out, ref = _gemm_case(C, 300, 328, 200, False, False, config)
+    err = (out - ref).abs().max().item()
+    assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
+
+
+@pytest.mark.parametrize("config", [0, 2])
+def test_gemm_many_tiles_per_cta(C, config):
+    # more tiles than SMs: exercises the accumulator double buffering and barrier phases
+    out, ref = _gemm_case(C, 4096, 3072, 768, False, False, config)
+    err = (out - ref).abs().max().item()
+    assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
+
+
+def test_gemm_bias_gelu_aux(C):
+    M, N, K = 512, 512, 256
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    aux = torch.empty_like(out)
+    C.gemm(a, b, out, bias=bias, epi=1, aux=aux)
+    pre = a.float() @ b.float().t() + bias
+    ref = torch.nn.functional.gelu(pre)
+    assert (aux.float() - pre).abs().max().item() < 0.05
+    assert (out.float() - ref).abs().max().item() < 0.05
+    # backward epilogue: dY * gelu'(aux)
+    g = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).bfloat16()
+    dpre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm(g, w, dpre, epi=2, aux=aux)
+    x = aux.float().requires_grad_(True)
+    torch.nn.functional.gelu(x).backward(g.float() @ w.float().t())
+    assert (dpre.float() - x.grad).abs().max().item() < 0.06
+
+
+def test_gemm_fp32_out_accumulate_splitk_alpha(C):
+    M, N, K = 256, 384, 1024
+    torch.manual_seed(1)
+    a = torch.randn(K, M, device="cuda").bfloat16()   # MN-major A: dW = dY^T X
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    ref = a.float().t() @ b.float()
+    base = torch.randn(M, N, device="cuda")
+    out = base.clone()
+    C.gemm(a, b, out, True, True, accumulate=True)
+    assert (out - (base + ref)).abs().max().item() < 0.02 * ref.abs().max().item()
+    out2 = base.clone()
+    C.gemm(a, b, out2, True, True, accumulate=True, split_k=4)
+    assert (out2 - (base + ref)).abs().max().item() < 0.02 * ref.abs().max().item()
+    alpha = torch.tensor([0.25], device="cuda")
+    out3 = torch.empty(M, N, device="cuda")
+    C.gemm(a, b, out3, True, True, alpha=alpha)
+    assert (out3 - 0.25 * ref).abs().max().item() < 0.02 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("cols", [768, 512, 16 * 8, 1024])
+def test_layernorm_fwd_bwd(C, dtype, cols):
+    rows = 1000
+    torch.manual_seed(2)
+    x = torch.randn(rows, cols, device="cuda").to(dtype)
+    r = torch.randn(rows, cols, device="cuda").to(dtype)
+    g = torch.randn(cols, device="cuda")
+    b = torch.randn(cols, device="cuda")
+    y, pre, mean, rstd = C.layernorm_fwd(x, r, g, b, 1e-5, 0.0, 0, True)
+    pre_ref = (x.float() + r.float()).to(dtype).float()
+    ref = torch.nn.functional.layer_norm(pre_ref, (cols,), g, b, 1e-5)
+    tol = 0.05 if dtype == torch.bfloat16 else 1e-4
+    assert (y.float() - ref).abs().max().item() < tol
+    assert (pre.float() - pre_ref).abs().max().item() < 1e-6
+    dy = torch.randn(rows, cols, device="cuda").to(dtype)
+    dpre, _, dg, db = C.layernorm_bwd(dy, pre, mean, rstd, g, 0.0, 0, False, True, None, None)
+    xr = pre_ref.clone().requires_grad_(True)
+    gr = g.clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True)
+    torch.nn.functional.layer_norm(xr, (cols,), gr, br, 1e-5).backward(dy.float())
+    assert (dpre.float() - xr.grad).abs().max().item() < (0.06 if dtype == torch.bfloat16 else 1e-3)
+    assert (dg - gr.grad).abs().max().item() < 5e-2 * max(1.0, gr.grad.abs().max().item()) * (1 if dtype == torch.bfloat16 else 0.01)
+    assert (db - br.grad).abs().max().item() < 1e-2 * max(1.0, br.grad.abs().max().item())
+
+
+def test_layernorm_dropout_mask_consistent(C):
+    rows, cols, p = 512, 768, 0.1
+    x = torch.ones(rows, cols, device="cuda", dtype=torch.bfloat16)
+    r = torch.zeros_like(x)
+    _, pre, mean, rstd = C.layernorm_fwd(x, r, None, None, 1e-5, p, 1234, True)
+    keep = (pre.float() != 0)
+    frac = keep.float().mean().item()
+    assert abs(frac - (1 - p)) < 0.01
+    assert torch.allclose(pre.float()[keep], torch.full_like(pre.float()[keep], 1 / (1 - p)), atol=1e-2)
+    # the standalone dropout kernel and the LN backward regenerate the same mask
+    d = C.dropout(x, p, 1234)
+    assert torch.equal(d.float() != 0, keep)
+    dy = torch.ones_like(x)
+    dpre, dxd, _, _ = C.layernorm_bwd(dy, pre, mean, rstd, None, p, 1234, True, False, None, None)
+    assert ((dxd.float() != 0) & ~keep).sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tanh", [False, True])
+def test_gelu(C, dtype, tanh):
+    x = torch.randn(4099 * 3, device="cuda").to(dtype)
+    y = C.gelu_fwd(x, tanh)
+    xr = x.float().requires_grad_(True)
+    ref = torch.nn.functional.gelu(xr, approximate="tanh" if tanh else "none")
+    tol = 0.02 if dtype == torch.bfloat16 else 1e-5
+    assert (y.float() - ref).abs().max().item() < tol
+    dy = torch.randn_like(x)
+    dx = C.gelu_bwd(dy, x, tanh)
+    ref.backward(dy.float())
+    assert (dx.float() - xr.grad).abs().max().item() < (0.03 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,V,pad", [(256, 30522, 6), (128, 10, 0), (64, 32000, 0)])
+def test_softmax_ce(C, dtype, rows, V, pad):
+    torch.manual_seed(3)
+    buf = torch.randn(rows, V + pad, device="cuda").to(dtype) * 3
+    logits = buf[:, :V]
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    tgt[::3] = -100
+    lr = logits.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lr, tgt, ignore_index=-100)
+    ref.backward()
+    loss, dl, cinv = C.softmax_ce(logits, tgt, -100, True, False)
+    assert abs(loss.item() - ref.item()) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+    assert (dl.float() - lr.grad).abs().max().item() < (2e-3 if dtype == torch.bfloat16 else 1e-6)
+    assert cinv[0].item() == (tgt != -100).sum().item()
+
+
+def test_adam_matches_reference(C):
+    n = 100003
+    torch.manual_seed(4)
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = p.clone()
+    mr, vr = m.clone(), v.clone()
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.999, 1e-8, 0.01
+    for t in range(1, 4):
+        hyper = torch.tensor([lr, 1 - b1 ** t, 1 - b2 ** t, wd], device="cuda")
+        C.adam_step(p, g, m, v, p16, hyper, b1, b2, eps)
+        pr *= 1 - lr * wd
+        mr = b1 * mr + (1 - b1) * g
+        vr = b2 * vr + (1 - b2) * g * g
+        pr -= (lr / (1 - b1 ** t)) * mr / ((vr / (1 - b2 ** t)).sqrt() + eps)
+    assert (p - pr).abs().max().item() < 1e-5
+    assert (p16.float() - pr).abs().max().item() < 2e-2
+    # bf16 gradients + device-side gradient scale
+    gs = torch.tensor([0.5], device="cuda")
+    p2, m2, v2 = pr.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    hyper = torch.tensor([lr, 1 - b1, 1 - b2, 0.0], device="cuda")
+    C.adam_step(p2, g.bfloat16(), m2, v2, None, hyper, b1, b2, eps, gs)
+    gq = g.bfloat16().float() * 0.5
+    ref = pr - (lr / (1 - b1)) * ((1 - b1) * gq) / ((((1 - b2) * gq * gq) / (1 - b2)).sqrt() + eps)
+    assert (p2 - ref).abs().max().item() < 1e-5
+
+
+def test_sgd_matches_reference(C):
+    n = 5001
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    buf = torch.zeros(n, device="cuda")
+    pr, br = p.clone(), None
+    lr, mu, wd = 0.1, 0.9, 1e-4
+    for step in range(3):
+        hyper = torch.tensor([lr, mu, wd, 1.0 if step == 0 else 0.0], device="cuda")
+        C.sgd_step(p, g, buf, None, hyper)
+        gg = g + wd * pr
+        br = gg.clone() if br is None else mu * br + gg
+        pr = pr - lr * br
+    assert (p - pr).abs().max().item() < 1e-5
+
+
+def test_grad_norm_and_clip(C):
+    g = torch.randn(1_000_003, device="cuda")
+    out = C.grad_norm(g, 1.0, 1.0)
+    ref = g.double().norm().item()
+    assert abs(out[0].item() - ref) / ref < 1e-5
+    assert abs(out[1].item() - 1.0 / (ref + 1e-6)) < 1e-6
+    out = C.grad_norm(g.bfloat16(), 0.0, 1.0)
+    assert abs(out[0].item() - g.bfloat16().double().norm().item()) / ref < 1e-4
+    assert out[1].item() == 1.0
+
+
+def test_colsum_and_cast(C):
+    x = torch.randn(4096, 770, device="cuda").bfloat16()
+    out = torch.zeros(770, device="cuda")
+    C.colsum(x, out)
+    assert (out - x.float().sum(0)).abs().max().item() < 1e-2
+    y = torch.empty(4096 * 770, device="cuda")
+    C.cast_into(x.view(-1), y, 2.0)
+    assert torch.equal(y, x.view(-1).float() * 2)
