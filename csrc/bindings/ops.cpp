@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <torch/extension.h>
 
+#include <array>
 #include <optional>
 #include <vector>
 
@@ -36,6 +37,12 @@ void want_float_kind(const Tensor& t, const char* name) {
 }
 template <typename T = void>
 T* ptr(const OptTensor& t) { return t.has_value() ? static_cast<T*>(t->data_ptr()) : nullptr; }
+
+const unsigned long long* seed_ptr(const OptTensor& t) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kLong && t->numel() == 1, "seed_dev must be one int64 on CUDA");
+  return reinterpret_cast<const unsigned long long*>(t->data_ptr());
+}
 
 // one status word per device, shared by every kernel that has bounded waits
 Tensor& status_word(int device) {
@@ -82,7 +89,8 @@ void clear_status(int device) { status_word(device).zero_(); }
 
 // ------------------------------------------------------------------------------------- LayerNorm
 std::vector<Tensor> layernorm_fwd(const Tensor& x, const OptTensor& residual, const OptTensor& gamma,
-                                  const OptTensor& beta, double eps, double p_drop, uint64_t seed, bool want_pre) {
+                                  const OptTensor& beta, double eps, double p_drop, uint64_t seed, bool want_pre,
+                                  const OptTensor& seed_dev) {
   want_float_kind(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
@@ -97,7 +105,7 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const OptTensor& residual, co
   Tensor mean = torch::empty({rows}, fopts), rstd = torch::empty({rows}, fopts);
   int rc = fb_layernorm_fwd(x.data_ptr(), ptr<const void>(residual), ptr<const float>(gamma), ptr<const float>(beta),
                             y.data_ptr(), want_pre ? pre.data_ptr() : nullptr, mean.data_ptr<float>(),
-                            rstd.data_ptr<float>(), (int)rows, (int)cols, (float)eps, (float)p_drop, seed, is_bf16(x),
+                            rstd.data_ptr<float>(), (int)rows, (int)cols, (float)eps, (float)p_drop, seed, seed_ptr(seed_dev), is_bf16(x),
                             stream_of(x));
   check(rc, "fb_layernorm_fwd");
   return {y, pre, mean, rstd};
@@ -106,7 +114,8 @@ std::vector<Tensor> layernorm_fwd(const Tensor& x, const OptTensor& residual, co
 // returns {dpre, dx_drop (or undefined), dgamma, dbeta}
 std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& pre, const Tensor& mean, const Tensor& rstd,
                                   const OptTensor& gamma, double p_drop, uint64_t seed, bool want_dx_drop,
-                                  bool want_param_grads, const OptTensor& dgamma_acc, const OptTensor& dbeta_acc) {
+                                  bool want_param_grads, const OptTensor& dgamma_acc, const OptTensor& dbeta_acc,
+                                  const OptTensor& seed_dev) {
   want_float_kind(dy, "dy");
   c10::cuda::CUDAGuard guard(dy.device());
   TORCH_CHECK(dy.is_contiguous() && pre.is_contiguous() && dy.scalar_type() == pre.scalar_type());
@@ -136,7 +145,7 @@ std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& pre, const Ten
                             want_param_grads ? partial.data_ptr<float>() : nullptr,
                             want_param_grads ? dgamma.data_ptr<float>() : nullptr,
                             want_param_grads ? dbeta.data_ptr<float>() : nullptr, accumulate, (int)rows, (int)cols,
-                            (float)p_drop, seed, is_bf16(dy), stream_of(dy));
+                            (float)p_drop, seed, seed_ptr(seed_dev), is_bf16(dy), stream_of(dy));
   check(rc, "fb_layernorm_bwd");
   return {dpre, dxd, dgamma, dbeta};
 }
@@ -158,12 +167,12 @@ Tensor gelu_bwd(const Tensor& dy, const Tensor& x, bool tanh_approx) {
   check(fb_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), tanh_approx, is_bf16(x), stream_of(x)), "fb_gelu_bwd");
   return dx;
 }
-Tensor dropout(const Tensor& x, double p, uint64_t seed) {
+Tensor dropout(const Tensor& x, double p, uint64_t seed, const OptTensor& seed_dev) {
   want_float_kind(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous());
   Tensor y = torch::empty_like(x);
-  check(fb_dropout(x.data_ptr(), y.data_ptr(), x.numel(), (float)p, seed, is_bf16(x), stream_of(x)), "fb_dropout");
+  check(fb_dropout(x.data_ptr(), y.data_ptr(), x.numel(), (float)p, seed, seed_ptr(seed_dev), is_bf16(x), stream_of(x)), "fb_dropout");
   return y;
 }
 void colsum(const Tensor& x, Tensor& out) {
@@ -258,6 +267,58 @@ Tensor grad_norm(const Tensor& g, double max_norm, double extra_scale) {
   return out;
 }
 
+// ------------------------------------------------------------------------------------ attention
+// q, k, v: bf16 views [B, S, H, 64] sharing one stride set (e.g. slices of a fused QKV buffer).
+void check_bshd(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.dim() == 4 && t.size(3) == 64 && t.stride(3) == 1, name,
+              " must be bf16 [B, S, H, 64] with a unit inner stride");
+}
+std::array<long long, 3> bsh_strides(const Tensor& t) { return {t.stride(0), t.stride(1), t.stride(2)}; }
+
+std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const OptTensor& mask, double scale,
+                             bool causal, double p_drop, uint64_t seed, const OptTensor& seed_dev) {
+  check_bshd(q, "q");
+  check_bshd(k, "k");
+  check_bshd(v, "v");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(k.strides() == q.strides() && v.strides() == q.strides() && k.sizes() == q.sizes() && v.sizes() == q.sizes(),
+              "q, k, v must share shape and strides");
+  const int64_t B = q.size(0), S = q.size(1), H = q.size(2);
+  if (mask.has_value()) TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == at::kFloat && mask->is_contiguous() && mask->numel() == B * S, "mask must be fp32 [B, S]");
+  Tensor o = torch::empty({B, S, H, 64}, q.options());
+  Tensor lse = torch::empty({B, H, S}, q.options().dtype(torch::kFloat));
+  auto qs = bsh_strides(q), os = bsh_strides(o);
+  Tensor& st = status_word(q.get_device());
+  check(fb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), ptr<const float>(mask), (int)B,
+                    (int)H, (int)S, qs.data(), os.data(), (float)scale, causal, (float)p_drop, seed, seed_ptr(seed_dev),
+                    st.data_ptr<int>(), stream_of(q)),
+        "fb_attn_fwd");
+  return {o, lse};
+}
+
+// Returns one fused gradient buffer [B, S, 3, H, 64] (dq, dk, dv are its slices along dim 2).
+Tensor attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
+                const OptTensor& mask, double scale, bool causal, double p_drop, uint64_t seed, const OptTensor& seed_dev) {
+  check_bshd(q, "q");
+  check_bshd(o, "o");
+  check_bshd(d_o, "d_o");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(d_o.strides() == o.strides(), "dO must share o's strides");
+  const int64_t B = q.size(0), S = q.size(1), H = q.size(2);
+  Tensor dqkv = torch::empty({B, S, 3, H, 64}, q.options());
+  Tensor dq = dqkv.select(2, 0), dk = dqkv.select(2, 1), dv = dqkv.select(2, 2);
+  Tensor acc;
+  if (S > 128) acc = torch::empty({B, H, S, 64}, q.options().dtype(torch::kFloat));
+  auto qs = bsh_strides(q), os = bsh_strides(o), gs = bsh_strides(dq);
+  Tensor& st = status_word(q.get_device());
+  check(fb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                    ptr<const float>(mask), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), acc.defined() ? acc.data_ptr<float>() : nullptr,
+                    (int)B, (int)H, (int)S, qs.data(), os.data(), gs.data(), (float)scale, causal, (float)p_drop, seed,
+                    seed_ptr(seed_dev), st.data_ptr<int>(), stream_of(q)),
+        "fb_attn_bwd");
+  return dqkv;
+}
+
 }  // namespace
 
 void bind_comm(py::module_& m);     // comm.cpp
@@ -271,11 +332,14 @@ PYBIND11_MODULE(_C, m) {
   m.def("gemm_pick_config", &gemm_pick_config);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
-  m.def("layernorm_fwd", &layernorm_fwd);
-  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("layernorm_fwd", &layernorm_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("eps"),
+        py::arg("p_drop"), py::arg("seed"), py::arg("want_pre"), py::arg("seed_dev") = py::none());
+  m.def("layernorm_bwd", &layernorm_bwd, py::arg("dy"), py::arg("pre"), py::arg("mean"), py::arg("rstd"), py::arg("gamma"),
+        py::arg("p_drop"), py::arg("seed"), py::arg("want_dx_drop"), py::arg("want_param_grads"), py::arg("dgamma_acc"),
+        py::arg("dbeta_acc"), py::arg("seed_dev") = py::none());
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
-  m.def("dropout", &dropout);
+  m.def("dropout", &dropout, py::arg("x"), py::arg("p"), py::arg("seed"), py::arg("seed_dev") = py::none());
   m.def("colsum", &colsum);
   m.def("cast_into", &cast_into);
   m.def("softmax_ce", &softmax_ce);
@@ -285,6 +349,10 @@ PYBIND11_MODULE(_C, m) {
   m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
         py::arg("grad_scale") = py::none());
   m.def("grad_norm", &grad_norm);
+  m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("mask"), py::arg("scale"), py::arg("causal"),
+        py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());
+  m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("d_o"), py::arg("lse"), py::arg("mask"),
+        py::arg("scale"), py::arg("causal"), py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());
   bind_comm(m);
   bind_runtime(m);
 }

@@ -60,26 +60,30 @@ int fb_gemm_pick_config(int M, int N, int K, int split_k);
 
 /* ---- attention ----------------------------------------------------------------------------- */
 /* q,k,v,o,do,dq,dk,dv: bf16 [B, S, H, 64] with the given element strides for (batch, seq, head);
- * S a multiple of 128. mask: optional fp32 additive [B, S] key mask. lse: fp32 [B, H, S]. */
+ * Strides are host arrays {batch, seq, head} in elements (multiples of 8); q/k/v share one set, o/dO another,
+ * dq/dk/dv a third. mask: optional fp32 additive [B, S] key mask. lse: fp32 [B, H, S]. */
 int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* mask, int B, int H,
-                int S, long long stride_b, long long stride_s, long long stride_h, float scale, int causal,
-                float p_drop, unsigned long long seed, int* status, void* stream);
+                int S, const long long* qkv_strides, const long long* o_strides, float scale, int causal, float p_drop,
+                unsigned long long seed, const unsigned long long* seed_dev, int* status, void* stream);
 int fb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                 const float* mask, void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int S,
-                long long stride_b, long long stride_s, long long stride_h, float scale, int causal, float p_drop,
-                unsigned long long seed, int* status, void* stream);
+                const long long* qkv_strides, const long long* o_strides, const long long* g_strides, float scale,
+                int causal, float p_drop, unsigned long long seed, const unsigned long long* seed_dev, int* status,
+                void* stream);
 
 /* ---- normalisation / activation / loss ----------------------------------------------------- */
 int fb_layernorm_fwd(const void* x, const void* residual, const float* gamma, const float* beta, void* y,
                      void* pre_out, float* mean, float* rstd, int rows, int cols, float eps, float p_drop,
-                     unsigned long long seed, int is_bf16, void* stream);
+                     unsigned long long seed, const unsigned long long* seed_dev, int is_bf16, void* stream);
 int fb_layernorm_bwd_grid(int rows);
 int fb_layernorm_bwd(const void* dy, const void* pre, const float* mean, const float* rstd, const float* gamma,
                      void* dpre, void* dx_drop, float* partial, float* dgamma, float* dbeta, int accumulate,
-                     int rows, int cols, float p_drop, unsigned long long seed, int is_bf16, void* stream);
+                     int rows, int cols, float p_drop, unsigned long long seed, const unsigned long long* seed_dev, int is_bf16,
+                     void* stream);
 int fb_gelu_fwd(const void* x, void* y, long long n, int tanh_approx, int is_bf16, void* stream);
 int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int tanh_approx, int is_bf16, void* stream);
-int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, int is_bf16, void* stream);
+int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, const unsigned long long* seed_dev,
+               int is_bf16, void* stream);
 int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream);
 int fb_cast(const void* x, void* y, long long n, float scale, int in_bf16, int out_bf16, void* stream);
 int fb_softmax_ce(const void* logits, long long ld, const long long* targets, int rows, int V,

@@ -68,8 +68,9 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
 // y = x * mask(seed, idx) / (1 - p); used for forward and (with dy as x) for backward.
 template <typename T>
 __global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, float p,
-                               unsigned long long seed) {
+                               unsigned long long seed_in, const unsigned long long* __restrict__ seed_dev) {
   constexpr int V = VecIO<T>::kVec;
+  const unsigned long long seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   const float inv_keep = 1.f / (1.f - p);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * V;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
@@ -154,16 +155,16 @@ extern "C" int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n,
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, int is_bf16,
-                          void* stream) {
+extern "C" int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed,
+                          const unsigned long long* seed_dev, int is_bf16, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
     fb::dropout_kernel<__nv_bfloat16><<<fb::grid_for(n, 8, 256), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, p, seed);
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, p, seed, seed_dev);
   else
     fb::dropout_kernel<float><<<fb::grid_for(n, 4, 256), 256, 0, st>>>(static_cast<const float*>(x),
-                                                                       static_cast<float*>(y), n, p, seed);
+                                                                       static_cast<float*>(y), n, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
 

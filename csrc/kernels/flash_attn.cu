@@ -1,0 +1,672 @@
+// Flash-style attention forward / backward for head dim 64 on tcgen05 tensor cores.
+//
+// Replaces `at::scaled_dot_product_attention` (flodl-sys/ops_nn.cpp:367-388) behind the encoder
+// layers (flodl-hf/src/models/transformer_layer.rs:243-251) and the decomposed
+// matmul / masked_fill / softmax / matmul chain of `MultiheadAttention`
+// (flodl/src/nn/attention.rs:108-151): additive key mask [B,S], causal masking, attention-prob
+// dropout, O(S) memory (only the log-sum-exp per row is saved).
+//
+// Work split: one CTA per (query block of 128 rows, head, batch) in the forward pass, one CTA per
+// (head, batch) in the backward pass. 4 warps (one TMEM lane = one query row per thread) do the
+// softmax arithmetic; a fifth warp issues every TMA load and every `tcgen05.mma` from one thread.
+// Q, K, V, dO tiles arrive by TMA with 128-byte swizzle in their natural [row][64] layout; the
+// same tile serves as a K-major operand (QK^T, dO V^T) or an MN-major operand (P V, P^T dO,
+// dS^T Q, dS K) by flipping the major bit of the instruction descriptor, so nothing is transposed.
+// P and dS are written to shared memory by the softmax threads in the swizzled layout the MMA
+// expects. All accumulators (S, dP, O, dQ, dK, dV) live in TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../include/flodl_b200.h"
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace fb {
+
+constexpr int kHD = 64;        // head dim
+constexpr int kBlk = 128;      // rows per query / key block
+constexpr int kAttnThreads = 160;
+constexpr float kLog2e = 1.4426950408889634f;
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                      uint32_t box_inner, uint32_t box_outer);  // gemm_tcgen05.cu
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static int make_tmap_bshd(CUtensorMap* out, const void* base, int B, int H, int S, long long sb, long long ss, long long sh) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHD), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(sb) * 2};
+  cuuint32_t box[4] = {kHD, kBlk, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Address of the 16-byte chunk holding columns [8*chunk, 8*chunk+8) of `row` in a [128][64] bf16
+// tile stored with the 128-byte swizzle (tile base 1024-byte aligned).
+__device__ __forceinline__ uint32_t swz_chunk(uint32_t tile_base, int row, int chunk) {
+  return tile_base + row * 128 + ((chunk ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return r;
+}
+
+struct AttnParams {
+  int B, H, S;
+  long long sb, ss, sh;      // element strides of q/k/v
+  long long osb, oss, osh;   // ... of o / dO
+  long long gsb, gss, gsh;   // ... of dq / dk / dv
+  const float* mask;         // [B, S] additive, may be null
+  float scale;
+  int causal;
+  float p_drop;
+  unsigned long long seed;
+  const unsigned long long* seed_dev;
+  int* status;
+};
+
+// ===================================================================================== forward
+struct FwdSmem {
+  static constexpr int Q = 0;                    // 16 KB
+  static constexpr int K = 16384;                // 2 x 16 KB
+  static constexpr int V = K + 2 * 16384;        // 2 x 16 KB
+  static constexpr int P = V + 2 * 16384;        // 2 panels x 16 KB
+  static constexpr int MASK = P + 2 * 16384;     // 128 floats
+  static constexpr int BARS = MASK + 512;
+  static constexpr int TOTAL = BARS + 256;
+};
+
+__global__ void __launch_bounds__(kAttnThreads)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ o, float* __restrict__ lse,
+                const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BARS);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint64_t* o_done = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* mask_s = reinterpret_cast<float*>(smem + FwdSmem::MASK);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * kBlk;
+  const int n_kv_all = (p.S + kBlk - 1) / kBlk;
+  const int n_kv = p.causal ? min(n_kv_all, qb + 1) : n_kv_all;
+  const unsigned long long seed = p.seed + (p.seed_dev ? *p.seed_dev : 0ull);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_full, 1);
+    mbar_init(o_done, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc<1>(tmem_slot, 256);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;
+  const uint32_t tmem_O = tmem_base + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------------------------------------------------- loads + MMA issue (one thread)
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, kHD, 0, 1);
+      const uint32_t sQ = smem_u32(smem + FwdSmem::Q);
+      const uint32_t sP = smem_u32(smem + FwdSmem::P);
+      mbar_expect_tx(q_full, 16384);
+      tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, q0, h, b);
+      for (int j = 0; j < min(2, n_kv); ++j) {
+        mbar_expect_tx(&kv_full[j], 32768);
+        tma_load_4d(smem + FwdSmem::K + j * 16384, &tmK, &kv_full[j], 0, j * kBlk, h, b);
+        tma_load_4d(smem + FwdSmem::V + j * 16384, &tmV, &kv_full[j], 0, j * kBlk, h, b);
+      }
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusWaitFull);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t sK = smem_u32(smem + FwdSmem::K + st * 16384);
+        const uint32_t sV = smem_u32(smem + FwdSmem::V + st * 16384);
+        ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, p.status, kStatusWaitFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // S = Q K^T (the softmax threads have drained S of block j-1: they arrived on p_ready)
+#pragma unroll
+        for (int k4 = 0; k4 < kHD / 16; ++k4)
+          umma_bf16<1>(tmem_S, make_smem_desc(sQ + k4 * 32, 16, 1024), make_smem_desc(sK + k4 * 32, 16, 1024), idesc_s, k4 > 0);
+        umma_commit(s_full);
+        ok = mbar_wait(p_ready, j & 1, abort_flag, p.status, kStatusWaitEpi);
+        if (!ok) break;
+        if (j > 0) {
+          ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, p.status, kStatusWaitEpi);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        // O_j = P V
+#pragma unroll
+        for (int k8 = 0; k8 < kBlk / 16; ++k8) {
+          const uint32_t a = sP + (k8 >> 2) * 16384 + (k8 & 3) * 32;
+          umma_bf16<1>(tmem_O, make_smem_desc(a, 16, 1024), make_smem_desc(sV + k8 * 2048, 8192, 1024), idesc_o, k8 > 0);
+        }
+        umma_commit(o_full);
+        umma_commit(&kv_empty[st]);
+        if (j + 2 < n_kv) {
+          ok = mbar_wait(&kv_empty[st], (j >> 1) & 1, abort_flag, p.status, kStatusWaitEmpty);
+          if (!ok) break;
+          mbar_expect_tx(&kv_full[st], 32768);
+          tma_load_4d(smem + FwdSmem::K + st * 16384, &tmK, &kv_full[st], 0, (j + 2) * kBlk, h, b);
+          tma_load_4d(smem + FwdSmem::V + st * 16384, &tmV, &kv_full[st], 0, (j + 2) * kBlk, h, b);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax threads
+    const int t = threadIdx.x;            // row within the block == TMEM lane
+    const int q = q0 + t;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t sP = smem_u32(smem + FwdSmem::P);
+    const float sc = p.scale * kLog2e;
+    const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[kHD];
+#pragma unroll
+    for (int i = 0; i < kHD; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int kv0 = j * kBlk;
+      // stage the additive mask of this key block (mask * log2e; -inf beyond S)
+      asm volatile("bar.sync 1, 128;");
+      {
+        const int kv = kv0 + t;
+        float mv = (kv < p.S) ? (p.mask ? p.mask[static_cast<long long>(b) * p.S + kv] * kLog2e : 0.f) : -INFINITY;
+        mask_s[t] = mv;
+      }
+      asm volatile("bar.sync 1, 128;");
+      ok = mbar_wait(s_full, j & 1, abort_flag, p.status, kStatusWaitAccum);
+      if (!ok) break;
+      tc_fence_after_sync();
+      // pass 1: row maximum
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kBlk; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_S + lane_base + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]) * sc + mask_s[c + i];
+          if (p.causal && kv0 + c + i > q) s = -INFINITY;
+          m_blk = fmaxf(m_blk, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);   // m_run = -inf on the first block -> 0
+      float l_blk = 0.f;
+      // pass 2: probabilities -> shared memory (bf16, swizzled), row sum
+#pragma unroll 1
+      for (int c = 0; c < kBlk; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_S + lane_base + c, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]) * sc + mask_s[c + i];
+          if (p.causal && kv0 + c + i > q) s = -INFINITY;
+          pr[i] = exp2f(s - m_use);
+          l_blk += pr[i];
+        }
+        if (p.p_drop > 0.f) {
+          const unsigned long long base = ((static_cast<unsigned long long>(b) * p.H + h) * p.S + q) * p.S + kv0 + c;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float s4[4];
+            dropout_scale4(seed, base + i, p.p_drop, inv_keep, s4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) pr[i + k] *= s4[k];
+          }
+        }
+        const uint32_t panel = sP + (c >> 6) * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) st_shared_v4(swz_chunk(panel, t, ((c & 63) >> 3) + g), pack8(pr + 8 * g));
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(p_ready);
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      ok = mbar_wait(o_full, j & 1, abort_flag, p.status, kStatusWaitAccum);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < kHD; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_O + lane_base + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(o_done);
+    }
+    if (ok && q < p.S) {
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
+#pragma unroll
+      for (int g = 0; g < kHD / 8; ++g) {
+        float tmp[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tmp[i] = acc[g * 8 + i] * inv_l;
+        *reinterpret_cast<uint4*>(orow + g * 8) = pack8(tmp);
+      }
+      // natural-log LSE of the scaled, masked scores
+      lse[(static_cast<long long>(b) * p.H + h) * p.S + q] = (l_run > 0.f) ? (m_run + log2f(l_run)) / kLog2e : -INFINITY;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, 256);
+  }
+}
+
+// ==================================================================================== backward
+struct BwdSmem {
+  static constexpr int Q = 0;
+  static constexpr int DO = 16384;
+  static constexpr int K = 2 * 16384;
+  static constexpr int V = 3 * 16384;
+  static constexpr int P = 4 * 16384;       // 2 panels
+  static constexpr int DS = 6 * 16384;      // 2 panels
+  static constexpr int MASK = 8 * 16384;
+  static constexpr int BARS = MASK + 512;
+  static constexpr int TOTAL = BARS + 256;
+};
+
+__global__ void __launch_bounds__(kAttnThreads)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                const float* __restrict__ lse, __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk,
+                __nv_bfloat16* __restrict__ dv, float* __restrict__ dq_accum, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;
+  uint64_t* sdp_full = bars + 2;
+  uint64_t* pds_ready = bars + 3;
+  uint64_t* grads_full = bars + 4;
+  uint64_t* tile_done = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* mask_s = reinterpret_cast<float*>(smem + BwdSmem::MASK);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int nblk = (p.S + kBlk - 1) / kBlk;
+  const unsigned long long seed = p.seed + (p.seed_dev ? *p.seed_dev : 0ull);
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(q_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 128);
+    mbar_init(grads_full, 1);
+    mbar_init(tile_done, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc<1>(tmem_slot, 512);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 320, tDQ = tmem_base + 384;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);      // S, dP: both operands K-major
+      const uint32_t idesc_mn = make_idesc_bf16(128, kHD, 1, 1);      // dV, dK: A^T (MN-major) x MN-major
+      const uint32_t idesc_kn = make_idesc_bf16(128, kHD, 0, 1);      // dQ: K-major x MN-major
+      const uint32_t sQ = smem_u32(smem + BwdSmem::Q), sDO = smem_u32(smem + BwdSmem::DO);
+      const uint32_t sK = smem_u32(smem + BwdSmem::K), sV = smem_u32(smem + BwdSmem::V);
+      const uint32_t sP = smem_u32(smem + BwdSmem::P), sDS = smem_u32(smem + BwdSmem::DS);
+      int it = 0;
+      bool ok = true;
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int i0 = p.causal ? j : 0;
+        if (j > 0) {  // the previous key block's tiles (and their dK/dV drain) are finished
+          ok = mbar_wait(tile_done, (it - 1) & 1, abort_flag, p.status, kStatusWaitEpi);
+          if (!ok) break;
+        }
+        mbar_expect_tx(kv_full, 32768);
+        tma_load_4d(smem + BwdSmem::K, &tmK, kv_full, 0, j * kBlk, h, b);
+        tma_load_4d(smem + BwdSmem::V, &tmV, kv_full, 0, j * kBlk, h, b);
+        for (int i = i0; i < nblk && ok; ++i, ++it) {
+          if (i > i0) {
+            ok = mbar_wait(tile_done, (it - 1) & 1, abort_flag, p.status, kStatusWaitEpi);
+            if (!ok) break;
+          }
+          mbar_expect_tx(q_full, 32768);
+          tma_load_4d(smem + BwdSmem::Q, &tmQ, q_full, 0, i * kBlk, h, b);
+          tma_load_4d(smem + BwdSmem::DO, &tmDO, q_full, 0, i * kBlk, h, b);
+          if (i == i0) {
+            ok = mbar_wait(kv_full, j & 1, abort_flag, p.status, kStatusWaitFull);
+            if (!ok) break;
+          }
+          ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kStatusWaitFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k4 = 0; k4 < kHD / 16; ++k4) {
+            umma_bf16<1>(tS, make_smem_desc(sQ + k4 * 32, 16, 1024), make_smem_desc(sK + k4 * 32, 16, 1024), idesc_kk, k4 > 0);
+          }
+#pragma unroll
+          for (int k4 = 0; k4 < kHD / 16; ++k4) {
+            umma_bf16<1>(tDP, make_smem_desc(sDO + k4 * 32, 16, 1024), make_smem_desc(sV + k4 * 32, 16, 1024), idesc_kk, k4 > 0);
+          }
+          umma_commit(sdp_full);
+          ok = mbar_wait(pds_ready, it & 1, abort_flag, p.status, kStatusWaitEpi);
+          if (!ok) break;
+          tc_fence_after_sync();
+          // dV += P^T dO ; dK += dS^T Q   (M = key index, K = query index: 8 steps of 16 rows)
+#pragma unroll
+          for (int k8 = 0; k8 < kBlk / 16; ++k8) {
+            umma_bf16<1>(tDV, make_smem_desc(sP + k8 * 2048, 16384, 1024), make_smem_desc(sDO + k8 * 2048, 8192, 1024), idesc_mn,
+                         (i > i0 || k8 > 0));
+          }
+#pragma unroll
+          for (int k8 = 0; k8 < kBlk / 16; ++k8) {
+            umma_bf16<1>(tDK, make_smem_desc(sDS + k8 * 2048, 16384, 1024), make_smem_desc(sQ + k8 * 2048, 8192, 1024), idesc_mn,
+                         (i > i0 || k8 > 0));
+          }
+          // dQ_tile = dS K   (M = query, K = key index)
+#pragma unroll
+          for (int k8 = 0; k8 < kBlk / 16; ++k8) {
+            const uint32_t a = sDS + (k8 >> 2) * 16384 + (k8 & 3) * 32;
+            umma_bf16<1>(tDQ, make_smem_desc(a, 16, 1024), make_smem_desc(sK + k8 * 2048, 8192, 1024), idesc_kn, k8 > 0);
+          }
+          umma_commit(grads_full);
+        }
+      }
+    }
+  } else {
+    const int t = threadIdx.x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t sP = smem_u32(smem + BwdSmem::P), sDS = smem_u32(smem + BwdSmem::DS);
+    const float sc = p.scale * kLog2e;
+    const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
+    int it = 0;
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int kv0 = j * kBlk;
+      const int i0 = p.causal ? j : 0;
+      asm volatile("bar.sync 1, 128;");
+      {
+        const int kv = kv0 + t;
+        mask_s[t] = (kv < p.S) ? (p.mask ? p.mask[static_cast<long long>(b) * p.S + kv] * kLog2e : 0.f) : -INFINITY;
+      }
+      asm volatile("bar.sync 1, 128;");
+      for (int i = i0; i < nblk && ok; ++i, ++it) {
+        const int q = i * kBlk + t;
+        const bool q_ok = q < p.S;
+        // D = rowsum(dO * O), LSE for this row
+        float Dq = 0.f, lse_q = 0.f;
+        if (q_ok) {
+          const long long off = static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
+#pragma unroll
+          for (int g = 0; g < kHD / 8; ++g) {
+            float a[8], c[8];
+            VecIO<__nv_bfloat16>::load(o + off + g * 8, a);
+            VecIO<__nv_bfloat16>::load(d_o + off + g * 8, c);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) Dq += a[e] * c[e];
+          }
+          lse_q = lse[(static_cast<long long>(b) * p.H + h) * p.S + q] * kLog2e;
+        }
+        ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < kBlk; c += 32) {
+          uint32_t sv[32], dpv[32];
+          tmem_ld32(tS + lane_base + c, sv);
+          tmem_ld32(tDP + lane_base + c, dpv);
+          tmem_ld_wait();
+          float pr[32], ds[32];
+          float z[32];
+          if (p.p_drop > 0.f) {
+            const unsigned long long base = ((static_cast<unsigned long long>(b) * p.H + h) * p.S + q) * p.S + kv0 + c;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float s4[4];
+              dropout_scale4(seed, base + e, p.p_drop, inv_keep, s4);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) z[e + k] = s4[k];
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) z[e] = 1.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float s = __uint_as_float(sv[e]) * sc + mask_s[c + e];
+            if (p.causal && kv0 + c + e > q) s = -INFINITY;
+            const float pe = (q_ok && lse_q != -INFINITY) ? exp2f(s - lse_q) : 0.f;
+            const float dpe = __uint_as_float(dpv[e]) * z[e];
+            pr[e] = pe * z[e];
+            ds[e] = pe * (dpe - Dq) * p.scale;
+          }
+          const uint32_t pp = sP + (c >> 6) * 16384, dp = sDS + (c >> 6) * 16384;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            st_shared_v4(swz_chunk(pp, t, ((c & 63) >> 3) + g), pack8(pr + 8 * g));
+            st_shared_v4(swz_chunk(dp, t, ((c & 63) >> 3) + g), pack8(ds + 8 * g));
+          }
+        }
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(pds_ready);
+        ok = mbar_wait(grads_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // ---- dQ tile: single key block -> write bf16; otherwise accumulate in the fp32 scratch
+        {
+          const int j_first = 0;
+          const int j_last = p.causal ? min(i, nblk - 1) : nblk - 1;
+          const long long off = static_cast<long long>(b) * p.gsb + static_cast<long long>(q) * p.gss + static_cast<long long>(h) * p.gsh;
+          float* acc_row = dq_accum ? dq_accum + ((static_cast<long long>(b) * p.H + h) * p.S + q) * kHD : nullptr;
+#pragma unroll
+          for (int c = 0; c < kHD; c += 32) {
+            uint32_t v[32];
+            tmem_ld32(tDQ + lane_base + c, v);
+            tmem_ld_wait();
+            if (q_ok) {
+              float f[32];
+#pragma unroll
+              for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+              if (j != j_first) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4) {
+                  float4 old = *reinterpret_cast<const float4*>(acc_row + c + e);
+                  f[e] += old.x; f[e + 1] += old.y; f[e + 2] += old.z; f[e + 3] += old.w;
+                }
+              }
+              if (j == j_last) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(dq + off + c + g * 8) = pack8(f + 8 * g);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                  *reinterpret_cast<float4*>(acc_row + c + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+              }
+            }
+          }
+        }
+        // ---- last query block of this key block: drain dK, dV
+        if (i == nblk - 1) {
+          const int kv = kv0 + t;
+          const long long off = static_cast<long long>(b) * p.gsb + static_cast<long long>(kv) * p.gss + static_cast<long long>(h) * p.gsh;
+#pragma unroll
+          for (int c = 0; c < kHD; c += 32) {
+            uint32_t v[32], w[32];
+            tmem_ld32(tDK + lane_base + c, v);
+            tmem_ld32(tDV + lane_base + c, w);
+            tmem_ld_wait();
+            if (kv < p.S) {
+              float f[32], g2[32];
+#pragma unroll
+              for (int e = 0; e < 32; ++e) { f[e] = __uint_as_float(v[e]); g2[e] = __uint_as_float(w[e]); }
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                *reinterpret_cast<uint4*>(dk + off + c + g * 8) = pack8(f + 8 * g);
+                *reinterpret_cast<uint4*>(dv + off + c + g * 8) = pack8(g2 + 8 * g);
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(tile_done);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+static AttnParams make_params(int B, int H, int S, const long long* qs, const long long* os, const long long* gs, const float* mask,
+                              float scale, int causal, float p_drop, unsigned long long seed,
+                              const unsigned long long* seed_dev, int* status) {
+  AttnParams p;
+  p.B = B; p.H = H; p.S = S; p.sb = qs[0]; p.ss = qs[1]; p.sh = qs[2]; p.mask = mask;
+  p.osb = os[0]; p.oss = os[1]; p.osh = os[2];
+  p.gsb = gs[0]; p.gss = gs[1]; p.gsh = gs[2]; p.scale = scale; p.causal = causal;
+  p.p_drop = p_drop; p.seed = seed; p.seed_dev = seed_dev; p.status = status;
+  return p;
+}
+
+static bool strides_ok(const void* ptr, long long sb, long long ss, long long sh) {
+  return (reinterpret_cast<uintptr_t>(ptr) % 16 == 0) && sb % 8 == 0 && ss % 8 == 0 && sh % 8 == 0;
+}
+
+}  // namespace fb
+
+extern "C" int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* mask, int B, int H,
+                           int S, const long long* qkv_strides, const long long* o_strides, float scale, int causal,
+                           float p_drop, unsigned long long seed, const unsigned long long* seed_dev, int* status,
+                           void* stream) {
+  using namespace fb;
+  if (B <= 0 || H <= 0 || S <= 0) return 0;
+  const long long sb = qkv_strides[0], ss = qkv_strides[1], sh = qkv_strides[2];
+  if (!strides_ok(q, sb, ss, sh) || !strides_ok(k, sb, ss, sh) || !strides_ok(v, sb, ss, sh) ||
+      !strides_ok(o, o_strides[0], o_strides[1], o_strides[2]))
+    return -3;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_tmap_bshd(&tq, q, B, H, S, sb, ss, sh))) return r;
+  if ((r = make_tmap_bshd(&tk, k, B, H, S, sb, ss, sh))) return r;
+  if ((r = make_tmap_bshd(&tv, v, B, H, S, sb, ss, sh))) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::TOTAL + 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  AttnParams p = make_params(B, H, S, qkv_strides, o_strides, o_strides, mask, scale, causal, p_drop, seed, seed_dev, status);
+  dim3 grid((S + kBlk - 1) / kBlk, H, B);
+  attn_fwd_kernel<<<grid, kAttnThreads, FwdSmem::TOTAL + 1024, static_cast<cudaStream_t>(stream)>>>(
+      tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dq_accum: fp32 scratch [B, H, S, 64]; only touched when a query block meets more than one key block
+// (S > 128), may be null otherwise.
+extern "C" int fb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                           const float* mask, void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int S,
+                           const long long* qkv_strides, const long long* o_strides, const long long* g_strides,
+                           float scale, int causal, float p_drop, unsigned long long seed,
+                           const unsigned long long* seed_dev, int* status, void* stream) {
+  using namespace fb;
+  if (B <= 0 || H <= 0 || S <= 0) return 0;
+  if (S > kBlk && !dq_accum) return -4;
+  const long long sb = qkv_strides[0], ss = qkv_strides[1], sh = qkv_strides[2];
+  if (!strides_ok(q, sb, ss, sh) || !strides_ok(k, sb, ss, sh) || !strides_ok(v, sb, ss, sh)) return -3;
+  if (!strides_ok(o, o_strides[0], o_strides[1], o_strides[2]) || !strides_ok(d_o, o_strides[0], o_strides[1], o_strides[2])) return -3;
+  if (!strides_ok(dq, g_strides[0], g_strides[1], g_strides[2]) || !strides_ok(dk, g_strides[0], g_strides[1], g_strides[2]) ||
+      !strides_ok(dv, g_strides[0], g_strides[1], g_strides[2]))
+    return -3;
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_tmap_bshd(&tq, q, B, H, S, sb, ss, sh))) return r;
+  if ((r = make_tmap_bshd(&tk, k, B, H, S, sb, ss, sh))) return r;
+  if ((r = make_tmap_bshd(&tv, v, B, H, S, sb, ss, sh))) return r;
+  if ((r = make_tmap_bshd(&tdo, d_o, B, H, S, o_strides[0], o_strides[1], o_strides[2]))) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL + 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  AttnParams p = make_params(B, H, S, qkv_strides, o_strides, g_strides, mask, scale, causal, p_drop, seed, seed_dev, status);
+  dim3 grid(H, B);
+  attn_bwd_kernel<<<grid, kAttnThreads, BwdSmem::TOTAL + 1024, static_cast<cudaStream_t>(stream)>>>(
+      tq, tk, tv, tdo, static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse,
+      static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), dq_accum, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -23,8 +23,9 @@ __global__ void __launch_bounds__(kLnWarps * 32)
 ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
               const float* __restrict__ beta, T* __restrict__ y, T* __restrict__ pre_out,
               float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols, float eps,
-              float p_drop, uint64_t seed) {
+              float p_drop, uint64_t seed_in, const unsigned long long* __restrict__ seed_dev) {
   constexpr int V = VecIO<T>::kVec;
+  const uint64_t seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kLnWarps + warp;
   if (row >= rows) return;
@@ -106,8 +107,9 @@ __global__ void __launch_bounds__(kLnWarps * 32)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* __restrict__ mean,
               const float* __restrict__ rstd, const float* __restrict__ gamma, T* __restrict__ dpre,
               T* __restrict__ dx_drop, float* __restrict__ partial, int rows, int cols, float p_drop,
-              uint64_t seed) {
+              uint64_t seed_in, const unsigned long long* __restrict__ seed_dev) {
   constexpr int V = VecIO<T>::kVec;
+  const uint64_t seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   __shared__ float red[kLnWarps][32 * VPL * V + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = cols / V;
@@ -202,21 +204,21 @@ __global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, float*
 template <typename T, int VPL>
 static int ln_fwd_launch(const void* x, const void* res, const float* gamma, const float* beta, void* y,
                          void* pre, float* mean, float* rstd, int rows, int cols, float eps, float p,
-                         uint64_t seed, cudaStream_t st) {
+                         uint64_t seed, const unsigned long long* seed_dev, cudaStream_t st) {
   const int grid = (rows + kLnWarps - 1) / kLnWarps;
   ln_fwd_kernel<T, VPL><<<grid, kLnWarps * 32, 0, st>>>(
       static_cast<const T*>(x), static_cast<const T*>(res), gamma, beta, static_cast<T*>(y),
-      static_cast<T*>(pre), mean, rstd, rows, cols, eps, p, seed);
+      static_cast<T*>(pre), mean, rstd, rows, cols, eps, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <typename T, int VPL>
 static int ln_bwd_launch(const void* dy, const void* pre, const float* mean, const float* rstd,
                          const float* gamma, void* dpre, void* dxd, float* partial, int grid, int rows,
-                         int cols, float p, uint64_t seed, cudaStream_t st) {
+                         int cols, float p, uint64_t seed, const unsigned long long* seed_dev, cudaStream_t st) {
   ln_bwd_kernel<T, VPL><<<grid, kLnWarps * 32, 0, st>>>(
       static_cast<const T*>(dy), static_cast<const T*>(pre), mean, rstd, gamma, static_cast<T*>(dpre),
-      static_cast<T*>(dxd), partial, rows, cols, p, seed);
+      static_cast<T*>(dxd), partial, rows, cols, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -251,11 +253,11 @@ extern "C" int fb_layernorm_max_cols(int is_bf16) { return 1024; }
 
 extern "C" int fb_layernorm_fwd(const void* x, const void* residual, const float* gamma, const float* beta,
                                 void* y, void* pre_out, float* mean, float* rstd, int rows, int cols,
-                                float eps, float p_drop, unsigned long long seed, int is_bf16, void* stream) {
+                                float eps, float p_drop, unsigned long long seed, const unsigned long long* seed_dev, int is_bf16, void* stream) {
   if (rows <= 0) return 0;
   if (cols % (is_bf16 ? 8 : 4) || cols > 1024) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  FB_LN_DISPATCH(ln_fwd_launch, x, residual, gamma, beta, y, pre_out, mean, rstd, rows, cols, eps, p_drop, seed, st);
+  FB_LN_DISPATCH(ln_fwd_launch, x, residual, gamma, beta, y, pre_out, mean, rstd, rows, cols, eps, p_drop, seed, seed_dev, st);
 }
 
 extern "C" int fb_layernorm_bwd_grid(int rows) {
@@ -267,13 +269,13 @@ extern "C" int fb_layernorm_bwd_grid(int rows) {
 extern "C" int fb_layernorm_bwd(const void* dy, const void* pre, const float* mean, const float* rstd,
                                 const float* gamma, void* dpre, void* dx_drop, float* partial, float* dgamma,
                                 float* dbeta, int accumulate, int rows, int cols, float p_drop,
-                                unsigned long long seed, int is_bf16, void* stream) {
+                                unsigned long long seed, const unsigned long long* seed_dev, int is_bf16, void* stream) {
   if (rows <= 0) return 0;
   if (cols % (is_bf16 ? 8 : 4) || cols > 1024) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = fb_layernorm_bwd_grid(rows);
   auto run = [&]() -> int {
-    FB_LN_DISPATCH(ln_bwd_launch, dy, pre, mean, rstd, gamma, dpre, dx_drop, partial, grid, rows, cols, p_drop, seed, st);
+    FB_LN_DISPATCH(ln_bwd_launch, dy, pre, mean, rstd, gamma, dpre, dx_drop, partial, grid, rows, cols, p_drop, seed, seed_dev, st);
   };
   int r = run();
   if (r) return r;
