@@ -1,0 +1,117 @@
+"""Graph-level data parallelism hooks (flodl/src/graph/distributed.rs). The methods are mixed
+into `Graph`; the machinery lives in `flodl_b200.parallel.ddp`."""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+
+class DistributedMixin:
+    def _init_distributed(self) -> None:
+        self._ddp = None            # parallel.ddp.DistributedState once distribute() ran
+        self._optimizer = None
+        self._scheduler = None
+        self._lr_scale = 1.0
+        self._training_step = 0
+        self._data_binding = None
+        self._loss_fn = None
+
+    # ---- setup ----------------------------------------------------------------------------------
+    def distribute(self, factory: Optional[Callable] = None, **kw):
+        from ..parallel import ddp
+        self._ddp = ddp.DistributedState.for_graph(self, factory, **kw)
+        return self
+
+    def auto_distribute(self, factory: Optional[Callable] = None, **kw):
+        from ..parallel import comm
+        if comm.world_size() > 1:
+            self.distribute(factory, **kw)
+        return self
+
+    def is_distributed(self) -> bool:
+        return self._ddp is not None and self._ddp.intercepts_forward()
+
+    def world_size(self) -> int:
+        return self._ddp.world_size if self._ddp is not None else 1
+
+    def devices(self) -> List:
+        return self._ddp.devices() if self._ddp is not None else [p.t.device for p in self.parameters()[:1]]
+
+    def has_el_che(self) -> bool:
+        return self._ddp is not None and self._ddp.el_che is not None
+
+    def chunk_ratios(self) -> List[float]:
+        return self._ddp.chunk_ratios() if self._ddp is not None else [1.0]
+
+    def throughput(self) -> List[float]:
+        return self._ddp.throughput() if self._ddp is not None else []
+
+    def shard_sizes(self, batch: int) -> List[int]:
+        return self._ddp.shard_sizes(batch) if self._ddp is not None else [batch]
+
+    def forward_distributed(self, x):
+        return self._ddp.forward(self, x)
+
+    # ---- optimizer / schedule -------------------------------------------------------------------
+    def set_optimizer(self, factory: Callable) -> None:
+        """`factory(parameters) -> Optimizer`; one optimizer per replica (here: per process)."""
+        self._optimizer = factory(self.parameters())
+
+    def optimizer(self):
+        return self._optimizer
+
+    def set_scheduler(self, scheduler) -> None:
+        self._scheduler = scheduler
+
+    def set_lr_scale(self, scale: float) -> None:
+        self._lr_scale = float(scale)
+
+    def set_lr(self, lr: float) -> None:
+        if self._optimizer is not None:
+            self._optimizer.set_lr(lr)
+
+    def training_step(self) -> int:
+        return self._training_step
+
+    def step(self) -> None:
+        """All-reduce gradients (when distributed), sync buffers, apply the scheduled learning
+        rate, optimizer step, zero gradients (graph/distributed.rs:239-452)."""
+        if self._optimizer is None:
+            from ..tensor import TensorError
+            raise TensorError("step(): call set_optimizer first")
+        if self._ddp is not None:
+            self._ddp.before_optimizer()
+        if self._scheduler is not None:
+            self._optimizer.set_lr(self._scheduler.lr(self._training_step) * self._lr_scale)
+        self._optimizer.step()
+        self._optimizer.zero_grad()
+        self._training_step += 1
+        if self._ddp is not None:
+            self._ddp.after_step()
+
+    # ---- data binding ---------------------------------------------------------------------------
+    def set_data_loader(self, loader, input_name: str = "input") -> None:
+        self._data_binding = (loader, input_name)
+
+    def set_loss_fn(self, f: Callable) -> None:
+        self._loss_fn = f
+
+    def has_loss_fn(self) -> bool:
+        return self._loss_fn is not None
+
+    def data_num_batches(self) -> int:
+        return self._data_binding[0].num_batches() if self._data_binding else 0
+
+    def data_batch_size(self) -> int:
+        return self._data_binding[0].batch_size if self._data_binding else 0
+
+    def epoch(self, epoch: int):
+        """Iterator over the bound loader's batches for `epoch` (each item: list of tensors)."""
+        if self._data_binding is None:
+            from ..tensor import TensorError
+            raise TensorError("epoch(): call set_data_loader first")
+        return self._data_binding[0].epoch(epoch)
+
+    def forward_batch(self, batch):
+        from ..autograd import Variable
+        x = batch[0] if isinstance(batch, (list, tuple)) else batch
+        return self.forward(x if isinstance(x, Variable) else Variable.wrap(x))
