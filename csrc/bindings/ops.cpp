@@ -183,6 +183,16 @@ void colsum(const Tensor& x, Tensor& out) {
   TORCH_CHECK(out.numel() == x.size(1));
   check(fb_colsum(x.data_ptr(), out.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), is_bf16(x), stream_of(x)), "fb_colsum");
 }
+void embedding_bwd(const Tensor& dy, const Tensor& ids, Tensor& dw, int64_t padding_idx) {
+  want_float_kind(dy, "dy");
+  want_f32(dw, "dw");
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous() && ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous());
+  TORCH_CHECK(dw.dim() == 2 && dy.size(-1) == dw.size(1) && dy.numel() / dw.size(1) == ids.numel());
+  check(fb_embedding_bwd(dy.data_ptr(), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dw.data_ptr<float>(), ids.numel(),
+                         (int)dw.size(1), dw.size(0), padding_idx, is_bf16(dy), stream_of(dy)),
+        "fb_embedding_bwd");
+}
 void cast_into(const Tensor& x, Tensor& y, double scale) {
   want_float_kind(x, "x");
   want_float_kind(y, "y");
@@ -342,6 +352,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("dropout", &dropout, py::arg("x"), py::arg("p"), py::arg("seed"), py::arg("seed_dev") = py::none());
   m.def("colsum", &colsum);
   m.def("cast_into", &cast_into);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("softmax_ce", &softmax_ce);
   m.def("scale_rows", &scale_rows);
   m.def("adam_step", &adam_step, py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p16"), py::arg("hyper"),

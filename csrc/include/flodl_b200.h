@@ -85,6 +85,8 @@ int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int tanh_a
 int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, const unsigned long long* seed_dev,
                int is_bf16, void* stream);
 int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream);
+int fb_embedding_bwd(const void* dy, const long long* ids, float* dw, long long tokens, int dim, long long vocab,
+                     long long padding_idx, int is_bf16, void* stream);
 int fb_cast(const void* x, void* y, long long n, float scale, int in_bf16, int out_bf16, void* stream);
 int fb_softmax_ce(const void* logits, long long ld, const long long* targets, int rows, int V,
                   long long ignore_index, void* dlogits, long long ldd, float* count_inv, float* row_loss,

@@ -113,6 +113,55 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   }
 }
 
+// Vectorised form: a lane owns V consecutive columns (16 bytes), a warp 32*V columns, the 8 warps of
+// a block different rows; partials meet in shared memory, one atomicAdd per column per block.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, int cols, long long ld, int rows_per_block) {
+  constexpr int V = VecIO<T>::kVec;
+  __shared__ float red[8][32 * V + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + lane) * V;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.f;
+  if (c0 < cols) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float v[V];
+      VecIO<T>::load(x + static_cast<long long>(r) * ld + c0, v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) red[warp][lane * V + j] = acc[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 32 * V; c += blockDim.x) {
+    const int col = blockIdx.x * 32 * V + c;
+    if (col < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[w][c];
+      atomicAdd(out + col, s);
+    }
+  }
+}
+
+// dW[ids[t]][:] += dy[t][:] for an embedding table (fp32 accumulation, rows equal to padding_idx skipped).
+template <typename T>
+__global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long long* __restrict__ ids, float* __restrict__ dw,
+                                     long long tokens, int dim, long long vocab, long long padding_idx) {
+  const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const long long id = ids[t];
+  if (id == padding_idx || id < 0 || id >= vocab) return;
+  const T* src = dy + t * dim;
+  float* dst = dw + id * dim;
+  for (int c = threadIdx.x & 31; c < dim; c += 32) atomicAdd(dst + c, VecIO<T>::get(src + c));
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long long n, float scale) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -172,6 +221,16 @@ extern "C" int fb_dropout(const void* x, void* y, long long n, float p, unsigned
 extern "C" int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int vec = is_bf16 ? 8 : 4;
+  if (cols % vec == 0 && ld % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int rpbv = 64;
+    dim3 gridv((cols + 32 * vec - 1) / (32 * vec), (rows + rpbv - 1) / rpbv);
+    if (is_bf16)
+      fb::colsum_vec_kernel<__nv_bfloat16><<<gridv, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld, rpbv);
+    else
+      fb::colsum_vec_kernel<float><<<gridv, 256, 0, st>>>(static_cast<const float*>(x), out, rows, cols, ld, rpbv);
+    return static_cast<int>(cudaGetLastError());
+  }
   int rpb = 256;
   dim3 grid((cols + 31) / 32, (rows + rpb - 1) / rpb);
   dim3 block(32, 32);
@@ -194,5 +253,21 @@ extern "C" int fb_cast(const void* x, void* y, long long n, float scale, int in_
     fb::cast_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, scale);
   else
     fb::cast_kernel<float, float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), n, scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dw (fp32 [vocab, dim]) += scatter of dy ([tokens, dim]) by ids; padding_idx < 0 disables the skip.
+extern "C" int fb_embedding_bwd(const void* dy, const long long* ids, float* dw, long long tokens, int dim, long long vocab,
+                                long long padding_idx, int is_bf16, void* stream) {
+  if (tokens <= 0 || dim <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int warps = 8;
+  const long long grid = (tokens + warps - 1) / warps;
+  if (is_bf16)
+    fb::embedding_bwd_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dy), ids, dw, tokens, dim, vocab, padding_idx);
+  else
+    fb::embedding_bwd_kernel<float><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(static_cast<const float*>(dy), ids, dw,
+                                                                                        tokens, dim, vocab, padding_idx);
   return static_cast<int>(cudaGetLastError());
 }

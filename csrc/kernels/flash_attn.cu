@@ -32,6 +32,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
                       uint32_t box_inner, uint32_t box_outer);  // gemm_tcgen05.cu
+void ensure_thread_context();                                    // gemm_tcgen05.cu
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -48,6 +49,7 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int B, int H, int 
       return -1;
     fn = reinterpret_cast<EncodeTiledFn>(ptr);
   }
+  ensure_thread_context();
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHD), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(sb) * 2};
   cuuint32_t box[4] = {kHD, kBlk, 1, 1};

@@ -429,11 +429,22 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// The tensor-map encoder is a driver-API call and wants a context current on the calling thread;
+// autograd's backward threads only have the runtime's lazy binding, so bind once per thread.
+void ensure_thread_context() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(nullptr);
+    ready = true;
+  }
+}
+
 // 2-D bf16 tensor map over a row-major [rows][ld] matrix with a {box_inner, box_outer} box.
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
                       uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
+  ensure_thread_context();
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {ld_elems * 2};
   cuuint32_t box[2] = {box_inner, box_outer};

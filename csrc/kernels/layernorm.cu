@@ -188,17 +188,29 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* 
   }
 }
 
-__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta, int nblocks, int cols, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(256)
+ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta, int nblocks,
+                       int cols, int accumulate) {
+  // block = 32 columns x 8 row-groups; each row-group strides over the partial rows
+  __shared__ float rg[8][33], rb[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float g = 0.f, b = 0.f;
-  for (int i = 0; i < nblocks; ++i) {
-    g += partial[(static_cast<long long>(i) * 2) * cols + c];
-    b += partial[(static_cast<long long>(i) * 2 + 1) * cols + c];
+  if (c < cols) {
+    for (int i = grp; i < nblocks; i += 8) {
+      g += partial[(static_cast<long long>(i) * 2) * cols + c];
+      b += partial[(static_cast<long long>(i) * 2 + 1) * cols + c];
+    }
   }
-  if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
-  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+  rg[grp][lane] = g;
+  rb[grp][lane] = b;
+  __syncthreads();
+  if (grp == 0 && c < cols) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) { g += rg[w][lane]; b += rb[w][lane]; }
+    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
+    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+  }
 }
 
 template <typename T, int VPL>
@@ -262,7 +274,7 @@ extern "C" int fb_layernorm_fwd(const void* x, const void* residual, const float
 
 extern "C" int fb_layernorm_bwd_grid(int rows) {
   int g = (rows + fb::kLnWarps - 1) / fb::kLnWarps;
-  return g < 296 ? g : 296;
+  return g < 148 ? g : 148;
 }
 
 // `partial` must hold fb_layernorm_bwd_grid(rows) * 2 * cols floats.
@@ -280,7 +292,7 @@ extern "C" int fb_layernorm_bwd(const void* dy, const void* pre, const float* me
   int r = run();
   if (r) return r;
   if (partial && (dgamma || dbeta)) {
-    fb::ln_bwd_finalize_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, dgamma, dbeta, grid, cols, accumulate);
+    fb::ln_bwd_finalize_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, grid, cols, accumulate);
     return static_cast<int>(cudaGetLastError());
   }
   return 0;

@@ -382,7 +382,7 @@ class Embedding(Module):
 
     def forward(self, x):
         idx = x.t if not x.t.is_floating_point() else x.t.long()
-        return W(F.embedding(idx, self.weight.t, self.padding_idx))
+        return W(_ops.embedding(idx, self.weight.t, self.padding_idx))
 
 
 class EmbeddingBag(Module):

@@ -126,6 +126,11 @@ class Module:
     def own_buffers(self) -> List[Buffer]:
         return []
 
+    def fuse_groups(self) -> List[List[Parameter]]:
+        """Groups of parameters a flat-buffer engine should place back to back so one kernel can
+        treat them as a single operand (e.g. the Q, K, V projection weights)."""
+        return []
+
     # ---- collection -----------------------------------------------------------------------------
     def parameters(self) -> List[Parameter]:
         out, seen = [], set()

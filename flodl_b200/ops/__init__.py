@@ -17,6 +17,7 @@ from .core import (  # noqa: F401
     batch_norm,
     cross_entropy,
     dropout,
+    embedding,
     feed_forward,
     gelu,
     layer_norm,

@@ -35,6 +35,8 @@ class _BatchNormFn(torch.autograd.Function):
                                     gslot.view(-1) if use_slots else None, bslot.view(-1) if use_slots else None)
         core._launched(2)
         if use_slots:
+            core._touched(w)
+            core._touched(b)
             dg = db = None
         else:
             dg = None if w is None else dg.to(w.dtype)

@@ -23,6 +23,18 @@ class _Flags(threading.local):
 
 FLAGS = _Flags()
 
+# Called with the parameter tensor each time one of the ops below has written (or accumulated) its
+# gradient straight into the flat gradient buffer. Process-wide on purpose: autograd runs backward
+# on its own thread. The gradient-sync manager uses it to launch a bucket's all-reduce as soon as
+# the bucket is complete.
+GRAD_HOOK = {"fn": None}
+
+
+def _touched(p) -> None:
+    fn = GRAD_HOOK["fn"]
+    if fn is not None and p is not None:
+        fn(p)
+
 
 def set_native(enabled: bool) -> None:
     """Switch the native kernels off (PyTorch ops only) or back on; used by A/B tests."""
@@ -144,6 +156,7 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=Non
     if slot is not None:
         C.gemm(dy2, x2, slot.view(N, K), True, True, alpha=alpha, accumulate=True, split_k=sk)
         _launched()
+        _touched(w)
         return None
     out = torch.zeros(N, K, dtype=torch.float32, device=dy2.device) if sk > 1 else torch.empty(N, K, dtype=torch.float32, device=dy2.device)
     C.gemm(dy2, x2, out, True, True, alpha=alpha, accumulate=sk > 1, split_k=sk)
@@ -157,6 +170,7 @@ def _bias_grad(dy2: torch.Tensor, b: torch.Tensor, alpha=None):
     if slot is not None and alpha is None:
         C.colsum(dy2, slot.view(-1))
         _launched()
+        _touched(b)
         return None
     tmp = torch.zeros(dy2.shape[1], dtype=torch.float32, device=dy2.device)
     C.colsum(dy2, tmp)
@@ -165,6 +179,7 @@ def _bias_grad(dy2: torch.Tensor, b: torch.Tensor, alpha=None):
         tmp = tmp * alpha
     if slot is not None:
         slot.view(-1).add_(tmp)
+        _touched(b)
         return None
     return tmp.to(b.dtype)
 
@@ -302,6 +317,7 @@ class _LayerNormFn(torch.autograd.Function):
         sd = seed_state(x.device) if p_drop > 0.0 else None
         y, pre, mean, rstd = C.layernorm_fwd(xc, rc, _f32(gamma), _f32(beta), eps, p_drop, seed, want_pre, sd)
         _launched()
+        ctx.set_materialize_grads(False)
         ctx.save_for_backward(pre if want_pre else xc, mean, rstd)
         ctx.gamma, ctx.beta, ctx.p, ctx.seed = gamma, beta, p_drop, seed
         ctx.has_res = rc is not None
@@ -313,6 +329,10 @@ class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dpre_extra):
         C = _C()
+        if dy is None:   # only the pre-normalisation output was used downstream
+            pre0 = ctx.saved_tensors[0]
+            return (dpre_extra if ctx.p == 0.0 else C.dropout(dpre_extra.contiguous(), ctx.p, ctx.seed, seed_state(pre0.device)),
+                    dpre_extra if ctx.has_res else None, None, None, None, None, None)
         pre, mean, rstd = ctx.saved_tensors
         gamma, beta, p = ctx.gamma, ctx.beta, ctx.p
         want_pg = (gamma is not None and ctx.needs_input_grad[2]) or (beta is not None and ctx.needs_input_grad[3])
@@ -329,6 +349,9 @@ class _LayerNormFn(torch.autograd.Function):
             dxd = C.dropout(dpre, p, ctx.seed, sd) if p > 0.0 else None
         dx = dxd if p > 0.0 else dpre
         dres = dpre if ctx.has_res else None
+        if use_slots:
+            _touched(gamma)
+            _touched(beta)
         if use_slots or not want_pg:
             dg = db = None
         else:
@@ -557,6 +580,40 @@ def _sdpa_causal_masked(qh, kh, vh, am, p, scale):
     S = qh.shape[-2]
     causal = torch.full((S, S), float("-inf"), device=qh.device, dtype=qh.dtype).triu(1)
     return F.scaled_dot_product_attention(qh, kh, vh, attn_mask=am + causal, dropout_p=p, scale=scale)
+
+
+# -------------------------------------------------------------------------------------- embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight, padding_idx):
+        src = weight
+        ctx.save_for_backward(ids)
+        ctx.weight, ctx.pad = weight, -1 if padding_idx is None else int(padding_idx)
+        return F.embedding(ids, src.detach())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        w = ctx.weight
+        slot = _grad_slot(w)
+        dyc = dy.contiguous()
+        if slot is not None:
+            _C().embedding_bwd(dyc, ids.contiguous(), slot.view(w.shape), ctx.pad)
+            _launched()
+            _touched(w)
+            return None, None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        _C().embedding_bwd(dyc, ids.contiguous(), dw, ctx.pad)
+        _launched()
+        return None, dw.to(w.dtype), None
+
+
+def embedding(ids: torch.Tensor, weight: torch.Tensor, padding_idx=None) -> torch.Tensor:
+    """Row gather; the backward scatter-add goes straight into the flat gradient buffer on CUDA
+    (`at::embedding`, flodl-sys/ops_training.cpp:1080)."""
+    if _native_ok(weight) and weight.dtype == torch.float32 and weight.requires_grad and ids.dtype == torch.int64:
+        return _EmbeddingFn.apply(ids, weight, padding_idx)
+    return F.embedding(ids, weight, padding_idx)
 
 
 # ------------------------------------------------------------------------------------- batch norm

@@ -1,0 +1,188 @@
+"""`TrainEngine`: the fused single-process-per-GPU training step.
+
+What one step does (eager or replayed from a CUDA graph):
+
+    zero the flat gradient buffer -> bump the dropout seed -> forward -> backward
+      (weight gradients are written by the backward GEMMs straight into the flat buffer; each
+       ~25 MB bucket is all-reduced over NVLink on a side stream as soon as it is complete)
+    -> global-norm clip coefficient on the device (optional) -> ONE fused optimizer kernel over
+       the flat parameter buffer, which also refreshes the bf16 shadow the next forward reads.
+
+This replaces the reference's step sequence `backward -> per-parameter ncclAllReduce ->
+per-buffer broadcast -> optimizer -> zero_grad` (flodl/src/graph/distributed.rs:239-452).
+With `capture()` the whole step becomes one CUDA graph launch (the reference exposes CUDA graphs
+through `cuda_graph_capture`, flodl/src/nn/cuda_graph.rs:166-190); per-step scalars (learning
+rate, Adam bias corrections, dropout seed, collective epochs) live in device memory so a replay
+is a correct new step.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .. import _ext, ops as _ops
+from ..nn.module import Module, Parameter, walk_modules
+from ..tensor import TensorError
+from . import comm as _comm
+from .flat import FlatParams
+from .grad_sync import GradSync
+
+SEED_STRIDE = 1_000_003
+
+
+class TrainEngine:
+    def __init__(self, model: Module, optimizer_factory: Callable[[List[Parameter]], object], *, max_grad_norm: Optional[float] = None,
+                 bucket_mb: float = 25.0, overlap: bool = True, comm_backend: str = "symm", comm_blocks: int = 24,
+                 comm_timeout_s: float = 10.0, sync_params: bool = True):
+        self.model = model
+        params = model.parameters()
+        tensors = [p.t for p in params]
+        if not tensors:
+            raise TensorError("TrainEngine: the model has no parameters")
+        self.device = tensors[0].device
+        self.world, self.rank = _comm.world_size(), _comm.rank()
+        groups = [[p.t for p in g] for m in walk_modules(model) for g in m.fuse_groups()]
+        self.symm_grads = self.symm_params = None
+        grad_alloc = param_alloc = None
+        if self.world > 1 and self.device.type == "cuda" and comm_backend == "symm":
+            def grad_alloc(n):
+                self.symm_grads = _comm.SymmetricBuffer(n * 4, self.device.index, comm_timeout_s)
+                return self.symm_grads.view(torch.float32, 0, n)
+
+            def param_alloc(n):
+                self.symm_params = _comm.SymmetricBuffer(n * 4, self.device.index, comm_timeout_s)
+                return self.symm_params.view(torch.float32, 0, n)
+        self.flat = FlatParams(tensors, shadow=self.device.type == "cuda", grad_alloc=grad_alloc, param_alloc=param_alloc, groups=groups)
+        if self.world > 1 and comm_backend != "symm":
+            comm_backend = "nccl"
+        self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend)
+        self.optimizer = optimizer_factory(params)
+        self.max_grad_norm = max_grad_norm
+        self.scheduler = None
+        self.lr_scale = 1.0
+        self.steps = 0
+        self._graph = None
+        self._static_in: List[torch.Tensor] = []
+        self._static_loss: Optional[torch.Tensor] = None
+        self._step_fn = None
+        self.norm_out: Optional[torch.Tensor] = None
+        if sync_params and self.world > 1:
+            self.broadcast_params(0)
+
+    # ---- parameter sync -------------------------------------------------------------------------
+    def broadcast_params(self, root: int = 0) -> None:
+        """Initial parameter sync: one P2P broadcast kernel over the flat buffer instead of one
+        `ncclBroadcast` per tensor (ddp.rs:160-167)."""
+        if self.world <= 1:
+            return
+        if self.symm_params is not None:
+            self.symm_params.broadcast(0, self.flat.total * 4, root, 32)
+        else:
+            torch.distributed.broadcast(self.flat.params, root)
+        self.flat.refresh_shadow()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        if self.symm_params is not None:
+            self.symm_params.check()
+
+    def sync_buffers(self, root: int = 0) -> None:
+        """Broadcast module buffers (BatchNorm running statistics) from `root`, packed into one message."""
+        if self.world <= 1:
+            return
+        bufs = [b.get() for b in self.model.buffers() if b.get().is_floating_point()]
+        if not bufs:
+            return
+        flatb = torch.cat([b.reshape(-1).float() for b in bufs])
+        torch.distributed.broadcast(flatb, root)
+        off = 0
+        for b in bufs:
+            b.copy_(flatb[off:off + b.numel()].view(b.shape))
+            off += b.numel()
+
+    def set_scheduler(self, scheduler, lr_scale: float = 1.0) -> None:
+        self.scheduler, self.lr_scale = scheduler, lr_scale
+
+    # ---- one step -------------------------------------------------------------------------------
+    def _pre(self) -> None:
+        if self.scheduler is not None:
+            self.optimizer.set_lr(self.scheduler.lr(self.steps) * self.lr_scale)
+        if hasattr(self.optimizer, "advance"):
+            self.optimizer.advance()
+
+    def _body(self, loss_fn: Callable[[], object]) -> torch.Tensor:
+        self.flat.zero_grad()
+        if self.device.type == "cuda":
+            _ops.seed_state(self.device).add_(SEED_STRIDE)
+        self.sync.begin_step()
+        loss = loss_fn()
+        lt = loss.t if hasattr(loss, "t") else loss
+        lt.backward()
+        self.sync.finish()
+        if self.max_grad_norm is not None and self.device.type == "cuda" and _ops.native_enabled():
+            self.norm_out = _ext.require().grad_norm(self.flat.grads, float(self.max_grad_norm), 1.0)
+            self.optimizer.set_grad_scale(self.norm_out[1:2])
+        elif self.max_grad_norm is not None:
+            from ..nn.clip import clip_grad_norm
+            clip_grad_norm(self.flat.tensors, self.max_grad_norm)
+        if hasattr(self.optimizer, "apply"):
+            self.optimizer.apply()
+        else:
+            self.optimizer.step()
+        return lt.detach()
+
+    def step(self, loss_fn: Callable[[], object]) -> torch.Tensor:
+        """Eager step; returns the (device) loss tensor."""
+        self._pre()
+        if not hasattr(self.optimizer, "advance"):
+            loss = self._body(loss_fn)
+        else:
+            loss = self._body(loss_fn)
+        self.steps += 1
+        return loss
+
+    # ---- CUDA graph -----------------------------------------------------------------------------
+    def capture(self, step_fn: Callable[..., object], example_inputs: Sequence[torch.Tensor], warmup: int = 3) -> None:
+        """Capture `loss = step_fn(*inputs)` + backward + gradient sync + optimizer as one CUDA graph.
+        `example_inputs` fix shapes and dtypes; `replay(inputs)` copies new data into the static
+        input buffers and launches the graph."""
+        if self.device.type != "cuda":
+            raise TensorError("capture() needs a CUDA device")
+        self._static_in = [t.to(self.device).clone() for t in example_inputs]
+        self._step_fn = step_fn
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):          # also learns the gradient-bucket readiness counts
+                self._pre()
+                self._body(lambda: step_fn(*self._static_in))
+                self.steps += 1
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.sync.check()
+        self._pre()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+            self._static_loss = self._body(lambda: step_fn(*self._static_in))
+        self.steps += 1
+        self._graph = g
+
+    def replay(self, inputs: Sequence[torch.Tensor]) -> torch.Tensor:
+        """One training step through the captured graph. `inputs` may be pinned host tensors (copied
+        asynchronously) or device tensors. Returns the static device loss tensor."""
+        if self._graph is None:
+            raise TensorError("replay() before capture()")
+        for dst, src in zip(self._static_in, inputs):
+            dst.copy_(src, non_blocking=True)
+        self._pre()
+        self._graph.replay()
+        self.steps += 1
+        return self._static_loss
+
+    def check(self) -> None:
+        """Raise if a device-side wait of this rank's collectives or GEMMs gave up."""
+        self.sync.check()
+        if self.device.type == "cuda":
+            st = _ext.require().read_status(self.device.index or 0)
+            if st != 0:
+                raise TensorError(f"a tensor-core kernel reported status {st} (bounded wait gave up)")

@@ -39,9 +39,25 @@ class FlatParams:
     """
 
     def __init__(self, tensors: Sequence[torch.Tensor], shadow: bool = True, grad_alloc: Optional[Callable[[int], torch.Tensor]] = None,
-                 param_alloc: Optional[Callable[[int], torch.Tensor]] = None):
+                 param_alloc: Optional[Callable[[int], torch.Tensor]] = None, groups: Optional[Sequence[Sequence[torch.Tensor]]] = None):
+        # `groups`: lists of tensors that must sit back to back (e.g. the Q, K, V weights of an
+        # attention block, so one GEMM can address them as a single operand)
+        follow = {}
+        for g in groups or ():
+            g = list(g)
+            for t in g[1:]:
+                follow[id(t)] = True
+            follow[("head", id(g[0]))] = g
         uniq, seen = [], set()
         for t in tensors:
+            if id(t) in seen or follow.get(id(t)):
+                continue
+            chain = follow.get(("head", id(t)), [t])
+            for c in chain:
+                if id(c) not in seen:
+                    seen.add(id(c))
+                    uniq.append(c)
+        for t in tensors:   # grouped tensors whose head was not in `tensors`
             if id(t) not in seen:
                 seen.add(id(t))
                 uniq.append(t)

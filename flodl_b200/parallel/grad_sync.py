@@ -1,0 +1,140 @@
+"""Bucketed gradient all-reduce overlapped with backward.
+
+The reference all-reduces one gradient tensor per NCCL call after backward has finished, on the
+default stream (flodl/src/distributed/ddp.rs:133-147; 65 calls per step for ResNet-20, ~200 for
+BERT-base). Here gradients live in one flat fp32 buffer in peer-mapped memory, cut into ~25 MB
+buckets; the moment the last gradient of a bucket has been produced during backward, the bucket's
+all-reduce kernel (csrc/comm: P2P loads/stores over NVLink, averaging fused) is launched on a
+high-priority side stream, and the optimizer waits for all of them through one event.
+
+Bucket readiness: every gradient producer reports the parameter it touched - the native ops
+through `ops.core.GRAD_HOOK` (they write into the flat buffer themselves), everything else through
+`register_post_accumulate_grad_hook`. The number of reports a parameter gets per step (tied
+weights get several) is learned on the first step, which runs without overlap.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..ops import core as _core
+from . import comm as _comm
+from .flat import FlatParams
+
+
+class GradSync:
+    def __init__(self, flat: FlatParams, symm: Optional[_comm.SymmetricBuffer], bucket_bytes: int = 25 * 1024 * 1024,
+                 overlap: bool = True, blocks: int = 24, backend: str = "symm"):
+        self.flat, self.symm, self.blocks = flat, symm, blocks
+        self.world = _comm.world_size()
+        self.backend = backend if self.world > 1 else "none"
+        self.overlap = overlap and self.world > 1
+        self.buckets = flat.buckets(bucket_bytes)
+        self.index: Dict[int, int] = {id(t): i for i, t in enumerate(flat.tensors)}
+        self.bucket_of: List[int] = [0] * len(flat.tensors)
+        for bi, b in enumerate(self.buckets):
+            for i in b["members"]:
+                self.bucket_of[i] = bi
+        self.expected: Optional[List[int]] = None
+        self.touch = [0] * len(flat.tensors)
+        self.pending = [0] * len(self.buckets)
+        self.launched = [False] * len(self.buckets)
+        self.weights: Optional[List[float]] = None
+        self.stream = torch.cuda.Stream(priority=-1) if flat.device.type == "cuda" and self.world > 1 else None
+        self.done = torch.cuda.Event() if self.stream is not None else None
+        self.active = False
+        self.launch_count = 0
+        self._hooks = []
+        if self.world > 1:
+            for t in flat.tensors:
+                if t.requires_grad:
+                    self._hooks.append(t.register_post_accumulate_grad_hook(self._on_touch))
+
+    # ---- per step -------------------------------------------------------------------------------
+    def begin_step(self) -> None:
+        """Call before forward: arms the readiness tracking for this step."""
+        if self.world <= 1:
+            return
+        self.active = True
+        _core.GRAD_HOOK["fn"] = self._on_touch
+        for i in range(len(self.touch)):
+            self.touch[i] = 0
+        for bi, b in enumerate(self.buckets):
+            self.launched[bi] = False
+            self.pending[bi] = sum(1 for i in b["members"] if self.expected is not None and self.expected[i] > 0)
+
+    def _on_touch(self, p: torch.Tensor) -> None:
+        if not self.active:
+            return
+        members = getattr(p, "_fb_members", None)
+        if members is not None:
+            for m in members:
+                self._on_touch(m)
+            return
+        i = self.index.get(id(p))
+        if i is None:
+            return
+        self.touch[i] += 1
+        if self.expected is None or not self.overlap:
+            return
+        if self.touch[i] == self.expected[i]:
+            bi = self.bucket_of[i]
+            self.pending[bi] -= 1
+            if self.pending[bi] == 0 and not self.launched[bi]:
+                self._launch(bi)
+
+    def _launch(self, bi: int) -> None:
+        b = self.buckets[bi]
+        self.launched[bi] = True
+        cur = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.stream.wait_event(ev)
+        with torch.cuda.stream(self.stream):
+            self._reduce_range(b["start"], b["end"])
+        self.launch_count += 1
+
+    def _reduce_range(self, start: int, end: int) -> None:
+        n = end - start
+        if self.backend == "symm":
+            self.symm.all_reduce(start * 4, n, torch.float32, self.weights, self.blocks)
+        elif self.backend == "nccl":
+            g = self.flat.grads[start:end]
+            if self.weights is not None:
+                g.mul_(self.weights[_comm.rank()])
+                torch.distributed.all_reduce(g, torch.distributed.ReduceOp.SUM)
+            else:
+                _comm.all_reduce_nccl([g], _comm.ReduceOp.Avg)
+
+    def finish(self) -> None:
+        """Call after backward: launches whatever has not been launched, then makes the current
+        stream wait for every bucket."""
+        if self.world <= 1:
+            return
+        self.active = False
+        _core.GRAD_HOOK["fn"] = None
+        if self.expected is None:
+            self.expected = list(self.touch)
+        for bi in range(len(self.buckets)):
+            if not self.launched[bi]:
+                self._launch(bi)
+        self.done.record(self.stream)
+        torch.cuda.current_stream().wait_event(self.done)
+
+    # ---- one-off collectives --------------------------------------------------------------------
+    def set_weights(self, weights: Optional[Sequence[float]]) -> None:
+        """Per-rank contribution weights (sum to 1) for unbalanced shards
+        (`weighted_all_reduce_gradients`, ddp.rs:206-225); None = plain average."""
+        self.weights = None if weights is None else [float(w) for w in weights]
+
+    def all_reduce_now(self) -> None:
+        """Non-overlapped all-reduce of the whole gradient buffer on the current stream."""
+        if self.world <= 1:
+            return
+        for b in self.buckets:
+            self._reduce_range(b["start"], b["end"])
+
+    def check(self) -> None:
+        if self.symm is not None:
+            self.symm.check()
