@@ -55,7 +55,7 @@ Tensor& status_word(int device) {
 
 // ------------------------------------------------------------------------------------------ GEMM
 void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, const OptTensor& bias, int epi,
-          const OptTensor& aux, const OptTensor& alpha, bool accumulate, int split_k, int config) {
+          const OptTensor& aux, const OptTensor& alpha, bool accumulate, int split_k, int config, const OptTensor& ts) {
   want_cuda(a, "a");
   c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(is_bf16(a) && is_bf16(b), "gemm operands must be bf16");
@@ -72,11 +72,12 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, c
   if (aux.has_value()) TORCH_CHECK(is_bf16(*aux) && aux->stride(1) == 1 && aux->size(0) == M && aux->size(1) == N, "aux must be bf16 [M,N]");
   if (alpha.has_value()) TORCH_CHECK(alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "alpha must be one fp32");
   Tensor& st = status_word(a.get_device());
-  int rc = fb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+  if (ts.has_value()) TORCH_CHECK(ts->is_cuda() && ts->scalar_type() == at::kLong && ts->numel() >= 8 * 160, "ts must be int64 [>=1280]");
+  int rc = fb_gemm_bf16_ts(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
                         out.stride(0), a_mn, b_mn, out.scalar_type() == at::kFloat, ptr<const void>(bias),
                         bias.has_value() && bias->scalar_type() == at::kFloat, epi, ptr<void>(aux),
                         aux.has_value() ? aux->stride(0) : 0, ptr<const float>(alpha), accumulate, split_k, config,
-                        st.data_ptr<int>(), stream_of(a));
+                        st.data_ptr<int>(), ts.has_value() ? reinterpret_cast<long long*>(ts->data_ptr<int64_t>()) : nullptr, stream_of(a));
   check(rc, "fb_gemm_bf16");
 }
 
@@ -338,7 +339,7 @@ PYBIND11_MODULE(_C, m) {
   m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("bias") = py::none(), py::arg("epi") = 0, py::arg("aux") = py::none(), py::arg("alpha") = py::none(),
-        py::arg("accumulate") = false, py::arg("split_k") = 1, py::arg("config") = -1);
+        py::arg("accumulate") = false, py::arg("split_k") = 1, py::arg("config") = -1, py::arg("ts") = py::none());
   m.def("gemm_pick_config", &gemm_pick_config);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);

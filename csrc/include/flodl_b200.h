@@ -56,6 +56,11 @@ int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lon
                  long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias, int bias_fp32, int epi,
                  void* aux, long long ldaux, const float* alpha, int accumulate, int split_k, int config,
                  int* status, void* stream);
+/* Same, plus an optional device buffer of 8 int64 per CTA that receives a coarse timeline (tuning aid). */
+int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                    long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias, int bias_fp32, int epi,
+                    void* aux, long long ldaux, const float* alpha, int accumulate, int split_k, int config,
+                    int* status, long long* ts, void* stream);
 int fb_gemm_pick_config(int M, int N, int K, int split_k);
 
 /* ---- attention ----------------------------------------------------------------------------- */

@@ -127,12 +127,18 @@ colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, in
   float acc[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) acc[j] = 0.f;
-  if (c0 < cols) {
+  if (c0 + V <= cols) {
     for (int r = r0 + warp; r < r1; r += 8) {
       float v[V];
       VecIO<T>::load(x + static_cast<long long>(r) * ld + c0, v);
 #pragma unroll
       for (int j = 0; j < V; ++j) acc[j] += v[j];
+    }
+  } else if (c0 < cols) {   // ragged last vector of the row
+    for (int r = r0 + warp; r < r1; r += 8) {
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (c0 + j < cols) acc[j] += VecIO<T>::get(x + static_cast<long long>(r) * ld + c0 + j);
     }
   }
 #pragma unroll
@@ -222,7 +228,7 @@ extern "C" int fb_colsum(const void* x, float* out, int rows, int cols, long lon
   if (rows <= 0 || cols <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vec = is_bf16 ? 8 : 4;
-  if (cols % vec == 0 && ld % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+  if (ld % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     const int rpbv = 64;
     dim3 gridv((cols + 32 * vec - 1) / (32 * vec), (rows + rpbv - 1) / rpbv);
     if (is_bf16)

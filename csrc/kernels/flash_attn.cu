@@ -100,23 +100,31 @@ struct AttnParams {
 };
 
 // ===================================================================================== forward
+// Shared-memory layout of the forward kernel for `st` K/V stages (1 when the sequence is a single
+// key block: 82 KB, so two CTAs share an SM; 2 otherwise).
 struct FwdSmem {
-  static constexpr int Q = 0;                    // 16 KB
-  static constexpr int K = 16384;                // 2 x 16 KB
-  static constexpr int V = K + 2 * 16384;        // 2 x 16 KB
-  static constexpr int P = V + 2 * 16384;        // 2 panels x 16 KB
-  static constexpr int MASK = P + 2 * 16384;     // 128 floats
-  static constexpr int BARS = MASK + 512;
-  static constexpr int TOTAL = BARS + 256;
+  int Q, K, V, P, MASK, BARS, TOTAL;
+  __host__ __device__ explicit FwdSmem(int st) {
+    Q = 0;                       // 16 KB
+    K = 16384;                   // st x 16 KB
+    V = K + st * 16384;          // st x 16 KB
+    P = V + st * 16384;          // 2 panels x 16 KB
+    MASK = P + 2 * 16384;        // 128 floats
+    BARS = MASK + 512;
+    TOTAL = BARS + 256;
+  }
 };
 
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ o, float* __restrict__ lse,
                 const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BARS);
+  const int n_kv_all = (p.S + kBlk - 1) / kBlk;
+  const int kv_stages = n_kv_all > 1 ? 2 : 1;
+  const FwdSmem L(kv_stages);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.BARS);
   uint64_t* q_full = bars + 0;
   uint64_t* kv_full = bars + 1;     // [2]
   uint64_t* kv_empty = bars + 3;    // [2]
@@ -126,12 +134,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* o_done = bars + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* mask_s = reinterpret_cast<float*>(smem + FwdSmem::MASK);
+  float* mask_s = reinterpret_cast<float*>(smem + L.MASK);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qb * kBlk;
-  const int n_kv_all = (p.S + kBlk - 1) / kBlk;
   const int n_kv = p.causal ? min(n_kv_all, qb + 1) : n_kv_all;
   const unsigned long long seed = p.seed + (p.seed_dev ? *p.seed_dev : 0ull);
 
@@ -161,21 +168,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // ---------------------------------------------------------- loads + MMA issue (one thread)
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(128, kHD, 0, 1);
-      const uint32_t sQ = smem_u32(smem + FwdSmem::Q);
-      const uint32_t sP = smem_u32(smem + FwdSmem::P);
+      const uint32_t sQ = smem_u32(smem + L.Q);
+      const uint32_t sP = smem_u32(smem + L.P);
       mbar_expect_tx(q_full, 16384);
-      tma_load_4d(smem + FwdSmem::Q, &tmQ, q_full, 0, q0, h, b);
-      for (int j = 0; j < min(2, n_kv); ++j) {
+      tma_load_4d(smem + L.Q, &tmQ, q_full, 0, q0, h, b);
+      for (int j = 0; j < min(kv_stages, n_kv); ++j) {
         mbar_expect_tx(&kv_full[j], 32768);
-        tma_load_4d(smem + FwdSmem::K + j * 16384, &tmK, &kv_full[j], 0, j * kBlk, h, b);
-        tma_load_4d(smem + FwdSmem::V + j * 16384, &tmV, &kv_full[j], 0, j * kBlk, h, b);
+        tma_load_4d(smem + L.K + j * 16384, &tmK, &kv_full[j], 0, j * kBlk, h, b);
+        tma_load_4d(smem + L.V + j * 16384, &tmV, &kv_full[j], 0, j * kBlk, h, b);
       }
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusWaitFull);
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t sK = smem_u32(smem + FwdSmem::K + st * 16384);
-        const uint32_t sV = smem_u32(smem + FwdSmem::V + st * 16384);
-        ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag, p.status, kStatusWaitFull);
+        const int st = j % kv_stages;
+        const int use = j / kv_stages;       // how many times this stage was used before
+        const uint32_t sK = smem_u32(smem + L.K + st * 16384);
+        const uint32_t sV = smem_u32(smem + L.V + st * 16384);
+        ok = mbar_wait(&kv_full[st], use & 1, abort_flag, p.status, kStatusWaitFull);
         if (!ok) break;
         tc_fence_after_sync();
         // S = Q K^T (the softmax threads have drained S of block j-1: they arrived on p_ready)
@@ -198,12 +206,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         umma_commit(o_full);
         umma_commit(&kv_empty[st]);
-        if (j + 2 < n_kv) {
-          ok = mbar_wait(&kv_empty[st], (j >> 1) & 1, abort_flag, p.status, kStatusWaitEmpty);
+        if (j + kv_stages < n_kv) {
+          ok = mbar_wait(&kv_empty[st], use & 1, abort_flag, p.status, kStatusWaitEmpty);
           if (!ok) break;
           mbar_expect_tx(&kv_full[st], 32768);
-          tma_load_4d(smem + FwdSmem::K + st * 16384, &tmK, &kv_full[st], 0, (j + 2) * kBlk, h, b);
-          tma_load_4d(smem + FwdSmem::V + st * 16384, &tmV, &kv_full[st], 0, (j + 2) * kBlk, h, b);
+          tma_load_4d(smem + L.K + st * 16384, &tmK, &kv_full[st], 0, (j + kv_stages) * kBlk, h, b);
+          tma_load_4d(smem + L.V + st * 16384, &tmV, &kv_full[st], 0, (j + kv_stages) * kBlk, h, b);
         }
       }
     }
@@ -212,7 +220,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int t = threadIdx.x;            // row within the block == TMEM lane
     const int q = q0 + t;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t sP = smem_u32(smem + FwdSmem::P);
+    const uint32_t sP = smem_u32(smem + L.P);
     const float sc = p.scale * kLog2e;
     const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
     float m_run = -INFINITY, l_run = 0.f;
@@ -333,7 +341,7 @@ struct BwdSmem {
   static constexpr int TOTAL = BARS + 256;
 };
 
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
@@ -626,13 +634,14 @@ extern "C" int fb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   if ((r = make_tmap_bshd(&tv, v, B, H, S, sb, ss, sh))) return r;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::TOTAL + 1024);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem(2).TOTAL + 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
+  const int smem_bytes = FwdSmem(S > kBlk ? 2 : 1).TOTAL + 1024;
   AttnParams p = make_params(B, H, S, qkv_strides, o_strides, o_strides, mask, scale, causal, p_drop, seed, seed_dev, status);
   dim3 grid((S + kBlk - 1) / kBlk, H, B);
-  attn_fwd_kernel<<<grid, kAttnThreads, FwdSmem::TOTAL + 1024, static_cast<cudaStream_t>(stream)>>>(
+  attn_fwd_kernel<<<grid, kAttnThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
       tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -52,7 +53,10 @@ struct GemmParams {
   const float* alpha;
   int accumulate;
   int split_k;
+  int c_mode;      // 0 = per-thread global stores, 1 = staged TMA store, 2 = staged TMA reduce-add (fp32)
+  int aux_tma;     // the GELU pre-activation goes out through its own staged TMA store
   int* status;
+  long long* ts;   // optional per-CTA timeline (8 slots each), for tuning
 };
 
 template <int kCG, int kBN>
@@ -61,9 +65,11 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = (160 * 1024) / STAGE_BYTES;
   static constexpr int TMEM_COLS = (2 * kBN < 32) ? 32 : 2 * kBN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  // epilogue staging: 4 KB (32 rows x 128 B, swizzled) per epilogue warp for C, the same again for aux
+  static constexpr int EPI_BYTES = 2 * kEpiWarps * 4096;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
   static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
 };
 
@@ -96,7 +102,89 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 
-// Epilogue for 32 consecutive columns of one output row.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack_bf16x2(uint32_t w, float& lo, float& hi) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  lo = f.x;
+  hi = f.y;
+}
+
+// Epilogue for 32 consecutive columns of one output row. Every loop over the 32 values is fully
+// unrolled with compile-time indices (tails are handled by predicates), so the values stay in
+// registers: a dynamically indexed copy would be demoted to local memory and every access to it
+// would become a memory transaction.
+// Registers-only part: alpha, bias, activation. `v` receives the output values, `pre` the
+// pre-activation (only meaningful for the GELU epilogues). Rows/cols outside the problem yield
+// harmless values; the caller's store clips them.
+__device__ __forceinline__ void epilogue_compute32(const GemmParams& p, const uint32_t (&acc)[32], int row, int col0,
+                                                   bool add_bias, float (&v)[32], float (&pre)[32]) {
+  const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
+  const int nvalid = (col0 + 32 <= p.N) ? 32 : (p.N > col0 ? p.N - col0 : 0);
+  if (p.bias && add_bias) {
+    if (p.bias_fp32) {
+      const float* b = static_cast<const float*>(p.bias) + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) v[i] += __ldg(b + i);
+    } else {
+      const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) v[i] += __bfloat162float(b[i]);
+    }
+  }
+  if (p.epi == FB_EPI_GELU_ERF) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { pre[i] = v[i]; v[i] = gelu_erf_f(v[i]); }
+  } else if (p.epi == FB_EPI_GELU_TANH) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { pre[i] = v[i]; v[i] = gelu_tanh_f(v[i]); }
+  } else if ((p.epi == FB_EPI_DGELU_ERF || p.epi == FB_EPI_DGELU_TANH) && row < p.M) {
+    const __nv_bfloat16* a =
+        static_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
+    const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float h[8];
+      if (vec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(a + j * 8);
+        unpack_bf16x2(raw.x, h[0], h[1]);
+        unpack_bf16x2(raw.y, h[2], h[3]);
+        unpack_bf16x2(raw.z, h[4], h[5]);
+        unpack_bf16x2(raw.w, h[6], h[7]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = (j * 8 + i < nvalid) ? __bfloat162float(a[j * 8 + i]) : 0.f;
+      }
+      if (p.epi == FB_EPI_DGELU_ERF) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j * 8 + i] *= dgelu_erf_f(h[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j * 8 + i] *= dgelu_tanh_f(h[i]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// 16-byte piece `piece` (0..7) of row `row` (0..31) in a 32 x 128-byte tile with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t stage_addr(uint32_t base, int row, int piece) {
+  return base + row * 128 + ((piece ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint32_t (&acc)[32],
                                                  int row, int col0, bool add_bias) {
   if (row >= p.M || col0 >= p.N) return;
@@ -105,17 +193,18 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
   const bool full = (col0 + 32 <= p.N);
+  const int nvalid = full ? 32 : (p.N - col0);
   if (p.bias && add_bias) {
     if (p.bias_fp32) {
       const float* b = static_cast<const float*>(p.bias) + col0;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (full || col0 + i < p.N) v[i] += __ldg(b + i);
+        if (i < nvalid) v[i] += __ldg(b + i);
     } else {
       const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (full || col0 + i < p.N) v[i] += __bfloat162float(b[i]);
+        if (i < nvalid) v[i] += __bfloat162float(b[i]);
     }
   }
   if (p.epi == FB_EPI_GELU_ERF || p.epi == FB_EPI_GELU_TANH) {
@@ -124,13 +213,17 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
       if (full && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 h[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j * 8 + 2 * i], v[j * 8 + 2 * i + 1]);
-          *reinterpret_cast<uint4*>(a + j * 8) = *reinterpret_cast<uint4*>(h);
+          uint4 pk;
+          pk.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+          pk.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+          pk.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+          pk.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+          *reinterpret_cast<uint4*>(a + j * 8) = pk;
         }
       } else {
-        for (int i = 0; i < 32 && col0 + i < p.N; ++i) a[i] = __float2bfloat16(v[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < nvalid) a[i] = __float2bfloat16(v[i]);
       }
     }
     if (p.epi == FB_EPI_GELU_ERF) {
@@ -143,48 +236,50 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
   } else if (p.epi == FB_EPI_DGELU_ERF || p.epi == FB_EPI_DGELU_TANH) {
     const __nv_bfloat16* a =
         static_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
-    float h[32];
-    if (full && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
+    const bool vec = full && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 raw = *reinterpret_cast<const uint4*>(a + j * 8);
-        const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int j = 0; j < 4; ++j) {
+      float h[8];
+      if (vec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(a + j * 8);
+        unpack_bf16x2(raw.x, h[0], h[1]);
+        unpack_bf16x2(raw.y, h[2], h[3]);
+        unpack_bf16x2(raw.z, h[4], h[5]);
+        unpack_bf16x2(raw.w, h[6], h[7]);
+      } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 f = __bfloat1622float2(hp[i]);
-          h[j * 8 + 2 * i] = f.x;
-          h[j * 8 + 2 * i + 1] = f.y;
-        }
+        for (int i = 0; i < 8; ++i) h[i] = (j * 8 + i < nvalid) ? __bfloat162float(a[j * 8 + i]) : 0.f;
       }
-    } else {
+      if (p.epi == FB_EPI_DGELU_ERF) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) h[i] = (col0 + i < p.N) ? __bfloat162float(a[i]) : 0.f;
-    }
-    if (p.epi == FB_EPI_DGELU_ERF) {
+        for (int i = 0; i < 8; ++i) v[j * 8 + i] *= dgelu_erf_f(h[i]);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= dgelu_erf_f(h[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= dgelu_tanh_f(h[i]);
+        for (int i = 0; i < 8; ++i) v[j * 8 + i] *= dgelu_tanh_f(h[i]);
+      }
     }
   }
 
   if (p.c_fp32) {
     float* c = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
     if (p.split_k > 1) {
-      for (int i = 0; i < 32 && col0 + i < p.N; ++i) atomicAdd(c + i, v[i]);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) atomicAdd(c + i, v[i]);
     } else if (full && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         if (p.accumulate) {
-          float4 old = *reinterpret_cast<float4*>(c + 4 * j);
+          const float4 old = *reinterpret_cast<const float4*>(c + 4 * j);
           o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
         }
         *reinterpret_cast<float4*>(c + 4 * j) = o;
       }
     } else {
-      for (int i = 0; i < 32 && col0 + i < p.N; ++i) c[i] = p.accumulate ? c[i] + v[i] : v[i];
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) c[i] = p.accumulate ? c[i] + v[i] : v[i];
     }
   } else {
     __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
@@ -192,25 +287,30 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (p.accumulate) {
-          uint4 raw = *reinterpret_cast<uint4*>(c + j * 8);
-          const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&raw);
+          const uint4 raw = *reinterpret_cast<const uint4*>(c + j * 8);
+          float o[8];
+          unpack_bf16x2(raw.x, o[0], o[1]);
+          unpack_bf16x2(raw.y, o[2], o[3]);
+          unpack_bf16x2(raw.z, o[4], o[5]);
+          unpack_bf16x2(raw.w, o[6], o[7]);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 f = __bfloat1622float2(op[i]);
-            v[j * 8 + 2 * i] += f.x;
-            v[j * 8 + 2 * i + 1] += f.y;
-          }
+          for (int i = 0; i < 8; ++i) v[j * 8 + i] += o[i];
         }
-        __nv_bfloat162 h[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j * 8 + 2 * i], v[j * 8 + 2 * i + 1]);
-        *reinterpret_cast<uint4*>(c + j * 8) = *reinterpret_cast<uint4*>(h);
+        uint4 pk;
+        pk.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+        pk.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+        pk.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+        pk.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+        *reinterpret_cast<uint4*>(c + j * 8) = pk;
       }
     } else {
-      for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-        float o = v[i];
-        if (p.accumulate) o += __bfloat162float(c[i]);
-        c[i] = __float2bfloat16(o);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < nvalid) {
+          float o = v[i];
+          if (p.accumulate) o += __bfloat162float(c[i]);
+          c[i] = __float2bfloat16(o);
+        }
       }
     }
   }
@@ -219,13 +319,14 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
 template <int kCG, int kBN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using Cfg = GemmCfg<kCG, kBN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint8_t* epi_smem = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_smem + Cfg::EPI_BYTES);
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
   uint64_t* tfull_bar = empty_bar + Cfg::STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -244,6 +345,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int kb_per = (num_kb + p.split_k - 1) / p.split_k;
   const int num_units = num_m * num_n * p.split_k;
 
+  if (p.ts && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    p.ts[blockIdx.x * 8 + 0] = static_cast<long long>(g);
+    p.ts[blockIdx.x * 8 + 1] = clock64();
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -259,6 +366,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.c_mode) tma_prefetch_desc(&tmC);
+    if (p.aux_tma) tma_prefetch_desc(&tmAux);
   }
   if (warp == 1) {
     tmem_alloc<kCG>(tmem_slot, Cfg::TMEM_COLS);
@@ -347,6 +456,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kStatusWaitFull);
           if (!ok) break;
           tc_fence_after_sync();
+          if (p.ts && it == 0 && kb == kb0) p.ts[blockIdx.x * 8 + 2] = clock64();
           const uint32_t sa = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
           const uint32_t sb = sa + Cfg::A_BYTES;
 #pragma unroll
@@ -362,6 +472,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         if constexpr (kCG == 1) umma_commit(&tfull_bar[acc]);
         else umma_commit_pair(&tfull_bar[acc], 3);
+        if (p.ts && it == 0) p.ts[blockIdx.x * 8 + 3] = clock64();
       }
     }
   } else {
@@ -380,27 +491,96 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, abort_flag, p.status, kStatusWaitAccum);
       if (!ok) break;
       tc_fence_after_sync();
+      if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 4] = clock64();
       const int row = m0 + q * 32 + lane;
+      const int row0 = m0 + q * 32;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * COLS_PER_WARP;
+      const int ncol0 = n0 + half * COLS_PER_WARP;
+      if (p.c_mode == 0) {
 #pragma unroll 1
-      for (int c = 0; c < COLS_PER_WARP; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c, v);
-        tmem_ld_wait();
-        epilogue_store32(p, v, row, n0 + half * COLS_PER_WARP + c, ks == 0);
+        for (int c = 0; c < COLS_PER_WARP; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          epilogue_store32(p, v, row, ncol0 + c, ks == 0);
+        }
+      } else {
+        const uint32_t sc = smem_u32(epi_smem + (warp - 2) * 4096);
+        const uint32_t sx = smem_u32(epi_smem + (kEpiWarps + warp - 2) * 4096);
+        if (!p.c_fp32) {
+          // bf16 output: 64 columns (128 bytes per row) per staged store
+#pragma unroll 1
+          for (int c = 0; c < COLS_PER_WARP; c += 64) {
+            if (ncol0 + c >= p.N) break;
+            if (lane == 0) tma_store_wait_read();   // the previous chunk's store has read the staging tile
+            __syncwarp();
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {          // two 32-column halves, one at a time (register pressure)
+              uint32_t r0[32];
+              tmem_ld32(taddr + c + 32 * hh, r0);
+              tmem_ld_wait();
+              float v0[32], p0[32];
+              epilogue_compute32(p, r0, row, ncol0 + c + 32 * hh, ks == 0, v0, p0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                st_shared_v4(stage_addr(sc, lane, 4 * hh + j), pack_bf16x2(v0[8 * j], v0[8 * j + 1]), pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]),
+                             pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]), pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]));
+              if (p.aux_tma) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  st_shared_v4(stage_addr(sx, lane, 4 * hh + j), pack_bf16x2(p0[8 * j], p0[8 * j + 1]), pack_bf16x2(p0[8 * j + 2], p0[8 * j + 3]),
+                               pack_bf16x2(p0[8 * j + 4], p0[8 * j + 5]), pack_bf16x2(p0[8 * j + 6], p0[8 * j + 7]));
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
+              if (p.aux_tma) tma_store_2d(&tmAux, epi_smem + (kEpiWarps + warp - 2) * 4096, ncol0 + c, row0);
+              tma_store_commit();
+            }
+          }
+        } else {
+          // fp32 output: 32 columns (128 bytes per row) per staged store or reduce-add
+#pragma unroll 1
+          for (int c = 0; c < COLS_PER_WARP; c += 32) {
+            if (ncol0 + c >= p.N) break;
+            uint32_t r0[32];
+            tmem_ld32(taddr + c, r0);
+            tmem_ld_wait();
+            float v0[32], p0[32];
+            epilogue_compute32(p, r0, row, ncol0 + c, ks == 0, v0, p0);
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_shared_v4(stage_addr(sc, lane, j), __float_as_uint(v0[4 * j]), __float_as_uint(v0[4 * j + 1]),
+                           __float_as_uint(v0[4 * j + 2]), __float_as_uint(v0[4 * j + 3]));
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.c_mode == 2) tma_reduce_add_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
+              else tma_store_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
+              tma_store_commit();
+            }
+          }
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
+      if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 5] = clock64();
       if (lane == 0) {
         if (kCG == 1 || rank == 0) mbar_arrive(&tempty_bar[acc]);
         else mbar_arrive_cluster(&tempty_bar[acc], 0);
       }
     }
+    if (p.c_mode && lane == 0) tma_store_wait_all();   // staged stores must land before the CTA retires
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 6] = clock64();
   if constexpr (kCG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
@@ -455,6 +635,22 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Tensor map for a staged epilogue store: 32 rows x 128 bytes per box, 128-byte swizzle.
+static int make_tmap_out(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t ld_elems, bool fp32) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  ensure_thread_context();
+  const uint64_t esz = fp32 ? 4 : 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_elems * esz};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esz), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 static int sm_count() {
   static int n = 0;
   if (!n) {
@@ -466,7 +662,8 @@ static int sm_count() {
 }
 
 template <int kCG, int kBN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx, const GemmParams& p,
+                       cudaStream_t stream) {
   using Cfg = GemmCfg<kCG, kBN>;
   static bool configured = false;
   auto kern = gemm_bf16_kernel<kCG, kBN>;
@@ -492,11 +689,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, p);
   return static_cast<int>(e);
 }
 
 }  // namespace fb
+
+extern "C" int fb_gemm_bf16_ts(const void*, const void*, void*, int, int, int, long long, long long, long long, int, int, int, const void*, int,
+                               int, void*, long long, const float*, int, int, int, int*, long long*, void*);
 
 extern "C" int fb_gemm_pick_config(int M, int N, int K, int split_k) {
   // Score = SM occupancy of the last wave x a per-tile efficiency prior (bigger tiles re-use
@@ -524,6 +724,14 @@ extern "C" int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                             long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias,
                             int bias_fp32, int epi, void* aux, long long ldaux, const float* alpha,
                             int accumulate, int split_k, int config, int* status, void* stream_) {
+  return fb_gemm_bf16_ts(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_fp32, bias, bias_fp32, epi, aux, ldaux, alpha, accumulate, split_k,
+                         config, status, nullptr, stream_);
+}
+
+extern "C" int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                               long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias,
+                               int bias_fp32, int epi, void* aux, long long ldaux, const float* alpha,
+                               int accumulate, int split_k, int config, int* status, long long* ts, void* stream_) {
   using namespace fb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -544,14 +752,36 @@ extern "C" int fb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   else       r = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
   if (r) return r;
 
+  // epilogue path: staged TMA stores need 16-byte aligned rows; bf16 accumulate keeps the direct path
+  const size_t c_esz = c_fp32 ? 4 : 2;
+  const bool c_aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * c_esz) % 16 == 0;
+  int c_mode = 0;
+  if (c_aligned) {
+    if (c_fp32) c_mode = (accumulate || split_k > 1) ? 2 : 1;
+    else if (!accumulate) c_mode = 1;
+  }
+  if (bn < 128) c_mode = 0;   // 32 columns per epilogue warp: narrower than one staged bf16 box
+  const bool gelu_fwd = (epi == FB_EPI_GELU_ERF || epi == FB_EPI_GELU_TANH);
+  int aux_tma = 0;
+  if (gelu_fwd && aux) {
+    if (c_mode == 1 && !c_fp32 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0 && (ldaux * 2) % 16 == 0) aux_tma = 1;
+    else c_mode = 0;
+  }
+  CUtensorMap tc, tx;
+  std::memset(&tc, 0, sizeof(tc));
+  std::memset(&tx, 0, sizeof(tx));
+  if (c_mode && (r = make_tmap_out(&tc, C, N, M, ldc, c_fp32 != 0))) return r;
+  if (aux_tma && (r = make_tmap_out(&tx, aux, N, M, ldaux, false))) return r;
+
   GemmParams p;
+  p.c_mode = c_mode; p.aux_tma = aux_tma;
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.epi = epi; p.aux = aux; p.ldaux = ldaux; p.alpha = alpha;
-  p.accumulate = accumulate; p.split_k = split_k; p.status = status;
+  p.accumulate = accumulate; p.split_k = split_k; p.status = status; p.ts = ts;
   switch (config) {
-    case 0: return launch_gemm<2, 256>(ta, tb, p, stream);
-    case 1: return launch_gemm<1, 256>(ta, tb, p, stream);
-    case 2: return launch_gemm<1, 128>(ta, tb, p, stream);
-    default: return launch_gemm<1, 64>(ta, tb, p, stream);
+    case 0: return launch_gemm<2, 256>(ta, tb, tc, tx, p, stream);
+    case 1: return launch_gemm<1, 256>(ta, tb, tc, tx, p, stream);
+    case 2: return launch_gemm<1, 128>(ta, tb, tc, tx, p, stream);
+    default: return launch_gemm<1, 64>(ta, tb, tc, tx, p, stream);
   }
 }

@@ -274,7 +274,7 @@ extern "C" int fb_layernorm_fwd(const void* x, const void* residual, const float
 
 extern "C" int fb_layernorm_bwd_grid(int rows) {
   int g = (rows + fb::kLnWarps - 1) / fb::kLnWarps;
-  return g < 148 ? g : 148;
+  return g < 592 ? g : 592;
 }
 
 // `partial` must hold fb_layernorm_bwd_grid(rows) * 2 * cols floats.

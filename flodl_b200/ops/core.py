@@ -135,11 +135,15 @@ def _f32(t: Optional[torch.Tensor]):
     return t if t.dtype == torch.float32 and t.is_contiguous() else t.float().contiguous()
 
 
-def _pick_split_k(m_out: int, n_out: int, k_red: int) -> int:
-    tiles = math.ceil(m_out / 128) * math.ceil(n_out / 128)
-    if tiles >= 96 or k_red < 1024:
-        return 1
-    return max(1, min(8, 148 // tiles, k_red // 512))
+def _pick_dw_plan(m_out: int, n_out: int, k_red: int):
+    """(config, split_k) for a weight-gradient GEMM (few output tiles, long reduction), from
+    measurements on B200: enough 256x256 pair tiles -> pair config, else split the reduction."""
+    pair_tiles = math.ceil(m_out / 256) * math.ceil(n_out / 256)
+    if pair_tiles >= 148 or k_red < 1024:
+        return -1, 1
+    if pair_tiles >= 24:
+        return 0, 2 if k_red >= 2048 else 1
+    return 2, max(1, min(4, k_red // 512))
 
 
 _EPI = {None: 0, "gelu": 1, "gelu_tanh": 3}
@@ -152,14 +156,14 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=Non
     C = _C()
     N, K = dy2.shape[1], x2.shape[1]
     slot = _grad_slot(w)
-    sk = _pick_split_k(N, K, dy2.shape[0])
+    cfg, sk = _pick_dw_plan(N, K, dy2.shape[0])
     if slot is not None:
-        C.gemm(dy2, x2, slot.view(N, K), True, True, alpha=alpha, accumulate=True, split_k=sk)
+        C.gemm(dy2, x2, slot.view(N, K), True, True, alpha=alpha, accumulate=True, split_k=sk, config=cfg)
         _launched()
         _touched(w)
         return None
     out = torch.zeros(N, K, dtype=torch.float32, device=dy2.device) if sk > 1 else torch.empty(N, K, dtype=torch.float32, device=dy2.device)
-    C.gemm(dy2, x2, out, True, True, alpha=alpha, accumulate=sk > 1, split_k=sk)
+    C.gemm(dy2, x2, out, True, True, alpha=alpha, accumulate=sk > 1, split_k=sk, config=cfg)
     _launched()
     return out.to(w.dtype)
 
