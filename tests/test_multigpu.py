@@ -1,0 +1,29 @@
+"""Multi-GPU tests: run the worker under torch.distributed.run on 2 GPUs (skipped with fewer)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(mode: str, nproc: int = 2, port: int = 29631):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "_mg_worker.py"), mode]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0 and f"MG_OK {mode}" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def test_symmetric_collectives_2gpu():
+    _run("collectives", 2, 29631)
+
+
+def test_train_engine_ddp_2gpu():
+    _run("engine", 2, 29632)
