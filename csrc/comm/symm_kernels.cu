@@ -149,31 +149,46 @@ allreduce_twoshot_kernel(SymmCtx c, long long byte_off, long long n, Weights wts
   const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
 
   if (symm_block_barrier(c, epoch, &sh_fail)) {
+    // U vectors per thread per trip: U*W independent 16-byte peer loads are in flight per thread,
+    // which is what it takes to cover the NVLink round trip at full rate.
+    constexpr int U = (W <= 2) ? 8 : (W <= 4 ? 4 : 2);
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long i = v0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < v1; i += stride) {
-      uint4 raw[W];
+    for (long long i0 = v0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * U) {
+      uint4 raw[U][W];
 #pragma unroll
-      for (int p = 0; p < W; ++p) {
-        const int src = (c.rank + p) % W;  // stagger so peers are not all hit in the same order
-        raw[p] = ld_peer(static_cast<const char*>(c.data[src]) + byte_off + i * 16);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) {
+#pragma unroll
+          for (int p = 0; p < W; ++p) {
+            const int src = (c.rank + p) % W;  // stagger so peers are not all hit in the same order
+            raw[u][p] = ld_peer(static_cast<const char*>(c.data[src]) + byte_off + i * 16);
+          }
+        }
       }
-      float acc[E];
 #pragma unroll
-      for (int j = 0; j < E; ++j) acc[j] = 0.f;
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < v1) {
+          float acc[E];
 #pragma unroll
-      for (int p = 0; p < W; ++p) {
-        const int src = (c.rank + p) % W;
-        float v[E];
-        Pack<T>::to_f(raw[p], v);
-        const float w = wts.w[src];
+          for (int j = 0; j < E; ++j) acc[j] = 0.f;
 #pragma unroll
-        for (int j = 0; j < E; ++j) acc[j] += v[j] * w;
-      }
-      const uint4 out = Pack<T>::from_f(acc);
+          for (int p = 0; p < W; ++p) {
+            const int src = (c.rank + p) % W;
+            float v[E];
+            Pack<T>::to_f(raw[u][p], v);
+            const float w = wts.w[src];
 #pragma unroll
-      for (int p = 0; p < W; ++p) {
-        const int dst = (c.rank + p) % W;
-        st_peer(static_cast<char*>(c.data[dst]) + byte_off + i * 16, out);
+            for (int j = 0; j < E; ++j) acc[j] += v[j] * w;
+          }
+          const uint4 out = Pack<T>::from_f(acc);
+#pragma unroll
+          for (int p = 0; p < W; ++p) {
+            const int dst = (c.rank + p) % W;
+            st_peer(static_cast<char*>(c.data[dst]) + byte_off + i * 16, out);
+          }
+        }
       }
     }
     symm_block_barrier(c, epoch, &sh_fail);
