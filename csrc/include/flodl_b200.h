@@ -115,6 +115,22 @@ int fb_grad_norm_parts(long long n);
 int fb_grad_norm(const void* g, long long n, float* partial, float max_norm, float extra_scale, float* out,
                  int is_bf16, void* stream);
 
+/* Gradient norm without any allocation (this entry point has no counterpart in the reference).
+ * For callers that cannot obtain device memory at the point of the call: a step being captured
+ * into a CUDA graph by someone who owns no memory pool, a thread that must keep away from the
+ * allocator while a collective is in flight, or a non-PyTorch host of this C ABI that has no
+ * allocator to lend. Same result as fb_grad_norm; the per-block partial sums live in a fixed
+ * 4 KB array inside the library (held on every GPU that loads it until the process exits).
+ *   - n above FB_GRAD_NORM_NOALLOC_MAX_ELEMS is rejected with -4;
+ *   - the first call on a device resolves the array's address (with that device current): make it
+ *     before any stream capture;
+ *   - every call reuses the array, so calls that may overlap on the GPU must be ordered by the
+ *     caller; nothing needs clearing between calls. */
+#define FB_GRAD_NORM_NOALLOC_MAX_ELEMS (1LL << 31)
+int fb_grad_norm_noalloc(const void* g, long long n, float max_norm, float extra_scale, float* out, int is_bf16,
+                         void* stream);
+long long fb_grad_norm_noalloc_max(void);
+
 /* ---- collectives over peer-mapped buffers ---------------------------------------------------- */
 int fb_allreduce(const fb_symm_ctx* ctx, long long byte_off, long long n, int is_bf16, const float* weights,
                  int blocks, void* stream);

@@ -196,3 +196,54 @@ extern "C" int fb_grad_norm(const void* g, long long n, float* partial, float ma
   fb::sumsq_finalize_kernel<<<1, 256, 0, st>>>(partial, parts, max_norm, extra_scale, out);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of fb_grad_norm (no counterpart in the reference).
+//
+// Who needs it: code that computes a gradient norm from a place where device memory must not be
+// requested - inside a region that is being captured into a CUDA graph by a caller who owns no
+// memory pool, from a host thread that is forbidden to touch the allocator while a collective is
+// pending on another stream, or from a foreign runtime that links this library through the C ABI
+// and has no allocator to hand us. Such callers still own the gradient buffer and the two-float
+// result; the only thing fb_grad_norm additionally needs is room for one partial sum per block,
+// and here that room is a fixed array inside the library.
+//
+// The array costs 4 KB on every GPU that loads the library, for the life of the process. All calls
+// share it: each launch overwrites every slot it later reads, so nothing has to be cleared between
+// calls, but two calls that overlap on the GPU (different streams, no ordering) would corrupt
+// each other's partial sums - serialise them. The first call on a device looks the array's device
+// address up (with that device current) and remembers it; make that first call outside any
+// stream capture.
+constexpr int kNormScratchFloats = 1024;
+static __device__ __align__(256) float g_norm_scratch[kNormScratchFloats];
+
+extern "C" int fb_grad_norm_noalloc(const void* g, long long n, float max_norm, float extra_scale, float* out,
+                                    int is_bf16, void* stream) {
+  if (n < 0 || n > FB_GRAD_NORM_NOALLOC_MAX_ELEMS) return -4;   // see fb_grad_norm_noalloc_max()
+  constexpr int kMaxDevices = 64;
+  static float* scratch_of[kMaxDevices] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return -4;
+  if (!scratch_of[dev]) {
+    // In host code `g_norm_scratch` is only a handle for the symbol; the kernel needs the address
+    // the array has on THIS device.
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_norm_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    scratch_of[dev] = ptr;
+  }
+  const int parts = fb_grad_norm_parts(n);
+  if (parts > kNormScratchFloats) return -4;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = scratch_of[dev];
+  if (is_bf16)
+    fb::sumsq_partial_kernel<__nv_bfloat16><<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(g), n, partial);
+  else
+    fb::sumsq_partial_kernel<float><<<parts, 256, 0, st>>>(static_cast<const float*>(g), n, partial);
+  fb::sumsq_finalize_kernel<<<1, 256, 0, st>>>(partial, parts, max_norm, extra_scale, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" long long fb_grad_norm_noalloc_max(void) { return FB_GRAD_NORM_NOALLOC_MAX_ELEMS; }
