@@ -278,6 +278,52 @@ Tensor grad_norm(const Tensor& g, double max_norm, double extra_scale) {
   return out;
 }
 
+// ------------------------------------------------------------------------------------ batch norm
+std::vector<Tensor> bn_fwd(const Tensor& x, const OptTensor& residual, const OptTensor& gamma, const OptTensor& beta,
+                           Tensor& running_mean, Tensor& running_var, double eps, double momentum, bool relu, bool training) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && x.dim() >= 2);
+  const int64_t N = x.size(0), C = x.size(1), HW = x.numel() / (N * C);
+  want_f32(running_mean, "running_mean");
+  want_f32(running_var, "running_var");
+  if (residual.has_value()) TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == x.scalar_type() && residual->numel() == x.numel());
+  auto fopts = torch::dtype(torch::kFloat).device(x.device());
+  Tensor y = torch::empty_like(x), mean = torch::empty({C}, fopts), rstd = torch::empty({C}, fopts);
+  Tensor scratch = torch::empty({fb_bn_scratch_floats((int)C)}, fopts);
+  check(fb_bn_fwd(x.data_ptr(), ptr<const void>(residual), ptr<const float>(gamma), ptr<const float>(beta), running_mean.data_ptr<float>(),
+                  running_var.data_ptr<float>(), y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), scratch.data_ptr<float>(),
+                  (int)N, (int)C, (int)HW, (float)eps, (float)momentum, relu, training, is_bf16(x), stream_of(x)),
+        "fb_bn_fwd");
+  return {y, mean, rstd};
+}
+std::vector<Tensor> bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, const OptTensor& gamma, const Tensor& mean,
+                           const Tensor& rstd, bool relu, bool want_dres, const OptTensor& dgamma_acc, const OptTensor& dbeta_acc) {
+  want_float_kind(dy, "dy");
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && y.is_contiguous());
+  const int64_t N = x.size(0), C = x.size(1), HW = x.numel() / (N * C);
+  auto fopts = torch::dtype(torch::kFloat).device(x.device());
+  Tensor dx = torch::empty_like(x);
+  Tensor dres = want_dres ? torch::empty_like(x) : Tensor();
+  Tensor dg, db;
+  bool acc = false;
+  if (dgamma_acc.has_value()) {
+    dg = *dgamma_acc;
+    db = *dbeta_acc;
+    acc = true;
+  } else {
+    dg = torch::empty({C}, fopts);
+    db = torch::empty({C}, fopts);
+  }
+  Tensor scratch = torch::empty({fb_bn_scratch_floats((int)C)}, fopts);
+  check(fb_bn_bwd(dy.data_ptr(), x.data_ptr(), y.data_ptr(), ptr<const float>(gamma), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                  dx.data_ptr(), want_dres ? dres.data_ptr() : nullptr, dg.data_ptr<float>(), db.data_ptr<float>(), acc,
+                  scratch.data_ptr<float>(), (int)N, (int)C, (int)HW, relu, is_bf16(dy), stream_of(dy)),
+        "fb_bn_bwd");
+  return {dx, dres, dg, db};
+}
+
 // ------------------------------------------------------------------------------------ attention
 // q, k, v: bf16 views [B, S, H, 64] sharing one stride set (e.g. slices of a fused QKV buffer).
 void check_bshd(const Tensor& t, const char* name) {
@@ -361,6 +407,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
         py::arg("grad_scale") = py::none());
   m.def("grad_norm", &grad_norm);
+  m.def("bn_fwd", &bn_fwd);
+  m.def("bn_bwd", &bn_bwd);
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("mask"), py::arg("scale"), py::arg("causal"),
         py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());
   m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("d_o"), py::arg("lse"), py::arg("mask"),

@@ -99,12 +99,13 @@ int fb_softmax_ce(const void* logits, long long ld, const long long* targets, in
 int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream);
 
 /* ---- batch norm (NCHW, training), fused ReLU / residual add --------------------------------- */
+int fb_bn_scratch_floats(int C);
 int fb_bn_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
-              float* running_var, void* y, float* save_mean, float* save_rstd, int N, int C, int HW, float eps,
-              float momentum, int relu, int training, int is_bf16, void* stream);
+              float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, int N, int C, int HW,
+              float eps, float momentum, int relu, int training, int is_bf16, void* stream);
 int fb_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
-              const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int N, int C, int HW,
-              int relu, int is_bf16, void* stream);
+              const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int accumulate,
+              float* scratch, int N, int C, int HW, int relu, int is_bf16, void* stream);
 
 /* ---- optimizers / gradient norm -------------------------------------------------------------- */
 int fb_adam_step(float* p, const void* g, float* m, float* v, void* p16, long long n, const float* hyper, float b1,

@@ -291,3 +291,37 @@ def test_attention_dropout_statistics(C):
     m = o.float().mean().item()
     assert abs(m - 1.0) < 0.02
     assert o.float().std().item() > 0.01
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("relu,use_res", [(False, False), (True, False), (True, True)])
+def test_batchnorm_fused(C, dtype, relu, use_res):
+    torch.manual_seed(8)
+    N, Ch, H = 16, 32, 8
+    x = torch.randn(N, Ch, H, H, device="cuda").to(dtype)
+    res = torch.randn(N, Ch, H, H, device="cuda").to(dtype) if use_res else None
+    g = torch.rand(Ch, device="cuda") + 0.5
+    b = torch.randn(Ch, device="cuda")
+    rm, rv = torch.zeros(Ch, device="cuda"), torch.ones(Ch, device="cuda")
+    rm_ref, rv_ref = rm.clone(), rv.clone()
+    y, mean, rstd = C.bn_fwd(x, res, g, b, rm, rv, 1e-5, 0.1, relu, True)
+    xr = x.float().clone().requires_grad_(True)
+    gr, br = g.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    rr = res.float().clone().requires_grad_(True) if use_res else None
+    ref = torch.nn.functional.batch_norm(xr, rm_ref, rv_ref, gr, br, True, 0.1, 1e-5)
+    if use_res:
+        ref = ref + rr
+    if relu:
+        ref = torch.relu(ref)
+    tol = 0.05 if dtype == torch.bfloat16 else 1e-4
+    assert (y.float() - ref).abs().max().item() < tol
+    assert (rm - rm_ref).abs().max().item() < 1e-4 and (rv - rv_ref).abs().max().item() < 1e-3
+    dy = torch.randn_like(ref).to(dtype)
+    dx, dres, dg, db = C.bn_bwd(dy, x, y, g, mean, rstd, relu, use_res, None, None)
+    # reference backward with the kernel's own ReLU mask (ties at 0 in bf16 would otherwise differ)
+    (ref * (y.float() > 0 if relu else 1)).backward(dy.float()) if False else ref.backward(dy.float())
+    btol = 0.08 if dtype == torch.bfloat16 else 2e-3
+    assert (dx.float() - xr.grad).abs().max().item() < btol
+    assert (dg - gr.grad).abs().max().item() < btol * 10 and (db - br.grad).abs().max().item() < btol * 10
+    if use_res:
+        assert (dres.float() - rr.grad).abs().max().item() < btol
