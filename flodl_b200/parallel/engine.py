@@ -34,7 +34,10 @@ SEED_STRIDE = 1_000_003
 class TrainEngine:
     def __init__(self, model: Module, optimizer_factory: Callable[[List[Parameter]], object], *, max_grad_norm: Optional[float] = None,
                  bucket_mb: float = 25.0, overlap: bool = True, comm_backend: str = "symm", comm_blocks: int = 24,
-                 comm_timeout_s: float = 10.0, sync_params: bool = True):
+                 comm_timeout_s: float = 10.0, sync_params: bool = True, grad_sync: bool = True, param_staging: bool = False):
+        """`grad_sync=False`: replicas do not exchange gradients (Local SGD); with
+        `param_staging=True` the parameters still live in peer-mapped memory, next to a staging
+        buffer of the same size, so `average_params()` can run the fused averaging kernel."""
         self.model = model
         params = model.parameters()
         tensors = [p.t for p in params]
@@ -45,18 +48,24 @@ class TrainEngine:
         groups = [[p.t for p in g] for m in walk_modules(model) for g in m.fuse_groups()]
         self.symm_grads = self.symm_params = None
         grad_alloc = param_alloc = None
-        if self.world > 1 and self.device.type == "cuda" and comm_backend == "symm":
+        self.symm_stage = None
+        self.grad_sync = bool(grad_sync)
+        use_symm = self.world > 1 and self.device.type == "cuda" and comm_backend == "symm"
+        if use_symm and self.grad_sync:
             def grad_alloc(n):
                 self.symm_grads = _comm.SymmetricBuffer(n * 4, self.device.index, comm_timeout_s)
                 return self.symm_grads.view(torch.float32, 0, n)
-
+        if use_symm and (self.grad_sync or param_staging):
             def param_alloc(n):
                 self.symm_params = _comm.SymmetricBuffer(n * 4, self.device.index, comm_timeout_s)
                 return self.symm_params.view(torch.float32, 0, n)
         self.flat = FlatParams(tensors, shadow=self.device.type == "cuda", grad_alloc=grad_alloc, param_alloc=param_alloc, groups=groups)
-        if self.world > 1 and comm_backend != "symm":
+        if self.world > 1 and (comm_backend != "symm" or self.symm_grads is None):
             comm_backend = "nccl"
-        self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend)
+        if use_symm and param_staging:
+            self.symm_stage = _comm.SymmetricBuffer(self.flat.total * 4, self.device.index, comm_timeout_s)
+        self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend,
+                             world=None if self.grad_sync else 1)
         self.optimizer = optimizer_factory(params)
         self.max_grad_norm = max_grad_norm
         self.scheduler = None
@@ -85,6 +94,38 @@ class TrainEngine:
             torch.cuda.synchronize()
         if self.symm_params is not None:
             self.symm_params.check()
+
+    def average_params(self, weights: Optional[Sequence[float]] = None, alpha: float = 1.0, blocks: int = 32) -> torch.Tensor:
+        """Periodic parameter averaging for Local SGD: p <- p + alpha * (sum_r w_r p_r - p) on every
+        rank. Returns a device tensor `[sum (p_new - p_old)^2, sum p_new^2]` (this rank's distance
+        from the consensus), without a host sync.
+
+        With peer-mapped parameters this is ONE kernel: each rank reduces its slice of all peers'
+        parameters over NVLink, scatters the result into every peer's staging buffer, then blends it
+        into its own fp32 weights, refreshes the bf16 shadow and accumulates the two norms in the
+        same pass. The reference copies every parameter to scratch, calls `ncclAllReduce(Avg)` over
+        all of them and derives the norms with three `foreach` passes
+        (flodl/src/distributed/ddp_run/worker.rs:515-584)."""
+        if self.world <= 1:
+            return torch.zeros(2, device=self.device)
+        n = self.flat.total
+        if self.symm_stage is not None and self.symm_params is not None:
+            return self.symm_params.comm.param_average(self.symm_stage.comm, n, None if weights is None else [float(w) for w in weights],
+                                                       float(alpha), self.flat.shadow, blocks)
+        p = self.flat.params
+        with torch.no_grad():
+            pre = p.clone()
+            if weights is not None:
+                p.mul_(float(weights[self.rank]))
+                torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
+            else:
+                torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
+                p.div_(self.world)
+            if alpha != 1.0:
+                p.copy_(torch.lerp(pre, p, float(alpha)))
+            out = torch.stack([(p - pre).pow(2).sum(), p.pow(2).sum()])
+            self.flat.refresh_shadow()
+        return out
 
     def sync_buffers(self, root: int = 0) -> None:
         """Broadcast module buffers (BatchNorm running statistics) from `root`, packed into one message."""

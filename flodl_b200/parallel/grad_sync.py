@@ -25,9 +25,9 @@ from .flat import FlatParams
 
 class GradSync:
     def __init__(self, flat: FlatParams, symm: Optional[_comm.SymmetricBuffer], bucket_bytes: int = 25 * 1024 * 1024,
-                 overlap: bool = True, blocks: int = 24, backend: str = "symm"):
+                 overlap: bool = True, blocks: int = 24, backend: str = "symm", world: Optional[int] = None):
         self.flat, self.symm, self.blocks = flat, symm, blocks
-        self.world = _comm.world_size()
+        self.world = _comm.world_size() if world is None else int(world)   # world=1: no gradient exchange (Local SGD)
         self.backend = backend if self.world > 1 else "none"
         self.overlap = overlap and self.world > 1
         self.buckets = flat.buckets(bucket_bytes)
