@@ -225,6 +225,8 @@ class DistributedState:
             s = sum(raw)
             self._ratios = [x / s for x in raw]
         self.el_che = e
+        # several backward passes per step: a bucket is complete only after the last one
+        self.sync.overlap = False
 
     # ---- queries ------------------------------------------------------------------------------
     def intercepts_forward(self) -> bool:
@@ -271,6 +273,9 @@ class DistributedState:
         start = sum(sizes[:self.rank])
         n = sizes[self.rank]
         self._last_shards = sizes
+        # unequal shards: every bucket (also those reduced while backward still runs) must be
+        # combined with the shard weights, so they are fixed before the step starts
+        self.sync.set_weights(None if self.is_balanced() else [s / batch for s in sizes])
         shard = [Variable.wrap(t.narrow(0, start, n)) if t.dim() > 0 and t.shape[0] == batch else Variable.wrap(t) for t in ts]
         self.begin_batch(n)
         return graph.forward_impl(shard)
@@ -341,8 +346,8 @@ class DistributedState:
                 self.flat.grads.div_(float(local))   # mean over this rank's batches
             self.weighted_all_reduce_gradients(counts)
             self._el_counts = [int(c) for c in counts]
-        elif self.scatter and self._last_shards and not self.is_balanced():
-            self.weighted_all_reduce_gradients(self._last_shards)
+        elif self.scatter and self._last_shards and self.sync.weights is not None:
+            self._finish_sync()
         else:
             self.all_reduce_gradients()
         self.sync_buffers()

@@ -200,6 +200,7 @@ class Coordinator:
         self.avg_state: tuple = ("idle",)
         self.stop = threading.Event()
         self.error: Optional[BaseException] = None
+        self.failed_ranks: List[int] = []
 
     # ---- small accessors ------------------------------------------------------------------------
     def is_calibrated(self) -> bool: return self.calibrated
@@ -399,6 +400,12 @@ class Coordinator:
             self.acks_pending[r] += 1
         elif isinstance(msg, TimingExiting):
             self.active_count = max(0, self.active_count - 1)
+            if msg.error is not None:
+                # a replica died: no collective may be started with it, and in a multi-process job
+                # nobody else will tell the survivors, so wind the whole run down
+                log.msg(f"  ddp: rank {msg.rank} failed ({msg.error}); stopping the run")
+                self.failed_ranks.append(msg.rank)
+                self.stop.set()
 
     def drain_timing(self) -> int:
         n = 0
@@ -465,8 +472,8 @@ class Coordinator:
 
     # ---- when to average ------------------------------------------------------------------------
     def should_average(self) -> bool:
-        if self.fixed_cadence is not None:
-            return False                       # workers keep their own cadence; see poll_fixed_cadence
+        if self.fixed_cadence is not None or self.world_size < 2:
+            return False                       # workers keep their own cadence (poll_fixed_cadence) / nothing to average
         if self.avg_state[0] != "idle":
             return False
         if self.backend == AverageBackend.Nccl and not all(self.nccl_ack):
@@ -708,7 +715,7 @@ class Coordinator:
     def collect_final_state(self, timeout_s: float = 10.0) -> Optional[TrainedState]:
         snaps = []
         for rank, box in enumerate(self.fin):
-            s = box.recv(timeout=timeout_s)
+            s = box.recv(timeout=0.05 if rank in self.failed_ranks else timeout_s)
             if s is None:
                 log.verbose(f"  ddp: timeout waiting for final snapshot from rank {rank}")
             else:

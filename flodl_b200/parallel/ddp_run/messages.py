@@ -90,6 +90,7 @@ class TimingSyncAck:
 @dataclass
 class TimingExiting:
     rank: int
+    error: Optional[str] = None      # set when the worker leaves because of an exception
 
 
 class TimingMsg:

@@ -59,6 +59,10 @@ class DdpHandle:
     def architecture_svg(self) -> Optional[str]: return self._svg
     def training_meta(self) -> Optional[dict]: return self._meta
 
+    def errors(self) -> List[BaseException]:
+        """Exceptions raised by this process's workers or coordinator so far."""
+        return [v for k, v in self._results.items() if k.startswith("worker_err") or k == "coord_err"]
+
     def setup_monitor(self, monitor) -> None:
         """Hand the model's picture, identity and the run's metadata to a `Monitor`."""
         if self._svg is not None and hasattr(monitor, "set_architecture_svg"):
@@ -187,7 +191,7 @@ class DdpBuilder:
 
     # ---- launch ---------------------------------------------------------------------------------
     def _el_che(self, world: int) -> ElChe:
-        e = ElChe(world, self._cfg.anchor if self._cfg.anchor is not None else DEFAULT_ANCHOR)
+        e = ElChe(max(2, world), self._cfg.anchor if self._cfg.anchor is not None else DEFAULT_ANCHOR)   # a lone device never consults it
         if self._cfg.overhead_target is not None:
             e.with_overhead_target(self._cfg.overhead_target)
         if self._cfg.max_anchor is not None:
@@ -283,7 +287,7 @@ class DdpBuilder:
                 results[f"worker_err{wcfg.rank}"] = e
                 try:
                     from .messages import TimingExiting
-                    transport.box(f"tim{wcfg.rank}").send(TimingExiting(wcfg.rank))
+                    transport.box(f"tim{wcfg.rank}").send(TimingExiting(wcfg.rank, repr(e)))
                 except Exception:
                     pass
                 stop.set()

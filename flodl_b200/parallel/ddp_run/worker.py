@@ -88,6 +88,7 @@ class GpuWorker:
         self._pending_div = False
         self._loss_sum = 0.0
         self._loss_n = 0
+        self._shutdown_seen = False
 
     # ---- accessors (worker.rs:371-436) ----------------------------------------------------------
     def rank(self) -> int: return self.rank_
@@ -251,6 +252,7 @@ class GpuWorker:
                 except Exception as e:
                     log.msg(f"  ddp: checkpoint failed (v{msg.payload}): {e}")
         elif k == "Shutdown":
+            self._shutdown_seen = True
             return True
         return False
 
@@ -267,6 +269,7 @@ class GpuWorker:
             if msg.kind == "StartEpoch":
                 return msg.payload
             if msg.kind == "Shutdown":
+                self._shutdown_seen = True
                 return None
             if self.dispatch_control(msg):
                 return None
@@ -321,6 +324,8 @@ class GpuWorker:
                 s.abort()
 
     def drain_until_shutdown(self, timeout_s: float = 30.0) -> None:
+        if self._shutdown_seen:
+            return
         deadline = time.monotonic() + timeout_s
         while time.monotonic() < deadline:
             msg = self.ctl.recv(timeout=0.1)

@@ -87,6 +87,10 @@ class GradSync:
     def _launch(self, bi: int) -> None:
         b = self.buckets[bi]
         self.launched[bi] = True
+        if self.stream is None:               # CPU replicas (gloo): reduce in line
+            self._reduce_range(b["start"], b["end"])
+            self.launch_count += 1
+            return
         cur = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(cur)
@@ -119,8 +123,9 @@ class GradSync:
         for bi in range(len(self.buckets)):
             if not self.launched[bi]:
                 self._launch(bi)
-        self.done.record(self.stream)
-        torch.cuda.current_stream().wait_event(self.done)
+        if self.stream is not None:
+            self.done.record(self.stream)
+            torch.cuda.current_stream().wait_event(self.done)
 
     # ---- one-off collectives --------------------------------------------------------------------
     def set_weights(self, weights: Optional[Sequence[float]]) -> None:
