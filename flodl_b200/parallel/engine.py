@@ -66,6 +66,25 @@ class TrainEngine:
             self.symm_stage = _comm.SymmetricBuffer(self.flat.total * 4, self.device.index, comm_timeout_s)
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend,
                              world=None if self.grad_sync else 1)
+        # Buffers (BatchNorm running statistics) follow rank 0 after every step, as in the reference
+        # (one ncclBroadcast per buffer per step, flodl/src/distributed/ddp.rs:150-157). Here they are
+        # re-homed into one peer-mapped block and refreshed by ONE pull-broadcast launch per step.
+        self.symm_bufs = None
+        self._buf_bytes = 0
+        self._float_bufs = [b.get() for b in model.buffers() if b.get().is_floating_point() and b.get().numel() > 0]
+        if use_symm and self.grad_sync and self._float_bufs:
+            n = sum((t.numel() + 3) // 4 * 4 for t in self._float_bufs)
+            self.symm_bufs = _comm.SymmetricBuffer(n * 4, self.device.index, comm_timeout_s)
+            block = self.symm_bufs.view(torch.float32, 0, n)
+            block.zero_()
+            off = 0
+            with torch.no_grad():
+                for t in self._float_bufs:
+                    v = block[off:off + t.numel()].view(t.shape)
+                    v.copy_(t.float())
+                    t.data = v
+                    off += (t.numel() + 3) // 4 * 4
+            self._buf_bytes = off * 4
         self.optimizer = optimizer_factory(params)
         self.max_grad_norm = max_grad_norm
         self.scheduler = None
@@ -160,6 +179,10 @@ class TrainEngine:
         lt = loss.t if hasattr(loss, "t") else loss
         lt.backward()
         self.sync.finish()
+        if self.symm_bufs is not None:
+            self.symm_bufs.broadcast(0, self._buf_bytes, 0, 1)
+        elif self.world > 1 and self.grad_sync and self._float_bufs:
+            self.sync_buffers(0)
         if self.max_grad_norm is not None and self.device.type == "cuda" and _ops.native_enabled():
             self.norm_out = _ext.require().grad_norm(self.flat.grads, float(self.max_grad_norm), 1.0)
             self.optimizer.set_grad_scale(self.norm_out[1:2])

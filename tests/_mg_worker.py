@@ -135,6 +135,100 @@ def main():
                 ps = gather_all(eng.flat.params.clone())
                 assert all(torch.equal(ps[0], a) for a in ps), f"parameters diverged at step {step}"
             assert len(eng.sync.buckets) > 1 and eng.sync.launch_count >= 4 * len(eng.sync.buckets)
+    elif mode == "resnet_buffers":
+        # BatchNorm statistics differ per rank (different data); after every step all ranks must
+        # hold rank 0's running statistics, through the one-launch pull broadcast
+        from flodl_b200 import nn
+        from flodl_b200.autograd import Variable
+        from flodl_b200.models.resnet import resnet20
+        from flodl_b200.parallel.engine import TrainEngine
+        torch.manual_seed(1)
+        model = resnet20(10, dev)
+        model.set_training(True)
+        g = torch.Generator().manual_seed(50 + rank)
+        x = torch.randn(16, 3, 32, 32, generator=g).to(dev).bfloat16()
+        y = torch.randint(0, 10, (16,), generator=g).to(dev)
+        with nn.AutocastGuard(torch.bfloat16):
+            eng = TrainEngine(model, lambda ps: nn.SGD(ps, 0.05, 0.9, 1e-4))
+            assert eng.symm_bufs is not None and eng._buf_bytes > 0
+            for step in range(3):
+                eng.step(lambda: nn.cross_entropy_loss(model.forward(Variable.wrap(x)), Variable.wrap(y)))
+                torch.cuda.synchronize()
+                eng.check()
+                pack = torch.cat([b.reshape(-1) for b in eng._float_bufs])
+                allb = gather_all(pack)
+                assert all(torch.equal(allb[0], a) for a in allb), f"buffers differ across ranks at step {step}"
+                assert pack.abs().sum().item() > 0
+    elif mode == "graph_ddp":
+        # the reference's user-facing path: Trainer.setup + model.forward(global batch) + model.step()
+        from flodl_b200 import nn
+        from flodl_b200.graph import FlowBuilder
+        from flodl_b200.parallel.ddp import Trainer
+
+        def build(seed):
+            torch.manual_seed(seed)
+            return (FlowBuilder.from_(nn.Linear.on_device(64, 128, dev)).through(nn.GELU()).through(nn.LayerNorm.on_device(128, dev))
+                    .through(nn.Linear.on_device(128, 64, dev)).build())
+        m = build(100 + rank)
+        Trainer.setup(m, None, lambda ps: nn.Adam(ps, 1e-2))
+        assert m.is_distributed() and m.world_size() == world
+        ref = build(100)
+        ropt = nn.Adam(ref.parameters(), 1e-2)
+        gen = torch.Generator().manual_seed(9)
+        X = torch.randn(5, 8 * world, 64, generator=gen).to(dev)
+        Y = torch.randn(5, 8 * world, 64, generator=gen).to(dev)
+        for step in range(5):
+            out = m.forward(X[step])
+            nn.mse_loss(out, Y[step][rank * 8:(rank + 1) * 8]).backward()
+            m.step()
+            nn.mse_loss(ref.forward(X[step]), Y[step]).backward()
+            ropt.step()
+            ropt.zero_grad()
+        torch.cuda.synchronize()
+        for (n1, p1), (_, p2) in zip(m.named_parameters(), ref.named_parameters()):
+            err = (p1.t.detach() - p2.t.detach()).abs().max().item()
+            assert err < 5e-3, (n1, err)       # bf16-free fp32 path: only reduction order differs
+        ps = gather_all(m._ddp.flat.params.clone())
+        assert all(torch.equal(ps[0], a) for a in ps)
+    elif mode in ("async_fixed", "async_cadence", "async_cpu"):
+        from flodl_b200 import nn
+        from flodl_b200.data import TensorDataSet
+        from flodl_b200.models.gpt import DecoderLM, DecoderLMConfig
+        from flodl_b200.parallel.ddp import Trainer
+        from flodl_b200.parallel.ddp_run import ApplyPolicy, AverageBackend
+        cfg = DecoderLMConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, max_seq=128, dropout=0.0)
+        gen = torch.Generator().manual_seed(3)
+        base = torch.randint(0, 512, (64,), generator=gen)
+        ids = base.repeat(40 * 129 // 64 + 1)[:40 * 129].view(40, 129)      # a periodic stream: learnable quickly
+        ds = TensorDataSet(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+
+        def factory(d):
+            torch.manual_seed(11)
+            return DecoderLM(cfg, d)
+
+        def train_fn(model, batch):
+            return model.loss(batch[0], batch[1])
+        b = (Trainer.builder(factory, lambda ps: nn.AdamW(ps, 2e-3, 0.0), train_fn).dataset(ds).batch_size(4).num_epochs(4)
+             .lr_scale_ratio(0.0))
+        if mode == "async_fixed":
+            b = b.policy(ApplyPolicy.Cadence).backend(AverageBackend.Nccl).anchor(2).max_anchor(2)
+        elif mode == "async_cadence":
+            b = b.policy(ApplyPolicy.Cadence).backend(AverageBackend.Nccl)
+        else:
+            b = b.policy(ApplyPolicy.Async).backend(AverageBackend.Cpu)
+        with nn.AutocastGuard(torch.bfloat16):
+            h = b.run()
+            state = h.join()
+        assert state is not None and len(state.params) > 0 and not h.errors(), h.errors()
+        if rank == 0:
+            ms = h.poll_metrics()
+            assert [m.epoch for m in ms] == [0, 1, 2, 3], [m.epoch for m in ms]
+            assert ms[-1].avg_loss < 0.7 * ms[0].avg_loss, [m.avg_loss for m in ms]
+        w = h._gpu_workers[0]
+        if mode != "async_cpu":
+            assert w.current_version() > 0, "no averaging round ran"
+            assert w.engine.symm_stage is not None, "the fused averaging kernel was not in use"
+            w.engine.check()
     dist.barrier()
     if rank == 0:
         print("MG_OK", mode, flush=True)

@@ -27,3 +27,16 @@ def test_symmetric_collectives_2gpu():
 
 def test_train_engine_ddp_2gpu():
     _run("engine", 2, 29632)
+
+
+def test_engine_broadcasts_batchnorm_buffers_2gpu():
+    _run("resnet_buffers", 2, 29633)
+
+
+def test_graph_ddp_trainer_setup_2gpu():
+    _run("graph_ddp", 2, 29634)
+
+
+@pytest.mark.parametrize("mode,port", [("async_fixed", 29635), ("async_cadence", 29636), ("async_cpu", 29637)])
+def test_async_ddp_2gpu(mode, port):
+    _run(mode, 2, port)
