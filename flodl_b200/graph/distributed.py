@@ -2,7 +2,50 @@
 into `Graph`; the machinery lives in `flodl_b200.parallel.ddp`."""
 from __future__ import annotations
 
-from typing import Callable, List, Optional
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+
+@dataclass
+class LossContext:
+    """What a loss function bound with `set_loss_fn` receives for every batch
+    (flodl/src/graph/mod.rs:60-69): the live forward output, the batch with all named fields,
+    the tagged outputs and the loop traces of this forward pass."""
+    output: object
+    batch: object
+    tags: Dict[str, object] = field(default_factory=dict)
+    traces: Dict[str, list] = field(default_factory=dict)
+
+
+class GraphEpochIterator:
+    """Iterator over the bound loader's batches for one epoch. With a loss function bound
+    (`set_loss_fn`) each item has already been run: forward on the batch's input field, loss,
+    backward; the item is then `(batch, loss)`. Without one the item is the `Batch`."""
+
+    def __init__(self, graph, epoch: int):
+        self.graph, self.epoch_index = graph, epoch
+        loader, self.input_name = graph._data_binding
+        self._it = iter(loader.epoch(epoch))
+
+    def activate(self) -> "GraphEpochIterator":
+        return self
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        batch = next(self._it)
+        g = self.graph
+        if g._loss_fn is None:
+            return batch
+        x = batch[self.input_name] if hasattr(batch, "has") and batch.has(self.input_name) else batch[0]
+        if g._ddp is not None and not g._ddp.scatter:
+            g._ddp.begin_batch(int(x.shape[0]))
+        out = g.forward(x)
+        tags = {n: g.tagged(n) for n in g.tag_names_list()} if hasattr(g, "tag_names_list") else {}
+        loss = g._loss_fn(LossContext(out, batch, tags, {}))
+        loss.backward()
+        return batch, loss
 
 
 class DistributedMixin:
@@ -90,6 +133,15 @@ class DistributedMixin:
 
     # ---- data binding ---------------------------------------------------------------------------
     def set_data_loader(self, loader, input_name: str = "input") -> None:
+        """Bind a `DataLoader`; in a multi-rank job the loader is restricted to this rank's shard
+        and the forward pass no longer scatters (the data arrives pre-sharded,
+        flodl/src/graph/distributed.rs:843-939)."""
+        from ..parallel import comm
+        if comm.world_size() > 1 and hasattr(loader, "distributed"):
+            loader.distributed(comm.rank(), comm.world_size())
+            if self._ddp is not None:
+                self._ddp.scatter = False
+                loader.set_shard_ratios(None if self._ddp.is_balanced() else self._ddp.chunk_ratios())
         self._data_binding = (loader, input_name)
 
     def set_loss_fn(self, f: Callable) -> None:
@@ -104,12 +156,12 @@ class DistributedMixin:
     def data_batch_size(self) -> int:
         return self._data_binding[0].batch_size if self._data_binding else 0
 
-    def epoch(self, epoch: int):
-        """Iterator over the bound loader's batches for `epoch` (each item: list of tensors)."""
+    def epoch(self, epoch: int) -> "GraphEpochIterator":
+        """Batches of `epoch` from the bound loader (see `GraphEpochIterator`)."""
         if self._data_binding is None:
             from ..tensor import TensorError
             raise TensorError("epoch(): call set_data_loader first")
-        return self._data_binding[0].epoch(epoch)
+        return GraphEpochIterator(self, epoch)
 
     def forward_batch(self, batch):
         from ..autograd import Variable

@@ -217,3 +217,109 @@ def broadcast_nccl(tensors: Sequence[torch.Tensor], root: int = 0) -> None:
 class _null:
     def __enter__(self): return self
     def __exit__(self, *a): return False
+
+
+# ---- NCCL-shaped wrappers (flodl/src/distributed/nccl.rs:56-571) ---------------------------------
+class NcclUniqueId:
+    """The reference passes a 128-byte `ncclUniqueId` between threads to join one communicator.
+    Here ranks rendezvous through `torch.distributed`; the id is an opaque 128-byte token kept for
+    API parity (`NcclRankComm.init_rank` accepts and ignores it)."""
+    BYTES = 128
+
+    def __init__(self, raw: Optional[bytes] = None):
+        self.raw = raw if raw is not None else os.urandom(self.BYTES)
+        if len(self.raw) != self.BYTES:
+            raise TensorError(f"NcclUniqueId must be {self.BYTES} bytes")
+
+    @classmethod
+    def new(cls) -> "NcclUniqueId":
+        return cls()
+
+    def as_bytes(self) -> bytes:
+        return self.raw
+
+
+class NcclAbortHandle:
+    """Unblocks a rank stuck in a collective: sets the host-mapped abort flag of every symmetric
+    buffer registered with it (the device-side waits of this library poll that flag) and asks
+    the NCCL process group to abort where the installed torch supports it."""
+
+    def __init__(self, buffers: Optional[List["SymmetricBuffer"]] = None):
+        self.buffers = list(buffers or [])
+
+    def register(self, buf: "SymmetricBuffer") -> None:
+        self.buffers.append(buf)
+
+    def abort(self) -> None:
+        for b in self.buffers:
+            b.abort()
+        if dist.is_initialized():
+            pg = dist.distributed_c10d._get_default_group()
+            for name in ("abort", "_abort"):
+                f = getattr(pg, name, None)
+                if callable(f):
+                    try:
+                        f()
+                    except Exception:
+                        pass
+                    break
+
+
+class NcclRankComm:
+    """This rank's end of the job-wide communicator: multi-tensor all-reduce in one group
+    (flodl-sys/ops_cuda.cpp:496-537)."""
+
+    def __init__(self):
+        self._abort = NcclAbortHandle()
+
+    @classmethod
+    def init_rank(cls, rank: int, world_size: int, uid: Optional[NcclUniqueId] = None) -> "NcclRankComm":
+        init_process_group()
+        if world_size != globals()["world_size"]() or rank != globals()["rank"]():
+            raise TensorError(f"init_rank({rank}, {world_size}) does not match the process group ({globals()['rank']()}, {globals()['world_size']()})")
+        return cls()
+
+    def rank(self) -> int: return rank()
+    def world_size(self) -> int: return world_size()
+    def abort_handle(self) -> NcclAbortHandle: return self._abort
+
+    def all_reduce(self, tensors: Sequence[torch.Tensor], op: ReduceOp = ReduceOp.Sum) -> None:
+        all_reduce_nccl(list(tensors), op)
+
+    def all_reduce_on_stream(self, tensors: Sequence[torch.Tensor], op: ReduceOp, stream: CudaStream) -> None:
+        with stream.guard():
+            all_reduce_nccl(list(tensors), op)
+
+
+class NcclComms:
+    """Group view used by the synchronous path (`NcclComms::new(devices)` in the reference holds one
+    communicator per device of the process; here each process holds its own rank's)."""
+
+    def __init__(self, devices: Optional[Sequence] = None):
+        init_process_group()
+        self._devices = list(devices) if devices is not None else [f"cuda:{i}" for i in range(world_size())]
+
+    @classmethod
+    def new(cls, devices: Optional[Sequence] = None) -> "NcclComms":
+        return cls(devices)
+
+    def size(self) -> int: return world_size()
+    def devices(self) -> List: return list(self._devices)
+
+    def all_reduce(self, tensors: Sequence[torch.Tensor], op: ReduceOp = ReduceOp.Sum) -> None:
+        all_reduce_nccl(list(tensors), op)
+
+    def all_reduce_on_streams(self, tensors: Sequence[torch.Tensor], op: ReduceOp, streams: Sequence[CudaStream]) -> None:
+        with streams[0].guard():
+            all_reduce_nccl(list(tensors), op)
+
+    def broadcast(self, tensors: Sequence[torch.Tensor], root: int = 0) -> None:
+        broadcast_nccl(list(tensors), root)
+
+    def broadcast_on_streams(self, tensors: Sequence[torch.Tensor], root: int, streams: Sequence[CudaStream]) -> None:
+        with streams[0].guard():
+            broadcast_nccl(list(tensors), root)
+
+    def split(self) -> List[NcclRankComm]:
+        """One rank communicator per local device: exactly one in a process-per-GPU job."""
+        return [NcclRankComm()]

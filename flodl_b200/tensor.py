@@ -308,3 +308,37 @@ def to_f32_vec(t: Tensor) -> List[float]:
 
 def all_finite(t: Tensor) -> bool:
     return bool(torch.isfinite(t).all().item())
+
+
+# ---- remaining device utilities of the root namespace (flodl/src/tensor/cuda.rs) -------------------
+def current_cuda_device() -> int:
+    return torch.cuda.current_device() if torch.cuda.is_available() else 0
+
+
+def cuda_manual_seed_all(seed: int) -> None:
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(int(seed))
+
+
+def set_cudnn_benchmark(enabled: bool) -> None:
+    torch.backends.cudnn.benchmark = bool(enabled)
+
+
+class DeviceInfo:
+    """Index, name, memory and compute capability of one CUDA device."""
+
+    def __init__(self, index: int):
+        p = torch.cuda.get_device_properties(index)
+        self.index, self.name, self.total_memory = index, p.name, int(p.total_memory)
+        self.sm_major, self.sm_minor, self.multi_processor_count = p.major, p.minor, p.multi_processor_count
+
+    def __repr__(self) -> str:
+        return f"DeviceInfo({self.index}, {self.name!r}, {self.total_memory >> 30} GiB, sm_{self.sm_major}{self.sm_minor}, {self.multi_processor_count} SMs)"
+
+
+def cuda_devices() -> List["DeviceInfo"]:
+    return [DeviceInfo(i) for i in range(cuda_device_count())]
+
+
+def cuda_peak_reserved_bytes(index: int = 0) -> int:
+    return int(torch.cuda.max_memory_reserved(index)) if cuda_available() else 0
