@@ -84,3 +84,8 @@ def emit_architectures(a, default: str) -> List[str]:
 
 def emit_id2label(labels) -> Dict[str, str]:
     return {str(i): l for i, l in enumerate(labels)}
+
+
+def optional_bool(v, key: str, default: bool) -> bool:
+    x = v.get(key)
+    return bool(x) if isinstance(x, bool) else default

@@ -1,0 +1,235 @@
+"""HF encoder families on CPU: numerical parity with the `transformers` implementations (tiny random
+configs, weights moved through safetensors), key maps, config round trips, safetensors validation."""
+import json
+
+import pytest
+import torch
+
+from flodl_b200.hf import safetensors_io as st
+from flodl_b200.hf.models import albert, bert, deberta_v2, distilbert, roberta
+from flodl_b200.hf.path import HfPath, hf_key_from_flodl_key
+
+transformers = pytest.importorskip("transformers")
+
+IDS = torch.tensor([[2, 5, 6, 7, 3, 0, 0, 0], [2, 9, 10, 11, 12, 13, 14, 3]])
+PAD = 0
+
+
+def hf_state_bytes(model) -> bytes:
+    # like `save_pretrained`: tensors that share storage (tied weights) are written once
+    sd, seen = {}, set()
+    for k, v in sorted(model.state_dict().items()):
+        if not v.is_floating_point() or v.data_ptr() in seen:
+            continue
+        seen.add(v.data_ptr())
+        sd[k] = v.detach().clone().contiguous()
+    return st.write_safetensors(sd)
+
+
+def load_allowing_unused(graph, blob, rename=st.bert_legacy_key_rename):
+    return st.load_safetensors_into_graph_with_rename_allow_unused(graph, blob, rename)
+
+
+def close(a, b, tol=2e-5):
+    err = (a - b).abs().max().item()
+    assert err < tol, err
+
+
+def test_bert_parity_backbone_and_mlm():
+    hc = transformers.BertConfig(vocab_size=50, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                                 max_position_embeddings=16, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    torch.manual_seed(0)
+    hf = transformers.BertForMaskedLM(hc).eval()
+    cfg = bert.BertConfig.from_json_str(hc.to_json_string())
+    head = bert.BertForMaskedLM.on_device(cfg)
+    head.graph().set_training(False)
+    unused = load_allowing_unused(head.graph(), hf_state_bytes(hf))
+    assert all("position_ids" in k or k == "cls.predictions.decoder.weight" for k in unused), unused
+    mask = (IDS != PAD).float()
+    pos = torch.arange(8).expand(2, 8)
+    tt = torch.zeros_like(IDS)
+    mine = head.forward([IDS, pos, tt, bert.build_extended_attention_mask(mask)]).t
+    ref = hf(input_ids=IDS, attention_mask=mask.long(), token_type_ids=tt).logits
+    close(mine[mask.bool()], ref[mask.bool()], 1e-4)
+
+
+def test_roberta_parity_sequence_classification():
+    hc = transformers.RobertaConfig(vocab_size=50, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                                    max_position_embeddings=20, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, num_labels=3,
+                                    pad_token_id=1, type_vocab_size=1)
+    torch.manual_seed(1)
+    hf = transformers.RobertaForSequenceClassification(hc).eval()
+    cfg = roberta.RobertaConfig.from_json_str(hc.to_json_string())
+    assert cfg.num_labels == 3 and cfg.pad_token_id == 1
+    head = roberta.RobertaForSequenceClassification.on_device(cfg, 3)
+    head.graph().set_training(False)
+    load_allowing_unused(head.graph(), hf_state_bytes(hf))
+    ids = IDS.clone()
+    ids[ids == 0] = 1
+    mask = (ids != 1).float()
+    mine = head.forward([ids, torch.zeros_like(ids), bert.build_extended_attention_mask(mask)]).t
+    ref = hf(input_ids=ids, attention_mask=mask.long()).logits
+    close(mine, ref, 1e-4)
+
+
+def test_distilbert_parity():
+    hc = transformers.DistilBertConfig(vocab_size=50, dim=32, n_layers=2, n_heads=4, hidden_dim=64, max_position_embeddings=16, dropout=0.0,
+                                       attention_dropout=0.0)
+    torch.manual_seed(2)
+    hf = transformers.DistilBertModel(hc).eval()
+    cfg = distilbert.DistilBertConfig.from_json_str(hc.to_json_string())
+    g = distilbert.DistilBertModel.build(cfg)
+    g.set_training(False)
+    load_allowing_unused(g, hf_state_bytes(hf), lambda k: "distilbert." + k)
+    mask = (IDS != PAD).float()
+    mine = g.forward([IDS, bert.build_extended_attention_mask(mask)]).t
+    ref = hf(input_ids=IDS, attention_mask=mask.long()).last_hidden_state
+    close(mine[mask.bool()], ref[mask.bool()], 1e-4)
+
+
+def test_albert_parity():
+    hc = transformers.AlbertConfig(vocab_size=50, embedding_size=16, hidden_size=32, num_hidden_layers=3, num_attention_heads=4,
+                                   intermediate_size=64, max_position_embeddings=16, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    torch.manual_seed(3)
+    hf = transformers.AlbertModel(hc).eval()
+    cfg = albert.AlbertConfig.from_json_str(hc.to_json_string())
+    g = albert.AlbertModel.build(cfg)
+    g.set_training(False)
+    load_allowing_unused(g, hf_state_bytes(hf), lambda k: "albert." + k)
+    mask = (IDS != PAD).float()
+    pos = torch.arange(8).expand(2, 8)
+    mine = g.forward([IDS, pos, torch.zeros_like(IDS), bert.build_extended_attention_mask(mask)]).t
+    ref = hf(input_ids=IDS, attention_mask=mask.long()).pooler_output
+    close(mine, ref, 1e-4)
+
+
+def test_deberta_v2_parity():
+    hc = transformers.DebertaV2Config(vocab_size=50, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                                      max_position_embeddings=16, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                                      relative_attention=True, position_buckets=4, max_relative_positions=8, share_att_key=True,
+                                      pos_att_type=["p2c", "c2p"], norm_rel_ebd="layer_norm", position_biased_input=False, type_vocab_size=0)
+    torch.manual_seed(4)
+    hf = transformers.DebertaV2Model(hc).eval()
+    cfg = deberta_v2.DebertaV2Config.from_json_str(hc.to_json_string())
+    g = deberta_v2.DebertaV2Model.build(cfg)
+    g.set_training(False)
+    load_allowing_unused(g, hf_state_bytes(hf), lambda k: "deberta." + k)
+    mask = (IDS != PAD).float()
+    mine = g.forward([IDS, mask]).t
+    ref = hf(input_ids=IDS, attention_mask=mask.long()).last_hidden_state
+    close(mine[mask.bool()], ref[mask.bool()], 1e-4)
+
+
+def test_deberta_rejects_unsupported_configs():
+    base = json.loads(deberta_v2.DebertaV2Config().to_json_str())
+    for key, val in (("relative_attention", False), ("share_att_key", False), ("position_biased_input", True), ("pos_att_type", ["c2p"])):
+        bad = dict(base)
+        bad[key] = val
+        with pytest.raises(Exception):
+            deberta_v2.DebertaV2Config.from_json_str(json.dumps(bad))
+
+
+def test_bert_key_map_matches_hf_names():
+    cfg = bert.BertConfig(vocab_size=30, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32, max_position_embeddings=8)
+    g = bert.BertModel.build(cfg)
+    keys = {e.key for e in st.expected_from_graph(g)}
+    assert "bert.embeddings.word_embeddings.weight" in keys and "bert.embeddings.LayerNorm.bias" in keys
+    assert "bert.encoder.layer.0.attention.self.query.weight" in keys and "bert.encoder.layer.0.output.LayerNorm.weight" in keys
+    assert "bert.pooler.dense.bias" in keys and len(keys) == 5 + 16 + 2
+    assert hf_key_from_flodl_key("bert.encoder.layer.0/attention.self.query.weight") == "bert.encoder.layer.0.attention.self.query.weight"
+    assert str(HfPath("bert").sub("encoder").sub("layer").sub(3)) == "bert.encoder.layer.3"
+    with pytest.raises(Exception):
+        HfPath("a.b")
+
+
+def test_config_round_trips_and_presets():
+    for cfg in (bert.BertConfig.bert_base_uncased(), roberta.RobertaConfig.roberta_base(), roberta.XlmRobertaConfig.xlm_roberta_base(),
+                distilbert.DistilBertConfig.distilbert_base_uncased(), albert.AlbertConfig.albert_base_v2(),
+                deberta_v2.DebertaV2Config.deberta_v3_base()):
+        s = cfg.to_json_str()
+        assert type(cfg).from_json_str(s).to_json_str() == s
+        assert json.loads(s)["model_type"] == cfg.MODEL_TYPE
+    c = bert.BertConfig.from_json_str(json.dumps({**json.loads(bert.BertConfig().to_json_str()), "id2label": {"0": "neg", "1": "pos"}}))
+    assert c.num_labels == 2 and c.id2label == ["neg", "pos"]
+    with pytest.raises(Exception):
+        bert.BertConfig.from_json_str("{}")
+    with pytest.raises(Exception):
+        albert.AlbertConfig.from_json_str(json.dumps({**json.loads(albert.AlbertConfig().to_json_str()), "num_hidden_groups": 2}))
+
+
+def test_safetensors_validation_reports_everything_and_commits_nothing():
+    cfg = bert.BertConfig(vocab_size=30, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32, max_position_embeddings=8)
+    g = bert.BertModel.build(cfg)
+    before = [p.t.detach().clone() for p in g.parameters()]
+    tensors = st.read_safetensors(st.save_safetensors_from_graph(g))
+    tensors = {k: torch.zeros_like(v) for k, v in tensors.items()}
+    del tensors["bert.pooler.dense.bias"]
+    tensors["bert.pooler.dense.weight"] = torch.zeros(3, 3)
+    tensors["extra.key"] = torch.zeros(1)
+    with pytest.raises(Exception) as e:
+        st.load_safetensors_into_graph(g, st.write_safetensors(tensors))
+    msg = str(e.value)
+    assert "missing" in msg and "bert.pooler.dense.bias" in msg and "unused" in msg and "extra.key" in msg and "shape mismatch" in msg
+    assert all(torch.equal(a, p.t) for a, p in zip(before, g.parameters()))
+    v = st.validate_keys([st.ExpectedParam("a", [2])], {"a": [2], "b": [1]})
+    assert v.unused == ["b"] and not v.missing
+    v.into_result_allow_unused()
+    with pytest.raises(Exception):
+        v.into_result()
+
+
+def test_safetensors_format_interoperates_with_the_reference_package():
+    sft = pytest.importorskip("safetensors.torch")
+    t = {"w": torch.randn(3, 4), "h": torch.randn(5).half(), "b": torch.randn(2, 2).bfloat16(), "d": torch.randn(2).double()}
+    mine = st.write_safetensors(t)
+    theirs = sft.load(mine)
+    assert all(torch.equal(t[k], theirs[k]) for k in t)
+    back = st.read_safetensors(sft.save(t))
+    assert all(torch.equal(t[k], back[k]) for k in t)
+    with pytest.raises(Exception):
+        st.write_safetensors({"i": torch.arange(3)})
+    with pytest.raises(Exception):
+        st.read_safetensors(sft.save({"i": torch.arange(3)}))
+    with pytest.raises(Exception):
+        st.parse_header(b"\x00\x01")
+
+
+def test_legacy_renames_and_pooler_detection():
+    assert st.bert_legacy_key_rename("bert.embeddings.LayerNorm.gamma") == "bert.embeddings.LayerNorm.weight"
+    assert st.bert_legacy_key_rename("x.LayerNorm.beta") == "x.LayerNorm.bias"
+    assert st.bert_legacy_key_rename("cls.predictions.bias") == "cls.predictions.decoder.bias"
+    assert st.hf_canonical_save_key("lm_head.decoder.bias") == "lm_head.bias"
+    assert st.keys_have_pooler(["bert.pooler.dense.weight"]) and st.keys_have_pooler(["albert/pooler.weight"])
+    assert not st.keys_have_pooler(["bert.encoder.layer.0.output.dense.weight"])
+    blob = st.write_safetensors({"a.LayerNorm.gamma": torch.zeros(1), "a.LayerNorm.weight": torch.zeros(1)})
+
+    class G:
+        def named_parameters(self): return []
+        def named_buffers(self): return []
+    with pytest.raises(Exception) as e:
+        st.load_safetensors_into_graph_with_rename(G(), blob, st.bert_legacy_key_rename)
+    assert "collision" in str(e.value)
+
+
+def test_task_heads_losses_and_predictions():
+    cfg = bert.BertConfig(vocab_size=30, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32,
+                          max_position_embeddings=8, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, id2label=["a", "b", "c"])
+    ids = torch.randint(1, 30, (2, 8))
+    inputs = [ids, torch.arange(8).expand(2, 8), torch.zeros_like(ids), bert.build_extended_attention_mask(torch.ones(2, 8))]
+    clf = bert.BertForSequenceClassification.on_device(cfg, 3)
+    clf.graph().set_training(False)
+    loss = clf.compute_loss(inputs, torch.tensor([0, 2]))
+    loss.backward()
+    assert loss.t.dim() == 0 and clf.labels() == ["a", "b", "c"]
+    preds = clf.predict(inputs)
+    assert len(preds) == 2 and preds[0][0][0] in ("a", "b", "c")
+    tag = bert.BertForTokenClassification.on_device(cfg, 3)
+    assert tag.compute_loss(inputs, torch.randint(0, 3, (2, 8))).t.dim() == 0
+    qa = bert.BertForQuestionAnswering.on_device(cfg)
+    assert qa.compute_loss(inputs, torch.tensor([1, 2]), torch.tensor([3, 4])).t.dim() == 0
+    mlm = bert.BertForMaskedLM.on_device(cfg)
+    labels = torch.full((2, 8), -100)
+    labels[:, 2] = ids[:, 2]
+    assert mlm.compute_loss(inputs, labels).t.dim() == 0
+    with pytest.raises(Exception):
+        bert.BertForSequenceClassification.on_device(cfg, 0)
