@@ -1,0 +1,99 @@
+"""`from_pretrained`: resolve a repo id to local files and build + load the model
+(flodl-hf/src/hub/). Nothing here opens a network connection: files are looked up, in this order,
+in `<HF_HOME>/flodl-converted/<repo>/`, in the HuggingFace hub cache layout
+(`<HF_HOME>/hub/models--org--name/snapshots/*/`), or in `repo_id` itself when it is a directory.
+A repo that is not on disk is reported with the paths that were tried."""
+from __future__ import annotations
+
+import glob
+import os
+from typing import List, Optional, Tuple
+
+from ..tensor import TensorError
+from .export import build_for_export, parse_head
+from .models.auto import (AutoConfig, AutoModelForMaskedLM, AutoModelForQuestionAnswering, AutoModelForSequenceClassification,
+                          AutoModelForTokenClassification)
+from .safetensors_io import (bert_legacy_key_rename, load_safetensors_into_graph_with_rename_allow_unused, weights_have_pooler)
+
+
+def hf_home() -> str:
+    return os.environ.get("HF_HOME") or os.path.join(os.path.expanduser("~"), ".cache", "huggingface")
+
+
+def candidate_dirs(repo_id: str) -> List[str]:
+    out = []
+    if os.path.isdir(repo_id):
+        out.append(repo_id)
+    out.append(os.path.join(hf_home(), "flodl-converted", repo_id))
+    snap = os.path.join(hf_home(), "hub", "models--" + repo_id.replace("/", "--"), "snapshots")
+    out.extend(sorted(glob.glob(os.path.join(snap, "*")), reverse=True))
+    return out
+
+
+def resolve_files(repo_id: str) -> Tuple[str, str, Optional[str]]:
+    """(config.json, model.safetensors, tokenizer.json or None)."""
+    tried = candidate_dirs(repo_id)
+    cfg = st = tok = None
+    for d in tried:
+        c, s, t = (os.path.join(d, n) for n in ("config.json", "model.safetensors", "tokenizer.json"))
+        cfg = cfg or (c if os.path.exists(c) else None)
+        st = st or (s if os.path.exists(s) else None)
+        tok = tok or (t if os.path.exists(t) else None)
+    if cfg is None or st is None:
+        raise TensorError(f"from_pretrained({repo_id}): config.json / model.safetensors not found locally (no network access is attempted); "
+                          f"looked in: {tried}. If the repo ships only `pytorch_model.bin`, convert it to safetensors first.")
+    return cfg, st, tok
+
+
+def _rename_for(model_type: str):
+    prefix = {"distilbert": "distilbert.", "albert": "albert.", "deberta-v2": "deberta.", "bert": "bert.", "roberta": "roberta.",
+              "xlm-roberta": "roberta."}[model_type]
+
+    def rename(key: str) -> str:
+        k = bert_legacy_key_rename(key)
+        return k
+    return rename, prefix
+
+
+def _load(graph, weights: bytes, model_type: str, base_only: bool) -> List[str]:
+    rename, prefix = _rename_for(model_type)
+    if base_only:
+        # a bare backbone checkpoint may lack the family prefix (saved from `XModel`), a head
+        # checkpoint carries it: accept both
+        from .safetensors_io import parse_header
+        names = list(parse_header(weights)[0])
+        if not any(n.startswith(prefix) for n in names):
+            return load_safetensors_into_graph_with_rename_allow_unused(graph, weights, lambda k: prefix + rename(k))
+    return load_safetensors_into_graph_with_rename_allow_unused(graph, weights, rename)
+
+
+def from_pretrained(repo_id: str, device=None, head: Optional[str] = None):
+    """Backbone graph (`head` None/"base") or the graph of a task head ("seqcls", "tokcls", "qa", "mlm")."""
+    cfg_path, st_path, _ = resolve_files(repo_id)
+    cfg = AutoConfig.from_json_str(open(cfg_path).read())
+    weights = open(st_path, "rb").read()
+    kind = parse_head(head) if head else "base"
+    g = build_for_export(cfg, weights_have_pooler(weights), device, kind)
+    _load(g, weights, cfg.model_type(), kind == "base")
+    return g
+
+
+def _head_from_pretrained(auto_cls, repo_id: str, device=None):
+    cfg_path, st_path, tok_path = resolve_files(repo_id)
+    cfg = AutoConfig.from_json_str(open(cfg_path).read())
+    h = auto_cls.from_config(cfg, device)
+    _load(h.graph(), open(st_path, "rb").read(), cfg.model_type(), False)
+    h.graph().set_training(False)
+    if tok_path is not None:
+        try:
+            from .tokenizer import HfTokenizer
+            h = h.with_tokenizer(HfTokenizer.from_file(tok_path))
+        except TensorError:
+            pass
+    return h
+
+
+def sequence_classification_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForSequenceClassification, repo_id, device)
+def token_classification_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForTokenClassification, repo_id, device)
+def question_answering_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForQuestionAnswering, repo_id, device)
+def masked_lm_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForMaskedLM, repo_id, device)

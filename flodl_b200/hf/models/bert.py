@@ -200,6 +200,11 @@ class BertForSequenceClassification(ClassificationHead):
              .through(Linear(config.hidden_size, n, True, device)).tag("classifier").build())
         return cls(_attach(g, config.with_architectures("BertForSequenceClassification")), config, n, config.id2label)
 
+    @staticmethod
+    def num_labels_from_config(config):
+        from ._common import need_num_labels
+        return need_num_labels(config, "BertForSequenceClassification")
+
 
 class BertForTokenClassification(TaggingHead):
     @classmethod
@@ -208,6 +213,11 @@ class BertForTokenClassification(TaggingHead):
         g = (bert_backbone_flow(config, device, False).through(Dropout(config.hidden_dropout_prob))
              .through(Linear(config.hidden_size, n, True, device)).tag("classifier").build())
         return cls(_attach(g, config.with_architectures("BertForTokenClassification")), config, n, config.id2label)
+
+    @staticmethod
+    def num_labels_from_config(config):
+        from ._common import need_num_labels
+        return need_num_labels(config, "BertForTokenClassification")
 
 
 class BertForQuestionAnswering(QaHead):

@@ -233,3 +233,71 @@ def test_task_heads_losses_and_predictions():
     assert mlm.compute_loss(inputs, labels).t.dim() == 0
     with pytest.raises(Exception):
         bert.BertForSequenceClassification.on_device(cfg, 0)
+
+
+def test_auto_classes_export_and_local_from_pretrained(tmp_path, monkeypatch):
+    from flodl_b200 import hf
+    from flodl_b200.hf.export import classify_architecture, parse_head
+    cfg = roberta.RobertaConfig(vocab_size=40, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32,
+                                max_position_embeddings=12, id2label=["no", "yes"])
+    head = roberta.RobertaForSequenceClassification.on_device(cfg, 2)
+    out = str(tmp_path / "hub_home" / "flodl-converted" / "acme" / "tiny-roberta")
+    hf.export_hf_dir(head.graph(), head.graph().source_config(), out)
+    assert sorted(p.name for p in (tmp_path / "hub_home" / "flodl-converted" / "acme" / "tiny-roberta").iterdir()) == ["config.json", "model.safetensors"]
+    auto = hf.AutoConfig.from_json_str(open(out + "/config.json").read())
+    assert auto.model_type() == "roberta" and auto.architectures() == ["RobertaForSequenceClassification"] and auto.base_class_name() == "RobertaModel"
+    monkeypatch.setenv("HF_HOME", str(tmp_path / "hub_home"))
+    g = hf.from_pretrained("acme/tiny-roberta", head="seqcls")
+    for (n1, p1), (n2, p2) in zip(head.graph().named_parameters(), g.named_parameters()):
+        assert n1 == n2 and torch.equal(p1.t, p2.t)
+    h2 = hf.hub.sequence_classification_from_pretrained("acme/tiny-roberta")
+    assert h2.labels() == ["no", "yes"]
+    backbone = hf.from_pretrained("acme/tiny-roberta")            # head keys are simply unused
+    assert not any(n.startswith("classifier") for n, _ in backbone.named_parameters())
+    with pytest.raises(Exception) as e:
+        hf.from_pretrained("acme/not-there")
+    assert "not found locally" in str(e.value)
+    assert classify_architecture("BertForMaskedLM") == "mlm" and classify_architecture("BertModel") == "base"
+    assert parse_head("token-classification") == "tokcls"
+    with pytest.raises(Exception):
+        classify_architecture("BertForPreTraining")
+    with pytest.raises(Exception):
+        hf.AutoConfig.from_json_str('{"model_type": "gpt2"}')
+    for mt, c in (("bert", bert.BertConfig), ("distilbert", distilbert.DistilBertConfig), ("albert", albert.AlbertConfig),
+                  ("deberta-v2", deberta_v2.DebertaV2Config), ("xlm-roberta", roberta.XlmRobertaConfig)):
+        assert hf.AutoConfig.from_json_str(c().to_json_str()).model_type() == mt
+
+
+def test_fdl_checkpoint_exports_to_hf_dir(tmp_path):
+    from flodl_b200 import hf
+    cfg = bert.BertConfig(vocab_size=30, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32, max_position_embeddings=8)
+    g = bert.BertModel.on_device_without_pooler(cfg)
+    path = str(tmp_path / "m.fdl")
+    g.save_checkpoint(path)
+    hf.export_checkpoint(path, str(tmp_path / "out"))
+    back = st.read_safetensors(open(tmp_path / "out" / "model.safetensors", "rb").read())
+    assert "bert.embeddings.word_embeddings.weight" in back and not st.keys_have_pooler(list(back))
+    assert json.loads(open(tmp_path / "out" / "config.json").read())["model_type"] == "bert"
+
+
+def test_tokenizer_wrapper_builds_graph_inputs(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    from flodl_b200.hf.tokenizer import HfTokenizer
+    vocab = {"[PAD]": 0, "[UNK]": 1, "[CLS]": 2, "[SEP]": 3, "hello": 4, "world": 5, "again": 6}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.post_processor = tokenizers.processors.TemplateProcessing(single="[CLS] $A [SEP]", pair="[CLS] $A [SEP] $B:1 [SEP]:1",
+                                                                  special_tokens=[("[CLS]", 2), ("[SEP]", 3)])
+    path = str(tmp_path / "tokenizer.json")
+    tok.save(path)
+    t = HfTokenizer.from_file(path)
+    enc = t.encode(["hello world", "hello"])
+    assert enc.input_ids.tolist() == [[2, 4, 5, 3], [2, 4, 3, 0]] and enc.attention_mask.tolist() == [[1, 1, 1, 1], [1, 1, 1, 0]]
+    assert enc.position_ids.tolist()[1] == [0, 1, 2, 3]
+    pair = t.encode_pairs([("hello", "world again")])
+    assert pair.token_type_ids.tolist() == [[0, 0, 0, 1, 1, 1]]
+    ins = bert.BertConfig.encoder_inputs(enc)
+    assert len(ins) == 4 and list(ins[3].t.shape) == [2, 1, 1, 4]
+    assert "hello world" in t.decode([2, 4, 5, 3]) and t.token_to_id("world") == 5 and t.id_to_token(4) == "hello"
+    with pytest.raises(Exception):
+        t.encode([])
