@@ -115,4 +115,47 @@ __device__ __forceinline__ void dropout_scale4(uint64_t seed, uint64_t idx4, flo
   for (int i = 0; i < 4; ++i) s[i] = ((w[i] >> 8) * (1.0f / 16777216.0f)) >= p ? inv_keep : 0.f;
 }
 
+
+// ---- fast GELU for bf16 outputs ---------------------------------------------------------------------
+// One hardware tanh (tanh.approx.f32, relative error 2^-11) per value. For the erf form,
+// erf(x / sqrt(2)) is written as tanh(g(x)) with g an odd degree-5 polynomial fitted (minimax over
+// [0, 6]) so that |tanh(g(x)) - erf(x / sqrt(2))| < 3.7e-5, i.e. |GELU error| < 6e-5: below half a
+// bf16 ulp wherever |GELU(x)| > 0.03. x is clamped to +-8 before the polynomial (its quartic term is
+// negative, and tanh has long saturated there).
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float erf_tanh_arg(float x) {
+  const float u = fminf(fmaxf(x, -8.0f), 8.0f);
+  const float u2 = u * u;
+  return u * fmaf(u2, fmaf(u2, -0.00031580707f, 0.03679825612f), 0.7977178338f);
+}
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_approx(erf_tanh_arg(x)), hx);
+}
+__device__ __forceinline__ float dgelu_erf_fast(float x) {
+  const float cdf = fmaf(0.5f, tanh_approx(erf_tanh_arg(x)), 0.5f);
+  const float pdf = 0.3989422804f * ex2_approx(-0.7213475204f * x * x);   // exp(-x^2/2) / sqrt(2 pi)
+  return fmaf(x, pdf, cdf);
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float hx = 0.5f * x;
+  const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
+  return fmaf(hx, tanh_approx(u), hx);
+}
+__device__ __forceinline__ float dgelu_tanh_fast(float x) {
+  const float x2 = x * x;
+  const float t = tanh_approx(x * fmaf(x2, 0.0356774081f, 0.7978845608f));
+  const float du = fmaf(x2, 0.1070322243f, 0.7978845608f);
+  return fmaf(0.5f * x * (1.0f - t * t), du, fmaf(0.5f, t, 0.5f));
+}
+
 }  // namespace fb

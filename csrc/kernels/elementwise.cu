@@ -9,14 +9,20 @@
 
 namespace fb {
 
+// `kFast` (bf16 tensors): the one-MUFU formulas of common.cuh, whose error is below bf16 resolution;
+// fp32 tensors keep libdevice's erff / tanhf.
+template <bool kFast>
 __device__ __forceinline__ float gelu_fwd_f(float x, int tanh_approx) {
+  if (kFast) return tanh_approx ? gelu_tanh_fast(x) : gelu_erf_fast(x);
   if (tanh_approx) {
     const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     return 0.5f * x * (1.0f + tanhf(u));
   }
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
+template <bool kFast>
 __device__ __forceinline__ float gelu_bwd_f(float x, int tanh_approx) {
+  if (kFast) return tanh_approx ? dgelu_tanh_fast(x) : dgelu_erf_fast(x);
   if (tanh_approx) {
     const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     const float t = tanhf(u);
@@ -37,10 +43,10 @@ __global__ void gelu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long
       float v[V];
       VecIO<T>::load(x + i, v);
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = gelu_fwd_f(v[j], tanh_approx);
+      for (int j = 0; j < V; ++j) v[j] = gelu_fwd_f<sizeof(T) == 2>(v[j], tanh_approx);
       VecIO<T>::store(y + i, v);
     } else {
-      for (long long k = i; k < n; ++k) VecIO<T>::put(y + k, gelu_fwd_f(VecIO<T>::get(x + k), tanh_approx));
+      for (long long k = i; k < n; ++k) VecIO<T>::put(y + k, gelu_fwd_f<sizeof(T) == 2>(VecIO<T>::get(x + k), tanh_approx));
     }
   }
 }
@@ -56,11 +62,11 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
       VecIO<T>::load(dy + i, a);
       VecIO<T>::load(x + i, b);
 #pragma unroll
-      for (int j = 0; j < V; ++j) a[j] *= gelu_bwd_f(b[j], tanh_approx);
+      for (int j = 0; j < V; ++j) a[j] *= gelu_bwd_f<sizeof(T) == 2>(b[j], tanh_approx);
       VecIO<T>::store(dx + i, a);
     } else {
       for (long long k = i; k < n; ++k)
-        VecIO<T>::put(dx + k, VecIO<T>::get(dy + k) * gelu_bwd_f(VecIO<T>::get(x + k), tanh_approx));
+        VecIO<T>::put(dx + k, VecIO<T>::get(dy + k) * gelu_bwd_f<sizeof(T) == 2>(VecIO<T>::get(x + k), tanh_approx));
     }
   }
 }

@@ -30,6 +30,7 @@
 #include <unordered_map>
 
 #include "../include/flodl_b200.h"
+#include "common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fb {
@@ -73,24 +74,15 @@ struct GemmCfg {
   static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
 };
 
-__device__ __forceinline__ float gelu_erf_f(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-}
-__device__ __forceinline__ float dgelu_erf_f(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
-}
-__device__ __forceinline__ float gelu_tanh_f(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
-}
-__device__ __forceinline__ float dgelu_tanh_f(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = tanhf(u);
-  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
-}
+// The epilogue runs on 8 warps while the tensor cores work on the next tile, so its budget per
+// output element is about a dozen FP32 instructions and one special-function op (for K = 768 the
+// main loop of a 128x256 tile is ~3000 cycles). libdevice's erff/tanhf cost 3-4x that, which made
+// the GELU epilogue, not the MMA, the critical path. These bf16-output versions use the hardware
+// tanh (see common.cuh): erf through a fitted odd polynomial inside tanh, |error| < 6e-5 in GELU.
+__device__ __forceinline__ float gelu_erf_f(float x) { return gelu_erf_fast(x); }
+__device__ __forceinline__ float dgelu_erf_f(float x) { return dgelu_erf_fast(x); }
+__device__ __forceinline__ float gelu_tanh_f(float x) { return gelu_tanh_fast(x); }
+__device__ __forceinline__ float dgelu_tanh_f(float x) { return dgelu_tanh_fast(x); }
 
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -112,6 +104,43 @@ __device__ __forceinline__ void unpack_bf16x2(uint32_t w, float& lo, float& hi) 
   hi = f.y;
 }
 
+// v[0..32) += bias[col0 .. col0+32). Every lane of a warp reads the same addresses (one output row
+// per lane, the same 32 columns), so wide loads are broadcasts: 8 (fp32) or 4 (bf16) load
+// instructions per 32 columns instead of 32.
+__device__ __forceinline__ void add_bias32(const GemmParams& p, int col0, int nvalid, float (&v)[32]) {
+  if (p.bias_fp32) {
+    const float* b = static_cast<const float*>(p.bias) + col0;
+    if (nvalid == 32 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(b) + j);
+        v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) v[i] += __ldg(b + i);
+    }
+  } else {
+    const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
+    if (nvalid == 32 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(b) + j);
+        float h[8];
+        unpack_bf16x2(q.x, h[0], h[1]); unpack_bf16x2(q.y, h[2], h[3]);
+        unpack_bf16x2(q.z, h[4], h[5]); unpack_bf16x2(q.w, h[6], h[7]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[8 * j + i] += h[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) v[i] += __bfloat162float(b[i]);
+    }
+  }
+}
+
 // Epilogue for 32 consecutive columns of one output row. Every loop over the 32 values is fully
 // unrolled with compile-time indices (tails are handled by predicates), so the values stay in
 // registers: a dynamically indexed copy would be demoted to local memory and every access to it
@@ -121,23 +150,16 @@ __device__ __forceinline__ void unpack_bf16x2(uint32_t w, float& lo, float& hi) 
 // harmless values; the caller's store clips them.
 __device__ __forceinline__ void epilogue_compute32(const GemmParams& p, const uint32_t (&acc)[32], int row, int col0,
                                                    bool add_bias, float (&v)[32], float (&pre)[32]) {
-  const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+  if (p.alpha) {
+    const float alpha = __ldg(p.alpha);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
-  const int nvalid = (col0 + 32 <= p.N) ? 32 : (p.N > col0 ? p.N - col0 : 0);
-  if (p.bias && add_bias) {
-    if (p.bias_fp32) {
-      const float* b = static_cast<const float*>(p.bias) + col0;
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
+  } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < nvalid) v[i] += __ldg(b + i);
-    } else {
-      const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < nvalid) v[i] += __bfloat162float(b[i]);
-    }
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
   }
+  const int nvalid = (col0 + 32 <= p.N) ? 32 : (p.N > col0 ? p.N - col0 : 0);
+  if (p.bias && add_bias) add_bias32(p, col0, nvalid, v);
   if (p.epi == FB_EPI_GELU_ERF) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) { pre[i] = v[i]; v[i] = gelu_erf_f(v[i]); }
@@ -189,24 +211,17 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint
                                                  int row, int col0, bool add_bias) {
   if (row >= p.M || col0 >= p.N) return;
   float v[32];
-  const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+  if (p.alpha) {
+    const float alpha = __ldg(p.alpha);
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * alpha;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+  }
   const bool full = (col0 + 32 <= p.N);
   const int nvalid = full ? 32 : (p.N - col0);
-  if (p.bias && add_bias) {
-    if (p.bias_fp32) {
-      const float* b = static_cast<const float*>(p.bias) + col0;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < nvalid) v[i] += __ldg(b + i);
-    } else {
-      const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (i < nvalid) v[i] += __bfloat162float(b[i]);
-    }
-  }
+  if (p.bias && add_bias) add_bias32(p, col0, nvalid, v);
   if (p.epi == FB_EPI_GELU_ERF || p.epi == FB_EPI_GELU_TANH) {
     if (p.aux) {  // save the pre-activation for the backward pass
       __nv_bfloat16* a = static_cast<__nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;

@@ -18,6 +18,27 @@ namespace fb {
 
 constexpr int kLnWarps = 4;
 
+// N consecutive fp32 values p[off .. off+N) as 16-byte loads (N is 4 or 8, off a multiple of N, the
+// array 16-byte aligned as every parameter slot is); `fill` when p is null.
+template <int N>
+__device__ __forceinline__ void load_f32_vec(const float* __restrict__ p, int off, float fill, float (&out)[N]) {
+  if (!p) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) out[j] = fill;
+    return;
+  }
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(p + off + j));
+      out[j] = q.x; out[j + 1] = q.y; out[j + 2] = q.z; out[j + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) out[j] = __ldg(p + off + j);
+  }
+}
+
 template <typename T, int VPL>
 __global__ void __launch_bounds__(kLnWarps * 32)
 ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
@@ -89,14 +110,11 @@ ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const flo
   for (int i = 0; i < VPL; ++i) {
     const int vi = lane + i * 32;
     if (vi < nvec) {
-      float o[V];
+      float o[V], g[V], b[V];
+      load_f32_vec<V>(gamma, vi * V, 1.f, g);
+      load_f32_vec<V>(beta, vi * V, 0.f, b);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const int c = vi * V + j;
-        const float g = gamma ? __ldg(gamma + c) : 1.f;
-        const float b = beta ? __ldg(beta + c) : 0.f;
-        o[j] = (v[i][j] - mean) * rstd * g + b;
-      }
+      for (int j = 0; j < V; ++j) o[j] = fmaf((v[i][j] - mean) * rstd, g[j], b[j]);
       VecIO<T>::store(y + static_cast<long long>(row) * cols + vi * V, o);
     }
   }
@@ -120,6 +138,19 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* 
 #pragma unroll
     for (int j = 0; j < V; ++j) dg[i][j] = db[i][j] = 0.f;
 
+  // gamma does not change from row to row: one set of 16-byte loads per thread, kept in registers
+  float gm[VPL][V];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = lane + i * 32;
+    if (vi < nvec) {
+      load_f32_vec<V>(gamma, vi * V, 1.f, gm[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) gm[i][j] = 1.f;
+    }
+  }
+
   for (int row = blockIdx.x * kLnWarps + warp; row < rows; row += gridDim.x * kLnWarps) {
     const float mu = mean[row], rs = rstd[row];
     float g_dy[VPL][V], xh[VPL][V];
@@ -133,7 +164,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* 
         VecIO<T>::load(pre + static_cast<long long>(row) * cols + vi * V, b);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float g = gamma ? __ldg(gamma + vi * V + j) : 1.f;
+          const float g = gm[i][j];
           xh[i][j] = (b[j] - mu) * rs;
           dg[i][j] += a[j] * xh[i][j];
           db[i][j] += a[j];
