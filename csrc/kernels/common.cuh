@@ -2,6 +2,7 @@
 // packing, warp/block reductions and a counter-based RNG (Philox-4x32-10) for dropout masks that
 // the backward pass regenerates instead of storing.
 #pragma once
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -156,6 +157,25 @@ __device__ __forceinline__ float dgelu_tanh_fast(float x) {
   const float t = tanh_approx(x * fmaf(x2, 0.0356774081f, 0.7978845608f));
   const float du = fmaf(x2, 0.1070322243f, 0.7978845608f);
   return fmaf(0.5f * x * (1.0f - t * t), du, fmaf(0.5f, t, 0.5f));
+}
+
+
+// ---- programmatic dependent launch -----------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor
+// in the stream is still running. `pdl_wait()` blocks until the predecessor grid has completed and
+// its writes are visible; it must precede the first access to anything the predecessor produced
+// (and any write the predecessor might still read). `pdl_launch_dependents()` tells the scheduler
+// that the successor may begin its own preamble. Both are no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host switch: FLODL_B200_PDL=0 turns the launch attribute off everywhere.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("FLODL_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 }  // namespace fb

@@ -67,7 +67,11 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN_CTA * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (160 * 1024) / STAGE_BYTES;
-  static constexpr int TMEM_COLS = (2 * kBN < 32) ? 32 : 2 * kBN;
+  // two accumulators side by side; the allocation size must be a power of two
+  static constexpr int TMEM_COLS = (2 * kBN <= 32) ? 32 : (2 * kBN <= 64) ? 64 : (2 * kBN <= 128) ? 128 : (2 * kBN <= 256) ? 256 : 512;
+  // the 8 epilogue warps are 4 TMEM lane quarters x 2 column ranges; ranges are multiples of 64
+  // columns (one staged bf16 store), so a 192-wide tile splits 128 + 64
+  static constexpr int EPI_SPLIT = (kBN == 192) ? 128 : kBN / 2;
   // epilogue staging: 4 KB (32 rows x 128 B, swizzled) per epilogue warp for C, the same again for aux
   static constexpr int EPI_BYTES = 2 * kEpiWarps * 4096;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
@@ -393,6 +397,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if constexpr (kCG == 2) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above (barriers, descriptor prefetch, TMEM) touched
+  // no global data and may run while the previous kernel of the stream drains; from here on this
+  // kernel reads what that kernel wrote.
+  if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 7] = clock64();
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -494,7 +504,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;                 // TMEM lane quarter this warp may touch
     const int half = (warp - 2) >> 2;       // which half of the tile's columns
-    constexpr int COLS_PER_WARP = kBN / 2;
+    constexpr int kSplit = Cfg::EPI_SPLIT;
     int it = 0;
     bool ok = true;
     for (int u = group; u < num_units && ok; u += num_groups, ++it) {
@@ -509,8 +519,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 4] = clock64();
       const int row = m0 + q * 32 + lane;
       const int row0 = m0 + q * 32;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * COLS_PER_WARP;
-      const int ncol0 = n0 + half * COLS_PER_WARP;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * kSplit;
+      const int ncol0 = n0 + half * kSplit;
+      const int COLS_PER_WARP = half ? kBN - kSplit : kSplit;
       if (p.c_mode == 0) {
 #pragma unroll 1
         for (int c = 0; c < COLS_PER_WARP; c += 32) {
@@ -697,13 +708,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kCG;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (pdl_enabled()) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, p);
   return static_cast<int>(e);
 }
@@ -715,12 +731,16 @@ extern "C" int fb_gemm_bf16_ts(const void*, const void*, void*, int, int, int, l
 
 extern "C" int fb_gemm_pick_config(int M, int N, int K, int split_k) {
   // Score = SM occupancy of the last wave x a per-tile efficiency prior (bigger tiles re-use
-  // operands more and are less L2-bound). Configs: 0 = pair 256x256, 1 = 128x256, 2 = 128x128, 3 = 128x64.
+  // operands more and are less L2-bound). Configs: 0 = pair 256x256, 1 = 128x256, 2 = 128x128, 3 = 128x64, 4 = 128x192, 5 = pair 256x192.
   const int sms = 148;
-  const struct { int cg, bn; float prior; } cand[4] = {{2, 256, 1.00f}, {1, 256, 0.92f}, {1, 128, 0.80f}, {1, 64, 0.55f}};
+  // Single-CTA tiles read A and the whole B tile from shared memory for every MMA and run close to
+  // the shared-memory bandwidth limit; the pair configs (each CTA reads half of B) do not, hence
+  // their higher prior. The 256x192 pair needs a K-major B (its 96-column half tile is not a whole
+  // number of 64-column panels), so fb_gemm_bf16 falls back to 256x256 when B is MN-major.
+  const struct { int cg, bn; float prior; } cand[6] = {{2, 256, 1.00f}, {1, 256, 0.85f}, {1, 128, 0.70f}, {1, 64, 0.50f}, {1, 192, 0.80f}, {2, 192, 0.98f}};
   int best = 2;
   float best_score = -1.f;
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 6; ++i) {
     const int num_m = (M + 128 * cand[i].cg - 1) / (128 * cand[i].cg);
     const int num_n = (N + cand[i].bn - 1) / cand[i].bn;
     const long units = 1L * num_m * num_n * split_k;
@@ -753,9 +773,13 @@ extern "C" int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int
   if (split_k < 1) split_k = 1;
   if (split_k > 1 && !c_fp32) return -2;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
-  if (config < 0) config = fb_gemm_pick_config(M, N, K, split_k);
-  const int cg = (config == 0) ? 2 : 1;
-  const int bn = (config == 0 || config == 1) ? 256 : (config == 2 ? 128 : 64);
+  if (config < 0) {
+    config = fb_gemm_pick_config(M, N, K, split_k);
+    if (config == 5 && b_mn) config = 0;          // 256x192 pair tiles need a K-major B
+  }
+  if (config == 5 && b_mn) return -5;
+  const int cg = (config == 0 || config == 5) ? 2 : 1;
+  const int bn = (config == 0 || config == 1) ? 256 : (config == 2 ? 128 : (config == 4 || config == 5 ? 192 : 64));
   const int bn_cta = bn / cg;
 
   CUtensorMap ta, tb;
@@ -797,6 +821,8 @@ extern "C" int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int
     case 0: return launch_gemm<2, 256>(ta, tb, tc, tx, p, stream);
     case 1: return launch_gemm<1, 256>(ta, tb, tc, tx, p, stream);
     case 2: return launch_gemm<1, 128>(ta, tb, tc, tx, p, stream);
+    case 4: return launch_gemm<1, 192>(ta, tb, tc, tx, p, stream);
+    case 5: return launch_gemm<2, 192>(ta, tb, tc, tx, p, stream);
     default: return launch_gemm<1, 64>(ta, tb, tc, tx, p, stream);
   }
 }

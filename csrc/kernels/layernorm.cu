@@ -227,8 +227,22 @@ ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dg
   const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + lane;
   float g = 0.f, b = 0.f;
+  // gridDim.y slices of the partial rows run in parallel (only used with accumulate, where the
+  // slices can add into the destination atomically); 4 rows in flight per thread
   if (c < cols) {
-    for (int i = grp; i < nblocks; i += 8) {
+    const int step = 8 * gridDim.y;
+    int i = blockIdx.y * 8 + grp;
+    for (; i + 3 * step < nblocks; i += 4 * step) {
+      float gg[4], bb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        gg[u] = partial[(static_cast<long long>(i + u * step) * 2) * cols + c];
+        bb[u] = partial[(static_cast<long long>(i + u * step) * 2 + 1) * cols + c];
+      }
+      g += (gg[0] + gg[1]) + (gg[2] + gg[3]);
+      b += (bb[0] + bb[1]) + (bb[2] + bb[3]);
+    }
+    for (; i < nblocks; i += step) {
       g += partial[(static_cast<long long>(i) * 2) * cols + c];
       b += partial[(static_cast<long long>(i) * 2 + 1) * cols + c];
     }
@@ -239,8 +253,13 @@ ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dg
   if (grp == 0 && c < cols) {
 #pragma unroll
     for (int w = 1; w < 8; ++w) { g += rg[w][lane]; b += rb[w][lane]; }
-    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
-    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+    if (gridDim.y > 1) {
+      if (dgamma) atomicAdd(dgamma + c, g);
+      if (dbeta) atomicAdd(dbeta + c, b);
+    } else {
+      if (dgamma) dgamma[c] = accumulate ? dgamma[c] + g : g;
+      if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+    }
   }
 }
 
@@ -323,7 +342,8 @@ extern "C" int fb_layernorm_bwd(const void* dy, const void* pre, const float* me
   int r = run();
   if (r) return r;
   if (partial && (dgamma || dbeta)) {
-    fb::ln_bwd_finalize_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, grid, cols, accumulate);
+    const dim3 fgrid((cols + 31) / 32, accumulate ? 8 : 1);
+    fb::ln_bwd_finalize_kernel<<<fgrid, 256, 0, st>>>(partial, dgamma, dbeta, grid, cols, accumulate);
     return static_cast<int>(cudaGetLastError());
   }
   return 0;

@@ -33,7 +33,7 @@ def _gemm_case(C, M, N, K, a_mn, b_mn, config, out_dtype=torch.bfloat16, **kw):
     return out.float(), ref
 
 
-@pytest.mark.parametrize("config", [2, 1, 3, 0])
+@pytest.mark.parametrize("config", [2, 1, 3, 0, 4])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
 def test_gemm_layouts(C, config, a_mn, b_mn):
     out, ref = _gemm_case(C, 512, 768, 256, a_mn, b_mn, config)
@@ -41,7 +41,7 @@ def test_gemm_layouts(C, config, a_mn, b_mn):
     assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
 
 
-@pytest.mark.parametrize("config", [0, 1, 2, 3])
+@pytest.mark.parametrize("config", [0, 1, 2, 3, 4, 5])
 def test_gemm_ragged_edges(C, config):
     # M, N not multiples of the tile, K not a multiple of 64 (TMA zero-fills the tails)
     out, ref = _gemm_case(C, 300, 328, 200, False, False, config)
@@ -49,7 +49,7 @@ def test_gemm_ragged_edges(C, config):
     assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
 
 
-@pytest.mark.parametrize("config", [0, 2])
+@pytest.mark.parametrize("config", [0, 2, 4, 5])
 def test_gemm_many_tiles_per_cta(C, config):
     # more tiles than SMs: exercises the accumulator double buffering and barrier phases
     out, ref = _gemm_case(C, 4096, 3072, 768, False, False, config)
@@ -57,15 +57,16 @@ def test_gemm_many_tiles_per_cta(C, config):
     assert err <= 0.02 * ref.abs().max().item() + 0.05, f"max err {err}"
 
 
-def test_gemm_bias_gelu_aux(C):
-    M, N, K = 512, 512, 256
+@pytest.mark.parametrize("config", [-1, 0, 1, 4, 5])
+def test_gemm_bias_gelu_aux(C, config):
+    M, N, K = 512, 768, 256
     torch.manual_seed(0)
     a = torch.randn(M, K, device="cuda").bfloat16()
     b = (torch.randn(N, K, device="cuda") / math.sqrt(K)).bfloat16()
     bias = torch.randn(N, device="cuda")
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     aux = torch.empty_like(out)
-    C.gemm(a, b, out, bias=bias, epi=1, aux=aux)
+    C.gemm(a, b, out, bias=bias, epi=1, aux=aux, config=config)
     pre = a.float() @ b.float().t() + bias
     ref = torch.nn.functional.gelu(pre)
     assert (aux.float() - pre).abs().max().item() < 0.05
@@ -74,7 +75,7 @@ def test_gemm_bias_gelu_aux(C):
     g = torch.randn(M, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).bfloat16()
     dpre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    C.gemm(g, w, dpre, epi=2, aux=aux)
+    C.gemm(g, w, dpre, epi=2, aux=aux, config=config)
     x = aux.float().requires_grad_(True)
     torch.nn.functional.gelu(x).backward(g.float() @ w.float().t())
     assert (dpre.float() - x.grad).abs().max().item() < 0.06
@@ -93,6 +94,9 @@ def test_gemm_fp32_out_accumulate_splitk_alpha(C):
     out2 = base.clone()
     C.gemm(a, b, out2, True, True, accumulate=True, split_k=4)
     assert (out2 - (base + ref)).abs().max().item() < 0.02 * ref.abs().max().item()
+    out4 = base.clone()
+    C.gemm(a, b, out4, True, True, accumulate=True, split_k=2, config=4)     # 128x192 tiles, 128+64 epilogue split
+    assert (out4 - (base + ref)).abs().max().item() < 0.02 * ref.abs().max().item()
     alpha = torch.tensor([0.25], device="cuda")
     out3 = torch.empty(M, N, device="cuda")
     C.gemm(a, b, out3, True, True, alpha=alpha)
