@@ -1,0 +1,7 @@
+"""`fdl`-style command line: `python -m flodl_b200.cli <command>` (flodl-cli/src/main.rs).
+
+Built-ins: `diagnose`, `build`, `bench`, `export-hf`, `api-ref`, `schema`, `completions`,
+`config show`, `init`; anything else is looked up in the nearest `fdl.yml` manifest."""
+from .args import REQUIRED, ArgError, FdlArgs, arg  # noqa: F401
+from .main import main  # noqa: F401
+from .manifest import ManifestError, deep_merge, find_manifest, load_manifest, resolve_command, run_command  # noqa: F401

@@ -1,0 +1,296 @@
+from __future__ import annotations
+
+import inspect
+import json
+import os
+import subprocess
+import sys
+from dataclasses import dataclass
+from typing import List, Optional
+
+from .args import ArgError, FdlArgs, arg
+from .manifest import ManifestError, find_manifest, load_manifest, run_command
+
+BUILTINS = ["diagnose", "build", "bench", "export-hf", "api-ref", "schema", "completions", "config", "init", "help"]
+
+
+# ---- diagnose ---------------------------------------------------------------------------------------
+def diagnose(as_json: bool = False) -> int:
+    """Environment report: interpreter, torch, CUDA toolchain, GPUs, native library, NCCL."""
+    import platform
+    import shutil
+    info = {"python": platform.python_version(), "platform": platform.platform()}
+    try:
+        import torch
+        info["torch"] = torch.__version__
+        info["torch_cuda"] = torch.version.cuda
+        info["cuda_available"] = torch.cuda.is_available()
+        info["gpus"] = []
+        if torch.cuda.is_available():
+            for i in range(torch.cuda.device_count()):
+                p = torch.cuda.get_device_properties(i)
+                info["gpus"].append({"index": i, "name": p.name, "sm": f"{p.major}{p.minor}", "memory_gib": round(p.total_memory / 2 ** 30, 1),
+                                     "sms": p.multi_processor_count})
+        try:
+            info["nccl"] = ".".join(map(str, torch.cuda.nccl.version()))
+        except Exception:
+            info["nccl"] = None
+    except Exception as e:
+        info["torch"] = f"unavailable: {e}"
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    try:
+        out = subprocess.run([nvcc, "--version"], capture_output=True, text=True, timeout=20).stdout
+        info["nvcc"] = out.strip().splitlines()[-1] if out else None
+    except Exception:
+        info["nvcc"] = None
+    try:
+        from .. import _build, _ext
+        info["native_library"] = {"path": str(_build.TARGET), "built": not _build.needs_build(), "loads": _ext.available()}
+    except Exception as e:
+        info["native_library"] = {"error": repr(e)}
+    if as_json:
+        print(json.dumps(info, indent=2))
+    else:
+        for k, v in info.items():
+            if k == "gpus":
+                for g in v:
+                    print(f"  gpu {g['index']}: {g['name']} sm_{g['sm']} {g['memory_gib']} GiB {g['sms']} SMs")
+            else:
+                print(f"  {k}: {v}")
+    return 0
+
+
+# ---- api-ref ----------------------------------------------------------------------------------------
+def api_ref(as_json: bool = False) -> int:
+    """The public names of the package root with their signatures."""
+    import flodl_b200 as pkg
+    rows = []
+    for name in sorted(n for n in dir(pkg) if not n.startswith("_")):
+        obj = getattr(pkg, name)
+        if inspect.ismodule(obj):
+            continue
+        kind = "class" if inspect.isclass(obj) else "function" if callable(obj) else "value"
+        try:
+            sig = str(inspect.signature(obj)) if callable(obj) else ""
+        except (TypeError, ValueError):
+            sig = "(...)"
+        doc = (inspect.getdoc(obj) or "").strip().splitlines()
+        rows.append({"name": name, "kind": kind, "signature": sig, "doc": doc[0] if doc else ""})
+    if as_json:
+        print(json.dumps(rows, indent=1))
+    else:
+        for r in rows:
+            print(f"{r['kind']:8} {r['name']}{r['signature']}")
+    return 0
+
+
+# ---- typed commands -----------------------------------------------------------------------------------
+@dataclass
+class BenchArgs(FdlArgs):
+    """Run the headline training benchmark (bench.py) on N GPUs of this node."""
+    gpus: int = arg(1, help="number of GPUs", short="g")
+    steps: int = arg(20, help="timed steps")
+    warmup: int = arg(5, help="warm-up steps")
+    model: str = arg("bert-base", help="which configuration", choices=["bert-base", "resnet20", "lm"])
+    impl: str = arg("ours", help="implementation arm", choices=["ours", "twin", "reference"])
+
+
+@dataclass
+class ExportArgs(FdlArgs):
+    """Export a `.fdl` checkpoint (with its config sidecar) as a HuggingFace model directory."""
+    checkpoint: str = arg(help="path to the .fdl file", positional=True)
+    out: str = arg("hf_export", help="output directory", short="o")
+
+
+@dataclass
+class InitArgs(FdlArgs):
+    """Scaffold a small training project that uses this package."""
+    name: str = arg(help="project directory to create", positional=True)
+
+
+def _repo_root() -> str:
+    return os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def bench(argv: List[str]) -> int:
+    a = BenchArgs.parse(argv, "fdl bench")
+    script = os.path.join(_repo_root(), "bench.py")
+    tail = ["--gpus", str(a.gpus), "--steps", str(a.steps), "--warmup", str(a.warmup), "--model", a.model, "--impl", a.impl]
+    if a.gpus > 1:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}", "--master-addr", "127.0.0.1",
+               "--master-port", "29511", script] + tail
+    else:
+        cmd = [sys.executable, script] + tail
+    return subprocess.call(cmd)
+
+
+def export_hf(argv: List[str]) -> int:
+    a = ExportArgs.parse(argv, "fdl export-hf")
+    from ..hf import export_checkpoint
+    export_checkpoint(a.checkpoint, a.out)
+    print(f"wrote {a.out}/model.safetensors and {a.out}/config.json")
+    return 0
+
+
+_TEMPLATE_MAIN = '''"""Minimal training script: a small MLP on synthetic data."""
+import torch
+
+from flodl_b200 import Adam, FlowBuilder, GELU, LayerNorm, Linear, Variable, clip_grad_norm, mse_loss
+
+model = (FlowBuilder.from_(Linear(2, 16)).through(GELU()).through(LayerNorm(16)).also(Linear(16, 16)).through(Linear(16, 2)).build())
+opt = Adam(model.parameters(), 0.01)
+x = torch.randn(32, 2)
+y = torch.stack([torch.sin(x[:, 0]), torch.cos(x[:, 1])], dim=1)
+for step in range(200):
+    loss = mse_loss(model.forward(Variable.wrap(x)), Variable.wrap(y))
+    loss.backward()
+    clip_grad_norm(model.parameters(), 1.0)
+    opt.step()
+    opt.zero_grad()
+    if step % 50 == 0:
+        print(step, loss.item())
+'''
+
+_TEMPLATE_MANIFEST = '''description: {name}
+
+commands:
+  train:
+    description: Train the model
+    run: python train.py
+  test:
+    description: Run the tests
+    run: python -m pytest -q
+'''
+
+
+def init(argv: List[str]) -> int:
+    a = InitArgs.parse(argv, "fdl init")
+    if os.path.exists(a.name):
+        print(f"fdl init: {a.name} already exists", file=sys.stderr)
+        return 1
+    os.makedirs(a.name)
+    with open(os.path.join(a.name, "train.py"), "w") as f:
+        f.write(_TEMPLATE_MAIN)
+    with open(os.path.join(a.name, "fdl.yml"), "w") as f:
+        f.write(_TEMPLATE_MANIFEST.format(name=a.name))
+    print(f"created {a.name}/train.py and {a.name}/fdl.yml")
+    return 0
+
+
+def completions(shell: str, manifest: Optional[str]) -> int:
+    names = list(BUILTINS)
+    if manifest:
+        try:
+            names += list((load_manifest(manifest)[0].get("commands") or {}).keys())
+        except ManifestError:
+            pass
+    words = " ".join(sorted(set(names)))
+    if shell == "zsh":
+        print(f"#compdef fdl\n_arguments '1: :({words})'")
+    elif shell == "fish":
+        for w in sorted(set(names)):
+            print(f"complete -c fdl -f -n '__fish_use_subcommand' -a {w}")
+    else:
+        print(f"complete -W \"{words}\" fdl")
+    return 0
+
+
+def schema(argv: List[str]) -> int:
+    table = {"bench": BenchArgs, "export-hf": ExportArgs, "init": InitArgs}
+    if not argv or argv[0] not in table:
+        print(json.dumps({k: v.schema() for k, v in table.items()}, indent=2))
+    else:
+        print(json.dumps(table[argv[0]].schema(), indent=2))
+    return 0
+
+
+def config_show(manifest: Optional[str], env: Optional[str]) -> int:
+    if manifest is None:
+        print("no fdl.yml found", file=sys.stderr)
+        return 1
+    man, origin = load_manifest(manifest, env)
+
+    def walk(node, path, depth):
+        for k, v in node.items():
+            sub = f"{path}.{k}" if path else str(k)
+            if isinstance(v, dict):
+                print("  " * depth + f"{k}:")
+                walk(v, sub, depth + 1)
+            else:
+                print("  " * depth + f"{k}: {v!r}    # {origin.get(sub, '?')}")
+    walk(man, "", 0)
+    return 0
+
+
+def usage(manifest: Optional[str]) -> str:
+    lines = ["usage: python -m flodl_b200.cli [--env NAME] [--dry-run] <command> [args]", "", "built-in commands:",
+             "  diagnose [--json]       report interpreter, torch, CUDA, GPUs and the native library",
+             "  build                   compile the native library for sm_100a",
+             "  bench [options]         run the training benchmark",
+             "  export-hf <ckpt>        .fdl checkpoint -> HuggingFace directory",
+             "  api-ref [--json]        list the public API",
+             "  schema [command]        argument schemas as JSON",
+             "  completions <shell>     shell completion script (bash, zsh, fish)",
+             "  config show             the merged manifest with the origin of every value",
+             "  init <name>             scaffold a project"]
+    if manifest:
+        try:
+            cmds = load_manifest(manifest)[0].get("commands") or {}
+            if cmds:
+                lines += ["", f"commands from {manifest}:"]
+                for k, v in cmds.items():
+                    desc = (v or {}).get("description", "") if isinstance(v, dict) or v is None else ""
+                    lines.append(f"  {k:<23} {desc}")
+        except ManifestError as e:
+            lines += ["", f"(manifest error: {e})"]
+    return "\n".join(lines)
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    env = None
+    dry = False
+    while argv and argv[0] in ("--env", "--dry-run"):
+        if argv[0] == "--env":
+            if len(argv) < 2:
+                print("--env needs a name", file=sys.stderr)
+                return 2
+            env, argv = argv[1], argv[2:]
+        else:
+            dry, argv = True, argv[1:]
+    manifest = find_manifest(os.getcwd())
+    if not argv or argv[0] in ("help", "-h", "--help"):
+        print(usage(manifest))
+        return 0
+    cmd, rest = argv[0], argv[1:]
+    try:
+        if cmd == "diagnose":
+            return diagnose("--json" in rest)
+        if cmd == "build":
+            from .. import _build
+            _build.build()
+            return 0
+        if cmd == "bench":
+            return bench(rest)
+        if cmd == "export-hf":
+            return export_hf(rest)
+        if cmd == "api-ref":
+            return api_ref("--json" in rest)
+        if cmd == "schema":
+            return schema(rest)
+        if cmd == "completions":
+            return completions(rest[0] if rest else "bash", manifest)
+        if cmd == "config":
+            if rest[:1] == ["show"]:
+                return config_show(manifest, env)
+            print("usage: config show", file=sys.stderr)
+            return 2
+        if cmd == "init":
+            return init(rest)
+        if manifest is None:
+            print(f"unknown command {cmd!r} and no fdl.yml found", file=sys.stderr)
+            return 2
+        return run_command(manifest, argv, env, dry)
+    except (ArgError, ManifestError) as e:
+        print(f"fdl: {e}", file=sys.stderr)
+        return 2
