@@ -279,10 +279,41 @@ Tensor grad_norm(const Tensor& g, double max_norm, double extra_scale) {
 }
 
 // ------------------------------------------------------------------------------------ batch norm
+// one zeroed word per device for the channels-last BatchNorm "last block folds" counter
+Tensor& bn_counter(int device) {
+  static std::vector<Tensor> words(64);
+  TORCH_CHECK(device >= 0 && device < 64);
+  if (!words[device].defined())
+    words[device] = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  return words[device];
+}
+bool is_channels_last_4d(const Tensor& t) {
+  return t.dim() == 4 && t.is_contiguous(at::MemoryFormat::ChannelsLast) && !t.is_contiguous();
+}
+
 std::vector<Tensor> bn_fwd(const Tensor& x, const OptTensor& residual, const OptTensor& gamma, const OptTensor& beta,
                            Tensor& running_mean, Tensor& running_var, double eps, double momentum, bool relu, bool training) {
   want_float_kind(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
+  if (is_channels_last_4d(x) && training) {
+    const int64_t C = x.size(1), P = x.numel() / C;
+    want_f32(running_mean, "running_mean");
+    want_f32(running_var, "running_var");
+    if (residual.has_value())
+      TORCH_CHECK(is_channels_last_4d(*residual) && residual->scalar_type() == x.scalar_type() && residual->sizes() == x.sizes(),
+                  "residual must be channels-last like x");
+    auto fopts = torch::dtype(torch::kFloat).device(x.device());
+    Tensor y = torch::empty_like(x);   // keeps the channels-last strides
+    Tensor mean = torch::empty({C}, fopts), rstd = torch::empty({C}, fopts);
+    Tensor scratch = torch::empty({fb_bn_nhwc_scratch_floats((int)C)}, fopts);
+    check(fb_bn_nhwc_fwd(x.data_ptr(), ptr<const void>(residual), ptr<const float>(gamma), ptr<const float>(beta),
+                         running_mean.data_ptr<float>(), running_var.data_ptr<float>(), y.data_ptr(), mean.data_ptr<float>(),
+                         rstd.data_ptr<float>(), scratch.data_ptr<float>(),
+                         reinterpret_cast<unsigned int*>(bn_counter(x.get_device()).data_ptr<int>()), (long long)P, (int)C, (float)eps,
+                         (float)momentum, relu, training, is_bf16(x), stream_of(x)),
+          "fb_bn_nhwc_fwd");
+    return {y, mean, rstd};
+  }
   TORCH_CHECK(x.is_contiguous() && x.dim() >= 2);
   const int64_t N = x.size(0), C = x.size(1), HW = x.numel() / (N * C);
   want_f32(running_mean, "running_mean");
@@ -301,6 +332,24 @@ std::vector<Tensor> bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, c
                            const Tensor& rstd, bool relu, bool want_dres, const OptTensor& dgamma_acc, const OptTensor& dbeta_acc) {
   want_float_kind(dy, "dy");
   c10::cuda::CUDAGuard guard(dy.device());
+  if (is_channels_last_4d(x)) {
+    TORCH_CHECK(is_channels_last_4d(dy) && is_channels_last_4d(y), "channels-last BatchNorm backward needs channels-last dy and y");
+    const int64_t C = x.size(1), P = x.numel() / C;
+    auto fopts = torch::dtype(torch::kFloat).device(x.device());
+    Tensor dx = torch::empty_like(x);
+    Tensor dres = want_dres ? torch::empty_like(x) : Tensor();
+    Tensor dg, db;
+    bool acc = false;
+    if (dgamma_acc.has_value()) { dg = *dgamma_acc; db = *dbeta_acc; acc = true; }
+    else { dg = torch::empty({C}, fopts); db = torch::empty({C}, fopts); }
+    Tensor scratch = torch::empty({fb_bn_nhwc_scratch_floats((int)C)}, fopts);
+    check(fb_bn_nhwc_bwd(dy.data_ptr(), x.data_ptr(), y.data_ptr(), ptr<const float>(gamma), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                         dx.data_ptr(), want_dres ? dres.data_ptr() : nullptr, dg.data_ptr<float>(), db.data_ptr<float>(), acc,
+                         scratch.data_ptr<float>(), reinterpret_cast<unsigned int*>(bn_counter(x.get_device()).data_ptr<int>()), (long long)P,
+                         (int)C, relu, is_bf16(dy), stream_of(dy)),
+          "fb_bn_nhwc_bwd");
+    return {dx, dres, dg, db};
+  }
   TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && y.is_contiguous());
   const int64_t N = x.size(0), C = x.size(1), HW = x.numel() / (N * C);
   auto fopts = torch::dtype(torch::kFloat).device(x.device());

@@ -99,6 +99,13 @@ int fb_softmax_ce(const void* logits, long long ld, const long long* targets, in
 int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream);
 
 /* ---- batch norm (NCHW, training), fused ReLU / residual add --------------------------------- */
+int fb_bn_nhwc_scratch_floats(int C);
+int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
+                   float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, unsigned int* counter,
+                   long long P, int C, float eps, float momentum, int relu, int training, int is_bf16, void* stream);
+int fb_bn_nhwc_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
+                   const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int accumulate,
+                   float* scratch, unsigned int* counter, long long P, int C, int relu, int is_bf16, void* stream);
 int fb_bn_scratch_floats(int C);
 int fb_bn_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
               float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, int N, int C, int HW,

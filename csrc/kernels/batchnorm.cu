@@ -240,7 +240,276 @@ bn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
   }
 }
 
+
+// =============================================================================== channels-last
+// The same four passes for an N-H-W-C tensor, seen as a [P, C] matrix (P = N*H*W pixels, the C
+// channels of a pixel contiguous). This is the layout the tensor-core convolutions want, so a
+// ResNet that stays channels-last end to end never pays for a layout transpose.
+//
+// A thread owns one 16-byte vector of channels (a fixed column group) and walks down the pixels;
+// per-channel sums are folded across the block in shared memory and written as one partial row per
+// block. The last block to finish (device counter) folds the partial rows, so each pass is still
+// one launch: statistics pass -> mean / rstd / running stats, backward reduction -> dgamma, dbeta
+// and the two means the dx pass needs.
+constexpr int kBnMaxBlocks = 592;     // 4 per SM on a 148-SM part
+
+template <typename T>
+struct NhwcMap {
+  static constexpr int V = VecIO<T>::kVec;
+  int cv, lanes;          // vectors per pixel, pixels per block iteration
+  __device__ NhwcMap(int C) : cv(C / V), lanes(kBnThreads / (C / V)) {}
+  __device__ bool active() const { return static_cast<int>(threadIdx.x) < lanes * cv; }
+  __device__ int col() const { return (threadIdx.x % cv) * V; }
+  __device__ int lane() const { return threadIdx.x / cv; }
+};
+
+// Fold this block's per-thread channel sums (a[V], b[V]) and publish them as partial row
+// blockIdx.x; returns true in the block that finished last.
+template <typename T>
+__device__ __forceinline__ bool nhwc_publish(const NhwcMap<T>& m, int C, const float (&a)[VecIO<T>::kVec], const float (&b)[VecIO<T>::kVec],
+                                             float* __restrict__ partial, unsigned int* __restrict__ counter, float* sm) {
+  constexpr int V = VecIO<T>::kVec;
+  // sm: [2][lanes][C]
+  __shared__ bool last;
+  if (m.active()) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      sm[m.lane() * C + m.col() + j] = a[j];
+      sm[(m.lanes + m.lane()) * C + m.col() + j] = b[j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += kBnThreads) {
+    const int which = c / C, ch = c - which * C;
+    float acc = 0.f;
+    for (int l = 0; l < m.lanes; ++l) acc += sm[(which * m.lanes + l) * C + ch];
+    partial[(static_cast<long long>(blockIdx.x) * 2 + which) * C + ch] = acc;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = (atomicAdd(counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) __threadfence();
+  return last;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+bn_nhwc_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, unsigned int* __restrict__ counter,
+                     float* __restrict__ running_mean, float* __restrict__ running_var, float* __restrict__ save_mean,
+                     float* __restrict__ save_rstd, long long P, int C, float eps, float momentum) {
+  constexpr int V = VecIO<T>::kVec;
+  extern __shared__ float sm[];
+  const NhwcMap<T> m(C);
+  float a[V], b[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
+  if (m.active()) {
+    for (long long p = static_cast<long long>(blockIdx.x) * m.lanes + m.lane(); p < P; p += static_cast<long long>(gridDim.x) * m.lanes) {
+      float v[V];
+      VecIO<T>::load(x + p * C + m.col(), v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) { a[j] += v[j]; b[j] += v[j] * v[j]; }
+    }
+  }
+  if (!nhwc_publish<T>(m, C, a, b, partial, counter, sm)) return;
+  for (int c = threadIdx.x; c < C; c += kBnThreads) {
+    float sum = 0.f, sq = 0.f;
+    for (int i = 0; i < static_cast<int>(gridDim.x); ++i) {
+      sum += partial[(static_cast<long long>(i) * 2) * C + c];
+      sq += partial[(static_cast<long long>(i) * 2 + 1) * C + c];
+    }
+    const float cnt = static_cast<float>(P);
+    const float mean = sum / cnt;
+    const float var = fmaxf(sq / cnt - mean * mean, 0.f);
+    save_mean[c] = mean;
+    save_rstd[c] = rsqrtf(var + eps);
+    if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean;
+    if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * var * (cnt / fmaxf(cnt - 1.f, 1.f));
+  }
+  if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+bn_nhwc_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
+                     const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ rstd,
+                     T* __restrict__ y, long long P, int C, int relu) {
+  constexpr int V = VecIO<T>::kVec;
+  const NhwcMap<T> m(C);
+  if (!m.active()) return;
+  float scale[V], shift[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int c = m.col() + j;
+    const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+    scale[j] = rstd[c] * g;
+    shift[j] = b - mean[c] * scale[j];
+  }
+  for (long long p = static_cast<long long>(blockIdx.x) * m.lanes + m.lane(); p < P; p += static_cast<long long>(gridDim.x) * m.lanes) {
+    float v[V], r[V];
+    VecIO<T>::load(x + p * C + m.col(), v);
+    if (residual) VecIO<T>::load(residual + p * C + m.col(), r);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float o = fmaf(v[j], scale[j], shift[j]);
+      if (residual) o += r[j];
+      v[j] = relu ? fmaxf(o, 0.f) : o;
+    }
+    VecIO<T>::store(y + p * C + m.col(), v);
+  }
+}
+
+// fold[0..C) = mean of dy', fold[C..2C) = mean of dy' * xhat
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+bn_nhwc_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mean,
+                          const float* __restrict__ rstd, float* __restrict__ partial, unsigned int* __restrict__ counter,
+                          float* __restrict__ fold, float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate,
+                          long long P, int C, int relu) {
+  constexpr int V = VecIO<T>::kVec;
+  extern __shared__ float sm[];
+  const NhwcMap<T> m(C);
+  float a[V], b[V], mu[V], rs[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
+  if (m.active()) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) { mu[j] = mean[m.col() + j]; rs[j] = rstd[m.col() + j]; }
+    for (long long p = static_cast<long long>(blockIdx.x) * m.lanes + m.lane(); p < P; p += static_cast<long long>(gridDim.x) * m.lanes) {
+      float g[V], xv[V], yv[V];
+      VecIO<T>::load(dy + p * C + m.col(), g);
+      VecIO<T>::load(x + p * C + m.col(), xv);
+      if (relu) VecIO<T>::load(y + p * C + m.col(), yv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float gj = (relu && yv[j] <= 0.f) ? 0.f : g[j];
+        a[j] += gj;
+        b[j] += gj * (xv[j] - mu[j]) * rs[j];
+      }
+    }
+  }
+  if (!nhwc_publish<T>(m, C, a, b, partial, counter, sm)) return;
+  for (int c = threadIdx.x; c < C; c += kBnThreads) {
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = 0; i < static_cast<int>(gridDim.x); ++i) {
+      s1 += partial[(static_cast<long long>(i) * 2) * C + c];
+      s2 += partial[(static_cast<long long>(i) * 2 + 1) * C + c];
+    }
+    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + s2 : s2;
+    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + s1 : s1;
+    fold[c] = s1 / static_cast<float>(P);
+    fold[C + c] = s2 / static_cast<float>(P);
+  }
+  if (threadIdx.x == 0) *counter = 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+bn_nhwc_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ gamma,
+                         const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ fold,
+                         T* __restrict__ dx, T* __restrict__ dres, long long P, int C, int relu) {
+  constexpr int V = VecIO<T>::kVec;
+  const NhwcMap<T> m(C);
+  if (!m.active()) return;
+  float mu[V], rs[V], k[V], m1[V], m2[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const int c = m.col() + j;
+    mu[j] = mean[c];
+    rs[j] = rstd[c];
+    k[j] = (gamma ? gamma[c] : 1.f) * rs[j];
+    m1[j] = fold[c];
+    m2[j] = fold[C + c];
+  }
+  for (long long p = static_cast<long long>(blockIdx.x) * m.lanes + m.lane(); p < P; p += static_cast<long long>(gridDim.x) * m.lanes) {
+    float g[V], xv[V], yv[V];
+    VecIO<T>::load(dy + p * C + m.col(), g);
+    VecIO<T>::load(x + p * C + m.col(), xv);
+    if (relu) VecIO<T>::load(y + p * C + m.col(), yv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      if (relu && yv[j] <= 0.f) g[j] = 0.f;
+      xv[j] = k[j] * (g[j] - m1[j] - (xv[j] - mu[j]) * rs[j] * m2[j]);
+    }
+    VecIO<T>::store(dx + p * C + m.col(), xv);
+    if (dres) VecIO<T>::store(dres + p * C + m.col(), g);
+  }
+}
+
+static int nhwc_grid(long long P, int C, int V) {
+  const int lanes = kBnThreads / (C / V);
+  long long want = (P + lanes * 4LL - 1) / (lanes * 4LL);
+  if (want < 1) want = 1;
+  return static_cast<int>(want < kBnMaxBlocks ? want : kBnMaxBlocks);
+}
+
 }  // namespace fb
+
+// Channels-last entry points. C must be a multiple of the 16-byte vector (8 bf16 / 4 fp32) and at most
+// 2048; scratch holds fb_bn_nhwc_scratch_floats(C) floats; `counter` is one zero-initialised word the
+// kernels leave at zero.
+extern "C" int fb_bn_nhwc_scratch_floats(int C) { return (fb::kBnMaxBlocks * 2 + 2) * C; }
+
+extern "C" int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
+                              float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, unsigned int* counter,
+                              long long P, int C, float eps, float momentum, int relu, int training, int is_bf16, void* stream) {
+  using namespace fb;
+  if (P <= 0 || C <= 0) return 0;
+  const int V = is_bf16 ? 8 : 4;
+  if (C % V || C / V > kBnThreads) return -4;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = nhwc_grid(P, C, V);
+  const int lanes = kBnThreads / (C / V);
+  const size_t smem = sizeof(float) * 2 * lanes * C;
+  const float* mean = training ? save_mean : running_mean;
+  if (is_bf16) {
+    using T = __nv_bfloat16;
+    if (training)
+      bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
+                                                             save_mean, save_rstd, P, C, eps, momentum);
+    else return -6;   // evaluation mode goes through the framework's generic path
+    bn_nhwc_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+                                                        save_rstd, static_cast<T*>(y), P, C, relu);
+  } else {
+    using T = float;
+    if (training)
+      bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
+                                                             save_mean, save_rstd, P, C, eps, momentum);
+    else return -6;
+    bn_nhwc_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+                                                        save_rstd, static_cast<T*>(y), P, C, relu);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_bn_nhwc_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
+                              const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int accumulate,
+                              float* scratch, unsigned int* counter, long long P, int C, int relu, int is_bf16, void* stream) {
+  using namespace fb;
+  if (P <= 0 || C <= 0) return 0;
+  const int V = is_bf16 ? 8 : 4;
+  if (C % V || C / V > kBnThreads) return -4;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = nhwc_grid(P, C, V);
+  const int lanes = kBnThreads / (C / V);
+  const size_t smem = sizeof(float) * 2 * lanes * C;
+  float* fold = scratch + static_cast<long long>(kBnMaxBlocks) * 2 * C;
+  if (is_bf16) {
+    using T = __nv_bfloat16;
+    bn_nhwc_bwd_reduce_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+                                                                save_mean, save_rstd, scratch, counter, fold, dgamma, dbeta, accumulate, P, C, relu);
+    bn_nhwc_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
+                                                            save_mean, save_rstd, fold, static_cast<T*>(dx), static_cast<T*>(dresidual), P, C, relu);
+  } else {
+    using T = float;
+    bn_nhwc_bwd_reduce_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+                                                                save_mean, save_rstd, scratch, counter, fold, dgamma, dbeta, accumulate, P, C, relu);
+    bn_nhwc_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
+                                                            save_mean, save_rstd, fold, static_cast<T*>(dx), static_cast<T*>(dresidual), P, C, relu);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int fb_bn_scratch_floats(int C) { return C * fb::kBnSplits * 2; }
 

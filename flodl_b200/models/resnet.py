@@ -8,6 +8,8 @@ from __future__ import annotations
 
 from typing import List
 
+import torch
+
 from ..autograd import Variable
 from ..nn.layers import AdaptiveAvgPool2d, BatchNorm2d, Conv2d, Linear
 from ..nn.module import Module
@@ -55,6 +57,10 @@ class ResNet20(Module):
     def sub_modules(self): return [self.stem, self.stem_bn, *self.blocks, self.pool, self.fc]
 
     def forward(self, x: Variable) -> Variable:
+        if x.t.is_cuda and x.t.dim() == 4:
+            # channels-last from the stem on: convolutions and the fused BatchNorm kernels both work on
+            # N-H-W-C, so no layer pays for a layout transpose
+            x = Variable.wrap(x.t.contiguous(memory_format=torch.channels_last))
         h = self.stem_bn.forward(self.stem.forward(x), relu=True)
         for b in self.blocks:
             h = b.forward(h)

@@ -16,12 +16,15 @@ class _BatchNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, residual, weight, bias, running_mean, running_var, momentum, eps, relu):
         C = _ext.require()
-        xc = x.contiguous()
-        rc = None if residual is None else residual.contiguous()
+        # channels-last tensors stay channels-last (the NHWC kernels); everything else is made NCHW-contiguous
+        cl = _is_channels_last(x)
+        fmt = torch.channels_last if cl else torch.contiguous_format
+        xc = x.contiguous(memory_format=fmt)
+        rc = None if residual is None else residual.contiguous(memory_format=fmt)
         y, mean, rstd = C.bn_fwd(xc, rc, core._f32(weight), core._f32(bias), running_mean, running_var, eps, momentum, relu, True)
         core._launched(2)
         ctx.save_for_backward(xc, y, mean, rstd)
-        ctx.weight, ctx.bias, ctx.relu, ctx.has_res = weight, bias, relu, rc is not None
+        ctx.weight, ctx.bias, ctx.relu, ctx.has_res, ctx.fmt = weight, bias, relu, rc is not None, fmt
         return y
 
     @staticmethod
@@ -31,7 +34,7 @@ class _BatchNormFn(torch.autograd.Function):
         w, b = ctx.weight, ctx.bias
         gslot, bslot = core._grad_slot(w), core._grad_slot(b)
         use_slots = gslot is not None and bslot is not None
-        dx, dres, dg, db = C.bn_bwd(dy.contiguous(), x, y, core._f32(w), mean, rstd, ctx.relu, ctx.has_res,
+        dx, dres, dg, db = C.bn_bwd(dy.contiguous(memory_format=ctx.fmt), x, y, core._f32(w), mean, rstd, ctx.relu, ctx.has_res,
                                     gslot.view(-1) if use_slots else None, bslot.view(-1) if use_slots else None)
         core._launched(2)
         if use_slots:
@@ -42,6 +45,11 @@ class _BatchNormFn(torch.autograd.Function):
             dg = None if w is None else dg.to(w.dtype)
             db = None if b is None else db.to(b.dtype)
         return dx, (dres if ctx.has_res else None), dg, db, None, None, None, None, None
+
+
+def _is_channels_last(x: torch.Tensor) -> bool:
+    return x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous() \
+        and x.shape[1] % (8 if x.dtype == torch.bfloat16 else 4) == 0
 
 
 def _eligible(x: torch.Tensor, weight, training: bool) -> bool:

@@ -15,6 +15,11 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
         from . import conv_native
         if conv_native.eligible(x, weight, stride, padding, dilation, groups):
             return conv_native.conv2d(x, weight, bias, stride, padding)
-    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    if x.dim() == 4 and x.is_cuda and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
+        # channels-last activations: hand the filter over in the matching (KRSC) layout in the same
+        # cast, so the library convolution runs its NHWC tensor-core kernels without transposes
+        w = weight.to(dtype=x.dtype, memory_format=torch.channels_last)
+    else:
+        w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
     b = None if bias is None else (bias if bias.dtype == x.dtype else bias.to(x.dtype))
     return F.conv2d(x, w, b, stride, padding, dilation, groups)

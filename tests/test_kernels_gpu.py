@@ -299,11 +299,13 @@ def test_attention_dropout_statistics(C):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("relu,use_res", [(False, False), (True, False), (True, True)])
-def test_batchnorm_fused(C, dtype, relu, use_res):
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_batchnorm_fused(C, dtype, relu, use_res, channels_last):
     torch.manual_seed(8)
     N, Ch, H = 16, 32, 8
-    x = torch.randn(N, Ch, H, H, device="cuda").to(dtype)
-    res = torch.randn(N, Ch, H, H, device="cuda").to(dtype) if use_res else None
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    x = torch.randn(N, Ch, H, H, device="cuda").to(dtype).contiguous(memory_format=fmt)
+    res = torch.randn(N, Ch, H, H, device="cuda").to(dtype).contiguous(memory_format=fmt) if use_res else None
     g = torch.rand(Ch, device="cuda") + 0.5
     b = torch.randn(Ch, device="cuda")
     rm, rv = torch.zeros(Ch, device="cuda"), torch.ones(Ch, device="cuda")
@@ -320,7 +322,8 @@ def test_batchnorm_fused(C, dtype, relu, use_res):
     tol = 0.05 if dtype == torch.bfloat16 else 1e-4
     assert (y.float() - ref).abs().max().item() < tol
     assert (rm - rm_ref).abs().max().item() < 1e-4 and (rv - rv_ref).abs().max().item() < 1e-3
-    dy = torch.randn_like(ref).to(dtype)
+    assert y.is_contiguous(memory_format=fmt)
+    dy = torch.randn_like(ref).to(dtype).contiguous(memory_format=fmt)
     dx, dres, dg, db = C.bn_bwd(dy, x, y, g, mean, rstd, relu, use_res, None, None)
     # reference backward with the kernel's own ReLU mask (ties at 0 in bf16 would otherwise differ)
     (ref * (y.float() > 0 if relu else 1)).backward(dy.float()) if False else ref.backward(dy.float())
@@ -329,3 +332,26 @@ def test_batchnorm_fused(C, dtype, relu, use_res):
     assert (dg - gr.grad).abs().max().item() < btol * 10 and (db - br.grad).abs().max().item() < btol * 10
     if use_res:
         assert (dres.float() - rr.grad).abs().max().item() < btol
+
+
+def test_batchnorm_channels_last_many_blocks_accumulates(C):
+    # enough pixels for several hundred blocks: exercises the last-block fold, the counter reset
+    # (two calls in a row) and accumulation into existing gradient slots
+    torch.manual_seed(9)
+    x = torch.randn(64, 16, 32, 32, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    g, b = torch.rand(16, device="cuda") + 0.5, torch.randn(16, device="cuda")
+    rm, rv = torch.zeros(16, device="cuda"), torch.ones(16, device="cuda")
+    for _ in range(2):
+        y, mean, rstd = C.bn_fwd(x, None, g, b, rm, rv, 1e-5, 0.1, False, True)
+    ref = torch.nn.functional.batch_norm(x.float(), None, None, g, b, True, 0.1, 1e-5)
+    assert (y.float() - ref).abs().max().item() < 0.05
+    assert (mean - x.float().mean(dim=(0, 2, 3))).abs().max().item() < 1e-3
+    dy = torch.randn_like(x)
+    dg_acc, db_acc = torch.ones(16, device="cuda"), torch.ones(16, device="cuda")
+    dx, _, _, _ = C.bn_bwd(dy, x, y, g, mean, rstd, False, False, dg_acc, db_acc)
+    xr = x.float().clone().requires_grad_(True)
+    gr, br = g.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    torch.nn.functional.batch_norm(xr, None, None, gr, br, True, 0.1, 1e-5).backward(dy.float())
+    assert (dx.float() - xr.grad).abs().max().item() < 0.08
+    assert (dg_acc - 1 - gr.grad).abs().max().item() < 0.02 * gr.grad.abs().max().item() + 0.5
+    assert (db_acc - 1 - br.grad).abs().max().item() < 0.02 * br.grad.abs().max().item() + 0.5
