@@ -373,6 +373,28 @@ std::vector<Tensor> bn_bwd(const Tensor& dy, const Tensor& x, const Tensor& y, c
   return {dx, dres, dg, db};
 }
 
+// ------------------------------------------------------------------------------- convolution
+bool conv_wgrad_supported(int64_t N, int64_t H, int64_t W, int64_t Ci, int64_t Co, int64_t k, int64_t stride, int64_t pad) {
+  return fb_conv_wgrad_supported((int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)k, (int)stride, (int)pad) != 0;
+}
+// x, dy: channels-last bf16 4-D tensors; dw: fp32 tensor of logical shape [Co,Ci,k,k] whose memory is
+// K-R-S-C (channels-last strides), e.g. a flat-buffer gradient slot. The gradient is added to dw.
+void conv_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, int64_t pad) {
+  want_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_bf16(x) && is_bf16(dy) && x.dim() == 4 && dy.dim() == 4, "conv_wgrad takes bf16 4-D tensors");
+  TORCH_CHECK(x.is_contiguous(at::MemoryFormat::ChannelsLast) && dy.is_contiguous(at::MemoryFormat::ChannelsLast),
+              "conv_wgrad needs channels-last x and dy");
+  TORCH_CHECK(dw.scalar_type() == at::kFloat && dw.dim() == 4 && dw.is_contiguous(at::MemoryFormat::ChannelsLast),
+              "dw must be fp32 with channels-last (K-R-S-C) memory");
+  const int64_t N = x.size(0), Ci = x.size(1), H = x.size(2), W = x.size(3), Co = dy.size(1), k = dw.size(2);
+  TORCH_CHECK(dw.size(0) == Co && dw.size(1) == Ci && dw.size(3) == k, "dw shape mismatch");
+  Tensor& st = status_word(x.get_device());
+  check(fb_conv_wgrad(x.data_ptr(), dy.data_ptr(), dw.data_ptr<float>(), (int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)k, (int)stride,
+                      (int)pad, st.data_ptr<int>(), stream_of(x)),
+        "fb_conv_wgrad");
+}
+
 // ------------------------------------------------------------------------------------ attention
 // q, k, v: bf16 views [B, S, H, 64] sharing one stride set (e.g. slices of a fused QKV buffer).
 void check_bshd(const Tensor& t, const char* name) {
@@ -458,6 +480,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("grad_norm", &grad_norm);
   m.def("bn_fwd", &bn_fwd);
   m.def("bn_bwd", &bn_bwd);
+  m.def("conv_wgrad_supported", &conv_wgrad_supported);
+  m.def("conv_wgrad", &conv_wgrad, py::arg("x"), py::arg("dy"), py::arg("dw"), py::arg("stride"), py::arg("pad"));
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("mask"), py::arg("scale"), py::arg("causal"),
         py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());
   m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("d_o"), py::arg("lse"), py::arg("mask"),

@@ -99,6 +99,11 @@ int fb_softmax_ce(const void* logits, long long ld, const long long* targets, in
 int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream);
 
 /* ---- batch norm (NCHW, training), fused ReLU / residual add --------------------------------- */
+/* Convolution filter gradient for channels-last bf16 tensors on the tensor cores (csrc/kernels/conv_tcgen05.cu).
+   x: [N,H,W,Ci], dy: [N,Ho,Wo,Co]; dw: [Co][kh][kw][Ci] fp32, the gradient is added to it. */
+int fb_conv_wgrad_supported(int N, int H, int W, int Ci, int Co, int kh, int kw, int stride, int pad);
+int fb_conv_wgrad(const void* x, const void* dy, float* dw, int N, int H, int W, int Ci, int Co, int kh, int kw,
+                  int stride, int pad, int* status, void* stream);
 int fb_bn_nhwc_scratch_floats(int C);
 int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
                    float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, unsigned int* counter,

@@ -293,6 +293,51 @@ __device__ __forceinline__ bool nhwc_publish(const NhwcMap<T>& m, int C, const f
   return last;
 }
 
+// Sum of partial rows [0, nrows) for every channel, both planes, by the whole block: thread t takes
+// channel t % C and every (kBnThreads / C)-th row; slices are then folded through shared memory.
+// Results land in sm[0 .. 2C): plane 0 then plane 1. (The serial version, C threads walking all
+// rows, made this fold longer than the streaming pass it finishes.)
+__device__ __forceinline__ void nhwc_fold(const float* __restrict__ partial, int nrows, int C, float* sm) {
+  const int slices = kBnThreads / C > 0 ? kBnThreads / C : 1;
+  const int c = threadIdx.x % C, sl = threadIdx.x / C;
+  float a = 0.f, b = 0.f;
+  if (sl < slices) {
+    int i = sl;
+    for (; i + 3 * slices < nrows; i += 4 * slices) {
+      float a4[4], b4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a4[u] = __ldcg(partial + (static_cast<long long>(i + u * slices) * 2) * C + c);
+        b4[u] = __ldcg(partial + (static_cast<long long>(i + u * slices) * 2 + 1) * C + c);
+      }
+      a += (a4[0] + a4[1]) + (a4[2] + a4[3]);
+      b += (b4[0] + b4[1]) + (b4[2] + b4[3]);
+    }
+    for (; i < nrows; i += slices) {
+      a += __ldcg(partial + (static_cast<long long>(i) * 2) * C + c);
+      b += __ldcg(partial + (static_cast<long long>(i) * 2 + 1) * C + c);
+    }
+  }
+  __syncthreads();
+  // sm has room for 2 * lanes * C >= 2 * kBnThreads floats
+  sm[threadIdx.x] = a;
+  sm[kBnThreads + threadIdx.x] = b;
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  if (threadIdx.x < C) {
+    for (int k = 0; k < slices; ++k) {
+      ta += sm[k * C + threadIdx.x];
+      tb += sm[kBnThreads + k * C + threadIdx.x];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < C) {
+    sm[threadIdx.x] = ta;
+    sm[C + threadIdx.x] = tb;
+  }
+  __syncthreads();
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads)
 bn_nhwc_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, unsigned int* __restrict__ counter,
@@ -313,12 +358,9 @@ bn_nhwc_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, unsig
     }
   }
   if (!nhwc_publish<T>(m, C, a, b, partial, counter, sm)) return;
+  nhwc_fold(partial, static_cast<int>(gridDim.x), C, sm);
   for (int c = threadIdx.x; c < C; c += kBnThreads) {
-    float sum = 0.f, sq = 0.f;
-    for (int i = 0; i < static_cast<int>(gridDim.x); ++i) {
-      sum += partial[(static_cast<long long>(i) * 2) * C + c];
-      sq += partial[(static_cast<long long>(i) * 2 + 1) * C + c];
-    }
+    const float sum = sm[c], sq = sm[C + c];
     const float cnt = static_cast<float>(P);
     const float mean = sum / cnt;
     const float var = fmaxf(sq / cnt - mean * mean, 0.f);
@@ -390,12 +432,9 @@ bn_nhwc_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
     }
   }
   if (!nhwc_publish<T>(m, C, a, b, partial, counter, sm)) return;
+  nhwc_fold(partial, static_cast<int>(gridDim.x), C, sm);
   for (int c = threadIdx.x; c < C; c += kBnThreads) {
-    float s1 = 0.f, s2 = 0.f;
-    for (int i = 0; i < static_cast<int>(gridDim.x); ++i) {
-      s1 += partial[(static_cast<long long>(i) * 2) * C + c];
-      s2 += partial[(static_cast<long long>(i) * 2 + 1) * C + c];
-    }
+    const float s1 = sm[c], s2 = sm[C + c];
     if (dgamma) dgamma[c] = accumulate ? dgamma[c] + s2 : s2;
     if (dbeta) dbeta[c] = accumulate ? dbeta[c] + s1 : s1;
     fold[c] = s1 / static_cast<float>(P);
@@ -439,7 +478,7 @@ bn_nhwc_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 
 static int nhwc_grid(long long P, int C, int V) {
   const int lanes = kBnThreads / (C / V);
-  long long want = (P + lanes * 4LL - 1) / (lanes * 4LL);
+  long long want = (P + lanes * 8LL - 1) / (lanes * 8LL);
   if (want < 1) want = 1;
   return static_cast<int>(want < kBnMaxBlocks ? want : kBnMaxBlocks);
 }
@@ -447,7 +486,7 @@ static int nhwc_grid(long long P, int C, int V) {
 }  // namespace fb
 
 // Channels-last entry points. C must be a multiple of the 16-byte vector (8 bf16 / 4 fp32) and at most
-// 2048; scratch holds fb_bn_nhwc_scratch_floats(C) floats; `counter` is one zero-initialised word the
+// 256; scratch holds fb_bn_nhwc_scratch_floats(C) floats; `counter` is one zero-initialised word the
 // kernels leave at zero.
 extern "C" int fb_bn_nhwc_scratch_floats(int C) { return (fb::kBnMaxBlocks * 2 + 2) * C; }
 
@@ -457,7 +496,7 @@ extern "C" int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* 
   using namespace fb;
   if (P <= 0 || C <= 0) return 0;
   const int V = is_bf16 ? 8 : 4;
-  if (C % V || C / V > kBnThreads) return -4;
+  if (C % V || C > kBnThreads) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = nhwc_grid(P, C, V);
   const int lanes = kBnThreads / (C / V);
@@ -489,7 +528,7 @@ extern "C" int fb_bn_nhwc_bwd(const void* dy, const void* x, const void* y, cons
   using namespace fb;
   if (P <= 0 || C <= 0) return 0;
   const int V = is_bf16 ? 8 : 4;
-  if (C % V || C / V > kBnThreads) return -4;
+  if (C % V || C > kBnThreads) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = nhwc_grid(P, C, V);
   const int lanes = kBnThreads / (C / V);

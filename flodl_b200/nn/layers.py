@@ -101,6 +101,9 @@ class _ConvNd(Module):
             fan_in = (in_channels // groups) * ksz
         self.weight = Parameter(init.kaiming_uniform(shape, fan_in, math.sqrt(5.0), device), "weight")
         self.bias = Parameter(init.uniform_bias(fan_in, [out_channels], device), "bias") if bias else None
+        if n == 2 and not self.TRANSPOSED:
+            # a flat-buffer engine stores this filter K-R-S-C (see parallel/flat.py)
+            self.weight.t._fb_channels_last = True
 
     @classmethod
     def new(cls, in_channels, out_channels, kernel_size):

@@ -49,7 +49,7 @@ class _BatchNormFn(torch.autograd.Function):
 
 def _is_channels_last(x: torch.Tensor) -> bool:
     return x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous() \
-        and x.shape[1] % (8 if x.dtype == torch.bfloat16 else 4) == 0
+        and x.shape[1] % (8 if x.dtype == torch.bfloat16 else 4) == 0 and x.shape[1] <= 256
 
 
 def _eligible(x: torch.Tensor, weight, training: bool) -> bool:

@@ -27,6 +27,20 @@ def _align(n: int) -> int:
     return (n + ALIGN - 1) // ALIGN * ALIGN
 
 
+def _slot_view(buf: torch.Tensor, offset: int, like: torch.Tensor) -> torch.Tensor:
+    """View of `buf[offset : offset + numel]` shaped like `like`. 4-D tensors flagged
+    `_fb_channels_last` (2-D convolution filters) are stored K-R-S-C, i.e. the view has channels-last
+    strides: the tensor-core convolutions then take the bf16 shadow as it is, and the filter
+    gradient they produce adds into the slot without a layout change. Element-wise consumers (the
+    optimizer, norms, collectives) work on the flat range and never see the difference."""
+    n = like.numel()
+    flat = buf[offset:offset + n]
+    if like.dim() == 4 and getattr(like, "_fb_channels_last", False):
+        co, ci, kh, kw = like.shape
+        return flat.view(co, kh, kw, ci).permute(0, 3, 1, 2)
+    return flat.view(like.shape)
+
+
 class FlatParams:
     """Re-homes `tensors` (leaf parameter tensors) into flat buffers.
 
@@ -80,17 +94,17 @@ class FlatParams:
         with torch.no_grad():
             for t, o in zip(uniq, self.offsets):
                 n = t.numel()
-                view = self.params[o:o + n].view(t.shape)
+                view = _slot_view(self.params, o, t)
                 view.copy_(t.detach().float())
                 rg = t.requires_grad
                 t.data = view
                 t.requires_grad_(rg)
-                g = self.grads[o:o + n].view(t.shape)
+                g = _slot_view(self.grads, o, t)
                 t.grad = g
                 t._fb_grad = g
                 t._fb_flat = (self, o, n)
                 if self.shadow is not None:
-                    t._fb_bf16 = self.shadow[o:o + n].view(t.shape)
+                    t._fb_bf16 = _slot_view(self.shadow, o, t)
         self.refresh_shadow()
 
     # ---- maintenance --------------------------------------------------------------------------
@@ -105,7 +119,7 @@ class FlatParams:
         """Re-attach `.grad` after something set it to None (e.g. a foreign `zero_grad(set_to_none)`)."""
         for t, o in zip(self.tensors, self.offsets):
             if t.grad is None or t.grad.data_ptr() != self.grads.data_ptr() + 4 * o:
-                t.grad = self.grads[o:o + t.numel()].view(t.shape)
+                t.grad = _slot_view(self.grads, o, t)
 
     def range_of(self, t: torch.Tensor):
         _, o, n = t._fb_flat

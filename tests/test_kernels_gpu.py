@@ -355,3 +355,32 @@ def test_batchnorm_channels_last_many_blocks_accumulates(C):
     assert (dx.float() - xr.grad).abs().max().item() < 0.08
     assert (dg_acc - 1 - gr.grad).abs().max().item() < 0.02 * gr.grad.abs().max().item() + 0.5
     assert (db_acc - 1 - br.grad).abs().max().item() < 0.02 * br.grad.abs().max().item() + 0.5
+
+
+@pytest.mark.parametrize("N,Ci,Co,HW,k,stride", [(8, 16, 16, 32, 3, 1), (4, 16, 32, 32, 3, 2), (4, 32, 32, 16, 3, 1), (4, 32, 64, 16, 3, 2),
+                                                 (6, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 8, 16, 3, 1), (150, 16, 16, 32, 3, 1)])
+def test_conv_wgrad_tensor_core(C, N, Ci, Co, HW, k, stride):
+    torch.manual_seed(11)
+    pad = k // 2
+    assert C.conv_wgrad_supported(N, HW, HW, Ci, Co, k, stride, pad)
+    x = torch.randn(N, Ci, HW, HW, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    Ho = (HW + 2 * pad - k) // stride + 1
+    dy = (torch.randn(N, Co, Ho, Ho, device="cuda") * 0.1).bfloat16().contiguous(memory_format=torch.channels_last)
+    base = torch.randn(Co, Ci, k, k, device="cuda").contiguous(memory_format=torch.channels_last)
+    dw = base.clone()
+    assert dw.is_contiguous(memory_format=torch.channels_last)
+    C.conv_wgrad(x, dy, dw, stride, pad)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0
+    ref = torch.nn.grad.conv2d_weight(x.float(), (Co, Ci, k, k), dy.float(), stride=stride, padding=pad)
+    err = (dw - base - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 0.02, f"max err {err} (ref max {ref.abs().max().item()})"
+    # a second call accumulates again
+    C.conv_wgrad(x, dy, dw, stride, pad)
+    assert (dw - base - 2 * ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.04
+
+
+def test_conv_wgrad_rejects_unsupported(C):
+    assert not C.conv_wgrad_supported(4, 32, 32, 3, 16, 3, 1, 1)       # 3 input channels: rows are not 16-byte multiples
+    assert not C.conv_wgrad_supported(4, 32, 32, 16, 16, 5, 1, 2)      # 5x5
+    assert not C.conv_wgrad_supported(4, 28, 28, 16, 16, 3, 1, 1)      # width not a power of two
