@@ -318,33 +318,44 @@ def bench_gradnorm(args, hbm, tf):
 
 
 def bench_conv(args, hbm, tf):
-    from flodl_b200.ops import conv as oconv
+    """The three passes of the CIFAR-ResNet convolutions on channels-last bf16 tensors, native tcgen05
+    kernels against cuDNN (through ATen) on the same tensors."""
+    C = _ext_module()
     rows = []
-    shapes = [(128, 3, 16, 32, 3, 1), (128, 16, 16, 32, 3, 1), (128, 16, 32, 32, 3, 2), (128, 32, 32, 16, 3, 1), (128, 32, 64, 16, 3, 2),
+    shapes = [(128, 16, 16, 32, 3, 1), (128, 16, 32, 32, 3, 2), (128, 32, 32, 16, 3, 1), (128, 32, 64, 16, 3, 2),
               (128, 64, 64, 8, 3, 1), (128, 16, 32, 32, 1, 2)]
     if args.small:
-        shapes = [(128, 32, 32, 16, 3, 1)]
+        shapes = [(128, 16, 16, 32, 3, 1)]
+    cl = torch.channels_last
     for N, Ci, Co, HW, k, s in shapes:
-        x = torch.randn(N, Ci, HW, HW, device="cuda", dtype=BF16, requires_grad=True)
-        w = (torch.randn(Co, Ci, k, k, device="cuda") * 0.1).requires_grad_(True)
-        flat(w)
-        x2 = x.detach().clone().requires_grad_(True)
-        wb = w.detach().to(BF16).requires_grad_(True)
         pad = k // 2
+        x = torch.randn(N, Ci, HW, HW, device="cuda", dtype=BF16).contiguous(memory_format=cl)
+        w = (torch.randn(Co, Ci, k, k, device="cuda") * 0.1).to(BF16).contiguous(memory_format=cl)
         Ho = (HW + 2 * pad - k) // s + 1
         fl = 2.0 * N * Co * Ho * Ho * Ci * k * k / 1e12
-        dy = torch.randn(N, Co, Ho, Ho, device="cuda", dtype=BF16)
+        dy = torch.randn(N, Co, Ho, Ho, device="cuda", dtype=BF16).contiguous(memory_format=cl)
+        dw = torch.zeros(Co, Ci, k, k, device="cuda").contiguous(memory_format=cl)
+        sums = torch.zeros(2, Co, device="cuda")
+        shape = f"N{N} {Ci}->{Co} @{HW}^2 k{k} s{s}"
 
-        def ours():
-            x.grad = None
-            oconv.conv2d(x, w, None, (s, s), (pad, pad)).backward(dy)
-
-        def ref():
-            x2.grad = wb.grad = None
-            F.conv2d(x2, wb, None, s, pad).backward(dy)
-        o, r = time_ms(ours, args.iters, args.warmup), time_ms(ref, args.iters, args.warmup)
-        rows.append(Row("conv2d fwd+bwd", f"N{N} {Ci}->{Co} @{HW}^2 k{k} s{s}", o, r, 3 * fl, "TFLOP/s", tf, "cuDNN (F.conv2d) autograd"))
+        def bwd(mask):
+            return lambda: torch.ops.aten.convolution_backward(dy, x, w, None, [s, s], [pad, pad], [1, 1], False, [0, 0], 1, mask)
+        o = time_ms(lambda: C.conv_fprop(x, w, s, pad, sums), args.iters, args.warmup)
+        r = time_ms(lambda: F.conv2d(x, w, None, s, pad), args.iters, args.warmup)
+        rows.append(Row("conv fprop (+BN sums)", shape, o, r, fl, "TFLOP/s", tf, "cuDNN fprop"))
+        if C.conv_dgrad_supported(N, HW, HW, Ci, Co, k, s, pad):
+            o = time_ms(lambda: C.conv_dgrad(dy, w, s, pad), args.iters, args.warmup)
+            r = time_ms(bwd([True, False, False]), args.iters, args.warmup)
+            rows.append(Row("conv dgrad", shape, o, r, fl, "TFLOP/s", tf, "cuDNN dgrad"))
+        o = time_ms(lambda: C.conv_wgrad(x, dy, dw, s, pad), args.iters, args.warmup)
+        r = time_ms(bwd([False, True, False]), args.iters, args.warmup)
+        rows.append(Row("conv wgrad (fp32 accumulate in place)", shape, o, r, fl, "TFLOP/s", tf, "cuDNN wgrad"))
     return rows
+
+
+def _ext_module():
+    from flodl_b200 import _ext
+    return _ext.require()
 
 
 BENCHES = {"gemm": bench_gemm, "attention": bench_attention, "layernorm": bench_layernorm, "gelu": bench_gelu,

@@ -292,9 +292,30 @@ bool is_channels_last_4d(const Tensor& t) {
 }
 
 std::vector<Tensor> bn_fwd(const Tensor& x, const OptTensor& residual, const OptTensor& gamma, const OptTensor& beta,
-                           Tensor& running_mean, Tensor& running_var, double eps, double momentum, bool relu, bool training) {
+                           Tensor& running_mean, Tensor& running_var, double eps, double momentum, bool relu, bool training,
+                           const OptTensor& sums) {
   want_float_kind(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
+  if (sums.has_value()) {
+    // statistics already accumulated by the producer of x (fp32 [2, C]: sum, sum of squares)
+    TORCH_CHECK(is_channels_last_4d(x) && training, "precomputed sums need a channels-last input in training mode");
+    const int64_t C = x.size(1), P = x.numel() / C;
+    TORCH_CHECK(sums->is_cuda() && sums->scalar_type() == at::kFloat && sums->is_contiguous() && sums->numel() == 2 * C, "sums must be fp32 [2, C]");
+    want_f32(running_mean, "running_mean");
+    want_f32(running_var, "running_var");
+    if (residual.has_value())
+      TORCH_CHECK(is_channels_last_4d(*residual) && residual->scalar_type() == x.scalar_type() && residual->sizes() == x.sizes(),
+                  "residual must be channels-last like x");
+    auto fopts = torch::dtype(torch::kFloat).device(x.device());
+    Tensor y = torch::empty_like(x);
+    Tensor mean = torch::empty({C}, fopts), rstd = torch::empty({C}, fopts);
+    check(fb_bn_nhwc_fwd_sums(x.data_ptr(), ptr<const void>(residual), ptr<const float>(gamma), ptr<const float>(beta),
+                              running_mean.data_ptr<float>(), running_var.data_ptr<float>(), y.data_ptr(), mean.data_ptr<float>(),
+                              rstd.data_ptr<float>(), sums->data_ptr<float>(), (long long)P, (int)C, (float)eps, (float)momentum, relu,
+                              is_bf16(x), stream_of(x)),
+          "fb_bn_nhwc_fwd_sums");
+    return {y, mean, rstd};
+  }
   if (is_channels_last_4d(x) && training) {
     const int64_t C = x.size(1), P = x.numel() / C;
     want_f32(running_mean, "running_mean");
@@ -395,6 +416,56 @@ void conv_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, int64_t stride, i
         "fb_conv_wgrad");
 }
 
+bool conv_fprop_supported(int64_t N, int64_t H, int64_t W, int64_t Ci, int64_t Co, int64_t k, int64_t stride, int64_t pad) {
+  return fb_conv_fprop_supported((int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)stride, (int)pad) != 0;
+}
+bool conv_dgrad_supported(int64_t N, int64_t H, int64_t W, int64_t Ci, int64_t Co, int64_t k, int64_t stride, int64_t pad) {
+  return fb_conv_dgrad_supported((int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)stride, (int)pad) != 0;
+}
+void check_filter(const Tensor& w) {
+  TORCH_CHECK(w.is_cuda() && is_bf16(w) && w.dim() == 4 && w.is_contiguous(at::MemoryFormat::ChannelsLast) && w.size(2) == w.size(3),
+              "filter must be a square bf16 [Co,Ci,k,k] tensor with channels-last (K-R-S-C) memory");
+}
+// y = conv2d(x, w) for channels-last bf16 x; `stats` (fp32 [2, Co], zeroed) optionally receives sum / sum of squares of y.
+Tensor conv_fprop(const Tensor& x, const Tensor& w, int64_t stride, int64_t pad, const OptTensor& stats, const OptTensor& ts) {
+  want_cuda(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_bf16(x) && x.dim() == 4 && x.is_contiguous(at::MemoryFormat::ChannelsLast), "conv_fprop needs a channels-last bf16 input");
+  check_filter(w);
+  const int64_t N = x.size(0), Ci = x.size(1), H = x.size(2), W = x.size(3), Co = w.size(0), k = w.size(2);
+  TORCH_CHECK(w.size(1) == Ci, "filter/input channel mismatch");
+  const int64_t Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1;
+  if (stats.has_value()) TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == at::kFloat && stats->is_contiguous() && stats->numel() == 2 * Co, "stats must be fp32 [2, Co]");
+  Tensor y = torch::empty({N, Co, Ho, Wo}, x.options().memory_format(at::MemoryFormat::ChannelsLast));
+  Tensor& st = status_word(x.get_device());
+  if (ts.has_value()) {
+    TORCH_CHECK(ts->is_cuda() && ts->scalar_type() == at::kLong && ts->is_contiguous() && ts->numel() >= 64, "ts must be an int64 CUDA tensor of 64 slots");
+    check(fb_conv_fprop_ts(x.data_ptr(), w.data_ptr(), y.data_ptr(), ptr<float>(stats), (int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)stride,
+                           (int)pad, st.data_ptr<int>(), reinterpret_cast<long long*>(ts->data_ptr<int64_t>()), stream_of(x)),
+          "fb_conv_fprop_ts");
+    return y;
+  }
+  check(fb_conv_fprop(x.data_ptr(), w.data_ptr(), y.data_ptr(), ptr<float>(stats), (int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)stride, (int)pad,
+                      st.data_ptr<int>(), stream_of(x)),
+        "fb_conv_fprop");
+  return y;
+}
+// dx for a stride-1 "same" convolution.
+Tensor conv_dgrad(const Tensor& dy, const Tensor& w, int64_t stride, int64_t pad) {
+  want_cuda(dy, "dy");
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(is_bf16(dy) && dy.dim() == 4 && dy.is_contiguous(at::MemoryFormat::ChannelsLast), "conv_dgrad needs a channels-last bf16 gradient");
+  check_filter(w);
+  const int64_t N = dy.size(0), Co = dy.size(1), H = dy.size(2), W = dy.size(3), Ci = w.size(1), k = w.size(2);
+  TORCH_CHECK(w.size(0) == Co, "filter/gradient channel mismatch");
+  Tensor dx = torch::empty({N, Ci, H, W}, dy.options().memory_format(at::MemoryFormat::ChannelsLast));
+  Tensor& st = status_word(dy.get_device());
+  check(fb_conv_dgrad(dy.data_ptr(), w.data_ptr(), dx.data_ptr(), (int)N, (int)H, (int)W, (int)Ci, (int)Co, (int)k, (int)stride, (int)pad,
+                      st.data_ptr<int>(), stream_of(dy)),
+        "fb_conv_dgrad");
+  return dx;
+}
+
 // ------------------------------------------------------------------------------------ attention
 // q, k, v: bf16 views [B, S, H, 64] sharing one stride set (e.g. slices of a fused QKV buffer).
 void check_bshd(const Tensor& t, const char* name) {
@@ -478,9 +549,14 @@ PYBIND11_MODULE(_C, m) {
   m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
         py::arg("grad_scale") = py::none());
   m.def("grad_norm", &grad_norm);
-  m.def("bn_fwd", &bn_fwd);
+  m.def("bn_fwd", &bn_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"), py::arg("running_var"),
+        py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("training"), py::arg("sums") = py::none());
   m.def("bn_bwd", &bn_bwd);
   m.def("conv_wgrad_supported", &conv_wgrad_supported);
+  m.def("conv_fprop_supported", &conv_fprop_supported);
+  m.def("conv_dgrad_supported", &conv_dgrad_supported);
+  m.def("conv_fprop", &conv_fprop, py::arg("x"), py::arg("w"), py::arg("stride"), py::arg("pad"), py::arg("stats") = py::none(), py::arg("ts") = py::none());
+  m.def("conv_dgrad", &conv_dgrad, py::arg("dy"), py::arg("w"), py::arg("stride"), py::arg("pad"));
   m.def("conv_wgrad", &conv_wgrad, py::arg("x"), py::arg("dy"), py::arg("dw"), py::arg("stride"), py::arg("pad"));
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("mask"), py::arg("scale"), py::arg("causal"),
         py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());

@@ -104,10 +104,28 @@ int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar
 int fb_conv_wgrad_supported(int N, int H, int W, int Ci, int Co, int kh, int kw, int stride, int pad);
 int fb_conv_wgrad(const void* x, const void* dy, float* dw, int N, int H, int W, int Ci, int Co, int kh, int kw,
                   int stride, int pad, int* status, void* stream);
+
+/* Forward convolution and stride-1 data gradient for channels-last bf16 tensors (same file). The filter is
+   bf16 [Co][k][k][Ci]. `stats` (optional, fp32 [2][Co], zeroed by the caller) receives the per-channel sum
+   and sum of squares of the rounded outputs, for the batch normalisation that follows. */
+int fb_conv_fprop_supported(int N, int H, int W, int Ci, int Co, int k, int stride, int pad);
+int fb_conv_fprop(const void* x, const void* w, void* y, float* stats, int N, int H, int W, int Ci, int Co, int k, int stride,
+                  int pad, int* status, void* stream);
+/* fb_conv_fprop for the 3x3 stride-1 kernel with a timeline: `ts` (64 int64, device) receives nanosecond
+   timestamps of CTA 0: [0] start, [1] after the dependency wait, [2+i] loads of tile i issued,
+   [12+i] tile i landed, [22+i] its MMAs issued, [32+i] accumulator ready, [42+i] stored, [52] end. */
+int fb_conv_fprop_ts(const void* x, const void* w, void* y, float* stats, int N, int H, int W, int Ci, int Co, int k, int stride,
+                     int pad, int* status, long long* ts, void* stream);
+int fb_conv_dgrad_supported(int N, int H, int W, int Ci, int Co, int k, int stride, int pad);
+int fb_conv_dgrad(const void* dy, const void* w, void* dx, int N, int H, int W, int Ci, int Co, int k, int stride, int pad,
+                  int* status, void* stream);
 int fb_bn_nhwc_scratch_floats(int C);
 int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
                    float* running_var, void* y, float* save_mean, float* save_rstd, float* scratch, unsigned int* counter,
                    long long P, int C, float eps, float momentum, int relu, int training, int is_bf16, void* stream);
+int fb_bn_nhwc_fwd_sums(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
+                        float* running_var, void* y, float* save_mean, float* save_rstd, const float* sums, long long P, int C,
+                        float eps, float momentum, int relu, int is_bf16, void* stream);
 int fb_bn_nhwc_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
                    const float* save_rstd, void* dx, void* dresidual, float* dgamma, float* dbeta, int accumulate,
                    float* scratch, unsigned int* counter, long long P, int C, int relu, int is_bf16, void* stream);

@@ -372,11 +372,17 @@ bn_nhwc_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, unsig
   if (threadIdx.x == 0) *counter = 0;      // ready for the next launch
 }
 
-template <typename T>
+// kFromSums: the per-channel sum and sum of squares were accumulated by the kernel that produced x (the
+// convolution's epilogue); every thread derives mean and 1/std of its own channels from them, block 0
+// also records them for the backward pass and updates the running statistics. One launch, no
+// statistics pass over x.
+template <typename T, bool kFromSums>
 __global__ void __launch_bounds__(kBnThreads)
 bn_nhwc_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, const float* __restrict__ gamma,
                      const float* __restrict__ beta, const float* __restrict__ mean, const float* __restrict__ rstd,
-                     T* __restrict__ y, long long P, int C, int relu) {
+                     T* __restrict__ y, long long P, int C, int relu, const float* __restrict__ sums, float* __restrict__ save_mean,
+                     float* __restrict__ save_rstd, float* __restrict__ running_mean, float* __restrict__ running_var, float eps,
+                     float momentum) {
   constexpr int V = VecIO<T>::kVec;
   const NhwcMap<T> m(C);
   if (!m.active()) return;
@@ -385,8 +391,24 @@ bn_nhwc_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, co
   for (int j = 0; j < V; ++j) {
     const int c = m.col() + j;
     const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
-    scale[j] = rstd[c] * g;
-    shift[j] = b - mean[c] * scale[j];
+    float mu, rs;
+    if (kFromSums) {
+      const float cnt = static_cast<float>(P);
+      mu = sums[c] / cnt;
+      const float var = fmaxf(sums[C + c] / cnt - mu * mu, 0.f);
+      rs = rsqrtf(var + eps);
+      if (blockIdx.x == 0 && m.lane() == 0) {
+        save_mean[c] = mu;
+        save_rstd[c] = rs;
+        if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
+        if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * var * (cnt / fmaxf(cnt - 1.f, 1.f));
+      }
+    } else {
+      mu = mean[c];
+      rs = rstd[c];
+    }
+    scale[j] = rs * g;
+    shift[j] = b - mu * scale[j];
   }
   for (long long p = static_cast<long long>(blockIdx.x) * m.lanes + m.lane(); p < P; p += static_cast<long long>(gridDim.x) * m.lanes) {
     float v[V], r[V];
@@ -508,16 +530,43 @@ extern "C" int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* 
       bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
                                                              save_mean, save_rstd, P, C, eps, momentum);
     else return -6;   // evaluation mode goes through the framework's generic path
-    bn_nhwc_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
-                                                        save_rstd, static_cast<T*>(y), P, C, relu);
+    bn_nhwc_apply_kernel<T, false><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+                                                               save_rstd, static_cast<T*>(y), P, C, relu, nullptr, nullptr, nullptr, nullptr,
+                                                               nullptr, 0.f, 0.f);
   } else {
     using T = float;
     if (training)
       bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
                                                              save_mean, save_rstd, P, C, eps, momentum);
     else return -6;
-    bn_nhwc_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
-                                                        save_rstd, static_cast<T*>(y), P, C, relu);
+    bn_nhwc_apply_kernel<T, false><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+                                                               save_rstd, static_cast<T*>(y), P, C, relu, nullptr, nullptr, nullptr, nullptr,
+                                                               nullptr, 0.f, 0.f);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Training-mode forward whose statistics come from `sums` (fp32 [2][C]: per-channel sum and sum of
+// squares of x over its P pixels, e.g. from fb_conv_fprop). One launch.
+extern "C" int fb_bn_nhwc_fwd_sums(const void* x, const void* residual, const float* gamma, const float* beta, float* running_mean,
+                                   float* running_var, void* y, float* save_mean, float* save_rstd, const float* sums, long long P, int C,
+                                   float eps, float momentum, int relu, int is_bf16, void* stream) {
+  using namespace fb;
+  if (P <= 0 || C <= 0) return 0;
+  const int V = is_bf16 ? 8 : 4;
+  if (C % V || C > kBnThreads || !sums) return -4;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = nhwc_grid(P, C, V);
+  if (is_bf16) {
+    using T = __nv_bfloat16;
+    bn_nhwc_apply_kernel<T, true><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
+                                                              nullptr, static_cast<T*>(y), P, C, relu, sums, save_mean, save_rstd, running_mean,
+                                                              running_var, eps, momentum);
+  } else {
+    using T = float;
+    bn_nhwc_apply_kernel<T, true><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
+                                                              nullptr, static_cast<T*>(y), P, C, relu, sums, save_mean, save_rstd, running_mean,
+                                                              running_var, eps, momentum);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -51,9 +51,12 @@ def conv1d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1) -> V
     return W(F.conv1d(_t(x), _cast(_t(weight), x), _castb(bias, x), stride, padding, dilation, groups))
 
 
-def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1) -> Variable:
+def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, bn_stats=False) -> Variable:
+    """`bn_stats`: the caller feeds the result straight into a training-mode BatchNorm, so the native
+    kernel may accumulate the per-channel sums in its epilogue and hand them over with the tensor."""
     from ..ops import conv as _conv
-    return W(_conv.conv2d(_t(x), _t(weight), None if bias is None else _t(bias), _pair(stride, 2), _pair(padding, 2), _pair(dilation, 2), groups))
+    return W(_conv.conv2d(_t(x), _t(weight), None if bias is None else _t(bias), _pair(stride, 2), _pair(padding, 2), _pair(dilation, 2), groups,
+                          bn_stats=bn_stats))
 
 
 def conv3d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1) -> Variable:

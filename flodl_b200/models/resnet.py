@@ -25,6 +25,10 @@ class BasicBlock(Module):
         if stride != 1 or in_c != out_c:
             self.down_conv = Conv2d(in_c, out_c, 1, stride, 0, bias=False, device=device)
             self.down_bn = BatchNorm2d(out_c, device)
+        # every convolution here feeds a BatchNorm directly: let its epilogue accumulate the statistics
+        for conv in (self.conv1, self.conv2, self.down_conv):
+            if conv is not None:
+                conv.bn_stats = True
 
     def name(self): return "basic_block"
 

@@ -104,6 +104,8 @@ class _ConvNd(Module):
         if n == 2 and not self.TRANSPOSED:
             # a flat-buffer engine stores this filter K-R-S-C (see parallel/flat.py)
             self.weight.t._fb_channels_last = True
+        # set by a model whose next layer is a BatchNorm over this output (see autograd.ops.conv2d)
+        self.bn_stats = False
 
     @classmethod
     def new(cls, in_channels, out_channels, kernel_size):
@@ -133,6 +135,8 @@ class _ConvNd(Module):
               (1, True): A.conv_transpose1d, (2, True): A.conv_transpose2d, (3, True): A.conv_transpose3d}[(self.ND, self.TRANSPOSED)]
         if self.TRANSPOSED:
             return fn(x, self.weight.variable, b, self.stride, self.padding, self.output_padding, self.groups, self.dilation)
+        if self.ND == 2 and self.bn_stats and self.bias is None:
+            return fn(x, self.weight.variable, b, self.stride, self.padding, self.dilation, self.groups, bn_stats=True)
         return fn(x, self.weight.variable, b, self.stride, self.padding, self.dilation, self.groups)
 
 

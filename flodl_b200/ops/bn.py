@@ -14,15 +14,17 @@ class _BatchNormFn(torch.autograd.Function):
     dx (and the residual gradient) in two passes."""
 
     @staticmethod
-    def forward(ctx, x, residual, weight, bias, running_mean, running_var, momentum, eps, relu):
+    def forward(ctx, x, residual, weight, bias, running_mean, running_var, momentum, eps, relu, sums=None):
         C = _ext.require()
         # channels-last tensors stay channels-last (the NHWC kernels); everything else is made NCHW-contiguous
         cl = _is_channels_last(x)
         fmt = torch.channels_last if cl else torch.contiguous_format
         xc = x.contiguous(memory_format=fmt)
         rc = None if residual is None else residual.contiguous(memory_format=fmt)
-        y, mean, rstd = C.bn_fwd(xc, rc, core._f32(weight), core._f32(bias), running_mean, running_var, eps, momentum, relu, True)
-        core._launched(2)
+        if sums is not None and not cl:
+            sums = None
+        y, mean, rstd = C.bn_fwd(xc, rc, core._f32(weight), core._f32(bias), running_mean, running_var, eps, momentum, relu, True, sums)
+        core._launched(1 if sums is not None else 2)
         ctx.save_for_backward(xc, y, mean, rstd)
         ctx.weight, ctx.bias, ctx.relu, ctx.has_res, ctx.fmt = weight, bias, relu, rc is not None, fmt
         return y
@@ -44,7 +46,7 @@ class _BatchNormFn(torch.autograd.Function):
         else:
             dg = None if w is None else dg.to(w.dtype)
             db = None if b is None else db.to(b.dtype)
-        return dx, (dres if ctx.has_res else None), dg, db, None, None, None, None, None
+        return dx, (dres if ctx.has_res else None), dg, db, None, None, None, None, None, None
 
 
 def _is_channels_last(x: torch.Tensor) -> bool:
@@ -60,7 +62,9 @@ def _eligible(x: torch.Tensor, weight, training: bool) -> bool:
 
 def batch_norm(x, running_mean, running_var, weight, bias, training, momentum=0.1, eps=1e-5, relu=False, residual=None):
     if _eligible(x, weight, training) and (residual is None or residual.dtype == x.dtype):
-        return _BatchNormFn.apply(x, residual, weight, bias, running_mean, running_var, float(momentum), float(eps), bool(relu))
+        # sums accumulated by the convolution that produced x (see ops.conv.conv2d), if any
+        sums = getattr(x, "_fb_bn_sums", None)
+        return _BatchNormFn.apply(x, residual, weight, bias, running_mean, running_var, float(momentum), float(eps), bool(relu), sums)
     y = F.batch_norm(x, running_mean, running_var, weight, bias, training, momentum, eps)
     if residual is not None:
         y = y + residual

@@ -1,5 +1,7 @@
-"""conv2d dispatch. The native implicit-GEMM kernel covers the NCHW bf16 shapes of the CIFAR
-ResNet (3x3 / 1x1, stride 1 or 2, groups 1); everything else runs the PyTorch op."""
+"""conv2d dispatch. The native tcgen05 kernels cover channels-last bf16 activations with the CIFAR
+ResNet's filter shapes (3x3 / 1x1, stride 1 or 2, 16/32/64 channels, groups 1): forward, stride-1
+data gradient and filter gradient. Everything else (the 3-channel stem, strided data gradients,
+other layouts and dtypes) runs the PyTorch op."""
 from __future__ import annotations
 
 import torch
@@ -21,11 +23,19 @@ class _Conv2dShadowFn(torch.autograd.Function):
     accumulate chain per backward."""
 
     @staticmethod
-    def forward(ctx, x, weight, stride, padding, dilation, groups):
+    def forward(ctx, x, weight, stride, padding, dilation, groups, sums=None):
         w16 = weight._fb_bf16
         ctx.save_for_backward(x, w16)
         ctx.weight, ctx.conf = weight, (stride, padding, dilation, groups)
         core._launched()
+        C = _ext.require()
+        N, Ci, H, W = x.shape
+        Co, _, k, kw = w16.shape
+        ctx.simple = (dilation == (1, 1) and groups == 1 and k == kw and stride[0] == stride[1] and padding[0] == padding[1])
+        if ctx.simple and C.conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0]):
+            return C.conv_fprop(x, w16, stride[0], padding[0], sums)
+        if sums is not None:
+            raise RuntimeError("BatchNorm sums requested from a convolution the native kernel does not cover")
         return F.conv2d(x, w16, None, stride, padding, dilation, groups)
 
     @staticmethod
@@ -36,24 +46,45 @@ class _Conv2dShadowFn(torch.autograd.Function):
         C = _ext.require()
         N, Ci, H, W = x.shape
         Co, _, k, _ = w16.shape
-        native = (dilation == (1, 1) and groups == 1 and stride[0] == stride[1] and padding[0] == padding[1]
-                  and C.conv_wgrad_supported(N, H, W, Ci, Co, k, stride[0], padding[0]))
-        dx, dw, _ = torch.ops.aten.convolution_backward(dy, x, w16, None, list(stride), list(padding), list(dilation), False, [0, 0], groups,
-                                                        [ctx.needs_input_grad[0], not native, False])
-        core._launched(2)
-        if native:
+        shape = (N, H, W, Ci, Co, k, stride[0], padding[0])
+        native_w = ctx.simple and C.conv_wgrad_supported(*shape)
+        native_x = ctx.needs_input_grad[0] and ctx.simple and C.conv_dgrad_supported(*shape)
+        dx = dw = None
+        if (ctx.needs_input_grad[0] and not native_x) or not native_w:
+            dx, dw, _ = torch.ops.aten.convolution_backward(dy, x, w16, None, list(stride), list(padding), list(dilation), False, [0, 0], groups,
+                                                            [ctx.needs_input_grad[0] and not native_x, not native_w, False])
+            core._launched()
+        if native_x:
+            dx = C.conv_dgrad(dy, w16, stride[0], padding[0])
+            core._launched()
+        if native_w:
             # filter gradient on the tensor cores, accumulated into the fp32 slot in place
             C.conv_wgrad(x, dy, ctx.weight._fb_grad, stride[0], padding[0])
+            core._launched()
         else:
             ctx.weight._fb_grad.add_(dw)
         core._touched(ctx.weight)
-        return dx, None, None, None, None, None
+        return dx, None, None, None, None, None, None
 
 
-def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1):
+def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, bn_stats=False):
+    """`bn_stats`: a training-mode BatchNorm consumes the result directly; when the native forward
+    kernel runs, it accumulates the per-channel sum and sum of squares in its epilogue and the result
+    carries them as `_fb_bn_sums` (fp32 [2, Co]), which `ops.bn.batch_norm` picks up instead of making
+    its own statistics pass."""
     if (x.dim() == 4 and x.is_cuda and core.FLAGS.native and x.dtype == torch.bfloat16 and getattr(weight, "_fb_bf16", None) is not None
             and getattr(weight, "_fb_channels_last", False) and x.is_contiguous(memory_format=torch.channels_last)):
-        y = _Conv2dShadowFn.apply(x, weight, _pair(stride), _pair(padding), _pair(dilation), int(groups))
+        stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+        sums = None
+        if bn_stats and bias is None and torch.is_grad_enabled():
+            N, Ci, H, W = x.shape
+            Co, _, k, kw = weight.shape
+            if (dilation == (1, 1) and groups == 1 and k == kw and stride[0] == stride[1] and padding[0] == padding[1]
+                    and _ext.require().conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0])):
+                sums = core.zero_scratch(2 * Co, x.device)
+        y = _Conv2dShadowFn.apply(x, weight, stride, padding, dilation, int(groups), sums)
+        if sums is not None:
+            y._fb_bn_sums = sums.view(2, -1)
         return y if bias is None else y + bias.to(y.dtype).view(1, -1, 1, 1)
     C = _ext.load() if x.is_cuda else None
     if C is not None and core.FLAGS.native and hasattr(C, "conv2d_fwd"):

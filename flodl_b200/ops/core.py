@@ -54,6 +54,33 @@ def _launched(n: int = 1) -> None:
         FLAGS.launches += n
 
 
+# ------------------------------------------------------------------------------- zeroed scratch
+# Kernels that accumulate with atomics (the convolution's BatchNorm sums) need zeroed fp32 scratch.
+# One `torch.zeros` chunk serves many requests, so a step pays for one fill instead of one per layer.
+# A slice is handed out once and never again. A chunk made outside a CUDA-graph capture is not used
+# inside one (and vice versa): a graph must own the fill of everything it accumulates into, or a replay
+# would find the previous replay's sums.
+_ARENA = threading.local()
+_ARENA_FLOATS = 8192
+
+
+def reset_zero_arena() -> None:
+    _ARENA.state = None
+
+
+def zero_scratch(n: int, device) -> torch.Tensor:
+    """`n` zeroed fp32 elements on `device`, 128-byte aligned, valid for one use."""
+    capturing = torch.cuda.is_current_stream_capturing()
+    st = getattr(_ARENA, "state", None)
+    if st is None or st["capturing"] != capturing or st["device"] != device or st["off"] + n > st["buf"].numel():
+        st = {"buf": torch.zeros(max(_ARENA_FLOATS, n), device=device, dtype=torch.float32), "off": 0, "capturing": capturing, "device": device}
+        _ARENA.state = st
+        _launched()
+    out = st["buf"][st["off"]:st["off"] + n]
+    st["off"] += (n + 31) // 32 * 32
+    return out
+
+
 # ------------------------------------------------------------------------------------------ seeds
 _SEED = {"base": 0x5EED, "counter": 0, "dev": {}}
 

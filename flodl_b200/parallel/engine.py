@@ -226,8 +226,11 @@ class TrainEngine:
         self.sync.check()
         self._pre()
         g = torch.cuda.CUDAGraph()
+        from ..ops import core as _core
+        _core.reset_zero_arena()     # zeroed scratch used inside the graph must be allocated (and re-zeroed) by the graph itself
         with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
             self._static_loss = self._body(lambda: step_fn(*self._static_in))
+        _core.reset_zero_arena()
         self.steps += 1
         self._graph = g
 

@@ -3,6 +3,7 @@ import math
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 pytestmark = pytest.mark.gpu
 
@@ -358,7 +359,7 @@ def test_batchnorm_channels_last_many_blocks_accumulates(C):
 
 
 @pytest.mark.parametrize("N,Ci,Co,HW,k,stride", [(8, 16, 16, 32, 3, 1), (4, 16, 32, 32, 3, 2), (4, 32, 32, 16, 3, 1), (4, 32, 64, 16, 3, 2),
-                                                 (6, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 8, 16, 3, 1), (150, 16, 16, 32, 3, 1)])
+                                                 (6, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 8, 16, 3, 1), (150, 16, 16, 32, 3, 1), (2, 64, 16, 64, 3, 1)])
 def test_conv_wgrad_tensor_core(C, N, Ci, Co, HW, k, stride):
     torch.manual_seed(11)
     pad = k // 2
@@ -384,3 +385,76 @@ def test_conv_wgrad_rejects_unsupported(C):
     assert not C.conv_wgrad_supported(4, 32, 32, 3, 16, 3, 1, 1)       # 3 input channels: rows are not 16-byte multiples
     assert not C.conv_wgrad_supported(4, 32, 32, 16, 16, 5, 1, 2)      # 5x5
     assert not C.conv_wgrad_supported(4, 28, 28, 16, 16, 3, 1, 1)      # width not a power of two
+
+
+@pytest.mark.parametrize("N,Ci,Co,HW,k,stride", [(8, 16, 16, 32, 3, 1), (4, 16, 32, 32, 3, 2), (4, 32, 32, 16, 3, 1), (4, 32, 64, 16, 3, 2),
+                                                 (5, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 16, 16, 3, 1), (160, 16, 16, 32, 3, 1),
+                                                 (2, 64, 48, 64, 3, 1), (3, 16, 32, 28, 3, 1), (2, 32, 32, 7, 3, 1)])
+def test_conv_fprop_tensor_core(C, N, Ci, Co, HW, k, stride):
+    torch.manual_seed(12)
+    pad = k // 2
+    assert C.conv_fprop_supported(N, HW, HW, Ci, Co, k, stride, pad)
+    x = torch.randn(N, Ci, HW, HW, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(Co, Ci, k, k, device="cuda") * 0.1).bfloat16().contiguous(memory_format=torch.channels_last)
+    stats = torch.zeros(2, Co, device="cuda")
+    y = C.conv_fprop(x, w, stride, pad, stats)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0
+    ref = F.conv2d(x.float(), w.float(), None, stride, pad)
+    assert y.shape == ref.shape and y.is_contiguous(memory_format=torch.channels_last)
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 0.01, f"max err {err} (ref max {ref.abs().max().item()})"
+    # the fused statistics are those of the rounded output
+    yf = y.float()
+    s1, s2 = yf.sum((0, 2, 3)), (yf * yf).sum((0, 2, 3))
+    assert (stats[0] - s1).abs().max().item() <= 1e-3 * s1.abs().max().item() + 0.05
+    assert (stats[1] - s2).abs().max().item() <= 1e-3 * s2.abs().max().item() + 0.05
+    # without statistics
+    y2 = C.conv_fprop(x, w, stride, pad)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("N,Ci,Co,HW,k", [(8, 16, 16, 32, 3), (4, 32, 32, 16, 3), (5, 64, 64, 8, 3), (4, 16, 32, 32, 1), (2, 32, 16, 16, 3),
+                                          (2, 16, 64, 64, 3), (3, 32, 16, 28, 3), (2, 64, 32, 7, 3)])
+def test_conv_dgrad_tensor_core(C, N, Ci, Co, HW, k):
+    torch.manual_seed(13)
+    pad = k // 2
+    assert C.conv_dgrad_supported(N, HW, HW, Ci, Co, k, 1, pad)
+    dy = torch.randn(N, Co, HW, HW, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(Co, Ci, k, k, device="cuda") * 0.1).bfloat16().contiguous(memory_format=torch.channels_last)
+    dx = C.conv_dgrad(dy, w, 1, pad)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0
+    ref = torch.nn.grad.conv2d_input((N, Ci, HW, HW), w.float(), dy.float(), stride=1, padding=pad)
+    assert dx.shape == ref.shape and dx.is_contiguous(memory_format=torch.channels_last)
+    err = (dx.float() - ref).abs().max().item()
+    assert err <= 0.01 * ref.abs().max().item() + 0.01, f"max err {err} (ref max {ref.abs().max().item()})"
+
+
+def test_conv_fprop_dgrad_reject_unsupported(C):
+    assert not C.conv_fprop_supported(4, 32, 32, 3, 16, 3, 1, 1)       # 3-channel stem
+    assert not C.conv_fprop_supported(4, 28, 28, 16, 32, 3, 2, 1)      # strided, width not a power of two
+    assert not C.conv_fprop_supported(4, 4, 4, 32, 64, 3, 2, 1)        # strided, fewer than 64 output pixels per image
+    assert not C.conv_fprop_supported(4, 32, 32, 16, 16, 5, 1, 2)      # 5x5
+    assert not C.conv_dgrad_supported(4, 32, 32, 16, 32, 3, 2, 1)      # strided data gradient
+
+
+
+def test_bn_from_conv_sums_matches_stats_pass(C):
+    torch.manual_seed(14)
+    N, Ci, Co, HW = 16, 16, 32, 32
+    x = torch.randn(N, Ci, HW, HW, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(Co, Ci, 3, 3, device="cuda") * 0.1).bfloat16().contiguous(memory_format=torch.channels_last)
+    res = torch.randn(N, Co, HW, HW, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    gamma, beta = torch.rand(Co, device="cuda") + 0.5, torch.randn(Co, device="cuda")
+    sums = torch.zeros(2, Co, device="cuda")
+    y = C.conv_fprop(x, w, 1, 1, sums)
+    rm1, rv1 = torch.zeros(Co, device="cuda"), torch.ones(Co, device="cuda")
+    rm2, rv2 = rm1.clone(), rv1.clone()
+    o1, m1, r1 = C.bn_fwd(y, res, gamma, beta, rm1, rv1, 1e-5, 0.1, True, True)
+    o2, m2, r2 = C.bn_fwd(y, res, gamma, beta, rm2, rv2, 1e-5, 0.1, True, True, sums)
+    torch.cuda.synchronize()
+    assert (m1 - m2).abs().max().item() < 1e-4
+    assert ((r1 - r2).abs() / r1.abs()).max().item() < 1e-3
+    assert (rm1 - rm2).abs().max().item() < 1e-4 and (rv1 - rv2).abs().max().item() < 1e-3
+    assert (o1.float() - o2.float()).abs().max().item() <= 0.04
