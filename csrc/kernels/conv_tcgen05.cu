@@ -604,16 +604,33 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmW, const HaloParams p)
   if (warp < 4) {
     // ---------------------------------------------------------------- producers (cp.async)
     // Each warp loads whole tiles on its own (tile i of this CTA belongs to warp i % 4) and keeps two
-    // of them in flight, so eight tiles are on their way at any time. A warp publishes a tile after
+    // of them in flight, so up to eight tiles are on their way at any time. A warp publishes a tile after
     // its own copies have landed and a proxy fence has made them visible to the tensor core's
     // (async-proxy) reads.
     const int items = ((p.span + 7) / 8) * 8 * p.nch;       // the plane has room for the rounded-up pixels
     bool ok = true;
     int pending = -1;                        // stage of the tile whose copies are still in flight
+    // A parity wait can only tell "one phase behind" from "caught up", so a warp's successive tiles must
+    // not skip a whole turn of the ring: no more producer warps than stages.
+    const int nprod = p.stages < 4 ? p.stages : 4;
     int it = warp;
-    for (int tile = blockIdx.x + warp * gridDim.x; tile < p.tiles && ok; tile += 4 * gridDim.x, it += 4) {
+    for (int tile = blockIdx.x + warp * gridDim.x; warp < nprod && tile < p.tiles && ok; tile += nprod * gridDim.x, it += nprod) {
       const int s = it % p.stages;
-      ok = mbar_wait(&empty_bar[s], ((it / p.stages) & 1) ^ 1, abort_flag, p.status, kStatusWaitEmpty);
+      const uint32_t parity = ((it / p.stages) & 1) ^ 1;
+      if (pending >= 0) {
+        // Never hold back a finished tile while waiting for a stage: with a short ring the stage this
+        // warp wants next may only be released after the MMA warp has consumed the tile it has not
+        // published yet.
+        const bool ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_test(&empty_bar[s], parity)) : 0, 0) != 0;
+        if (!ready) {
+          cp_async_wait_group<0>();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[pending]);
+          pending = -1;
+        }
+      }
+      ok = mbar_wait(&empty_bar[s], parity, abort_flag, p.status, kStatusWaitEmpty);
       if (!ok) break;
       const uint32_t base = smem_u32(ring + s * p.a_bytes);
       const int q_first = tile * 128 - p.halo;
@@ -783,6 +800,236 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmW, const HaloParams p)
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Filter gradient of the 3x3, stride-1, "same" convolution in the same padded linear pixel space:
+//   dW[co][tap][ci] = sum over q of dYp[q][co] * Xp[q + shift(tap)][ci]
+// (dYp and Xp are zero at padding positions, so padding outputs add nothing). The reduction index is the
+// pixel, so both operands are "MN-major", and the per-8-channel planes [pixel][8 channels] are the
+// un-swizzled MN-major layout (8 pixels x 16 bytes per core matrix, 128 bytes between pixel groups, one
+// plane between channel groups).
+//
+// An MMA with M = 128 holds the tensor core for about 128 cycles whatever N is, so the kernel is bound by
+// the NUMBER of instructions: with one instruction per tap (N = Ci) a 128-pixel chunk needs 72. Here the
+// three horizontal taps are folded into N instead: the X tile is stored three times, shifted by -1, 0
+// and +1 pixel (planes [dx][channel group], all at one stride), so one instruction with N = 3 * Ci covers
+// a whole filter row and the row (dy) is picked by a start address shifted by +-(W+1) pixels: 24
+// instructions per chunk. The copies are cheap next to that: each 16-byte piece of X is fetched once
+// per plane through L1. M is 128 with Co real rows; planes Co/8 .. 15 of the A tile are zeros written
+// once. Accumulators (tap t in columns [t*Ci, (t+1)*Ci)) and the epilogue follow conv_wgrad_kernel; Ci = 64
+// (576 columns) stays with that kernel.
+struct WgHaloParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* dy;
+  float* dw;
+  int N, H, W, Ci, Co;
+  int pitch, img, q_total, chunks;
+  int span;                                    // pixels per B plane: 128 + 2 * (W + 1)
+  int a_planes, b_planes, a_log2, b_log2, b_plane_bytes, stage_bytes, stages, bars_off;
+  FastDiv div_img, div_pitch;
+  int* status;
+};
+
+constexpr int kWgAPlane = 128 * 16;          // bytes of one 8-channel plane of the 128-pixel dY chunk
+constexpr int kWgABytes = 16 * kWgAPlane;    // M = 128 = 16 planes
+
+__device__ __forceinline__ void cp_async16_ca_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// element offset of padded-linear pixel q (channel group c8) in an N-H-W-C tensor with C channels; *bytes
+// is 16 when q is a real pixel and 0 (zero fill) when it is padding or out of range. Branch-free.
+__device__ __forceinline__ uint32_t halo_off(int q, const WgHaloParams& p, int C, int c8, uint32_t* bytes) {
+  const uint32_t qc = static_cast<uint32_t>(min(max(q, 0), p.q_total - 1));
+  const uint32_t n = p.div_img.div(qc), r = qc - n * p.img;
+  const uint32_t h = p.div_pitch.div(r), w = r - h * p.pitch;
+  const bool valid = q >= 0 && q < p.q_total && h < static_cast<uint32_t>(p.H) && w < static_cast<uint32_t>(p.W);
+  *bytes = valid ? 16u : 0u;
+  return valid ? ((n * p.H + h) * p.W + w) * C + c8 * 8 : 0u;
+}
+
+__global__ void __launch_bounds__(kHaloThreads, 1)
+conv3x3_wgrad_halo_kernel(const WgHaloParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.bars_off);
+  uint64_t* empty_bar = full_bar + kHaloMaxStages;
+  uint64_t* acc_bar = empty_bar + kHaloMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc<1>(tmem_slot, 512);
+    tmem_relinquish<1>();
+  }
+  // planes Co/8 .. 15 of every stage's A tile stay zero for the kernel's lifetime
+  for (int s = 0; s < p.stages; ++s) {
+    uint4* z = reinterpret_cast<uint4*>(smem + s * p.stage_bytes + p.a_planes * kWgAPlane);
+    const int n16 = (16 - p.a_planes) * kWgAPlane / 16;
+    for (int i = threadIdx.x; i < n16; i += kHaloThreads) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  const int per_pass = (p.chunks - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+
+  if (warp < 4) {
+    // ---------------------------------------------------------------- producers (cp.async)
+    // as in conv3x3_halo_kernel: a warp per chunk, two chunks in flight per warp
+    const int a_items = 128 * p.a_planes;
+    const int span8 = (p.span + 7) / 8 * 8;
+    const int b_items = (span8 + 8) * p.b_planes;        // pixels -1 .. span8 + 6 of the tile: every plane's share
+    const uint32_t plane_set = static_cast<uint32_t>(p.b_planes * p.b_plane_bytes);   // the planes of one dx
+    bool ok = true;
+    {
+      int pending = -1;
+      // no more producer warps than stages (see conv3x3_halo_kernel)
+      const int nprod = p.stages < 4 ? p.stages : 4;
+      for (int j = warp; warp < nprod && j < per_pass && ok; j += nprod) {
+        const int it = j;
+        const int c = blockIdx.x + j * gridDim.x;
+        const int s = it % p.stages;
+        const uint32_t parity = ((it / p.stages) & 1) ^ 1;
+        if (pending >= 0) {     // see conv3x3_halo_kernel: publish before a wait that may depend on it
+          const bool ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_test(&empty_bar[s], parity)) : 0, 0) != 0;
+          if (!ready) {
+            cp_async_wait_group<0>();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_bar[pending]);
+            pending = -1;
+          }
+        }
+        ok = mbar_wait(&empty_bar[s], parity, abort_flag, p.status, kStatusWaitEmpty);
+        if (!ok) break;
+        const uint32_t a_base = smem_u32(smem + s * p.stage_bytes), b_base = a_base + kWgABytes;
+        const int q0 = c * 128;
+#pragma unroll 4
+        for (int i = lane; i < a_items; i += 32) {
+          const int c8 = (i >> 3) & (p.a_planes - 1), pix = ((i >> (3 + p.a_log2)) << 3) + (i & 7);
+          uint32_t bytes;
+          const uint32_t off = halo_off(q0 + pix, p, p.Co, c8, &bytes);
+          cp_async16_zfill(a_base + c8 * kWgAPlane + pix * 16, p.dy + off, bytes);
+        }
+        // plane set dx holds X shifted by dx - 1 pixels: index u of set dx is pixel q0 - pitch + u + dx - 1,
+        // so the piece of pixel q0 - pitch - 1 + v goes to index v, v - 1, v - 2 of sets 0, 1, 2
+#pragma unroll 2
+        for (int i = lane; i < b_items; i += 32) {
+          const int c8 = (i >> 3) & (p.b_planes - 1), v = ((i >> (3 + p.b_log2)) << 3) + (i & 7);
+          uint32_t bytes;
+          const uint32_t off = halo_off(q0 - p.pitch - 1 + v, p, p.Ci, c8, &bytes);
+          const uint32_t dst = b_base + c8 * p.b_plane_bytes + v * 16;
+          if (v < span8) cp_async16_ca_zfill(dst, p.x + off, bytes);
+          if (v >= 1 && v - 1 < span8) cp_async16_ca_zfill(dst + plane_set - 16, p.x + off, bytes);
+          if (v >= 2 && v - 2 < span8) cp_async16_ca_zfill(dst + 2 * plane_set - 32, p.x + off, bytes);
+        }
+        cp_async_commit();
+        if (pending >= 0) {
+          cp_async_wait_group<1>();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[pending]);
+        }
+        pending = s;
+      }
+      cp_async_wait_group<0>();
+      if (pending >= 0 && ok) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_bar[pending]);
+      }
+    }
+  } else if (warp == 4) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, 3 * p.Ci, 1, 1);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      {
+        bool first = true;
+        for (int j = 0; j < per_pass && ok; ++j) {
+          ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kStatusWaitFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(smem + s * p.stage_bytes);
+          const uint64_t da0 = conv_desc(a_base, 128, kWgAPlane, 0);
+          // index u of a plane is pixel q0 - pitch + u (+ dx - 1): row dy of the filter starts at u = dy * pitch
+          const uint64_t db0 = conv_desc(a_base + kWgABytes, 128, p.b_plane_bytes, 0);
+          // pixel group outermost, filter row innermost: consecutive instructions go to different accumulators
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t acc = (first && ks == 0) ? 0u : 1u;
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr)
+              umma_bf16<1>(tmem_base + rr * 3 * p.Ci, da0 + ks * 16, db0 + static_cast<uint64_t>(rr * p.pitch + ks * 16), idesc, acc);
+          }
+          first = false;
+          umma_commit(&empty_bar[s]);
+          if (++s == p.stages) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(acc_bar);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue warps
+    const int q4 = warp & 3;
+    const int co = q4 * 32 + lane;
+    float* stage = reinterpret_cast<float*>(smem);
+    bool ok = mbar_wait(acc_bar, 0, abort_flag, p.status, kStatusWaitAccum);
+    if (ok) {
+      tc_fence_after_sync();
+      const int t0 = 0, nt = 9;
+      const int row_floats = nt * p.Ci;
+      if (q4 * 32 < p.Co) {
+        for (int col = 0; col < row_floats; col += 16) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + (static_cast<uint32_t>(q4 * 32) << 16) + col, v);
+          tmem_ld_wait();
+          if (co < p.Co) {
+            float4* dst = reinterpret_cast<float4*>(stage + static_cast<size_t>(co) * row_floats + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                   __uint_as_float(v[4 * j + 3]));
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (co < p.Co) {
+          bulk_reduce_add_f32(p.dw + (static_cast<size_t>(co) * 9 + t0) * p.Ci, stage + static_cast<size_t>(co) * row_floats,
+                              static_cast<uint32_t>(row_floats * 4));
+          tma_store_commit();
+        }
+      }
+      tc_fence_before_sync();
+    }
+    tma_store_wait_all();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -818,8 +1065,77 @@ int make_tmap_nhwc(CUtensorMap* out, const void* base, int N, int H, int W, int 
 }  // namespace
 }  // namespace fb
 
+namespace fb {
+namespace {
+int launch_wgrad_halo(const void* x, const void* dy, float* dw, int N, int H, int W, int Ci, int Co, int* status, void* stream) {
+  WgHaloParams p;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.dy = static_cast<const __nv_bfloat16*>(dy);
+  p.dw = dw;
+  p.N = N; p.H = H; p.W = W; p.Ci = Ci; p.Co = Co;
+  p.pitch = W + 1;
+  p.img = (H + 1) * (W + 1);
+  const long long qt = static_cast<long long>(N) * p.img;
+  if (qt > (1LL << 30)) return -4;
+  if (static_cast<long long>(N) * H * W * (Ci > Co ? Ci : Co) >= (1LL << 31)) return -4;   // 32-bit element offsets
+  p.q_total = static_cast<int>(qt);
+  p.chunks = (p.q_total + 127) / 128;
+  p.span = 128 + 2 * p.pitch;
+  p.a_planes = Co / 8;
+  p.b_planes = Ci / 8;
+  p.a_log2 = p.a_planes == 1 ? 0 : p.a_planes == 2 ? 1 : p.a_planes == 4 ? 2 : 3;
+  p.b_log2 = p.b_planes == 2 ? 1 : p.b_planes == 4 ? 2 : 3;
+  p.div_img = make_fastdiv(p.img);
+  p.div_pitch = make_fastdiv(p.pitch);
+  p.b_plane_bytes = (p.span + 7) / 8 * 8 * 16;
+  p.stage_bytes = (kWgABytes + 3 * p.b_planes * p.b_plane_bytes + 1023) / 1024 * 1024;
+  p.stages = (196 * 1024) / p.stage_bytes;
+  if (p.stages > kHaloMaxStages) p.stages = kHaloMaxStages;
+  if (p.stages < 2) return -4;
+  const int staging = Co * 9 * Ci * 4;
+  int ring = p.stages * p.stage_bytes;
+  if (ring < staging) ring = (staging + 1023) / 1024 * 1024;
+  p.bars_off = ring;
+  p.status = status;
+  const int smem = p.bars_off + 512 + 1024;
+  if (smem > 220 * 1024) return -4;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(conv3x3_wgrad_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  int grid = p.chunks / 2;       // at least two chunks per CTA amortise the epilogue's reduce-add
+  if (grid > 148) grid = 148;
+  if (grid < 1) grid = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kHaloThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = 0;
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 1;
+  }
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, conv3x3_wgrad_halo_kernel, p));
+}
+bool wgrad_halo_ok(int H, int W, int Ci, int Co, int k, int stride, int pad) {
+  if (!(k == 3 && stride == 1 && pad == 1 && (Ci == 16 || Ci == 32) && (Co == 8 || Co == 16 || Co == 32 || Co == 64) && W >= 2 && H >= 1))
+    return false;     // Ci = 64 would need 576 accumulator columns: conv_wgrad_kernel's two passes take it
+  // two pipeline stages must fit (launch_wgrad_halo's layout)
+  const int plane = (128 + 2 * (W + 1) + 7) / 8 * 8 * 16;
+  return 2 * (kWgABytes + 3 * (Ci / 8) * plane + 1023) <= 196 * 1024;
+}
+}  // namespace
+}  // namespace fb
+
 // 1 when fb_conv_wgrad covers the problem, else 0 (the caller then uses the library convolution).
 extern "C" int fb_conv_wgrad_supported(int N, int H, int W, int Ci, int Co, int kh, int kw, int stride, int pad) {
+  if (N > 0 && kh == kw && fb::wgrad_halo_ok(H, W, Ci, Co, kh, stride, pad)) return 1;
   if (kh != kw || (kh != 1 && kh != 3) || (stride != 1 && stride != 2)) return 0;
   if (pad != (kh == 3 ? 1 : 0)) return 0;
   if ((Ci != 16 && Ci != 32 && Ci != 64) || Co % 8 || Co < 8 || Co > 64) return 0;
@@ -838,6 +1154,7 @@ extern "C" int fb_conv_wgrad(const void* x, const void* dy, float* dw, int N, in
   using namespace fb;
   if (!fb_conv_wgrad_supported(N, H, W, Ci, Co, kh, kw, stride, pad)) return -4;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(dw) & 15)) return -3;
+  if (kh == kw && wgrad_halo_ok(H, W, Ci, Co, kh, stride, pad)) return launch_wgrad_halo(x, dy, dw, N, H, W, Ci, Co, status, stream);
   WgradParams p;
   p.N = N; p.Ci = Ci; p.Co = Co; p.kh = kh; p.kw = kw; p.stride = stride; p.pad = pad;
   p.Ho = (H + 2 * pad - kh) / stride + 1;

@@ -359,7 +359,7 @@ def test_batchnorm_channels_last_many_blocks_accumulates(C):
 
 
 @pytest.mark.parametrize("N,Ci,Co,HW,k,stride", [(8, 16, 16, 32, 3, 1), (4, 16, 32, 32, 3, 2), (4, 32, 32, 16, 3, 1), (4, 32, 64, 16, 3, 2),
-                                                 (6, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 8, 16, 3, 1), (150, 16, 16, 32, 3, 1), (2, 64, 16, 64, 3, 1)])
+                                                 (6, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 8, 16, 3, 1), (150, 16, 16, 32, 3, 1), (2, 64, 16, 64, 3, 1), (3, 16, 32, 28, 3, 1), (2, 32, 64, 7, 3, 1), (300, 32, 32, 16, 3, 1)])
 def test_conv_wgrad_tensor_core(C, N, Ci, Co, HW, k, stride):
     torch.manual_seed(11)
     pad = k // 2
@@ -384,12 +384,12 @@ def test_conv_wgrad_tensor_core(C, N, Ci, Co, HW, k, stride):
 def test_conv_wgrad_rejects_unsupported(C):
     assert not C.conv_wgrad_supported(4, 32, 32, 3, 16, 3, 1, 1)       # 3 input channels: rows are not 16-byte multiples
     assert not C.conv_wgrad_supported(4, 32, 32, 16, 16, 5, 1, 2)      # 5x5
-    assert not C.conv_wgrad_supported(4, 28, 28, 16, 16, 3, 1, 1)      # width not a power of two
+    assert not C.conv_wgrad_supported(4, 28, 28, 16, 16, 3, 2, 1)      # strided, width not a power of two
 
 
 @pytest.mark.parametrize("N,Ci,Co,HW,k,stride", [(8, 16, 16, 32, 3, 1), (4, 16, 32, 32, 3, 2), (4, 32, 32, 16, 3, 1), (4, 32, 64, 16, 3, 2),
                                                  (5, 64, 64, 8, 3, 1), (4, 16, 32, 32, 1, 2), (2, 32, 16, 16, 3, 1), (160, 16, 16, 32, 3, 1),
-                                                 (2, 64, 48, 64, 3, 1), (3, 16, 32, 28, 3, 1), (2, 32, 32, 7, 3, 1)])
+                                                 (2, 64, 48, 64, 3, 1), (3, 16, 32, 28, 3, 1), (2, 32, 32, 7, 3, 1), (12, 64, 64, 64, 3, 1)])
 def test_conv_fprop_tensor_core(C, N, Ci, Co, HW, k, stride):
     torch.manual_seed(12)
     pad = k // 2
@@ -415,7 +415,7 @@ def test_conv_fprop_tensor_core(C, N, Ci, Co, HW, k, stride):
 
 
 @pytest.mark.parametrize("N,Ci,Co,HW,k", [(8, 16, 16, 32, 3), (4, 32, 32, 16, 3), (5, 64, 64, 8, 3), (4, 16, 32, 32, 1), (2, 32, 16, 16, 3),
-                                          (2, 16, 64, 64, 3), (3, 32, 16, 28, 3), (2, 64, 32, 7, 3)])
+                                          (2, 16, 64, 64, 3), (3, 32, 16, 28, 3), (2, 64, 32, 7, 3), (12, 64, 64, 64, 3)])
 def test_conv_dgrad_tensor_core(C, N, Ci, Co, HW, k):
     torch.manual_seed(13)
     pad = k // 2
