@@ -8,6 +8,14 @@ ranks. Bus bandwidth = 2 (W-1)/W * bytes / time; roofline = the measured NVLink 
 (770 GB/s per direction per GPU). The NCCL columns are the reference's path: `flat` = one
 all-reduce over the same flat buffer, `per_tensor_25MB` = the same bytes as 25 MB chunks in one
 group (flodl-sys/ops_cuda.cpp:496-537). Rank 0 prints one JSON line per size and a final summary line.
+
+`--also param_average,broadcast` adds the two other collectives of the training loops:
+  * parameter averaging of Local SGD over P fp32 parameters (52 M = the decoder LM, 110 M = BERT-base):
+    the fused kernel (peer reduce + lerp + bf16 shadow + divergence sums, one launch) against the
+    reference's sequence (copy to scratch, ncclAllReduce(Avg), three foreach norm passes;
+    flodl/src/distributed/ddp_run/worker.rs:515-584);
+  * parameter broadcast from rank 0 (time-to-sync at start-up) and the per-step buffer broadcast:
+    one pull kernel over the flat buffer against one ncclBroadcast per tensor (flodl/src/distributed/ddp.rs:150-167).
 """
 from __future__ import annotations
 
@@ -41,11 +49,72 @@ def timed(fn, iters, dev):
     return float(t.item())
 
 
+def bench_param_average(buf, max_bytes, iters, dev, rank, world):
+    """W = world ranks average P fp32 parameters in place (alpha = 1) and get the two divergence sums."""
+    for name, P in (("decoder-lm", 52_000_000), ("bert-base", 110_000_000)):
+        if P * 4 > max_bytes:
+            continue
+        stage = comm.SymmetricBuffer(P * 4, timeout_s=10.0)
+        params = buf.view(torch.float32, 0, P)
+        params.copy_(torch.randn(P, device=dev) * 0.02)
+        shadow = torch.empty(P, device=dev, dtype=torch.bfloat16)
+        per_blocks = {nb: timed(lambda: buf.comm.param_average(stage.comm, P, None, 1.0, shadow, nb), max(5, iters // 2), dev) for nb in (32, 64, 128)}
+        ms_ours = min(per_blocks.values())
+        buf.check()
+        # the reference's sequence on a plain tensor of the same size
+        p2 = torch.randn(P, device=dev) * 0.02
+        chunks = list(p2.split(P // 200))          # ~200 parameter tensors
+
+        def reference():
+            pre = [c.clone() for c in chunks]
+            with dist._coalescing_manager(device=dev):
+                for c in chunks:
+                    dist.all_reduce(c, dist.ReduceOp.AVG)
+            diff = torch._foreach_sub(chunks, pre)
+            d2 = torch.stack(torch._foreach_norm(diff)).pow(2).sum()
+            n2 = torch.stack(torch._foreach_norm(chunks)).pow(2).sum()
+            shadow.copy_(p2)
+            return d2, n2
+        ms_ref = timed(reference, max(5, iters // 2), dev)
+        stage.close()
+        if rank == 0:
+            print(json.dumps({"collective": "param_average", "model": name, "params": P, "world": world, "ours_fused_us": round(ms_ours * 1e3, 1),
+                              "ours_us_by_blocks": {str(k): round(v * 1e3, 1) for k, v in per_blocks.items()}, "reference_sequence_us": round(ms_ref * 1e3, 1), "speedup": round(ms_ref / ms_ours, 3),
+                              "ours_bus_GBs": round(2 * (world - 1) / world * P * 4 / (ms_ours * 1e-3) / 1e9, 1)}), flush=True)
+
+
+def bench_broadcast(buf, max_bytes, iters, dev, rank, world):
+    """Rank 0's flat buffer to every rank: all parameters once (start-up), BatchNorm buffers every step."""
+    for name, nbytes, ntensors in (("resnet20 BN buffers", 11_000, 42), ("decoder-lm params", 208_000_000, 80), ("bert-base params", 440_000_000, 200)):
+        if nbytes > max_bytes:
+            continue
+        nbytes = nbytes // 16 * 16
+        ms_ours = min(timed(lambda: buf.broadcast(0, nbytes, 0, nb), max(5, iters // 2), dev) for nb in ((32, 96) if nbytes > (1 << 20) else (1,)))
+        buf.check()
+        t = torch.randn(nbytes // 4, device=dev)
+        parts = list(t.split(max(1, t.numel() // ntensors)))
+
+        def reference():
+            with dist._coalescing_manager(device=dev):
+                for c in parts:
+                    dist.broadcast(c, 0)
+        try:
+            ms_ref = timed(reference, max(5, iters // 2), dev)
+        except Exception:       # coalesced broadcast is not available in every torch build
+            ms_ref = timed(lambda: [dist.broadcast(c, 0) for c in parts], max(5, iters // 2), dev)
+        if rank == 0:
+            print(json.dumps({"collective": "broadcast", "what": name, "bytes": nbytes, "tensors": len(parts), "world": world,
+                              "ours_pull_kernel_us": round(ms_ours * 1e3, 1), "nccl_per_tensor_us": round(ms_ref * 1e3, 1),
+                              "speedup": round(ms_ref / ms_ours, 3), "ours_GBs_per_rank": round(nbytes / (ms_ours * 1e-3) / 1e9, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--also", default="", help="comma-separated extras: param_average, broadcast")
+    ap.add_argument("--skip-sweep", action="store_true", help="only run the --also benchmarks")
     args = ap.parse_args()
     comm.init_process_group()
     rank, world = comm.rank(), comm.world_size()
@@ -54,7 +123,7 @@ def main():
     max_bytes = args.max_mb << 20
     buf = comm.SymmetricBuffer(max_bytes, timeout_s=10.0)
     results = []
-    for dtype in (torch.float32, torch.bfloat16):
+    for dtype in (() if args.skip_sweep else (torch.float32, torch.bfloat16)):
         esz = 4 if dtype == torch.float32 else 2
         nbytes = 1024
         while nbytes <= max_bytes:
@@ -91,7 +160,12 @@ def main():
             if rank == 0:
                 print(json.dumps(row), flush=True)
             nbytes *= 2
-    if rank == 0:
+    extras = [e for e in args.also.split(",") if e]
+    if "param_average" in extras:
+        bench_param_average(buf, max_bytes, args.iters, dev, rank, world)
+    if "broadcast" in extras:
+        bench_broadcast(buf, max_bytes, args.iters, dev, rank, world)
+    if rank == 0 and results:
         big = [r for r in results if r["bytes"] >= (64 << 20)]
         print(json.dumps({"summary": True, "world": world, "peak_ours_bus_GBs": max(r["ours_bus_GBs"] for r in results),
                           "peak_nccl_bus_GBs": max(r["nccl_bus_GBs"] for r in results),

@@ -260,22 +260,36 @@ param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float a
     {
       const long long v0 = per * c.rank;
       const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
-      for (long long i = v0 + tid; i < v1; i += stride) {
-        uint4 raw[W];
+      // U * W independent 16-byte peer loads in flight per thread (see the all-reduce kernel)
+      constexpr int U = (W <= 2) ? 8 : (W <= 4 ? 4 : 2);
+      for (long long i0 = v0 + tid; i0 < v1; i0 += stride * U) {
+        uint4 raw[U][W];
 #pragma unroll
-        for (int p = 0; p < W; ++p) raw[p] = ld_peer(static_cast<const char*>(c.data[(c.rank + p) % W]) + i * 16);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < v1) {
 #pragma unroll
-        for (int p = 0; p < W; ++p) {
-          float v[4];
-          Pack<float>::to_f(raw[p], v);
-          const float w = wts.w[(c.rank + p) % W];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[j] += v[j] * w;
+            for (int p = 0; p < W; ++p) raw[u][p] = ld_peer(static_cast<const char*>(c.data[(c.rank + p) % W]) + i * 16);
+          }
         }
-        const uint4 o = Pack<float>::from_f(acc);
 #pragma unroll
-        for (int p = 0; p < W; ++p) st_peer(static_cast<char*>(stage.data[(c.rank + p) % W]) + i * 16, o);
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < v1) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int p = 0; p < W; ++p) {
+              float v[4];
+              Pack<float>::to_f(raw[u][p], v);
+              const float w = wts.w[(c.rank + p) % W];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[j] += v[j] * w;
+            }
+            const uint4 o = Pack<float>::from_f(acc);
+#pragma unroll
+            for (int p = 0; p < W; ++p) st_peer(static_cast<char*>(stage.data[(c.rank + p) % W]) + i * 16, o);
+          }
+        }
       }
     }
     if (symm_block_barrier(c, epoch, &sh_fail)) {
@@ -286,21 +300,37 @@ param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float a
       for (int s = 0; s < W; ++s) {
         const long long v0 = per * s;
         const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
-        for (long long i = v0 + tid; i < v1; i += stride) {
-          float avg[4], old[4], nw[4];
-          Pack<float>::to_f(ld_peer(st_local + i * 16), avg);
-          Pack<float>::to_f(*reinterpret_cast<const uint4*>(w_local + i * 4), old);
+        constexpr int U2 = 4;
+        for (long long i0 = v0 + tid; i0 < v1; i0 += stride * U2) {
+          uint4 ra[U2], ro[U2];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            nw[j] = old[j] + alpha * (avg[j] - old[j]);
-            const float d = nw[j] - old[j];
-            d2 += d * d;
-            n2 += nw[j] * nw[j];
+          for (int u = 0; u < U2; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < v1) {
+              ra[u] = ld_peer(st_local + i * 16);
+              ro[u] = *reinterpret_cast<const uint4*>(w_local + i * 4);
+            }
           }
-          *reinterpret_cast<uint4*>(w_local + i * 4) = Pack<float>::from_f(nw);
-          if (p16) {
-            __nv_bfloat162 h[2] = {__floats2bfloat162_rn(nw[0], nw[1]), __floats2bfloat162_rn(nw[2], nw[3])};
-            *reinterpret_cast<uint2*>(p16 + i * 4) = *reinterpret_cast<uint2*>(h);
+#pragma unroll
+          for (int u = 0; u < U2; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < v1) {
+              float avg[4], old[4], nw[4];
+              Pack<float>::to_f(ra[u], avg);
+              Pack<float>::to_f(ro[u], old);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                nw[j] = old[j] + alpha * (avg[j] - old[j]);
+                const float d = nw[j] - old[j];
+                d2 += d * d;
+                n2 += nw[j] * nw[j];
+              }
+              *reinterpret_cast<uint4*>(w_local + i * 4) = Pack<float>::from_f(nw);
+              if (p16) {
+                __nv_bfloat162 h[2] = {__floats2bfloat162_rn(nw[0], nw[1]), __floats2bfloat162_rn(nw[2], nw[3])};
+                *reinterpret_cast<uint2*>(p16 + i * 4) = *reinterpret_cast<uint2*>(h);
+              }
+            }
           }
         }
       }
@@ -348,8 +378,16 @@ broadcast_kernel(SymmCtx c, long long byte_off, long long nbytes, int root) {
       const char* src = static_cast<const char*>(c.data[root]) + byte_off;
       char* dst = static_cast<char*>(c.data[c.rank]) + byte_off;
       const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-      for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride)
-        *reinterpret_cast<uint4*>(dst + i * 16) = ld_peer(src + i * 16);
+      constexpr int U = 8;      // independent peer loads in flight per thread
+      for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < nvec) raw[u] = ld_peer(src + (i0 + u * stride) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < nvec) *reinterpret_cast<uint4*>(dst + (i0 + u * stride) * 16) = raw[u];
+      }
     }
     symm_block_barrier(c, epoch, &sh_fail);
   }

@@ -294,7 +294,7 @@ class DistributedState:
         if self.world_size <= 1:
             return
         if self.symm_params is not None:
-            self.symm_params.broadcast(0, self.flat.total * 4, root, 32)
+            self.symm_params.broadcast(0, self.flat.total * 4, root, 96)
             torch.cuda.synchronize()
             self.symm_params.check()
         else:
