@@ -1,0 +1,127 @@
+"""Run the benchmark suite and print one JSON line per (model, implementation), then a comparison table.
+
+    python -m benchmarks.run [--models mlp,convnet] [--impl flodl,torch] [--device cuda] [--rounds 1]
+                             [--quick] [--out report.md]
+
+`--rounds N` interleaves the implementations N times and keeps each one's best round (the reference's
+run.sh does the same to cancel drift; it also locks the GPU clocks, which this runner never does: it
+reads and reports them instead)."""
+from __future__ import annotations
+
+import argparse
+import json
+import subprocess
+import sys
+from typing import Dict, List
+
+import torch
+
+from flodl_b200 import nn
+from flodl_b200.autograd import Variable
+
+from .harness import BenchConfig, BenchResult, run_benchmark
+from .models import MODELS, TIER1, TIER2
+
+
+def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0) -> BenchResult:
+    build, cfg = MODELS[name]
+    if quick:
+        cfg = cfg.quick()
+    torch.manual_seed(seed)
+    dev = torch.device(device)
+    model, make_batch, loss_kind, lr = build(cfg, impl, dev, 8 if quick else 1)
+    gen = torch.Generator().manual_seed(seed + 1)
+    batches = [make_batch(dev, gen) for _ in range(cfg.batches_per_epoch)]
+    if impl == "flodl":
+        model.train()
+        params = model.parameters()
+        count = sum(p.t.numel() for p in params)
+        opt = nn.Adam(params, lr)
+
+        def epoch(_i, _warm):
+            total = 0.0
+            for x, y in batches:
+                pred = model.forward(Variable.wrap(x))
+                if loss_kind == "ce":
+                    loss = nn.cross_entropy_loss(pred.reshape([-1, pred.t.shape[-1]]), Variable.wrap(y.reshape(-1)))
+                else:
+                    loss = nn.mse_loss(pred, Variable.wrap(y))
+                opt.zero_grad()
+                loss.backward()
+                opt.step()
+                total += loss.item()
+            return total / len(batches)
+    else:
+        model.train()
+        count = sum(p.numel() for p in model.parameters())
+        opt = torch.optim.Adam(model.parameters(), lr=lr)
+
+        def epoch(_i, _warm):
+            total = 0.0
+            for x, y in batches:
+                pred = model(x)
+                loss = (torch.nn.functional.cross_entropy(pred.reshape(-1, pred.shape[-1]), y.reshape(-1)) if loss_kind == "ce"
+                        else torch.nn.functional.mse_loss(pred, y))
+                opt.zero_grad(set_to_none=True)
+                loss.backward()
+                opt.step()
+                total += loss.item()
+            return total / len(batches)
+    return run_benchmark(cfg, impl, count, epoch, dev)
+
+
+def gpu_clocks() -> str:
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.active", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=10).stdout.strip().splitlines()
+        return out[0] if out else "n/a"
+    except Exception:
+        return "n/a"
+
+
+def report(results: Dict[str, Dict[str, BenchResult]]) -> str:
+    lines = ["| model | params | flodl_b200 ms/epoch | PyTorch ms/epoch | speed-up | flodl_b200 peak MB | PyTorch peak MB |", "|---|---|---|---|---|---|---|"]
+    for name, by in results.items():
+        a, b = by.get("flodl"), by.get("torch")
+        fmt = lambda r, f: "-" if r is None or f(r) is None else f"{f(r):.1f}"
+        ratio = "-" if a is None or b is None else f"{b.median_epoch_ms / a.median_epoch_ms:.2f}x"
+        lines.append(f"| {name} | {(a or b).param_count} | {fmt(a, lambda r: r.median_epoch_ms)} | {fmt(b, lambda r: r.median_epoch_ms)} | {ratio} | "
+                     f"{fmt(a, lambda r: r.peak_vram_mb)} | {fmt(b, lambda r: r.peak_vram_mb)} |")
+    return "\n".join(lines)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="benchmarks.run")
+    ap.add_argument("--models", default="all", help="comma list, or all / tier1 / tier2")
+    ap.add_argument("--impl", default="flodl,torch")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--rounds", type=int, default=1)
+    ap.add_argument("--quick", action="store_true", help="tiny shapes and two epochs: a smoke test, not a measurement")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args(argv)
+    names = {"all": TIER1 + TIER2, "tier1": TIER1, "tier2": TIER2}.get(args.models) or [m for m in args.models.split(",") if m]
+    impls = [i for i in args.impl.split(",") if i]
+    for n in names:
+        if n not in MODELS:
+            print(f"unknown model {n!r}; known: {', '.join(MODELS)}", file=sys.stderr)
+            return 2
+    best: Dict[str, Dict[str, BenchResult]] = {n: {} for n in names}
+    for _round in range(max(1, args.rounds)):
+        for n in names:
+            for impl in impls:           # interleaved: flodl, torch, flodl, torch, ...
+                r = run_model(n, impl, args.device, args.quick)
+                print(r.json(), flush=True)
+                if impl not in best[n] or r.median_epoch_ms < best[n][impl].median_epoch_ms:
+                    best[n][impl] = r
+    table = report(best)
+    head = f"device {args.device}; clocks (sm, max, reasons): {gpu_clocks()}; rounds {args.rounds}{'; QUICK MODE' if args.quick else ''}"
+    print(head)
+    print(table)
+    if args.out:
+        with open(args.out, "w") as f:
+            f.write(head + "\n\n" + table + "\n")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

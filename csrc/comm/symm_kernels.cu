@@ -365,31 +365,58 @@ param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float a
 }
 
 // ---------------------------------------------------------------------------------------------
-// broadcast: every rank != root pulls the root's bytes
+// broadcast from `root`
 // ---------------------------------------------------------------------------------------------
+// Two ranks (or a message too small to matter): every other rank pulls the root's bytes. More ranks:
+// the root's NVLink egress would be shared by W-1 pullers, so the message is cut in W shards; rank r
+// first pulls shard r from the root (the root sends each byte once), then every rank pulls the other
+// shards from their owners, which spreads that traffic over all links (scatter + all-gather).
+// Block b of every rank copies the same element set of a shard, so the per-block barrier between the
+// phases is enough.
+__device__ __forceinline__ void pull_range(const char* src, char* dst, long long v0, long long v1, long long tid, long long stride) {
+  constexpr int U = 8;      // independent peer loads in flight per thread
+  for (long long i0 = v0 + tid; i0 < v1; i0 += stride * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i0 + u * stride < v1) raw[u] = ld_peer(src + (i0 + u * stride) * 16);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i0 + u * stride < v1) *reinterpret_cast<uint4*>(dst + (i0 + u * stride) * 16) = raw[u];
+  }
+}
+
 __global__ void __launch_bounds__(512)
 broadcast_kernel(SymmCtx c, long long byte_off, long long nbytes, int root) {
   __shared__ int sh_fail;
   if (threadIdx.x == 0) sh_fail = 0;
   uint32_t epoch = c.epochs[blockIdx.x];
+  const long long nvec = nbytes / 16;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  char* dst = static_cast<char*>(c.data[c.rank]) + byte_off;
+  const bool sharded = c.world > 2 && nbytes >= (1 << 20);
   if (symm_block_barrier(c, epoch, &sh_fail)) {
-    if (c.rank != root) {
-      const long long nvec = nbytes / 16;
-      const char* src = static_cast<const char*>(c.data[root]) + byte_off;
-      char* dst = static_cast<char*>(c.data[c.rank]) + byte_off;
-      const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-      constexpr int U = 8;      // independent peer loads in flight per thread
-      for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
-        uint4 raw[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (i0 + u * stride < nvec) raw[u] = ld_peer(src + (i0 + u * stride) * 16);
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (i0 + u * stride < nvec) *reinterpret_cast<uint4*>(dst + (i0 + u * stride) * 16) = raw[u];
+    if (!sharded) {
+      if (c.rank != root) pull_range(static_cast<const char*>(c.data[root]) + byte_off, dst, 0, nvec, tid, stride);
+      symm_block_barrier(c, epoch, &sh_fail);
+    } else {
+      const long long per = (nvec + c.world - 1) / c.world;
+      if (c.rank != root) {
+        const long long v0 = per * c.rank, v1 = (v0 + per < nvec) ? v0 + per : nvec;
+        pull_range(static_cast<const char*>(c.data[root]) + byte_off, dst, v0, v1, tid, stride);
+      }
+      if (symm_block_barrier(c, epoch, &sh_fail)) {
+        if (c.rank != root) {
+          for (int k = 1; k < c.world; ++k) {
+            const int s = (c.rank + k) % c.world;       // staggered so the owners are not all hit in the same order
+            const long long v0 = per * s, v1 = (v0 + per < nvec) ? v0 + per : nvec;
+            pull_range(static_cast<const char*>(c.data[s]) + byte_off, dst, v0, v1, tid, stride);
+          }
+        }
+        symm_block_barrier(c, epoch, &sh_fail);
       }
     }
-    symm_block_barrier(c, epoch, &sh_fail);
   }
   if (threadIdx.x == 0) c.epochs[blockIdx.x] = epoch;
 }

@@ -180,6 +180,10 @@ class Graph(Module, TreeMixin, ObserveMixin, ProfileMixin, RenderMixin, Distribu
     def sub_modules(self) -> List[Module]:
         return [n.module for n in self.nodes if n.module is not None]
 
+    def as_loop_body(self):
+        # `step()` on a graph is the distributed training step, not the loop-body protocol
+        return None
+
     def forward(self, x) -> Variable:
         if self.is_distributed():
             return self.forward_distributed(x)

@@ -25,8 +25,12 @@ from .flat import FlatParams
 
 class GradSync:
     def __init__(self, flat: FlatParams, symm: Optional[_comm.SymmetricBuffer], bucket_bytes: int = 25 * 1024 * 1024,
-                 overlap: bool = True, blocks: int = 24, backend: str = "symm", world: Optional[int] = None):
+                 overlap: bool = True, blocks: int = 24, backend: str = "symm", world: Optional[int] = None, tail_blocks: int = 96):
         self.flat, self.symm, self.blocks = flat, symm, blocks
+        # The last bucket of a step (and anything launched after backward has ended) has no compute
+        # left to overlap with, so it may use most of the GPU instead of the few blocks that keep the
+        # overlapped buckets out of the GEMMs' way.
+        self.tail_blocks = max(int(tail_blocks), int(blocks))
         self.world = _comm.world_size() if world is None else int(world)   # world=1: no gradient exchange (Local SGD)
         self.backend = backend if self.world > 1 else "none"
         self.overlap = overlap and self.world > 1
@@ -84,9 +88,10 @@ class GradSync:
             if self.pending[bi] == 0 and not self.launched[bi]:
                 self._launch(bi)
 
-    def _launch(self, bi: int) -> None:
+    def _launch(self, bi: int, tail: bool = False) -> None:
         b = self.buckets[bi]
         self.launched[bi] = True
+        tail = tail or all(self.launched)     # the last one out
         if self.stream is None:               # CPU replicas (gloo): reduce in line
             self._reduce_range(b["start"], b["end"])
             self.launch_count += 1
@@ -96,13 +101,13 @@ class GradSync:
         ev.record(cur)
         self.stream.wait_event(ev)
         with torch.cuda.stream(self.stream):
-            self._reduce_range(b["start"], b["end"])
+            self._reduce_range(b["start"], b["end"], self.tail_blocks if tail else self.blocks)
         self.launch_count += 1
 
-    def _reduce_range(self, start: int, end: int) -> None:
+    def _reduce_range(self, start: int, end: int, blocks: Optional[int] = None) -> None:
         n = end - start
         if self.backend == "symm":
-            self.symm.all_reduce(start * 4, n, torch.float32, self.weights, self.blocks)
+            self.symm.all_reduce(start * 4, n, torch.float32, self.weights, self.blocks if blocks is None else blocks)
         elif self.backend == "nccl":
             g = self.flat.grads[start:end]
             if self.weights is not None:
@@ -122,7 +127,7 @@ class GradSync:
             self.expected = list(self.touch)
         for bi in range(len(self.buckets)):
             if not self.launched[bi]:
-                self._launch(bi)
+                self._launch(bi, tail=True)
         if self.stream is not None:
             self.done.record(self.stream)
             torch.cuda.current_stream().wait_event(self.done)

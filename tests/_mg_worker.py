@@ -77,6 +77,17 @@ def main():
         buf.broadcast(0, numel * 4, root=world - 1, blocks=8)
         torch.cuda.synchronize()
         assert torch.equal(v, root_vals)
+        # a message above 1 MB: with more than two ranks this takes the scatter + all-gather path
+        numel = 4 * 250_003
+        v = buf.view(torch.float32, 0, numel)
+        x = torch.randn(numel, device=dev)
+        v.copy_(x)
+        root_vals = gather_all(x)[0]
+        torch.cuda.synchronize(); dist.barrier()
+        buf.broadcast(0, numel * 4, root=0, blocks=24)
+        torch.cuda.synchronize()
+        buf.check()
+        assert torch.equal(v, root_vals)
         # ---- parameter averaging + lerp + divergence
         numel = 4 * 50001
         stage = comm.SymmetricBuffer(numel * 4, timeout_s=5.0)

@@ -25,6 +25,14 @@ def test_symmetric_collectives_2gpu():
     _run("collectives", 2, 29631)
 
 
+def test_symm_collectives_4gpu():
+    _run("collectives", 4, 29641)
+
+
+def test_train_engine_ddp_4gpu():
+    _run("engine", 4, 29642)
+
+
 def test_train_engine_ddp_2gpu():
     _run("engine", 2, 29632)
 
