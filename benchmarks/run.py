@@ -23,10 +23,13 @@ from .harness import BenchConfig, BenchResult, run_benchmark
 from .models import MODELS, TIER1, TIER2
 
 
-def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0) -> BenchResult:
+def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, runs: int = 0, epochs: int = 0, warmup: int = -1) -> BenchResult:
     build, cfg = MODELS[name]
     if quick:
         cfg = cfg.quick()
+    if runs or epochs or warmup >= 0:
+        cfg = BenchConfig(cfg.name, runs or cfg.runs, cfg.warmup_epochs if warmup < 0 else warmup, epochs or cfg.measured_epochs,
+                          cfg.batches_per_epoch, cfg.batch_size)
     torch.manual_seed(seed)
     dev = torch.device(device)
     model, make_batch, loss_kind, lr = build(cfg, impl, dev, 8 if quick else 1)
@@ -98,6 +101,9 @@ def main(argv=None) -> int:
     ap.add_argument("--rounds", type=int, default=1)
     ap.add_argument("--quick", action="store_true", help="tiny shapes and two epochs: a smoke test, not a measurement")
     ap.add_argument("--out", default="")
+    ap.add_argument("--runs", type=int, default=0, help="passes per model (default 4, the first is discarded)")
+    ap.add_argument("--epochs", type=int, default=0, help="measured epochs per pass (default 20)")
+    ap.add_argument("--warmup", type=int, default=-1, help="warm-up epochs per pass (default 3)")
     args = ap.parse_args(argv)
     names = {"all": TIER1 + TIER2, "tier1": TIER1, "tier2": TIER2}.get(args.models) or [m for m in args.models.split(",") if m]
     impls = [i for i in args.impl.split(",") if i]
@@ -109,7 +115,7 @@ def main(argv=None) -> int:
     for _round in range(max(1, args.rounds)):
         for n in names:
             for impl in impls:           # interleaved: flodl, torch, flodl, torch, ...
-                r = run_model(n, impl, args.device, args.quick)
+                r = run_model(n, impl, args.device, args.quick, 0, args.runs, args.epochs, args.warmup)
                 print(r.json(), flush=True)
                 if impl not in best[n] or r.median_epoch_ms < best[n][impl].median_epoch_ms:
                     best[n][impl] = r
