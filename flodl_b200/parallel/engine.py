@@ -17,6 +17,8 @@ is a correct new step.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
@@ -64,6 +66,7 @@ class TrainEngine:
             comm_backend = "nccl"
         if use_symm and param_staging:
             self.symm_stage = _comm.SymmetricBuffer(self.flat.total * 4, self.device.index, comm_timeout_s)
+        comm_blocks = int(os.environ.get("FLODL_B200_COMM_BLOCKS", comm_blocks))
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend,
                              world=None if self.grad_sync else 1)
         # Buffers (BatchNorm running statistics) follow rank 0 after every step, as in the reference
