@@ -25,7 +25,7 @@ from .flat import FlatParams
 
 class GradSync:
     def __init__(self, flat: FlatParams, symm: Optional[_comm.SymmetricBuffer], bucket_bytes: int = 25 * 1024 * 1024,
-                 overlap: bool = True, blocks: int = 24, backend: str = "symm", world: Optional[int] = None, tail_blocks: int = 256):
+                 overlap: bool = True, blocks: int = 24, backend: str = "symm", world: Optional[int] = None, tail_blocks: int = 96):
         self.flat, self.symm, self.blocks = flat, symm, blocks
         # The last bucket of a step (and anything launched after backward has ended) has no compute
         # left to overlap with, so it may use most of the GPU instead of the few blocks that keep the
