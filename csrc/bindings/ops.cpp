@@ -252,6 +252,14 @@ void adam_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor
                      stream_of(p)),
         "fb_adam_step");
 }
+// The same update for a list of parameters that do not share a flat buffer: one call from Python, one
+// launch per tensor (the per-parameter Python loop cost more than the kernels on small models).
+void adam_step_multi(std::vector<Tensor>& ps, const std::vector<Tensor>& gs, std::vector<Tensor>& ms, std::vector<Tensor>& vs,
+                     const std::vector<OptTensor>& p16s, const Tensor& hyper, double b1, double b2, double eps,
+                     const OptTensor& grad_scale) {
+  TORCH_CHECK(gs.size() == ps.size() && ms.size() == ps.size() && vs.size() == ps.size() && p16s.size() == ps.size(), "list lengths differ");
+  for (size_t i = 0; i < ps.size(); ++i) adam_step(ps[i], gs[i], ms[i], vs[i], p16s[i], hyper, b1, b2, eps, grad_scale);
+}
 void sgd_step(Tensor& p, const Tensor& g, const OptTensor& buf, const OptTensor& p16, const Tensor& hyper,
               const OptTensor& grad_scale) {
   want_f32(p, "p");
@@ -546,6 +554,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("scale_rows", &scale_rows);
   m.def("adam_step", &adam_step, py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p16"), py::arg("hyper"),
         py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none());
+  m.def("adam_step_multi", &adam_step_multi);
   m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
         py::arg("grad_scale") = py::none());
   m.def("grad_norm", &grad_norm);

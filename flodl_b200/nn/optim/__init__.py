@@ -243,6 +243,7 @@ class Adam(Optimizer):
                     from ... import ops
                     ops.core._launched()
                     continue
+                plist, glist, mlist, vlist, shlist = [], [], [], [], []
                 for i in range(s, e):
                     p = self.params[i]
                     if p.grad is None:
@@ -252,8 +253,13 @@ class Adam(Optimizer):
                     if not p.data.is_contiguous():
                         raise TensorError("Adam: non-contiguous parameter")
                     sh = getattr(p, "_fb_bf16", None)
-                    C.adam_step(p.data.view(-1), p.grad.contiguous().view(-1), self.m[i].view(-1), self.v[i].view(-1),
-                                None if sh is None else sh.view(-1), hyper, self.beta1, self.beta2, self.eps, self.grad_scale)
+                    plist.append(p.data.view(-1))
+                    glist.append(p.grad.contiguous().view(-1))
+                    mlist.append(self.m[i].view(-1))
+                    vlist.append(self.v[i].view(-1))
+                    shlist.append(None if sh is None else sh.view(-1))
+                if plist:
+                    C.adam_step_multi(plist, glist, mlist, vlist, shlist, hyper, self.beta1, self.beta2, self.eps, self.grad_scale)
                 continue
             with torch.no_grad():
                 for i in range(s, e):

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 import threading
 from typing import Optional
 
@@ -111,8 +112,28 @@ def next_seed() -> int:
 
 
 # ---------------------------------------------------------------------------------------- helpers
+# Below this many elements an eagerly launched op is bound by host time, and a Python autograd
+# function around a native kernel costs several times an ATen op's dispatch (measured on B200: the
+# small fp32 graph models of `benchmarks/` ran at 0.8x of plain PyTorch through the native path). So
+# in plain eager mode small tensors take the PyTorch op; inside a CUDA-graph capture, and for the
+# whole process once a flat-buffer engine exists (`set_eager_min_numel(0)`), the native kernels
+# always run. Process-wide on purpose (autograd's backward thread must see the same value).
+_EAGER = {"min_numel": int(os.environ.get("FLODL_B200_EAGER_MIN_NUMEL", str(1 << 20)))}
+
+
+def set_eager_min_numel(n: int) -> None:
+    _EAGER["min_numel"] = int(n)
+
+
+def eager_min_numel() -> int:
+    return _EAGER["min_numel"]
+
+
 def _native_ok(x: torch.Tensor) -> bool:
-    return FLAGS.native and x.is_cuda
+    if not (FLAGS.native and x.is_cuda):
+        return False
+    n = _EAGER["min_numel"]
+    return n <= 0 or x.numel() >= n or torch.cuda.is_current_stream_capturing()
 
 
 def _round_up(n: int, m: int) -> int:

@@ -28,6 +28,8 @@ import time
 from typing import Callable, List, Optional, Sequence
 
 import torch
+
+from ..ops import core as _core_ops
 import torch.distributed as dist
 
 from ..nn.module import Module, Parameter
@@ -165,6 +167,7 @@ class DistributedState:
             groups = [[p.t for p in g] for m in walk_modules(model) for g in m.fuse_groups()]
             self.flat = FlatParams(tensors, shadow=self.device.type == "cuda", grad_alloc=grad_alloc, param_alloc=param_alloc, groups=groups)
         backend = "symm" if self.symm_grads is not None else "nccl"
+        _core_ops.set_eager_min_numel(0)      # flat buffers and direct gradient slots: native kernels for every size
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, backend)
         # auto-balancer
         w = self.world_size

@@ -23,6 +23,8 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
+from ..ops import core as _core_ops
+
 from .. import _ext, ops as _ops
 from ..nn.module import Module, Parameter, walk_modules
 from ..tensor import TensorError
@@ -66,6 +68,7 @@ class TrainEngine:
             comm_backend = "nccl"
         if use_symm and param_staging:
             self.symm_stage = _comm.SymmetricBuffer(self.flat.total * 4, self.device.index, comm_timeout_s)
+        _core_ops.set_eager_min_numel(0)      # flat buffers and direct gradient slots: native kernels for every size
         comm_blocks = int(os.environ.get("FLODL_B200_COMM_BLOCKS", comm_blocks))
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend,
                              world=None if self.grad_sync else 1)

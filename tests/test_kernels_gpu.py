@@ -458,3 +458,21 @@ def test_bn_from_conv_sums_matches_stats_pass(C):
     assert ((r1 - r2).abs() / r1.abs()).max().item() < 1e-3
     assert (rm1 - rm2).abs().max().item() < 1e-4 and (rv1 - rv2).abs().max().item() < 1e-3
     assert (o1.float() - o2.float()).abs().max().item() <= 0.04
+
+
+def test_eager_adam_on_unflattened_parameters_matches_torch(C):
+    from flodl_b200 import nn
+    torch.manual_seed(15)
+    shapes = [(33, 17), (64,), (5, 4, 3)]
+    ours = [nn.Parameter(torch.randn(*s, device="cuda"), f"p{i}") for i, s in enumerate(shapes)]
+    ref = [p.t.detach().clone().requires_grad_(True) for p in ours]
+    opt, ropt = nn.Adam(ours, 0.01), torch.optim.Adam(ref, lr=0.01)
+    for step in range(3):
+        for p, r in zip(ours, ref):
+            g = torch.randn_like(r)
+            p.t.grad = g.clone()
+            r.grad = g.clone()
+        opt.step()
+        ropt.step()
+    for p, r in zip(ours, ref):
+        assert (p.t.detach() - r.detach()).abs().max().item() < 1e-5
