@@ -48,6 +48,7 @@ class ResNet20(Module):
     def __init__(self, num_classes: int = 10, device=None):
         self.stem = Conv2d(3, 16, 3, 1, 1, bias=False, device=device)
         self.stem_bn = BatchNorm2d(16, device)
+        self.stem.bn_stats = True
         self.blocks: List[BasicBlock] = []
         in_c = 16
         for out_c, stride in ((16, 1), (32, 2), (64, 2)):

@@ -15,6 +15,19 @@ def _pair(v):
     return (int(v), int(v)) if isinstance(v, int) else tuple(int(a) for a in v)
 
 
+def _padded_ci(x: torch.Tensor, ci: int) -> int:
+    """An input layer with fewer than 16 channels (RGB) runs on the native kernels with its channels
+    zero-padded to 16: the extra filter channels only ever see zeros, so neither the output nor the
+    gradient of the real channels changes. Only where no input gradient is wanted."""
+    return 16 if ci < 16 and not x.requires_grad else ci
+
+
+def _pad_channels(t: torch.Tensor, c: int) -> torch.Tensor:
+    out = torch.zeros((t.shape[0], c, t.shape[2], t.shape[3]), dtype=t.dtype, device=t.device).contiguous(memory_format=torch.channels_last)
+    out[:, :t.shape[1]] = t
+    return out
+
+
 class _Conv2dShadowFn(torch.autograd.Function):
     """Convolution on channels-last bf16 activations whose filter lives in a flat parameter buffer:
     forward reads the bf16 shadow of the filter (already K-R-S-C, refreshed by the optimizer kernel),
@@ -32,6 +45,15 @@ class _Conv2dShadowFn(torch.autograd.Function):
         N, Ci, H, W = x.shape
         Co, _, k, kw = w16.shape
         ctx.simple = (dilation == (1, 1) and groups == 1 and k == kw and stride[0] == stride[1] and padding[0] == padding[1])
+        ctx.pad_ci = 0
+        cp = _padded_ci(x, Ci)
+        if ctx.simple and cp != Ci and C.conv_fprop_supported(N, H, W, cp, Co, k, stride[0], padding[0]) \
+                and C.conv_wgrad_supported(N, H, W, cp, Co, k, stride[0], padding[0]):
+            xp = _pad_channels(x, cp)
+            ctx.save_for_backward(xp, w16)
+            ctx.pad_ci = Ci
+            core._launched(4)
+            return C.conv_fprop(xp, _pad_channels(w16, cp), stride[0], padding[0], sums)
         if ctx.simple and C.conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0]):
             return C.conv_fprop(x, w16, stride[0], padding[0], sums)
         if sums is not None:
@@ -46,6 +68,14 @@ class _Conv2dShadowFn(torch.autograd.Function):
         C = _ext.require()
         N, Ci, H, W = x.shape
         Co, _, k, _ = w16.shape
+        if ctx.pad_ci:
+            # x is the zero-padded input saved by forward; only the real channels' filter gradient is kept
+            dwp = torch.zeros((Co, Ci, k, k), dtype=torch.float32, device=x.device).contiguous(memory_format=torch.channels_last)
+            C.conv_wgrad(x, dy, dwp, stride[0], padding[0])
+            ctx.weight._fb_grad.add_(dwp[:, :ctx.pad_ci])
+            core._launched(3)
+            core._touched(ctx.weight)
+            return None, None, None, None, None, None, None
         shape = (N, H, W, Ci, Co, k, stride[0], padding[0])
         native_w = ctx.simple and C.conv_wgrad_supported(*shape)
         native_x = ctx.needs_input_grad[0] and ctx.simple and C.conv_dgrad_supported(*shape)
@@ -79,8 +109,11 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
         if bn_stats and bias is None and torch.is_grad_enabled():
             N, Ci, H, W = x.shape
             Co, _, k, kw = weight.shape
+            cp = _padded_ci(x, Ci)
+            Cx = _ext.require()
             if (dilation == (1, 1) and groups == 1 and k == kw and stride[0] == stride[1] and padding[0] == padding[1]
-                    and _ext.require().conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0])):
+                    and Cx.conv_fprop_supported(N, H, W, cp, Co, k, stride[0], padding[0])
+                    and (cp == Ci or Cx.conv_wgrad_supported(N, H, W, cp, Co, k, stride[0], padding[0]))):
                 sums = core.zero_scratch(2 * Co, x.device)
         y = _Conv2dShadowFn.apply(x, weight, stride, padding, dilation, int(groups), sums)
         if sums is not None:
