@@ -4,11 +4,21 @@ data gradient and filter gradient. Everything else (the 3-channel stem, strided 
 other layouts and dtypes) runs the PyTorch op."""
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
 from .. import _ext
 from . import core
+
+
+# Widest channel count sent to the native data-gradient / forward kernels. Measured in a ResNet-20 step on
+# B200: the native data gradient wins up to 32 channels and loses at 64 (one 36-instruction tile per CTA
+# plus a 73 KB filter load; 1.264 ms per step against 1.183 with cuDNN there), while the native forward
+# pays for itself at every width because its epilogue saves the BatchNorm statistics pass (1.200 vs 1.237).
+_MAX_CI = int(os.environ.get("FLODL_B200_CONV_MAX_CI", "32"))
+_MAX_FPROP_CI = int(os.environ.get("FLODL_B200_CONV_MAX_FPROP_CI", "64"))
 
 
 def _pair(v):
@@ -54,7 +64,7 @@ class _Conv2dShadowFn(torch.autograd.Function):
             ctx.pad_ci = Ci
             core._launched(4)
             return C.conv_fprop(xp, _pad_channels(w16, cp), stride[0], padding[0], sums)
-        if ctx.simple and C.conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0]):
+        if ctx.simple and (Ci <= _MAX_FPROP_CI or sums is not None) and C.conv_fprop_supported(N, H, W, Ci, Co, k, stride[0], padding[0]):
             return C.conv_fprop(x, w16, stride[0], padding[0], sums)
         if sums is not None:
             raise RuntimeError("BatchNorm sums requested from a convolution the native kernel does not cover")
@@ -78,7 +88,7 @@ class _Conv2dShadowFn(torch.autograd.Function):
             return None, None, None, None, None, None, None
         shape = (N, H, W, Ci, Co, k, stride[0], padding[0])
         native_w = ctx.simple and C.conv_wgrad_supported(*shape)
-        native_x = ctx.needs_input_grad[0] and ctx.simple and C.conv_dgrad_supported(*shape)
+        native_x = ctx.needs_input_grad[0] and ctx.simple and max(Ci, Co) <= _MAX_CI and C.conv_dgrad_supported(*shape)
         dx = dw = None
         if (ctx.needs_input_grad[0] and not native_x) or not native_w:
             dx, dw, _ = torch.ops.aten.convolution_backward(dy, x, w16, None, list(stride), list(padding), list(dilation), False, [0, 0], groups,
@@ -106,7 +116,7 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
             and getattr(weight, "_fb_channels_last", False) and x.is_contiguous(memory_format=torch.channels_last)):
         stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
         sums = None
-        if bn_stats and bias is None and torch.is_grad_enabled():
+        if bn_stats and bias is None and torch.is_grad_enabled() and x.shape[1] <= _MAX_FPROP_CI:
             N, Ci, H, W = x.shape
             Co, _, k, kw = weight.shape
             cp = _padded_ci(x, Ci)
