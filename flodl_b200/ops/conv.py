@@ -19,6 +19,7 @@ from . import core
 # pays for itself at every width because its epilogue saves the BatchNorm statistics pass (1.200 vs 1.237).
 _MAX_CI = int(os.environ.get("FLODL_B200_CONV_MAX_CI", "32"))
 _MAX_FPROP_CI = int(os.environ.get("FLODL_B200_CONV_MAX_FPROP_CI", "64"))
+_MAX_WGRAD_CI = int(os.environ.get("FLODL_B200_CONV_MAX_WGRAD_CI", "64"))
 
 
 def _pair(v):
@@ -87,7 +88,7 @@ class _Conv2dShadowFn(torch.autograd.Function):
             core._touched(ctx.weight)
             return None, None, None, None, None, None, None
         shape = (N, H, W, Ci, Co, k, stride[0], padding[0])
-        native_w = ctx.simple and C.conv_wgrad_supported(*shape)
+        native_w = ctx.simple and Ci <= _MAX_WGRAD_CI and C.conv_wgrad_supported(*shape)
         native_x = ctx.needs_input_grad[0] and ctx.simple and max(Ci, Co) <= _MAX_CI and C.conv_dgrad_supported(*shape)
         dx = dw = None
         if (ctx.needs_input_grad[0] and not native_x) or not native_w:
