@@ -190,3 +190,19 @@ def test_shakespeare_parser():
     assert s.decode(s.data[0].tolist()) == "abca" and s.decode(s.targets[0].tolist()) == "bcab"
     with pytest.raises(Exception):
         Shakespeare.parse("ab", 4)
+
+
+def test_eager_dispatch_threshold_is_process_wide_and_cpu_never_native():
+    import threading
+    import torch
+    from flodl_b200.ops import core
+    old = core.eager_min_numel()
+    try:
+        core.set_eager_min_numel(123)
+        seen = []
+        t = threading.Thread(target=lambda: seen.append(core.eager_min_numel()))
+        t.start(); t.join()
+        assert seen == [123]                       # autograd's backward thread must see the same value
+        assert not core._native_ok(torch.zeros(4))  # CPU tensors never take the native path
+    finally:
+        core.set_eager_min_numel(old)
