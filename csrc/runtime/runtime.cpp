@@ -24,6 +24,7 @@
 #include <memory>
 #include <mutex>
 #include <optional>
+#include <set>
 #include <string>
 #include <thread>
 #include <vector>
@@ -618,7 +619,39 @@ struct ElChe {
 
 }  // namespace
 
+// Kahn levels of a DAG given as (from, to) node-index pairs (flodl/src/graph/graph.rs:180-260): level k holds
+// the nodes whose last dependency sits in level k-1; inside a level nodes appear in the order their last
+// dependency released them (dependents visited in ascending index). Duplicate edges count once. Throws on a cycle.
+static std::vector<std::vector<int64_t>> topo_levels(int64_t n, const std::vector<std::pair<int64_t, int64_t>>& edges) {
+  if (n < 0) throw std::runtime_error("topo_levels: negative node count");
+  std::vector<std::set<int64_t>> deps(n), dependents(n);
+  for (const auto& e : edges) {
+    if (e.first < 0 || e.first >= n || e.second < 0 || e.second >= n) throw std::runtime_error("topo_levels: edge endpoint out of range");
+    deps[e.second].insert(e.first);
+    dependents[e.first].insert(e.second);
+  }
+  std::vector<int64_t> indeg(n), queue;
+  for (int64_t i = 0; i < n; ++i) {
+    indeg[i] = static_cast<int64_t>(deps[i].size());
+    if (indeg[i] == 0) queue.push_back(i);
+  }
+  std::vector<std::vector<int64_t>> levels;
+  int64_t visited = 0;
+  while (!queue.empty()) {
+    levels.push_back(queue);
+    visited += static_cast<int64_t>(queue.size());
+    std::vector<int64_t> next;
+    for (int64_t ni : queue)
+      for (int64_t d : dependents[ni])
+        if (--indeg[d] == 0) next.push_back(d);
+    queue.swap(next);
+  }
+  if (visited != n) throw std::runtime_error("cycle detected in graph");
+  return levels;
+}
+
 void bind_runtime(py::module_& m) {
+  m.def("topo_levels", &topo_levels, py::arg("n"), py::arg("edges"));
   m.def("sha256_hex", [](py::bytes b) { return sha256_hex(std::string(b)); });
   m.def("fdl_save", &fdl_save, py::arg("path"), py::arg("entries"), py::arg("hash32"), py::arg("version") = 2);
   m.def("fdl_save_bytes", &fdl_save_bytes, py::arg("entries"), py::arg("hash32"), py::arg("version") = 2);

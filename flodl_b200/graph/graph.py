@@ -39,7 +39,10 @@ from .tree import TreeMixin
 def topological_levels(n: int, edges: Sequence[Tuple[int, int]]) -> List[List[int]]:
     C = _ext.load()
     if C is not None and hasattr(C, "topo_levels"):
-        return C.topo_levels(n, list(edges))
+        try:
+            return C.topo_levels(n, list(edges))
+        except RuntimeError as e:
+            raise TensorError(str(e))
     deps = [set() for _ in range(n)]
     dependents = [set() for _ in range(n)]
     for a, b in edges:

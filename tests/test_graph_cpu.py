@@ -329,3 +329,16 @@ def test_graph_as_module_inside_graph_shares_parameters():
     outer = FlowBuilder.from_(inner).through(nn.Linear(2, 2)).build()
     assert len(outer.parameters()) == 6
     assert isinstance(outer.sub_modules()[0], Graph)
+
+
+def test_native_topological_levels_match_python_rule():
+    from flodl_b200 import _ext
+    from flodl_b200.graph import topological_levels
+    import pytest as _pytest
+    assert topological_levels(5, [(0, 1), (0, 2), (1, 3), (2, 3), (0, 1), (3, 4)]) == [[0], [1, 2], [3], [4]]
+    assert topological_levels(4, [(2, 0), (3, 0), (0, 1)]) == [[2, 3], [0], [1]]
+    assert topological_levels(0, []) == []
+    with _pytest.raises(Exception, match="cycle"):
+        topological_levels(2, [(0, 1), (1, 0)])
+    C = _ext.load()
+    assert C is None or hasattr(C, "topo_levels")
