@@ -12,9 +12,9 @@ and `--model lm` run the other two training configurations. Rank 0 prints ONE JS
 `value` is device-timed (CUDA events around exactly K steps, max over ranks) with the step's
 inputs already resident; `e2e.value` times the same K steps through the public API including, per
 step, the pinned-host -> device copy of that step's inputs and a device -> host read of the loss.
-`--impl reference` is the unmodified reference's arm; `--impl twin` runs a plain PyTorch + NCCL
-restatement of the reference's call sequence for the same model (per-parameter all-reduce after
-backward, stock ATen kernels).
+`--impl reference` runs the reference's own C++ shim (`flodl-sys/shim.cpp`, compiled unmodified into
+`baseline/_ref/libflodl_shim.so`) with the call sequence of its Rust host; `--impl twin` runs a
+plain PyTorch + NCCL restatement of the same sequence as a second opinion.
 """
 from __future__ import annotations
 
@@ -39,10 +39,6 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="eager steps instead of one CUDA graph per step")
     ap.add_argument("--comm", default="symm", choices=["symm", "nccl"])
     return ap.parse_args()
-
-
-REFERENCE_UNAVAILABLE = ("the reference is a Rust workspace (no setup.py / pyproject.toml; pip reports 'not installable') and "
-                         "this image has no cargo/rustc, so it cannot be built or run here")
 
 
 class ClockSampler(threading.Thread):
@@ -279,8 +275,10 @@ def run_ours(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}), flush=True)
+        # the reference's own C++ shim (compiled unmodified into baseline/_ref), driven through its C ABI;
+        # nothing of this repository's package or kernels is imported on this path
+        from baseline import reference_arm
+        reference_arm.run(args, ClockSampler)
         return
     if args.impl == "twin":
         from baseline import twin
