@@ -217,8 +217,11 @@ def run_ours(args):
         dist.all_reduce(t, dist.ReduceOp.MAX)
         return float(t.item())
 
+    first_loss = float("nan")
     for i in range(max(args.warmup, 3)):
-        run(dev_pool[i % len(dev_pool)])
+        l0 = run(dev_pool[i % len(dev_pool)])
+        if i == 0:
+            first_loss = float(l0.float().item())
     sync_all()
     eng.check()
 
@@ -248,6 +251,17 @@ def run_ours(args):
     clocks = sampler.stop()
     eng.check()
 
+    # ---- replicas must still agree: compare a checksum of the flat parameter buffer across ranks --
+    params_in_sync = None
+    if world > 1:
+        if local_sgd:
+            eng.average_params()          # Local SGD replicas only agree right after an averaging round
+        p = eng.flat.params
+        sums = torch.stack([p.double().sum(), p.double().abs().sum(), p[:: max(1, p.numel() // 4096)].double().pow(2).sum()])
+        allsums = [torch.empty_like(sums) for _ in range(world)]
+        dist.all_gather(allsums, sums)
+        params_in_sync = all(torch.equal(allsums[0], a) for a in allsums)
+
     if rank == 0:
         value = world * B / (ms_dev / 1e3)
         e2e = world * B / (ms_e2e / 1e3)
@@ -263,7 +277,10 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "samples/s", "ms_per_step": round(ms_e2e, 4), "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4},
-            "gpu_launches": int(per_step * args.steps + (args.steps // AVG_EVERY if local_sgd else 0)), "final_loss": round(last, 4),
+            "gpu_launches": int(per_step * args.steps + (args.steps // AVG_EVERY if local_sgd else 0)),
+            "first_loss": round(first_loss, 4), "final_loss": round(last, 4), "params_in_sync": params_in_sync,
+            "collective": (None if world == 1 else ("this repository's kernels over " + ("NVLS multimem" if getattr(eng.symm_grads or eng.symm_params, "nvls", False)
+                           else "peer loads/stores") if args.comm == "symm" else "NCCL")),
         }
         print(json.dumps(out), flush=True)
     guard.release()

@@ -3,6 +3,8 @@
 // One process drives one GPU. A SymmAlloc is a raw cudaMalloc block that is exported with CUDA IPC;
 // the Python layer exchanges the 64-byte handles through torch.distributed's store and every rank
 // maps every peer's block, which gives the pointer table the kernels in csrc/comm index by rank.
+// A VmmAlloc is the same thing built on the virtual-memory-management API (file descriptors instead
+// of IPC handles), which is what an NVLink-switch multicast object can be bound to (csrc/runtime/vmm.cpp).
 // This is the counterpart of the reference's NCCL communicator objects
 // (flodl-sys/ops_cuda.cpp:265-562, flodl/src/distributed/nccl.rs:56-571): `SymmComm` is what
 // `NcclRankComm` is there, `abort()` is what `NcclAbortHandle::abort` is there (a host flag the
@@ -18,6 +20,7 @@
 #include <string>
 #include <vector>
 
+#include "fb_vmm.hpp"
 #include "flodl_b200.h"
 
 namespace {
@@ -64,6 +67,22 @@ struct SymmAlloc {
   }
 };
 
+
+// VMM-backed symmetric block with an optional multicast (NVLS) mapping; see fb_vmm.hpp.
+struct VmmAlloc {
+  fb::VmmBlock block;
+  VmmAlloc(size_t bytes, int dev) : block(bytes, dev) {}
+  uint64_t address() const { return block.address(); }
+  size_t nbytes() const { return block.size(); }
+  Tensor tensor(py::object dtype, int64_t byte_offset, int64_t numel) const {
+    auto st = torch::python::detail::py_object_to_dtype(dtype);
+    TORCH_CHECK(byte_offset >= 0 && static_cast<size_t>(byte_offset + numel * c10::elementSize(st)) <= block.size(),
+                "view exceeds the allocation");
+    auto opts = torch::TensorOptions().dtype(st).device(torch::kCUDA, block.device());
+    return at::from_blob(reinterpret_cast<char*>(block.address()) + byte_offset, {numel}, opts);
+  }
+};
+
 uint64_t open_ipc(const std::string& handle) {
   TORCH_CHECK(handle.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
   cudaIpcMemHandle_t h;
@@ -77,8 +96,8 @@ void close_ipc(uint64_t p) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(p)); 
 struct SymmComm {
   fb_symm_ctx ctx;
   int device;
-  Tensor epochs, status;
-  int* abort_host = nullptr;  // mapped pinned word
+  Tensor epochs;
+  int* abort_host = nullptr;  // mapped pinned words: [0] abort (host -> device), [1] status (device -> host)
   int* abort_dev = nullptr;
 
   SymmComm(int rank, int world, std::vector<uint64_t> data, std::vector<uint64_t> sig, int dev, int64_t timeout_ns)
@@ -91,12 +110,11 @@ struct SymmComm {
     }
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(dev));
     epochs = torch::zeros({FB_MAX_BLOCKS}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
-    status = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
-    cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&abort_host), sizeof(int), cudaHostAllocMapped), "cudaHostAlloc");
-    *abort_host = 0;
+    cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&abort_host), 64 * sizeof(int), cudaHostAllocMapped), "cudaHostAlloc");
+    std::memset(abort_host, 0, 64 * sizeof(int));
     cuda_check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&abort_dev), abort_host, 0), "cudaHostGetDevicePointer");
     ctx.epochs = epochs.data_ptr();
-    ctx.status = status.data_ptr();
+    ctx.status = abort_dev + 32;   // its own cache line; the host reads it without a device sync
     ctx.abort = abort_dev;
     ctx.timeout_ns = timeout_ns;
     ctx.rank = rank;
@@ -113,8 +131,21 @@ struct SymmComm {
   void abort() { *abort_host = 1; }
   void clear_abort() { *abort_host = 0; }
   bool aborted() const { return *abort_host != 0; }
-  int read_status() { return status.item<int>(); }
-  void clear_status() { status.zero_(); }
+  // The status word is host-mapped: `poll_status` reads what has arrived so far without waiting for
+  // the device, `read_status` first waits for the device to finish what it was given.
+  int poll_status() const { return *reinterpret_cast<volatile int*>(abort_host + 32); }
+  int read_status() {
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    cudaDeviceSynchronize();
+    return poll_status();
+  }
+  void clear_status() { *reinterpret_cast<volatile int*>(abort_host + 32) = 0; }
+  uint64_t status_device_address() const { return reinterpret_cast<uint64_t>(abort_dev + 32); }
+  void set_mc(uint64_t addr) { ctx.mc = reinterpret_cast<void*>(addr); }
+  bool has_mc() const { return ctx.mc != nullptr; }
+  // After a wait gave up the per-block epochs of the ranks no longer agree: start again from zero
+  // (every rank, between two host barriers, with the signal pad zeroed as well).
+  void reset_epochs() { epochs.zero_(); }
   void set_timeout_ns(int64_t t) { ctx.timeout_ns = t; }
 
   static std::vector<float> wvec(const std::optional<std::vector<float>>& w, int world) {
@@ -176,6 +207,21 @@ struct SymmComm {
 }  // namespace
 
 void bind_comm(py::module_& m) {
+  py::class_<VmmAlloc, std::shared_ptr<VmmAlloc>>(m, "VmmAlloc")
+      .def(py::init<size_t, int>(), py::arg("nbytes"), py::arg("device"))
+      .def("address", &VmmAlloc::address)
+      .def_property_readonly("nbytes", &VmmAlloc::nbytes)
+      .def("tensor", &VmmAlloc::tensor, py::arg("dtype"), py::arg("byte_offset"), py::arg("numel"))
+      .def("export_fd", [](VmmAlloc& a) { return a.block.export_fd(); })
+      .def("import_peer", [](VmmAlloc& a, int fd) { return a.block.import_peer(fd); })
+      .def("mc_create", [](VmmAlloc& a, int world) { return a.block.mc_create(world); })
+      .def("mc_import", [](VmmAlloc& a, int fd) { a.block.mc_import(fd); })
+      .def("mc_add_device", [](VmmAlloc& a) { a.block.mc_add_device(); })
+      .def("mc_bind", [](VmmAlloc& a) { a.block.mc_bind(); })
+      .def("mc_map", [](VmmAlloc& a) { return a.block.mc_map(); })
+      .def("mc_address", [](VmmAlloc& a) { return a.block.mc_address(); })
+      .def("release", [](VmmAlloc& a) { a.block.release(); });
+  m.def("multicast_supported", [](int device) { return fb::VmmBlock::multicast_supported(device); });
   py::class_<SymmAlloc, std::shared_ptr<SymmAlloc>>(m, "SymmAlloc")
       .def(py::init<size_t, int>(), py::arg("nbytes"), py::arg("device"))
       .def("ipc_handle", &SymmAlloc::ipc_handle)
@@ -196,6 +242,11 @@ void bind_comm(py::module_& m) {
       .def("clear_abort", &SymmComm::clear_abort)
       .def("aborted", &SymmComm::aborted)
       .def("read_status", &SymmComm::read_status)
+      .def("poll_status", &SymmComm::poll_status)
+      .def("status_device_address", &SymmComm::status_device_address)
+      .def("set_mc", &SymmComm::set_mc)
+      .def("has_mc", &SymmComm::has_mc)
+      .def("reset_epochs", &SymmComm::reset_epochs)
       .def("clear_status", &SymmComm::clear_status)
       .def("set_timeout_ns", &SymmComm::set_timeout_ns)
       .def("allreduce", &SymmComm::allreduce, py::arg("byte_off"), py::arg("n"), py::arg("is_bf16"),

@@ -238,7 +238,7 @@ void scale_rows(Tensor& x, const Tensor& scalar) {
 
 // ---------------------------------------------------------------------------------- optimizers
 void adam_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor& p16, const Tensor& hyper, double b1,
-               double b2, double eps, const OptTensor& grad_scale) {
+               double b2, double eps, const OptTensor& grad_scale, uint64_t skip) {
   want_f32(p, "p");
   want_f32(m, "m");
   want_f32(v, "v");
@@ -249,19 +249,19 @@ void adam_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor
   if (p16.has_value()) TORCH_CHECK(is_bf16(*p16) && p16->is_contiguous() && p16->numel() == p.numel());
   check(fb_adam_step(p.data_ptr<float>(), g.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), ptr<void>(p16), p.numel(),
                      hyper.data_ptr<float>(), (float)b1, (float)b2, (float)eps, ptr<const float>(grad_scale), is_bf16(g),
-                     stream_of(p)),
+                     reinterpret_cast<const int*>(skip), stream_of(p)),
         "fb_adam_step");
 }
 // The same update for a list of parameters that do not share a flat buffer: one call from Python, one
 // launch per tensor (the per-parameter Python loop cost more than the kernels on small models).
 void adam_step_multi(std::vector<Tensor>& ps, const std::vector<Tensor>& gs, std::vector<Tensor>& ms, std::vector<Tensor>& vs,
                      const std::vector<OptTensor>& p16s, const Tensor& hyper, double b1, double b2, double eps,
-                     const OptTensor& grad_scale) {
+                     const OptTensor& grad_scale, uint64_t skip) {
   TORCH_CHECK(gs.size() == ps.size() && ms.size() == ps.size() && vs.size() == ps.size() && p16s.size() == ps.size(), "list lengths differ");
-  for (size_t i = 0; i < ps.size(); ++i) adam_step(ps[i], gs[i], ms[i], vs[i], p16s[i], hyper, b1, b2, eps, grad_scale);
+  for (size_t i = 0; i < ps.size(); ++i) adam_step(ps[i], gs[i], ms[i], vs[i], p16s[i], hyper, b1, b2, eps, grad_scale, skip);
 }
 void sgd_step(Tensor& p, const Tensor& g, const OptTensor& buf, const OptTensor& p16, const Tensor& hyper,
-              const OptTensor& grad_scale) {
+              const OptTensor& grad_scale, uint64_t skip) {
   want_f32(p, "p");
   want_f32(hyper, "hyper");
   c10::cuda::CUDAGuard guard(p.device());
@@ -269,7 +269,7 @@ void sgd_step(Tensor& p, const Tensor& g, const OptTensor& buf, const OptTensor&
   TORCH_CHECK(g.is_contiguous() && g.numel() == p.numel() && hyper.numel() >= 4);
   if (buf.has_value()) want_f32(*buf, "buf");
   check(fb_sgd_step(p.data_ptr<float>(), g.data_ptr(), ptr<float>(buf), ptr<void>(p16), p.numel(), hyper.data_ptr<float>(),
-                    ptr<const float>(grad_scale), is_bf16(g), stream_of(p)),
+                    ptr<const float>(grad_scale), is_bf16(g), reinterpret_cast<const int*>(skip), stream_of(p)),
         "fb_sgd_step");
 }
 // returns fp32 [2] = {norm * extra_scale, clip coefficient}
@@ -553,10 +553,11 @@ PYBIND11_MODULE(_C, m) {
   m.def("softmax_ce", &softmax_ce);
   m.def("scale_rows", &scale_rows);
   m.def("adam_step", &adam_step, py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p16"), py::arg("hyper"),
-        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none());
-  m.def("adam_step_multi", &adam_step_multi);
+        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none(), py::arg("skip") = 0);
+  m.def("adam_step_multi", &adam_step_multi, py::arg("ps"), py::arg("gs"), py::arg("ms"), py::arg("vs"), py::arg("p16s"), py::arg("hyper"),
+        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none(), py::arg("skip") = 0);
   m.def("sgd_step", &sgd_step, py::arg("p"), py::arg("g"), py::arg("buf"), py::arg("p16"), py::arg("hyper"),
-        py::arg("grad_scale") = py::none());
+        py::arg("grad_scale") = py::none(), py::arg("skip") = 0);
   m.def("grad_norm", &grad_norm);
   m.def("bn_fwd", &bn_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("running_mean"), py::arg("running_var"),
         py::arg("eps"), py::arg("momentum"), py::arg("relu"), py::arg("training"), py::arg("sums") = py::none());

@@ -1,6 +1,13 @@
 // Collectives over peer-mapped ("symmetric") buffers: every rank holds a pointer to the same
 // buffer on every other GPU of the NVSwitch domain and the kernels below load from / store to
-// those peers directly (plain P2P ld/st over NVLink; no TMA, no multicast loads).
+// those peers directly. Two data paths, no TMA in either:
+//   * NVLS: when the buffers are bound to an NVLink-switch multicast object (csrc/runtime/vmm.cpp),
+//     `multimem.ld_reduce` lets the switch read one offset on every GPU and return the sum, and
+//     `multimem.st` lets it write every GPU's copy. An all-reduce then moves each byte over a
+//     GPU's links once per direction instead of twice, and costs one load + one store per vector
+//     instead of W + W.
+//   * plain P2P ld/st over NVLink (any world size, per-rank weights, and every test in which a
+//     rank leaves or a wait runs out).
 //
 //  * fb_allreduce       - replaces the per-tensor `ncclAllReduce` group the reference issues after
 //                         backward (flodl-sys/ops_cuda.cpp:326-369, flodl/src/distributed/ddp.rs:133-147,
@@ -39,8 +46,9 @@ struct SymmCtx {
   uint32_t* sig[FB_MAX_RANKS];   // peer pointers to the signal pads
   uint32_t* epochs;              // local: one epoch counter per block
   const int* abort;              // optional host-mapped abort word
-  int* status;                   // local status word
+  int* status;                   // status word (host-mapped when the host wants to poll it without a sync)
   long long timeout_ns;          // bound of every wait
+  char* mc;                      // multicast address of the payload buffer (nullptr: no NVLS)
   int rank, world;
 };
 
@@ -59,7 +67,26 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
+// The status word may live in host-mapped memory (the host polls it without a sync), where device
+// atomics are not dependable: first writer wins by a plain check-then-store, made visible system-wide.
+__device__ __forceinline__ void set_status_sys(int* status, int code) {
+  if (!status) return;
+  volatile int* s = status;
+  if (*s == 0) {
+    *s = code;
+    __threadfence_system();
+  }
+}
+
 // All threads of the block call this. Returns false after a bounded wait ran out.
+//
+// Failure spreads through the fabric: a rank whose wait runs out writes a "poison" word into every
+// peer's signal pad, and every barrier looks at its own poison word while it waits. So once one
+// rank has given up, the collectives of all ranks return at their next barrier with a status the
+// host reads, instead of pairing flags of different launches. The pad, the epochs and the poison
+// word are cleared together by the host (`SymmetricBuffer.recover`, between two host barriers).
+constexpr int kStatusPeerGaveUp = 7;
+
 __device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, uint32_t& epoch, int* sh_fail) {
   __syncthreads();
   epoch += 1;
@@ -68,19 +95,30 @@ __device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, uint32_t& e
     __threadfence_system();
     st_release_sys(c.sig[t] + blockIdx.x * FB_MAX_RANKS + c.rank, epoch);
     const uint32_t* mine = c.sig[c.rank] + blockIdx.x * FB_MAX_RANKS + t;
-    bool ok = false;
+    const uint32_t* poison = c.sig[c.rank] + FB_SIGNAL_POISON_INDEX;
+    int fail = 0;
     const unsigned long long t0 = global_ns();
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
-      if (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) >= 0) { ok = true; break; }
-      if ((it & 255) == 255) {
-        if (c.abort && *reinterpret_cast<const volatile int*>(c.abort)) break;
-        if (global_ns() - t0 > static_cast<unsigned long long>(c.timeout_ns)) break;
+    // The wait ends when the peer's flag arrives, when a peer has given up, when the host raises
+    // `abort`, or when `timeout_ns` has passed on the global timer. The iteration bound is a second
+    // line of defence derived from the same timeout (a poll with its back-off takes well over 16 ns).
+    const unsigned long long max_it = static_cast<unsigned long long>(c.timeout_ns) / 16ull + 4096ull;
+    if (ld_acquire_sys(poison) != 0) fail = kStatusPeerGaveUp;
+    if (!fail) {
+      fail = kStatusWaitPeer;
+      for (unsigned long long it = 0; it < max_it; ++it) {
+        if (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) >= 0) { fail = 0; break; }
+        if ((it & 63) == 63) {
+          if (ld_acquire_sys(poison) != 0) { fail = kStatusPeerGaveUp; break; }
+          if (c.abort && *reinterpret_cast<const volatile int*>(c.abort)) break;
+          if (global_ns() - t0 > static_cast<unsigned long long>(c.timeout_ns)) break;
+        }
+        if (it > 32) __nanosleep(64);
       }
-      if (it > 32) __nanosleep(64);
     }
-    if (!ok) {
+    if (fail) {
       *sh_fail = 1;
-      set_status(c.status, kStatusWaitPeer);
+      set_status_sys(c.status, fail);
+      st_release_sys(c.sig[t] + FB_SIGNAL_POISON_INDEX, 1u);   // tell peer t (and this rank's own later launches)
     }
   }
   __syncthreads();
@@ -196,6 +234,101 @@ allreduce_twoshot_kernel(SymmCtx c, long long byte_off, long long n, Weights wts
   if (threadIdx.x == 0) c.epochs[blockIdx.x] = epoch;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// NVLS (multimem) primitives and kernels
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+struct Multimem;
+template <>
+struct Multimem<float> {
+  __device__ static uint4 ld_reduce(const void* mc) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+    return r;
+  }
+};
+template <>
+struct Multimem<__nv_bfloat16> {
+  __device__ static uint4 ld_reduce(const void* mc) {   // eight bf16 values, accumulated in fp32 by the switch
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+    return r;
+  }
+};
+__device__ __forceinline__ void multimem_st(void* mc, const uint4& r) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+}
+
+// In-place all-reduce: rank r owns shard r, asks the switch for the sum of that shard over all
+// GPUs, scales it and multicasts the result into every GPU's buffer.
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_nvls_kernel(SymmCtx c, long long byte_off, long long n, float scale) {
+  __shared__ int sh_fail;
+  if (threadIdx.x == 0) sh_fail = 0;
+  uint32_t epoch = c.epochs[blockIdx.x];
+  constexpr int E = Pack<T>::N;
+  const long long nvec = n / E;
+  const long long per = (nvec + c.world - 1) / c.world;
+  const long long v0 = per * c.rank;
+  const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
+  if (symm_block_barrier(c, epoch, &sh_fail)) {
+    constexpr int U = 8;      // independent switch reductions in flight per thread
+    char* base = c.mc + byte_off;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = v0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < v1; i0 += stride * U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < v1) raw[u] = Multimem<T>::ld_reduce(base + (i0 + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * stride < v1) {
+          float v[E];
+          Pack<T>::to_f(raw[u], v);
+#pragma unroll
+          for (int j = 0; j < E; ++j) v[j] *= scale;
+          multimem_st(base + (i0 + u * stride) * 16, Pack<T>::from_f(v));
+        }
+      }
+    }
+    symm_block_barrier(c, epoch, &sh_fail);
+  }
+  if (threadIdx.x == 0) c.epochs[blockIdx.x] = epoch;
+}
+
+// Broadcast from `root`: the root reads its own bytes and multicasts them; each byte leaves the
+// root once and the switch replicates it.
+__global__ void __launch_bounds__(512)
+broadcast_nvls_kernel(SymmCtx c, long long byte_off, long long nbytes, int root) {
+  __shared__ int sh_fail;
+  if (threadIdx.x == 0) sh_fail = 0;
+  uint32_t epoch = c.epochs[blockIdx.x];
+  if (symm_block_barrier(c, epoch, &sh_fail)) {
+    if (c.rank == root) {
+      constexpr int U = 8;
+      const long long nvec = nbytes / 16;
+      const char* src = static_cast<const char*>(c.data[root]) + byte_off;
+      char* dst = c.mc + byte_off;
+      const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+      for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < nvec) raw[u] = *reinterpret_cast<const uint4*>(src + (i0 + u * stride) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < nvec) multimem_st(dst + (i0 + u * stride) * 16, raw[u]);
+      }
+    }
+    symm_block_barrier(c, epoch, &sh_fail);
+  }
+  if (threadIdx.x == 0) c.epochs[blockIdx.x] = epoch;
+}
+
 // ---------------------------------------------------------------------------------------------
 // one-shot all-reduce: out (local, any dtype) = sum_p w_p * in_p
 // ---------------------------------------------------------------------------------------------
@@ -240,7 +373,7 @@ allreduce_oneshot_kernel(SymmCtx c, long long byte_off, long long n, TO* __restr
 // c.data[]  : peer pointers to the fp32 parameter buffers
 // stage[]   : peer pointers to fp32 staging buffers of the same size
 // partial   : 2 * gridDim.x floats (local scratch); out2 = {sum (post-pre)^2, sum post^2}
-template <int W>
+template <int W, bool NVLS>
 __global__ void __launch_bounds__(512)
 param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float alpha,
                      __nv_bfloat16* __restrict__ p16, float* __restrict__ partial, unsigned int* __restrict__ done_counter,
@@ -251,13 +384,36 @@ param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float a
   if (threadIdx.x == 0) sh_fail = 0;
   uint32_t epoch = c.epochs[blockIdx.x];
   const long long nvec = n / 4;
-  const long long per = (nvec + W - 1) / W;
+  const int world = NVLS ? c.world : W;
+  const long long per = (nvec + world - 1) / world;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   float d2 = 0.f, n2 = 0.f;
 
   if (symm_block_barrier(c, epoch, &sh_fail)) {
-    {
+    if constexpr (NVLS) {
+      // the switch sums shard `rank` of every GPU's parameters; the mean goes to every staging buffer
+      const long long v0 = per * c.rank;
+      const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
+      constexpr int U = 8;
+      const float inv = wts.w[0];
+      for (long long i0 = v0 + tid; i0 < v1; i0 += stride * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * stride < v1) raw[u] = Multimem<float>::ld_reduce(c.mc + (i0 + u * stride) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * stride < v1) {
+            float v[4];
+            Pack<float>::to_f(raw[u], v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] *= inv;
+            multimem_st(stage.mc + (i0 + u * stride) * 16, Pack<float>::from_f(v));
+          }
+        }
+      }
+    } else {
       const long long v0 = per * c.rank;
       const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
       // U * W independent 16-byte peer loads in flight per thread (see the all-reduce kernel)
@@ -297,7 +453,7 @@ param_average_kernel(SymmCtx c, SymmCtx stage, long long n, Weights wts, float a
       // exactly those are complete in my staging buffer now, and only those are touched below.
       const char* st_local = static_cast<const char*>(stage.data[c.rank]);
       float* w_local = static_cast<float*>(c.data[c.rank]);
-      for (int s = 0; s < W; ++s) {
+      for (int s = 0; s < world; ++s) {
         const long long v0 = per * s;
         const long long v1 = (v0 + per < nvec) ? v0 + per : nvec;
         constexpr int U2 = 4;
@@ -440,6 +596,7 @@ static SymmCtx make_ctx(const fb_symm_ctx* h) {
   c.abort = static_cast<const int*>(h->abort);
   c.status = static_cast<int*>(h->status);
   c.timeout_ns = h->timeout_ns > 0 ? h->timeout_ns : 2000000000LL;
+  c.mc = static_cast<char*>(h->mc);
   c.rank = h->rank;
   c.world = h->world;
   return c;
@@ -463,7 +620,11 @@ static int clamp_blocks(int blocks) {
   switch (W) {                    \
     case 1: { constexpr int kW = 1; __VA_ARGS__; break; } \
     case 2: { constexpr int kW = 2; __VA_ARGS__; break; } \
+    case 3: { constexpr int kW = 3; __VA_ARGS__; break; } \
     case 4: { constexpr int kW = 4; __VA_ARGS__; break; } \
+    case 5: { constexpr int kW = 5; __VA_ARGS__; break; } \
+    case 6: { constexpr int kW = 6; __VA_ARGS__; break; } \
+    case 7: { constexpr int kW = 7; __VA_ARGS__; break; } \
     case 8: { constexpr int kW = 8; __VA_ARGS__; break; } \
     default: return -5;           \
   }
@@ -481,6 +642,13 @@ extern "C" int fb_allreduce(const fb_symm_ctx* h, long long byte_off, long long 
   // 512-thread blocks on few SMs: measured on 2 x B200 under a BERT-base step, spreading the same threads over
   // 96..222 blocks of 128 threads slowed the overlapped GEMMs more (7.29..7.85 ms per step against 7.22).
   const int threads = 512;
+  if (h->mc && !weights && h->world > 1) {
+    // equal weights: the switch does the sum (fp32 accumulate), the kernel applies 1/world
+    const float scale = 1.0f / static_cast<float>(h->world);
+    if (is_bf16) allreduce_nvls_kernel<__nv_bfloat16><<<blocks, threads, 0, st>>>(c, byte_off, n, scale);
+    else allreduce_nvls_kernel<float><<<blocks, threads, 0, st>>>(c, byte_off, n, scale);
+    return static_cast<int>(cudaGetLastError());
+  }
   FB_DISPATCH_WORLD(h->world,
     if (is_bf16) allreduce_twoshot_kernel<__nv_bfloat16, kW><<<blocks, threads, 0, st>>>(c, byte_off, n, w);
     else allreduce_twoshot_kernel<float, kW><<<blocks, threads, 0, st>>>(c, byte_off, n, w));
@@ -516,8 +684,12 @@ extern "C" int fb_param_average(const fb_symm_ctx* params, const fb_symm_ctx* st
   SymmCtx s = make_ctx(staging);
   Weights w = make_weights(params, weights);
   blocks = clamp_blocks(blocks);
+  if (params->mc && staging->mc && !weights && params->world > 1) {
+    param_average_kernel<1, true><<<blocks, 512, 0, st>>>(c, s, n, w, alpha, static_cast<__nv_bfloat16*>(p16), partial, counter, out2);
+    return static_cast<int>(cudaGetLastError());
+  }
   FB_DISPATCH_WORLD(params->world,
-    param_average_kernel<kW><<<blocks, 512, 0, st>>>(c, s, n, w, alpha, static_cast<__nv_bfloat16*>(p16), partial, counter, out2));
+    param_average_kernel<kW, false><<<blocks, 512, 0, st>>>(c, s, n, w, alpha, static_cast<__nv_bfloat16*>(p16), partial, counter, out2));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -528,6 +700,10 @@ extern "C" int fb_broadcast(const fb_symm_ctx* h, long long byte_off, long long 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SymmCtx c = make_ctx(h);
   blocks = clamp_blocks(blocks);
+  if (h->mc && h->world > 1 && nbytes >= (1 << 16)) {
+    broadcast_nvls_kernel<<<blocks, 512, 0, st>>>(c, byte_off, nbytes, root);
+    return static_cast<int>(cudaGetLastError());
+  }
   broadcast_kernel<<<blocks, 512, 0, st>>>(c, byte_off, nbytes, root);
   return static_cast<int>(cudaGetLastError());
 }

@@ -36,7 +36,8 @@ extern "C" {
 /* symmetric-memory collectives */
 #define FB_MAX_RANKS 16
 #define FB_MAX_BLOCKS 256
-#define FB_SIGNAL_PAD_BYTES (FB_MAX_BLOCKS * FB_MAX_RANKS * 4)
+#define FB_SIGNAL_POISON_INDEX (FB_MAX_BLOCKS * FB_MAX_RANKS)   /* uint32 index of the "a peer gave up" word */
+#define FB_SIGNAL_PAD_BYTES (FB_MAX_BLOCKS * FB_MAX_RANKS * 4 + 256)
 
 typedef struct fb_symm_ctx {
   void* data[FB_MAX_RANKS];  /* peer-mapped payload buffers, indexed by rank            */
@@ -45,6 +46,7 @@ typedef struct fb_symm_ctx {
   const void* abort;         /* optional device-visible int the host may set to 1        */
   void* status;              /* local int: 0 ok, else the code of the wait that gave up  */
   long long timeout_ns;      /* bound of every device-side wait; 0 = 2 s                 */
+  void* mc;                  /* multicast (NVLS) address of the payload buffer, or NULL  */
   int rank, world;
 } fb_symm_ctx;
 
@@ -138,10 +140,12 @@ int fb_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, 
               float* scratch, int N, int C, int HW, int relu, int is_bf16, void* stream);
 
 /* ---- optimizers / gradient norm -------------------------------------------------------------- */
+/* `skip` (optional, device-visible int): when it reads non-zero the launch changes nothing. The
+ * collectives raise such a word when a bounded wait gave up, so un-reduced gradients are never applied. */
 int fb_adam_step(float* p, const void* g, float* m, float* v, void* p16, long long n, const float* hyper, float b1,
-                 float b2, float eps, const float* grad_scale, int g_bf16, void* stream);
+                 float b2, float eps, const float* grad_scale, int g_bf16, const int* skip, void* stream);
 int fb_sgd_step(float* p, const void* g, float* buf, void* p16, long long n, const float* hyper,
-                const float* grad_scale, int g_bf16, void* stream);
+                const float* grad_scale, int g_bf16, const int* skip, void* stream);
 int fb_grad_norm_parts(long long n);
 int fb_grad_norm(const void* g, long long n, float* partial, float max_norm, float extra_scale, float* out,
                  int is_bf16, void* stream);
@@ -154,7 +158,8 @@ int fb_grad_norm(const void* g, long long n, float* partial, float max_norm, flo
  * 4 KB array inside the library (held on every GPU that loads it until the process exits).
  *   - n above FB_GRAD_NORM_NOALLOC_MAX_ELEMS is rejected with -4;
  *   - the first call on a device resolves the array's address (with that device current): make it
- *     before any stream capture;
+ *     before any stream capture. Two threads making that first call together is harmless (both
+ *     store the same address in an atomic slot);
  *   - every call reuses the array, so calls that may overlap on the GPU must be ordered by the
  *     caller; nothing needs clearing between calls. */
 #define FB_GRAD_NORM_NOALLOC_MAX_ELEMS (1LL << 31)

@@ -14,6 +14,8 @@
 //
 // Hyper-parameters that change every step (lr, bias corrections) are read from device memory so a
 // captured CUDA graph can replay the step with new values.
+#include <atomic>
+
 #include "../include/flodl_b200.h"
 #include "common.cuh"
 
@@ -24,7 +26,10 @@ template <typename TG>
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
             __nv_bfloat16* __restrict__ p16, long long n, const float* __restrict__ hyper, float b1, float b2,
-            float eps, const float* __restrict__ grad_scale) {
+            float eps, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
+  // `skip`: a device-visible word that a collective sets when it gave up; the update is then left out
+  // and the parameters stay as they were, so the host can raise before anything diverged.
+  if (skip && *reinterpret_cast<const volatile int*>(skip) != 0) return;
   const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], wd = hyper[3];
   const float gs = grad_scale ? *grad_scale : 1.f;
   const float step_size = lr / bc1;
@@ -82,7 +87,8 @@ adam_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__
 template <typename TG>
 __global__ void __launch_bounds__(256)
 sgd_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ buf, __nv_bfloat16* __restrict__ p16,
-           long long n, const float* __restrict__ hyper, const float* __restrict__ grad_scale) {
+           long long n, const float* __restrict__ hyper, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
+  if (skip && *reinterpret_cast<const volatile int*>(skip) != 0) return;
   const float lr = hyper[0], mu = hyper[1], wd = hyper[2];
   const bool first = hyper[3] != 0.f;
   const float gs = grad_scale ? *grad_scale : 1.f;
@@ -145,7 +151,7 @@ __global__ void sumsq_finalize_kernel(const float* __restrict__ partial, int npa
 
 extern "C" int fb_adam_step(float* p, const void* g, float* m, float* v, void* p16, long long n,
                             const float* hyper, float b1, float b2, float eps, const float* grad_scale,
-                            int g_bf16, void* stream) {
+                            int g_bf16, const int* skip, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   long long blocks = (n / 4 + 255) / 256;
@@ -153,26 +159,26 @@ extern "C" int fb_adam_step(float* p, const void* g, float* m, float* v, void* p
   if (blocks < 1) blocks = 1;
   if (g_bf16)
     fb::adam_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
-        p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale);
+        p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale, skip);
   else
     fb::adam_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(p, static_cast<const float*>(g), m, v,
                                                                      static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2,
-                                                                     eps, grad_scale);
+                                                                     eps, grad_scale, skip);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int fb_sgd_step(float* p, const void* g, float* buf, void* p16, long long n, const float* hyper,
-                           const float* grad_scale, int g_bf16, void* stream) {
+                           const float* grad_scale, int g_bf16, const int* skip, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (g_bf16)
     fb::sgd_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
-        p, static_cast<const __nv_bfloat16*>(g), buf, static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale);
+        p, static_cast<const __nv_bfloat16*>(g), buf, static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale, skip);
   else
     fb::sgd_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(p, static_cast<const float*>(g), buf,
-                                                                    static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale);
+                                                                    static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale, skip);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -221,23 +227,26 @@ extern "C" int fb_grad_norm_noalloc(const void* g, long long n, float max_norm, 
                                     int is_bf16, void* stream) {
   if (n < 0 || n > FB_GRAD_NORM_NOALLOC_MAX_ELEMS) return -4;   // see fb_grad_norm_noalloc_max()
   constexpr int kMaxDevices = 64;
-  static float* scratch_of[kMaxDevices] = {nullptr};
+  // Two host threads may make the first call on one device at the same time; both resolve the same
+  // address, so a relaxed atomic slot is all the cache needs.
+  static std::atomic<float*> scratch_of[kMaxDevices];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return -4;
-  if (!scratch_of[dev]) {
+  float* partial = scratch_of[dev].load(std::memory_order_relaxed);
+  if (!partial) {
     // In host code `g_norm_scratch` is only a handle for the symbol; the kernel needs the address
     // the array has on THIS device.
     float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_norm_scratch);
     if (e != cudaSuccess) return static_cast<int>(e);
-    scratch_of[dev] = ptr;
+    scratch_of[dev].store(ptr, std::memory_order_relaxed);
+    partial = ptr;
   }
   const int parts = fb_grad_norm_parts(n);
   if (parts > kNormScratchFloats) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* partial = scratch_of[dev];
   if (is_bf16)
     fb::sumsq_partial_kernel<__nv_bfloat16><<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(g), n, partial);
   else

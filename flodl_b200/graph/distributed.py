@@ -125,6 +125,8 @@ class DistributedMixin:
             self._ddp.before_optimizer()
         if self._scheduler is not None:
             self._optimizer.set_lr(self._scheduler.lr(self._training_step) * self._lr_scale)
+        if self._ddp is not None:
+            self._ddp.guard_optimizer(self._optimizer)
         self._optimizer.step()
         self._optimizer.zero_grad()
         self._training_step += 1

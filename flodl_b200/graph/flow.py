@@ -391,6 +391,8 @@ class _Composite(Module):
 
     def __init__(self, kind: str, subs: List[Module], rep: Module):
         self._kind, self._subs, self._rep = kind, subs, rep
+        # data-dependent control flow: which parameters receive a gradient can change from step to step
+        self.dynamic = kind == "switch"
 
     def name(self): return "module"   # composites keep the trait's default name in the reference
     def forward(self, x): return self._rep.forward(x)
@@ -445,6 +447,7 @@ class LoopBuilder:
         cur = fb.current[0]
         nid = fb.next_id("loop")
         comp = _Composite("loop", [body] + ([cond] if cond is not None else []), body)
+        comp.dynamic = kind in ("while", "until")
         node = Node(nid, [DEFAULT_INPUT], [DEFAULT_OUTPUT], None, comp)
         node.trace_buf = []
         node.named_trace_buf = {}

@@ -110,7 +110,9 @@ def _apply(raw, params, buffers, structural_hash) -> LoadReport:
 
 
 def load_checkpoint(data: bytes, params, buffers, structural_hash: Optional[str] = None) -> LoadReport:
-    return _apply(_ext.require().fdl_load_bytes(data, False), params, buffers, structural_hash)
+    rep = _apply(_ext.require().fdl_load_bytes(data, False), params, buffers, structural_hash)
+    _sync_shadows(params)
+    return rep
 
 
 def load_checkpoint_file(path: str, params, buffers, structural_hash: Optional[str] = None) -> LoadReport:

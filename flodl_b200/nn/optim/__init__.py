@@ -81,6 +81,7 @@ class Optimizer(Stateful):
         self._lr = float(lr)
         self.groups: List[_Group] = []
         self.grad_scale: Optional[torch.Tensor] = None   # device scalar multiplied into every gradient
+        self.skip_flag: int = 0    # device address of a word that, when non-zero, turns the fused update into a no-op
         self._hyper = None
         self._hyper_host = None
 
@@ -127,6 +128,30 @@ class Optimizer(Stateful):
     def set_grad_scale(self, scale: Optional[torch.Tensor]) -> None:
         """Device-resident multiplier for all gradients (clip coefficient, 1/loss-scale)."""
         self.grad_scale = scale
+
+    @property
+    def fused(self) -> bool:
+        """True when `step()` runs this library's fused kernels (which honour `set_skip_flag`)."""
+        return False
+
+    def set_skip_flag(self, address: int) -> None:
+        """Device-visible int the fused kernels read first: non-zero means "leave the parameters
+        alone" (the symmetric collectives raise their status word when a wait gave up, so
+        un-reduced gradients are never applied). 0 removes the guard."""
+        self.skip_flag = int(address)
+
+    def _sync_shadow(self) -> None:
+        """After an update that wrote the fp32 parameters without the fused kernels: bring the
+        bf16 copies the GEMMs and convolutions read up to date."""
+        flat = _flat.flat_of(self.params)
+        if flat is not None:
+            flat.refresh_shadow()
+            return
+        with torch.no_grad():
+            for p in self.params:
+                sh = getattr(p, "_fb_bf16", None)
+                if sh is not None:
+                    sh.copy_(p.data)
 
     # hyper-parameters travel through a pinned host buffer -> device tensor, so a captured CUDA
     # graph replays the optimizer kernel with fresh values and no host sync
@@ -221,6 +246,10 @@ class Adam(Optimizer):
             if e > s and _native(self.params[s]):
                 self._hyper_tensor(self.params[s].device, [lr, bc1, bc2, self.weight_decay], gi)
 
+    @property
+    def fused(self) -> bool:
+        return bool(self.params) and _native(self.params[0])
+
     def step(self) -> None:
         self.advance()
         self.apply()
@@ -239,7 +268,8 @@ class Adam(Optimizer):
                     flat, a, b = rng
                     m, v = self._flat_state(flat)
                     C.adam_step(flat.params[a:b], flat.grads[a:b], m[a:b], v[a:b],
-                                None if flat.shadow is None else flat.shadow[a:b], hyper, self.beta1, self.beta2, self.eps, self.grad_scale)
+                                None if flat.shadow is None else flat.shadow[a:b], hyper, self.beta1, self.beta2, self.eps, self.grad_scale,
+                                self.skip_flag)
                     from ... import ops
                     ops.core._launched()
                     continue
@@ -259,7 +289,7 @@ class Adam(Optimizer):
                     vlist.append(self.v[i].view(-1))
                     shlist.append(None if sh is None else sh.view(-1))
                 if plist:
-                    C.adam_step_multi(plist, glist, mlist, vlist, shlist, hyper, self.beta1, self.beta2, self.eps, self.grad_scale)
+                    C.adam_step_multi(plist, glist, mlist, vlist, shlist, hyper, self.beta1, self.beta2, self.eps, self.grad_scale, self.skip_flag)
                 continue
             with torch.no_grad():
                 for i in range(s, e):
@@ -277,6 +307,9 @@ class Adam(Optimizer):
                     self.v[i].mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
                     denom = (self.v[i] / bc2).sqrt_().add_(self.eps)
                     p.addcdiv_(self.m[i], denom, value=-(lr / bc1))
+                    sh = getattr(p, "_fb_bf16", None)
+                    if sh is not None:
+                        sh.copy_(p.data)
 
     def save_state(self, w) -> None:
         w.write(struct.pack("<Idq", len(self.params), self._lr, self.t))
@@ -343,6 +376,10 @@ class SGD(Optimizer):
             if e > s and _native(self.params[s]):
                 self._hyper_tensor(self.params[s].device, [lr, self.momentum, self.weight_decay, 1.0 if first else 0.0], gi)
 
+    @property
+    def fused(self) -> bool:
+        return bool(self.params) and _native(self.params[0])
+
     def step(self) -> None:
         self.advance()
         self.apply()
@@ -364,7 +401,7 @@ class SGD(Optimizer):
                             o, n = flat.range_of(p)
                             self.velocity[i] = self._flat_v[o:o + n].view(p.shape)
                     C.sgd_step(flat.params[a:b], flat.grads[a:b], self._flat_v[a:b] if self.momentum else None,
-                               None if flat.shadow is None else flat.shadow[a:b], self._hyper[gi], self.grad_scale)
+                               None if flat.shadow is None else flat.shadow[a:b], self._hyper[gi], self.grad_scale, self.skip_flag)
                     from ... import ops
                     ops.core._launched()
                     continue
@@ -378,7 +415,7 @@ class SGD(Optimizer):
                     hyper = self._hyper_tensor(p.device, [lr, self.momentum, self.weight_decay, 1.0 if fresh else 0.0], 32 + (1 if fresh else 0))
                     sh = getattr(p, "_fb_bf16", None)
                     C.sgd_step(p.data.view(-1), p.grad.contiguous().view(-1), self.velocity[i].view(-1) if self.momentum else None,
-                               None if sh is None else sh.view(-1), hyper, self.grad_scale)
+                               None if sh is None else sh.view(-1), hyper, self.grad_scale, self.skip_flag)
                 continue
             with torch.no_grad():
                 for i in range(s, e):
@@ -397,6 +434,9 @@ class SGD(Optimizer):
                             self.velocity[i].mul_(self.momentum).add_(g)
                         g = self.velocity[i]
                     p.sub_(g, alpha=lr)
+                    sh = getattr(p, "_fb_bf16", None)
+                    if sh is not None:
+                        sh.copy_(p.data)
 
     def save_state(self, w) -> None:
         w.write(struct.pack("<Idd", len(self.params), self._lr, self.weight_decay))
@@ -460,6 +500,7 @@ class RMSprop(Optimizer):
                         p.sub_(self.buf[i], alpha=lr)
                     else:
                         p.addcdiv_(g, denom, value=-lr)
+        self._sync_shadow()
 
     def save_state(self, w) -> None:
         w.write(struct.pack("<Id", len(self.params), self._lr))
@@ -514,6 +555,7 @@ class Adagrad(Optimizer):
                         self.ss[i] = torch.zeros_like(p.data)
                     self.ss[i].addcmul_(g, g)
                     p.addcdiv_(g, self.ss[i].sqrt().add_(self.eps), value=-clr)
+        self._sync_shadow()
 
     def save_state(self, w) -> None:
         w.write(struct.pack("<Idq", len(self.params), self._lr, self.t))
@@ -598,7 +640,7 @@ class RAdam(_AdamLike):
                         p.addcdiv_(m_hat, v_hat, value=-lr * r)
                     else:
                         p.sub_(m_hat, alpha=lr)
-
+        self._sync_shadow()
 
 class NAdam(_AdamLike):
     """m_hat = b1*m/(1-b1^(t+1)) + (1-b1) g/(1-b1^t); no momentum-decay schedule
@@ -617,3 +659,4 @@ class NAdam(_AdamLike):
                     g = self._moments(i, p)
                     m_hat = self.m[i] * (self.beta1 / bc1n) + g * ((1 - self.beta1) / bc1)
                     p.addcdiv_(m_hat, (self.v[i] / bc2).sqrt_().add_(self.eps), value=-lr)
+        self._sync_shadow()

@@ -3,13 +3,22 @@
 One process drives one GPU; `torch.distributed` (NCCL on GPUs, gloo on CPU) is the rendezvous and
 the baseline collective backend, the way the reference uses NCCL communicators
 (flodl/src/distributed/nccl.rs:56-571). What the reference does with `ncclAllReduce` /
-`ncclBroadcast` this package does with its own kernels over `SymmetricBuffer`s: a raw CUDA
-allocation per rank, exported through CUDA IPC, mapped by every peer, plus a small signal pad for
-the device-side barriers. `ReduceOp` keeps the reference's numbering (= `ncclRedOp_t`, nccl.rs:37-48).
+`ncclBroadcast` this package does with its own kernels over `SymmetricBuffer`s: one device
+allocation per rank, mapped by every peer, plus a small signal pad for the device-side barriers.
+Where the NVLink switch supports it the allocations come from the CUDA virtual-memory-management
+API and are bound to a multicast object, so the kernels can let the switch do the reduction
+(`multimem.ld_reduce` / `multimem.st`, "NVLS"); otherwise, or with `FLODL_B200_NVLS=0`, they are
+`cudaMalloc` blocks shared through CUDA IPC and the kernels use plain peer loads and stores.
+`ReduceOp` keeps the reference's numbering (= `ncclRedOp_t`, nccl.rs:37-48).
 """
 from __future__ import annotations
 
+import atexit
 import os
+import socket
+import threading
+import uuid
+import weakref
 from enum import IntEnum
 from typing import List, Optional, Sequence
 
@@ -69,6 +78,9 @@ def barrier() -> None:
 
 
 def destroy_process_group() -> None:
+    """Releases every live symmetric buffer (multicast bindings are undone on all ranks together,
+    while the group can still synchronise them), then leaves the group."""
+    close_all_symmetric()
     if dist.is_initialized():
         dist.destroy_process_group()
 
@@ -112,6 +124,70 @@ def _exchange(obj, group=None) -> list:
     return out
 
 
+def nvls_wanted() -> bool:
+    return os.environ.get("FLODL_B200_NVLS", "1") not in ("0", "false", "off", "no")
+
+
+def _exchange_fds(my_fds: Sequence[int], group=None) -> List[List[int]]:
+    """Every rank hands the same file descriptors to every other rank of the node; returns, per
+    rank, the descriptors received from it (this rank's own list at its own index). Descriptors
+    travel as SCM_RIGHTS messages over abstract unix-domain sockets; the socket names are agreed
+    through the process group."""
+    r, w = rank(), world_size()
+    token = _exchange(uuid.uuid4().hex if r == 0 else None, group)[0]
+    name = lambda k: f"\0flodl_b200_{token}_{k}"  # noqa: E731
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.bind(name(r))
+    srv.listen(w)
+    srv.settimeout(120.0)
+    counts = _exchange(len(my_fds), group)          # also: every server is listening from here on
+    err: List[BaseException] = []
+
+    def serve():
+        try:
+            for _ in range(w - 1):
+                conn, _a = srv.accept()
+                with conn:
+                    if my_fds:
+                        socket.send_fds(conn, [b"f"], list(my_fds))
+                    else:
+                        conn.sendall(b"n")
+        except BaseException as e:  # noqa: BLE001
+            err.append(e)
+
+    th = threading.Thread(target=serve, daemon=True)
+    th.start()
+    out: List[List[int]] = [[] for _ in range(w)]
+    out[r] = list(my_fds)
+    try:
+        for k in range(w):
+            if k == r:
+                continue
+            c = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            c.settimeout(120.0)
+            with c:
+                c.connect(name(k))
+                if counts[k]:
+                    _msg, fds, _flags, _addr = socket.recv_fds(c, 16, counts[k])
+                    out[k] = list(fds)
+                else:
+                    c.recv(1)
+    finally:
+        th.join(timeout=130.0)
+        srv.close()
+    if err:
+        raise TensorError(f"descriptor exchange failed: {err[0]}")
+    return out
+
+
+_LIVE_SYMM: "weakref.WeakSet[SymmetricBuffer]" = weakref.WeakSet()
+
+
+def close_all_symmetric() -> None:
+    for b in sorted(list(_LIVE_SYMM), key=lambda b: b._serial):
+        b.close()
+
+
 class SymmetricBuffer:
     """`nbytes` of device memory on every rank, each rank holding a pointer to every peer's block.
 
@@ -120,33 +196,124 @@ class SymmetricBuffer:
     the same sizes and block counts, on every rank. Device-side waits are bounded
     (`timeout_s`); `check()` turns a recorded give-up into an exception and `abort()` makes every
     pending wait on this rank return at once (the role `NcclAbortHandle` plays in the reference,
-    nccl.rs:384-417)."""
+    nccl.rs:384-417).
 
-    def __init__(self, nbytes: int, device: Optional[int] = None, timeout_s: float = 2.0, group=None):
+    `nvls=None` takes the switch-multicast path when the GPU reports support and
+    `FLODL_B200_NVLS` does not say otherwise; `nvls=False` forces plain peer loads and stores
+    (use that wherever a rank may leave or a wait is meant to run out)."""
+
+    _count = 0
+
+    def __init__(self, nbytes: int, device: Optional[int] = None, timeout_s: float = 2.0, group=None, nvls: Optional[bool] = None):
         C = _ext.require()
         self.C = C
         self.device = torch.cuda.current_device() if device is None else device
         self.nbytes = (nbytes + 255) // 256 * 256
         self.rank, self.world = rank(), world_size()
+        self.group = group
+        SymmetricBuffer._count += 1
+        self._serial = SymmetricBuffer._count
+        self._closed = False
         if self.world > C.MAX_RANKS:
             raise TensorError(f"world size {self.world} exceeds {C.MAX_RANKS}")
-        self.data = C.SymmAlloc(self.nbytes, self.device)
-        self.sig = C.SymmAlloc(C.SIGNAL_PAD_BYTES, self.device)
-        handles = _exchange((self.data.ipc_handle(), self.sig.ipc_handle()), group)
+        want = nvls_wanted() if nvls is None else bool(nvls)
+        want = want and self.world > 1 and C.multicast_supported(self.device)
+        want = all(_exchange(bool(want), group))
+        self.nvls = False
+        self.data = None
+        dptrs: List[int] = []
         self._opened: List[int] = []
-        dptrs, sptrs = [], []
+        if want:
+            dptrs = self._setup_vmm(group)
+        if not dptrs:
+            self.data = C.SymmAlloc(self.nbytes, self.device)
+        self.sig = C.SymmAlloc(C.SIGNAL_PAD_BYTES, self.device)
+        handles = _exchange((None if self.nvls else self.data.ipc_handle(), self.sig.ipc_handle()), group)
+        sptrs = []
+        ipc_d = []
         for r, (hd, hs) in enumerate(handles):
             if r == self.rank:
-                dptrs.append(self.data.address())
+                ipc_d.append(self.data.address())
                 sptrs.append(self.sig.address())
             else:
-                pd, ps = C.open_ipc(hd), C.open_ipc(hs)
-                self._opened += [pd, ps]
-                dptrs.append(pd)
+                ps = C.open_ipc(hs)
+                self._opened.append(ps)
                 sptrs.append(ps)
+                if not self.nvls:
+                    pd = C.open_ipc(hd)
+                    self._opened.append(pd)
+                    ipc_d.append(pd)
+        if not self.nvls:
+            dptrs = ipc_d
         self.peer_ptrs = dptrs
         self.comm = C.SymmComm(self.rank, self.world, dptrs, sptrs, self.device, int(timeout_s * 1e9))
+        if self.nvls:
+            self.comm.set_mc(self.data.mc_address())
+        _LIVE_SYMM.add(self)
         barrier()
+
+    def _setup_vmm(self, group) -> List[int]:
+        """VMM allocation + peer mapping + multicast binding. Every step that can fail is followed by
+        an agreement over the process group, so either all ranks end up on this path or none."""
+        C = self.C
+
+        def agree(ok: bool) -> bool:
+            return all(_exchange(bool(ok), group))
+
+        data, fds, err = None, [], None
+        try:
+            data = C.VmmAlloc(self.nbytes, self.device)
+            fds = [data.export_fd()]
+            if self.rank == 0:
+                fds.append(data.mc_create(self.world))
+        except Exception as e:  # noqa: BLE001
+            err = e
+        if not agree(err is None):
+            for fd in fds:
+                os.close(fd)
+            if data is not None:
+                data.release()
+            if self.rank == 0 and err is not None:
+                from .. import log
+                log.verbose(f"NVLS set-up not available ({err}); using CUDA IPC peer memory")
+            return []
+        got = _exchange_fds(fds, group)
+        ptrs: List[int] = []
+        try:
+            for r in range(self.world):
+                ptrs.append(data.address() if r == self.rank else data.import_peer(got[r][0]))
+            if self.rank != 0:
+                data.mc_import(got[0][1])
+            data.mc_add_device()
+        except Exception as e:  # noqa: BLE001
+            err = e
+        finally:
+            for r, lst in enumerate(got):
+                for fd in lst:
+                    try:
+                        os.close(fd)
+                    except OSError:
+                        pass
+        if not agree(err is None):           # all devices are in the team from here on (or nobody binds)
+            data.release()
+            return []
+        try:
+            data.mc_bind()
+        except Exception as e:  # noqa: BLE001
+            err = e
+        if not agree(err is None):
+            data.release()
+            return []
+        try:
+            data.mc_map()
+        except Exception as e:  # noqa: BLE001
+            err = e
+        if not agree(err is None):
+            data.release()
+            return []
+        self.data = data
+        self.nvls = True
+        return ptrs
 
     def view(self, dtype: torch.dtype, offset_bytes: int = 0, numel: Optional[int] = None) -> torch.Tensor:
         esz = torch.empty((), dtype=dtype).element_size()
@@ -156,8 +323,9 @@ class SymmetricBuffer:
     # collectives (current stream)
     def all_reduce(self, offset_bytes: int, numel: int, dtype: torch.dtype, weights: Optional[Sequence[float]] = None,
                    blocks: int = 32) -> None:
-        """In place over [offset, offset + numel): two-shot reduce-scatter + all-gather, result is the
-        weighted sum (default weights 1/world = average) on every rank."""
+        """In place over [offset, offset + numel): reduce-scatter + all-gather (through the switch
+        when the buffer is multicast-bound and the weights are equal, peer loads and stores
+        otherwise); the result is the weighted sum (default weights 1/world = average) on every rank."""
         self.comm.allreduce(offset_bytes, numel, dtype == torch.bfloat16, None if weights is None else list(weights), blocks)
 
     def all_reduce_into(self, offset_bytes: int, numel: int, dtype: torch.dtype, out: torch.Tensor,
@@ -171,14 +339,47 @@ class SymmetricBuffer:
     def barrier(self, blocks: int = 1) -> None:
         self.comm.barrier(blocks)
 
+    # ---- failure handling -----------------------------------------------------------------------
     def status(self) -> int:
+        """Waits for the device, then returns the status word (0 = every wait was answered)."""
         return self.comm.read_status()
+
+    def poll(self) -> int:
+        """The status word as it stands now, without waiting for the device (it is host-mapped)."""
+        return self.comm.poll_status()
+
+    def status_address(self) -> int:
+        """Device address of the status word, for kernels that must not run after a give-up
+        (the fused optimizers take it as their `skip` word)."""
+        return self.comm.status_device_address()
+
+    def _raise(self, st: int) -> None:
+        what = {4: "gave up waiting for a peer", 7: "stopped because a peer had given up"}.get(st, f"reported status {st}")
+        raise TensorError(f"symmetric collective {what} (status {st}); a rank is late, gone or aborted. "
+                          "Gradients were not applied; call recover() on every rank before the next collective")
 
     def check(self) -> None:
         st = self.comm.read_status()
         if st != 0:
-            self.comm.clear_status()
-            raise TensorError(f"symmetric collective gave up waiting for a peer (status {st}); a rank is late, gone or aborted")
+            self._raise(st)
+
+    def check_async(self) -> None:
+        """`check()` without a device sync: raises for a give-up that has already been reported."""
+        st = self.comm.poll_status()
+        if st != 0:
+            self._raise(st)
+
+    def recover(self) -> None:
+        """Collective: after a give-up, every rank calls this to put flags, epochs and status back to
+        their initial state (between two host barriers, with the device idle)."""
+        torch.cuda.synchronize(self.device)
+        barrier()
+        self.sig.tensor(torch.int32, 0, self.C.SIGNAL_PAD_BYTES // 4).zero_()
+        self.comm.reset_epochs()
+        self.comm.clear_abort()
+        torch.cuda.synchronize(self.device)
+        self.comm.clear_status()
+        barrier()
 
     def abort(self) -> None:
         self.comm.abort()
@@ -187,9 +388,31 @@ class SymmetricBuffer:
         self.comm.clear_abort()
 
     def close(self) -> None:
+        """Collective when multicast-bound: every rank unbinds before any rank frees its block."""
+        if self._closed:
+            return
+        self._closed = True
+        _LIVE_SYMM.discard(self)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize(self.device)
+        if self.nvls and dist.is_initialized():
+            try:
+                barrier()
+            except Exception:  # noqa: BLE001  (the group may be gone at interpreter exit)
+                pass
         for p in self._opened:
             self.C.close_ipc(p)
         self._opened = []
+        if self.nvls and self.data is not None:
+            self.data.release()
+            if dist.is_initialized():
+                try:
+                    barrier()
+                except Exception:  # noqa: BLE001
+                    pass
+
+
+atexit.register(close_all_symmetric)
 
 
 def all_reduce_nccl(tensors: Sequence[torch.Tensor], op: ReduceOp = ReduceOp.Avg) -> None:

@@ -167,6 +167,13 @@ class DistributedState:
             groups = [[p.t for p in g] for m in walk_modules(model) for g in m.fuse_groups()]
             self.flat = FlatParams(tensors, shadow=self.device.type == "cuda", grad_alloc=grad_alloc, param_alloc=param_alloc, groups=groups)
         backend = "symm" if self.symm_grads is not None else "nccl"
+        # Overlapping a bucket's all-reduce with backward relies on knowing how many gradient
+        # contributions each parameter gets per step. Data-dependent control flow (switch, while /
+        # until loops) changes that from step to step and from rank to rank, so such models
+        # exchange all gradients after backward instead.
+        from ..nn.module import walk_modules as _walk
+        if any(getattr(m, "dynamic", False) for m in _walk(model)):
+            overlap = False
         _core_ops.set_eager_min_numel(0)      # flat buffers and direct gradient slots: native kernels for every size
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, backend)
         # auto-balancer
@@ -330,6 +337,21 @@ class DistributedState:
             self.sync.finish()
         else:
             self.sync.all_reduce_now()
+
+    def guard_optimizer(self, optimizer) -> None:
+        """Make sure gradients whose exchange gave up are never applied (`Graph.step()` calls this
+        right before the optimizer). The fused optimizers read the collectives' status word on the
+        device and leave the parameters alone when it is set; the exception is then raised by the
+        next `check_async()` (start of the next step) without a host sync in between. Optimizers
+        without a fused path are guarded by a blocking check here."""
+        self.sync.guard(optimizer)
+
+    def recover(self) -> None:
+        """Collective: re-arm the symmetric buffers after a reported give-up."""
+        for b in (self.symm_grads, self.symm_params):
+            if b is not None:
+                b.recover()
+        self.sync.reset()
 
     # ---- Graph.step() hooks -------------------------------------------------------------------
     def before_optimizer(self) -> None:

@@ -92,6 +92,7 @@ class TrainEngine:
                     off += (t.numel() + 3) // 4 * 4
             self._buf_bytes = off * 4
         self.optimizer = optimizer_factory(params)
+        self.sync.guard(self.optimizer)       # a gradient exchange that gave up must never be applied
         self.max_grad_norm = max_grad_norm
         self.scheduler = None
         self.lr_scale = 1.0
@@ -202,6 +203,8 @@ class TrainEngine:
         if hasattr(self.optimizer, "apply"):
             self.optimizer.apply()
         else:
+            if self.sync.symm is not None and not torch.cuda.is_current_stream_capturing():
+                self.sync.check()         # no fused path to predicate on the device: wait and look
             self.optimizer.step()
         return lt.detach()
 
@@ -249,6 +252,8 @@ class TrainEngine:
         asynchronously) or device tensors. Returns the static device loss tensor."""
         if self._graph is None:
             raise TensorError("replay() before capture()")
+        if self.sync.symm is not None:
+            self.sync.symm.check_async()
         for dst, src in zip(self._static_in, inputs):
             dst.copy_(src, non_blocking=True)
         self._pre()
@@ -256,9 +261,19 @@ class TrainEngine:
         self.steps += 1
         return self._static_loss
 
+    def recover(self) -> None:
+        """Collective: re-arm every symmetric buffer after a reported give-up."""
+        for b in (self.symm_grads, self.symm_params, self.symm_stage, self.symm_bufs):
+            if b is not None:
+                b.recover()
+        self.sync.reset()
+
     def check(self) -> None:
         """Raise if a device-side wait of this rank's collectives or GEMMs gave up."""
         self.sync.check()
+        for b in (self.symm_params, self.symm_stage, self.symm_bufs):
+            if b is not None:
+                b.check_async()
         if self.device.type == "cuda":
             st = _ext.require().read_status(self.device.index or 0)
             if st != 0:

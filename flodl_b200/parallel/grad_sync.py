@@ -49,6 +49,8 @@ class GradSync:
         self.done = torch.cuda.Event() if self.stream is not None else None
         self.active = False
         self.launch_count = 0
+        self.next_bucket = 0
+        self.mismatch = False
         self._hooks = []
         if self.world > 1:
             for t in flat.tensors:
@@ -57,13 +59,19 @@ class GradSync:
 
     # ---- per step -------------------------------------------------------------------------------
     def begin_step(self) -> None:
-        """Call before forward: arms the readiness tracking for this step."""
+        """Call before forward: arms the readiness tracking for this step. Raises if a collective
+        of an earlier step has reported a give-up since (the status word is host-mapped, so this
+        costs one host read, no device sync)."""
         if self.world <= 1:
             return
+        if self.symm is not None:
+            self.symm.check_async()
         self.active = True
         _core.GRAD_HOOK["fn"] = self._on_touch
         for i in range(len(self.touch)):
             self.touch[i] = 0
+        self.next_bucket = 0
+        self.mismatch = False
         for bi, b in enumerate(self.buckets):
             self.launched[bi] = False
             self.pending[bi] = sum(1 for i in b["members"] if self.expected is not None and self.expected[i] > 0)
@@ -82,16 +90,29 @@ class GradSync:
         self.touch[i] += 1
         if self.expected is None or not self.overlap:
             return
+        bi = self.bucket_of[i]
+        if self.launched[bi] or self.touch[i] > self.expected[i]:
+            # a gradient arrived for a bucket that has already been reduced (or a parameter got more
+            # contributions than on the step the counts were learned from): this step's result for
+            # the bucket would miss it. finish() reports it and turns the overlap off.
+            self.mismatch = True
+            return
         if self.touch[i] == self.expected[i]:
-            bi = self.bucket_of[i]
             self.pending[bi] -= 1
-            if self.pending[bi] == 0 and not self.launched[bi]:
-                self._launch(bi)
+            self._launch_ready()
+
+    def _launch_ready(self) -> None:
+        """Buckets go out strictly in index order, each index always with the same block count, so
+        the per-block flags of a launch can only ever meet the same launch on the other ranks,
+        whatever the order in which gradients became ready there."""
+        while self.next_bucket < len(self.buckets) - 1 and self.pending[self.next_bucket] == 0 and not self.launched[self.next_bucket]:
+            self._launch(self.next_bucket)
+            self.next_bucket += 1
 
     def _launch(self, bi: int, tail: bool = False) -> None:
         b = self.buckets[bi]
         self.launched[bi] = True
-        tail = tail or all(self.launched)     # the last one out
+        tail = bi == len(self.buckets) - 1    # the last index has no compute left to overlap with: always the wide launch
         if self.stream is None:               # CPU replicas (gloo): reduce in line
             self._reduce_range(b["start"], b["end"])
             self.launch_count += 1
@@ -127,10 +148,16 @@ class GradSync:
             self.expected = list(self.touch)
         for bi in range(len(self.buckets)):
             if not self.launched[bi]:
-                self._launch(bi, tail=True)
+                self._launch(bi)
         if self.stream is not None:
             self.done.record(self.stream)
             torch.cuda.current_stream().wait_event(self.done)
+        if self.mismatch:
+            self.overlap = False
+            raise RuntimeError(
+                "gradient exchange: a gradient was produced after its bucket had been reduced (the set of parameters that "
+                "receive gradients changed between steps). This step's gradients are incomplete on this rank; overlap is now "
+                "off. Build the trainer with overlap=False for models whose backward differs from step to step.")
 
     # ---- one-off collectives --------------------------------------------------------------------
     def set_weights(self, weights: Optional[Sequence[float]]) -> None:
@@ -148,3 +175,21 @@ class GradSync:
     def check(self) -> None:
         if self.symm is not None:
             self.symm.check()
+
+    def guard(self, optimizer) -> None:
+        """Tie `optimizer` to the status word of the gradient exchange: fused kernels get the word's
+        device address as their `skip` argument, anything else waits for the exchange and checks."""
+        if self.symm is None or self.world <= 1:
+            return
+        if hasattr(optimizer, "set_skip_flag") and getattr(optimizer, "fused", False):
+            optimizer.set_skip_flag(self.symm.status_address())
+            self.symm.check_async()
+        else:
+            self.symm.check()
+
+    def reset(self) -> None:
+        """Forget the step in flight (after `SymmetricBuffer.recover`)."""
+        self.active = False
+        _core.GRAD_HOOK["fn"] = None
+        for bi in range(len(self.buckets)):
+            self.launched[bi] = False

@@ -106,7 +106,8 @@ def main():
         n2 = (mean ** 2).sum().item()
         assert abs(out2[0].item() - d2) / d2 < 1e-3 and abs(out2[1].item() - n2) / n2 < 1e-3
         # ---- bounded wait: a barrier nobody else joins must time out with a status, not hang
-        lone = comm.SymmetricBuffer(4096, timeout_s=0.3)
+        # (plain peer memory for this one: nothing that is meant to time out runs on a multicast binding)
+        lone = comm.SymmetricBuffer(4096, timeout_s=0.3, nvls=False)
         torch.cuda.synchronize(); dist.barrier()
         if rank == 0:
             lone.barrier()
@@ -115,6 +116,19 @@ def main():
             z = torch.ones(4, device=dev).sum().item()      # the context is still usable
             assert z == 4.0
         dist.barrier()
+        # the give-up was published to every peer: their next launch on this buffer returns at once
+        if rank != 0:
+            lone.barrier()
+            torch.cuda.synchronize()
+            assert lone.status() == 7, lone.status()
+        dist.barrier()
+        # recover() on every rank re-arms the buffer: the same barrier, joined by all, now passes
+        lone.recover()
+        lone.barrier()
+        torch.cuda.synchronize()
+        assert lone.status() == 0, lone.status()
+        # ---- world sizes that are not powers of two use the same kernels (peer path)
+        assert buf.nvls == (os.environ.get("FLODL_B200_NVLS", "1") != "0" and buf.C.multicast_supported(dev.index)), buf.nvls
     elif mode == "engine":
         from flodl_b200 import nn
         from flodl_b200.hf.models.bert import BertConfig, BertForMaskedLM, build_extended_attention_mask
@@ -146,6 +160,48 @@ def main():
                 ps = gather_all(eng.flat.params.clone())
                 assert all(torch.equal(ps[0], a) for a in ps), f"parameters diverged at step {step}"
             assert len(eng.sync.buckets) > 1 and eng.sync.launch_count >= 4 * len(eng.sync.buckets)
+    elif mode == "giveup":
+        # A rank that is late by more than the collectives' time limit: the others must not apply
+        # un-reduced gradients. The fused optimizer is predicated on the exchange's status word, so
+        # parameters stay as they were on every rank; the next check raises; recover() re-arms.
+        import time
+        from flodl_b200 import nn
+        from flodl_b200.models.gpt import DecoderLM, DecoderLMConfig
+        from flodl_b200.parallel.engine import TrainEngine
+        from flodl_b200.tensor import TensorError
+        cfg = DecoderLMConfig(vocab_size=256, d_model=64, n_layers=2, n_heads=2, d_ff=128, max_seq=64, dropout=0.0)
+        torch.manual_seed(3)
+        model = DecoderLM(cfg, dev)
+        model.set_training(True)
+        g = torch.Generator().manual_seed(20 + rank)
+        ids = torch.randint(0, 256, (4, 65), generator=g).to(dev)
+        x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        with nn.AutocastGuard(torch.bfloat16):
+            eng = TrainEngine(model, lambda ps: nn.AdamW(ps, 1e-2, 0.0), bucket_mb=0.05, comm_timeout_s=0.4)
+            assert eng.symm_grads is not None and not eng.symm_grads.nvls
+            for _ in range(2):
+                eng.step(lambda: model.loss(x, y))
+            torch.cuda.synchronize(); eng.check(); dist.barrier()
+            before = eng.flat.params.clone()
+            if rank == world - 1:
+                time.sleep(1.5)                       # the failure is made on the host: this rank is late
+            raised = False
+            try:
+                eng.step(lambda: model.loss(x, y))
+                torch.cuda.synchronize()
+                eng.check()
+            except TensorError:
+                raised = True
+            assert raised, "a collective that gave up must surface as an exception"
+            torch.cuda.synchronize()
+            assert torch.equal(eng.flat.params, before), "parameters changed although the gradient exchange gave up"
+            eng.recover()
+            eng.step(lambda: model.loss(x, y))
+            torch.cuda.synchronize()
+            eng.check()
+            ps = gather_all(eng.flat.params.clone())
+            assert all(torch.equal(ps[0], a) for a in ps), "replicas differ after recovery"
+            assert not torch.equal(eng.flat.params, before)
     elif mode == "resnet_buffers":
         # BatchNorm statistics differ per rank (different data); after every step all ranks must
         # hold rank 0's running statistics, through the one-launch pull broadcast
