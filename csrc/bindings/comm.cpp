@@ -96,7 +96,7 @@ void close_ipc(uint64_t p) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(p)); 
 struct SymmComm {
   fb_symm_ctx ctx;
   int device;
-  Tensor epochs;
+  Tensor epochs, status_dev;
   int* abort_host = nullptr;  // mapped pinned words: [0] abort (host -> device), [1] status (device -> host)
   int* abort_dev = nullptr;
 
@@ -110,11 +110,13 @@ struct SymmComm {
     }
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(dev));
     epochs = torch::zeros({FB_MAX_BLOCKS}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
+    status_dev = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, dev));
     cuda_check(cudaHostAlloc(reinterpret_cast<void**>(&abort_host), 64 * sizeof(int), cudaHostAllocMapped), "cudaHostAlloc");
     std::memset(abort_host, 0, 64 * sizeof(int));
     cuda_check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&abort_dev), abort_host, 0), "cudaHostGetDevicePointer");
     ctx.epochs = epochs.data_ptr();
     ctx.status = abort_dev + 32;   // its own cache line; the host reads it without a device sync
+    ctx.status_dev = status_dev.data_ptr();
     ctx.abort = abort_dev;
     ctx.timeout_ns = timeout_ns;
     ctx.rank = rank;
@@ -139,8 +141,12 @@ struct SymmComm {
     cudaDeviceSynchronize();
     return poll_status();
   }
-  void clear_status() { *reinterpret_cast<volatile int*>(abort_host + 32) = 0; }
-  uint64_t status_device_address() const { return reinterpret_cast<uint64_t>(abort_dev + 32); }
+  void clear_status() {
+    *reinterpret_cast<volatile int*>(abort_host + 32) = 0;
+    status_dev.zero_();
+  }
+  // Device-memory copy of the status word: what kernels on the hot path (the optimizers' skip check) read.
+  uint64_t status_device_address() const { return reinterpret_cast<uint64_t>(status_dev.data_ptr()); }
   void set_mc(uint64_t addr) { ctx.mc = reinterpret_cast<void*>(addr); }
   bool has_mc() const { return ctx.mc != nullptr; }
   // After a wait gave up the per-block epochs of the ranks no longer agree: start again from zero

@@ -55,7 +55,8 @@ Tensor& status_word(int device) {
 
 // ------------------------------------------------------------------------------------------ GEMM
 void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, const OptTensor& bias, int epi,
-          const OptTensor& aux, const OptTensor& alpha, bool accumulate, int split_k, int config, const OptTensor& ts) {
+          const OptTensor& aux, const OptTensor& alpha, bool accumulate, int split_k, int config, const OptTensor& ts,
+          const OptTensor& m_dyn, const OptTensor& k_dyn) {
   want_cuda(a, "a");
   c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(is_bf16(a) && is_bf16(b), "gemm operands must be bf16");
@@ -73,11 +74,17 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, c
   if (alpha.has_value()) TORCH_CHECK(alpha->scalar_type() == at::kFloat && alpha->numel() == 1, "alpha must be one fp32");
   Tensor& st = status_word(a.get_device());
   if (ts.has_value()) TORCH_CHECK(ts->is_cuda() && ts->scalar_type() == at::kLong && ts->numel() >= 8 * 160, "ts must be int64 [>=1280]");
-  int rc = fb_gemm_bf16_ts(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+  auto dyn_ptr = [](const OptTensor& t) -> const int* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->numel() >= 1, "dynamic size must be an int32 CUDA tensor");
+    return t->data_ptr<int>();
+  };
+  int rc = fb_gemm_bf16_dyn(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
                         out.stride(0), a_mn, b_mn, out.scalar_type() == at::kFloat, ptr<const void>(bias),
                         bias.has_value() && bias->scalar_type() == at::kFloat, epi, ptr<void>(aux),
                         aux.has_value() ? aux->stride(0) : 0, ptr<const float>(alpha), accumulate, split_k, config,
-                        st.data_ptr<int>(), ts.has_value() ? reinterpret_cast<long long*>(ts->data_ptr<int64_t>()) : nullptr, stream_of(a));
+                        st.data_ptr<int>(), ts.has_value() ? reinterpret_cast<long long*>(ts->data_ptr<int64_t>()) : nullptr,
+                        dyn_ptr(m_dyn), dyn_ptr(k_dyn), stream_of(a));
   check(rc, "fb_gemm_bf16");
 }
 
@@ -176,13 +183,47 @@ Tensor dropout(const Tensor& x, double p, uint64_t seed, const OptTensor& seed_d
   check(fb_dropout(x.data_ptr(), y.data_ptr(), x.numel(), (float)p, seed, seed_ptr(seed_dev), is_bf16(x), stream_of(x)), "fb_dropout");
   return y;
 }
-void colsum(const Tensor& x, Tensor& out) {
+void colsum(const Tensor& x, Tensor& out, const OptTensor& rows_dyn) {
   want_float_kind(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1);
   want_f32(out, "out");
   TORCH_CHECK(out.numel() == x.size(1));
-  check(fb_colsum(x.data_ptr(), out.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), is_bf16(x), stream_of(x)), "fb_colsum");
+  if (rows_dyn.has_value()) TORCH_CHECK(rows_dyn->is_cuda() && rows_dyn->scalar_type() == at::kInt);
+  check(fb_colsum_dyn(x.data_ptr(), out.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), is_bf16(x),
+                      rows_dyn.has_value() ? rows_dyn->data_ptr<int>() : nullptr, stream_of(x)),
+        "fb_colsum");
+}
+// Row compaction (masked-LM): returns {idx int32 [rows], targets_c int64 [rows], counts int32 [2] = {n, n_pad}}.
+std::vector<Tensor> compact_targets(const Tensor& targets, int64_t ignore_index) {
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous());
+  c10::cuda::CUDAGuard guard(targets.device());
+  const int64_t rows = targets.numel();
+  Tensor idx = torch::empty({rows}, torch::dtype(torch::kInt32).device(targets.device()));
+  Tensor tc = torch::empty({rows}, targets.options());
+  Tensor counts = torch::empty({2}, torch::dtype(torch::kInt32).device(targets.device()));
+  check(fb_compact_targets(reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), (int)rows, ignore_index, idx.data_ptr<int>(),
+                           reinterpret_cast<long long*>(tc.data_ptr<int64_t>()), counts.data_ptr<int>(), stream_of(targets)),
+        "fb_compact_targets");
+  return {idx, tc, counts};
+}
+void gather_rows(const Tensor& x, const Tensor& idx, const Tensor& counts, Tensor& xc) {
+  want_float_kind(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && xc.dim() == 2 && x.stride(1) == 1 && xc.stride(1) == 1 && x.sizes() == xc.sizes() && x.scalar_type() == xc.scalar_type());
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.numel() == x.size(0) && counts.scalar_type() == at::kInt && counts.numel() == 2);
+  check(fb_gather_rows(x.data_ptr(), x.stride(0), idx.data_ptr<int>(), counts.data_ptr<int>(), xc.data_ptr(), xc.stride(0), (int)x.size(0),
+                       (int)x.size(1), is_bf16(x), stream_of(x)),
+        "fb_gather_rows");
+}
+void scatter_rows(const Tensor& dxc, const Tensor& idx, const Tensor& counts, Tensor& dx) {
+  want_float_kind(dxc, "dxc");
+  c10::cuda::CUDAGuard guard(dxc.device());
+  TORCH_CHECK(dx.dim() == 2 && dxc.dim() == 2 && dx.stride(1) == 1 && dxc.stride(1) == 1 && dx.sizes() == dxc.sizes() && dx.scalar_type() == dxc.scalar_type());
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.numel() == dx.size(0) && counts.scalar_type() == at::kInt && counts.numel() == 2);
+  check(fb_scatter_rows(dxc.data_ptr(), dxc.stride(0), idx.data_ptr<int>(), counts.data_ptr<int>(), dx.data_ptr(), dx.stride(0), (int)dx.size(0),
+                        (int)dx.size(1), is_bf16(dx), stream_of(dx)),
+        "fb_scatter_rows");
 }
 void embedding_bwd(const Tensor& dy, const Tensor& ids, Tensor& dw, int64_t padding_idx) {
   want_float_kind(dy, "dy");
@@ -205,7 +246,8 @@ void cast_into(const Tensor& x, Tensor& y, double scale) {
 // ------------------------------------------------------------------------------------------- CE
 // logits [rows, V] (unit inner stride). Returns {loss (0-dim fp32), dlogits, count_inv}.
 // With `inplace` the gradient overwrites the logits.
-std::vector<Tensor> softmax_ce(Tensor& logits, const Tensor& targets, int64_t ignore_index, bool want_grad, bool inplace) {
+std::vector<Tensor> softmax_ce(Tensor& logits, const Tensor& targets, int64_t ignore_index, bool want_grad, bool inplace,
+                               const OptTensor& counts) {
   want_float_kind(logits, "logits");
   c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [rows, V] with unit inner stride");
@@ -222,9 +264,11 @@ std::vector<Tensor> softmax_ce(Tensor& logits, const Tensor& targets, int64_t ig
       dl = torch::empty({rows, ld}, logits.options()).narrow(1, 0, V);
     }
   }
-  int rc = fb_softmax_ce(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), (int)rows, (int)V, ignore_index,
-                         want_grad ? dl.data_ptr() : nullptr, want_grad ? dl.stride(0) : 0, count_inv.data_ptr<float>(),
-                         row_loss.data_ptr<float>(), loss.data_ptr<float>(), is_bf16(logits), stream_of(logits));
+  if (counts.has_value()) TORCH_CHECK(counts->is_cuda() && counts->scalar_type() == at::kInt && counts->numel() == 2);
+  int rc = fb_softmax_ce_dyn(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), (int)rows, (int)V, ignore_index,
+                             want_grad ? dl.data_ptr() : nullptr, want_grad ? dl.stride(0) : 0, count_inv.data_ptr<float>(),
+                             row_loss.data_ptr<float>(), loss.data_ptr<float>(), is_bf16(logits),
+                             counts.has_value() ? counts->data_ptr<int>() : nullptr, stream_of(logits));
   check(rc, "fb_softmax_ce");
   return {loss, dl, count_inv};
 }
@@ -535,7 +579,8 @@ PYBIND11_MODULE(_C, m) {
   m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("bias") = py::none(), py::arg("epi") = 0, py::arg("aux") = py::none(), py::arg("alpha") = py::none(),
-        py::arg("accumulate") = false, py::arg("split_k") = 1, py::arg("config") = -1, py::arg("ts") = py::none());
+        py::arg("accumulate") = false, py::arg("split_k") = 1, py::arg("config") = -1, py::arg("ts") = py::none(),
+        py::arg("m_dyn") = py::none(), py::arg("k_dyn") = py::none());
   m.def("gemm_pick_config", &gemm_pick_config);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
@@ -547,10 +592,14 @@ PYBIND11_MODULE(_C, m) {
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("dropout", &dropout, py::arg("x"), py::arg("p"), py::arg("seed"), py::arg("seed_dev") = py::none());
-  m.def("colsum", &colsum);
+  m.def("colsum", &colsum, py::arg("x"), py::arg("out"), py::arg("rows_dyn") = py::none());
+  m.def("compact_targets", &compact_targets);
+  m.def("gather_rows", &gather_rows);
+  m.def("scatter_rows", &scatter_rows);
   m.def("cast_into", &cast_into);
   m.def("embedding_bwd", &embedding_bwd);
-  m.def("softmax_ce", &softmax_ce);
+  m.def("softmax_ce", &softmax_ce, py::arg("logits"), py::arg("targets"), py::arg("ignore_index"), py::arg("want_grad"), py::arg("inplace"),
+        py::arg("counts") = py::none());
   m.def("scale_rows", &scale_rows);
   m.def("adam_step", &adam_step, py::arg("p"), py::arg("g"), py::arg("m"), py::arg("v"), py::arg("p16"), py::arg("hyper"),
         py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("grad_scale") = py::none(), py::arg("skip") = 0);

@@ -47,6 +47,7 @@ struct SymmCtx {
   uint32_t* epochs;              // local: one epoch counter per block
   const int* abort;              // optional host-mapped abort word
   int* status;                   // status word (host-mapped when the host wants to poll it without a sync)
+  int* status_dev;               // the same word in device memory (read by kernels, e.g. the optimizers' skip check)
   long long timeout_ns;          // bound of every wait
   char* mc;                      // multicast address of the payload buffer (nullptr: no NVLS)
   int rank, world;
@@ -69,7 +70,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 // The status word may live in host-mapped memory (the host polls it without a sync), where device
 // atomics are not dependable: first writer wins by a plain check-then-store, made visible system-wide.
-__device__ __forceinline__ void set_status_sys(int* status, int code) {
+__device__ __forceinline__ void set_status_sys(int* status, int* status_dev, int code) {
+  if (status_dev) atomicCAS(status_dev, 0, code);
   if (!status) return;
   volatile int* s = status;
   if (*s == 0) {
@@ -117,7 +119,7 @@ __device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, uint32_t& e
     }
     if (fail) {
       *sh_fail = 1;
-      set_status_sys(c.status, fail);
+      set_status_sys(c.status, c.status_dev, fail);
       st_release_sys(c.sig[t] + FB_SIGNAL_POISON_INDEX, 1u);   // tell peer t (and this rank's own later launches)
     }
   }
@@ -595,6 +597,7 @@ static SymmCtx make_ctx(const fb_symm_ctx* h) {
   c.epochs = static_cast<uint32_t*>(h->epochs);
   c.abort = static_cast<const int*>(h->abort);
   c.status = static_cast<int*>(h->status);
+  c.status_dev = static_cast<int*>(h->status_dev);
   c.timeout_ns = h->timeout_ns > 0 ? h->timeout_ns : 2000000000LL;
   c.mc = static_cast<char*>(h->mc);
   c.rank = h->rank;

@@ -44,7 +44,9 @@ typedef struct fb_symm_ctx {
   void* sig[FB_MAX_RANKS];   /* peer-mapped signal pads (FB_SIGNAL_PAD_BYTES, zeroed)    */
   void* epochs;              /* local: FB_MAX_BLOCKS uint32, zeroed                      */
   const void* abort;         /* optional device-visible int the host may set to 1        */
-  void* status;              /* local int: 0 ok, else the code of the wait that gave up  */
+  void* status;              /* int: 0 ok, else the code of the wait that gave up (may be host-mapped) */
+  void* status_dev;          /* optional device-memory copy of the same word, for kernels that
+                                must look at it on their hot path (the optimizers' `skip`) */
   long long timeout_ns;      /* bound of every device-side wait; 0 = 2 s                 */
   void* mc;                  /* multicast (NVLS) address of the payload buffer, or NULL  */
   int rank, world;
@@ -63,6 +65,15 @@ int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int N, int K, 
                     long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias, int bias_fp32, int epi,
                     void* aux, long long ldaux, const float* alpha, int accumulate, int split_k, int config,
                     int* status, long long* ts, void* stream);
+/* Same, with device-side problem sizes: the kernel works on min(M, *m_dyn) rows and min(K, *k_dyn) of the
+ * reduction (either pointer may be NULL). The values are read on the device after the preceding kernels of
+ * the stream have finished, so a captured graph replays with whatever an earlier kernel computed. Rows of
+ * A past *m_dyn inside the last tile, and rows of both operands past *k_dyn inside the last 64-wide K
+ * block, are still read: the producer of the operands zero-fills them. */
+int fb_gemm_bf16_dyn(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                     long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias, int bias_fp32, int epi,
+                     void* aux, long long ldaux, const float* alpha, int accumulate, int split_k, int config,
+                     int* status, long long* ts, const int* m_dyn, const int* k_dyn, void* stream);
 int fb_gemm_pick_config(int M, int N, int K, int split_k);
 
 /* ---- attention ----------------------------------------------------------------------------- */
@@ -92,12 +103,30 @@ int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int tanh_a
 int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, const unsigned long long* seed_dev,
                int is_bf16, void* stream);
 int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream);
+/* As fb_colsum over the first min(rows, *rows_dyn) rows (device-side count). */
+int fb_colsum_dyn(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, const int* rows_dyn, void* stream);
+/* Row compaction for losses that ignore most rows (masked-LM): idx[i] = position of the i-th row whose target is
+ * not `ignore_index`, targets_c[i] its target (ignore_index past the count), counts = {n, n rounded up to 256 and
+ * clipped to rows}. One launch; idx and targets_c hold `rows` entries. */
+int fb_compact_targets(const long long* targets, int rows, long long ignore_index, int* idx, long long* targets_c,
+                       int* counts, void* stream);
+/* xc[i] = x[idx[i]] for i < counts[0], zero rows up to counts[1], later rows untouched (bf16 or fp32 rows of `cols`). */
+int fb_gather_rows(const void* x, long long ld, const int* idx, const int* counts, void* xc, long long ldc, int rows,
+                   int cols, int is_bf16, void* stream);
+/* dx[idx[i]] = dxc[i] for i < counts[0]; dx must be zeroed by the caller. */
+int fb_scatter_rows(const void* dxc, long long ldc, const int* idx, const int* counts, void* dx, long long ld, int rows,
+                    int cols, int is_bf16, void* stream);
 int fb_embedding_bwd(const void* dy, const long long* ids, float* dw, long long tokens, int dim, long long vocab,
                      long long padding_idx, int is_bf16, void* stream);
 int fb_cast(const void* x, void* y, long long n, float scale, int in_bf16, int out_bf16, void* stream);
 int fb_softmax_ce(const void* logits, long long ld, const long long* targets, int rows, int V,
                   long long ignore_index, void* dlogits, long long ldd, float* count_inv, float* row_loss,
                   float* loss, int is_bf16, void* stream);
+/* As fb_softmax_ce for compacted rows: `counts` = {n, n_pad} on the device; rows past n_pad are neither read nor
+ * written, rows in [n, n_pad) get a zero gradient. */
+int fb_softmax_ce_dyn(const void* logits, long long ld, const long long* targets, int rows, int V,
+                      long long ignore_index, void* dlogits, long long ldd, float* count_inv, float* row_loss,
+                      float* loss, int is_bf16, const int* counts, void* stream);
 int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream);
 
 /* ---- batch norm (NCHW, training), fused ReLU / residual add --------------------------------- */

@@ -57,6 +57,7 @@ __device__ __forceinline__ bool bn_aligned(const void* p) {
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads)
 bn_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, int N, int C, int HW) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   __shared__ float scratch[32];
   const int c = blockIdx.x, s = blockIdx.y;
@@ -95,6 +96,7 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, const f
                 const float* __restrict__ beta, const float* __restrict__ partial, float* __restrict__ running_mean,
                 float* __restrict__ running_var, float* __restrict__ save_mean, float* __restrict__ save_rstd,
                 T* __restrict__ y, int N, int C, int HW, float eps, float momentum, int relu, int training) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const int c = blockIdx.x, s = blockIdx.y;
   float mean, rstd;
@@ -152,6 +154,7 @@ __global__ void __launch_bounds__(kBnThreads)
 bn_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y,
                      const float* __restrict__ save_mean, const float* __restrict__ save_rstd, float* __restrict__ partial,
                      int N, int C, int HW, int relu) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   __shared__ float scratch[32];
   const int c = blockIdx.x, s = blockIdx.y;
@@ -195,6 +198,7 @@ bn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* 
                     const float* __restrict__ save_mean, const float* __restrict__ save_rstd, const float* __restrict__ partial,
                     T* __restrict__ dx, T* __restrict__ dres, float* __restrict__ dgamma, float* __restrict__ dbeta,
                     int accumulate, int N, int C, int HW, int relu) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const int c = blockIdx.x, s = blockIdx.y;
   float s1 = 0.f, s2 = 0.f;
@@ -343,6 +347,7 @@ __global__ void __launch_bounds__(kBnThreads)
 bn_nhwc_stats_kernel(const T* __restrict__ x, float* __restrict__ partial, unsigned int* __restrict__ counter,
                      float* __restrict__ running_mean, float* __restrict__ running_var, float* __restrict__ save_mean,
                      float* __restrict__ save_rstd, long long P, int C, float eps, float momentum) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   extern __shared__ float sm[];
   const NhwcMap<T> m(C);
@@ -383,6 +388,7 @@ bn_nhwc_apply_kernel(const T* __restrict__ x, const T* __restrict__ residual, co
                      T* __restrict__ y, long long P, int C, int relu, const float* __restrict__ sums, float* __restrict__ save_mean,
                      float* __restrict__ save_rstd, float* __restrict__ running_mean, float* __restrict__ running_var, float eps,
                      float momentum) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const NhwcMap<T> m(C);
   if (!m.active()) return;
@@ -431,6 +437,7 @@ bn_nhwc_bwd_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ x, con
                           const float* __restrict__ rstd, float* __restrict__ partial, unsigned int* __restrict__ counter,
                           float* __restrict__ fold, float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate,
                           long long P, int C, int relu) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   extern __shared__ float sm[];
   const NhwcMap<T> m(C);
@@ -470,6 +477,7 @@ __global__ void __launch_bounds__(kBnThreads)
 bn_nhwc_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ gamma,
                          const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ fold,
                          T* __restrict__ dx, T* __restrict__ dres, long long P, int C, int relu) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const NhwcMap<T> m(C);
   if (!m.active()) return;
@@ -537,19 +545,19 @@ extern "C" int fb_bn_nhwc_fwd(const void* x, const void* residual, const float* 
   if (is_bf16) {
     using T = __nv_bfloat16;
     if (training)
-      bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
+      launch_pdl(bn_nhwc_stats_kernel<T>, dim3(grid), dim3(kBnThreads), smem, st, static_cast<const T*>(x), scratch, counter, running_mean, running_var,
                                                              save_mean, save_rstd, P, C, eps, momentum);
     else return -6;   // evaluation mode goes through the framework's generic path
-    bn_nhwc_apply_kernel<T, false><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+    launch_pdl(bn_nhwc_apply_kernel<T, false>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
                                                                save_rstd, static_cast<T*>(y), P, C, relu, nullptr, nullptr, nullptr, nullptr,
                                                                nullptr, 0.f, 0.f);
   } else {
     using T = float;
     if (training)
-      bn_nhwc_stats_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(x), scratch, counter, running_mean, running_var,
+      launch_pdl(bn_nhwc_stats_kernel<T>, dim3(grid), dim3(kBnThreads), smem, st, static_cast<const T*>(x), scratch, counter, running_mean, running_var,
                                                              save_mean, save_rstd, P, C, eps, momentum);
     else return -6;
-    bn_nhwc_apply_kernel<T, false><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
+    launch_pdl(bn_nhwc_apply_kernel<T, false>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, mean,
                                                                save_rstd, static_cast<T*>(y), P, C, relu, nullptr, nullptr, nullptr, nullptr,
                                                                nullptr, 0.f, 0.f);
   }
@@ -569,12 +577,12 @@ extern "C" int fb_bn_nhwc_fwd_sums(const void* x, const void* residual, const fl
   const int grid = nhwc_grid(P, C, V);
   if (is_bf16) {
     using T = __nv_bfloat16;
-    bn_nhwc_apply_kernel<T, true><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
+    launch_pdl(bn_nhwc_apply_kernel<T, true>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
                                                               nullptr, static_cast<T*>(y), P, C, relu, sums, save_mean, save_rstd, running_mean,
                                                               running_var, eps, momentum);
   } else {
     using T = float;
-    bn_nhwc_apply_kernel<T, true><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
+    launch_pdl(bn_nhwc_apply_kernel<T, true>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, nullptr,
                                                               nullptr, static_cast<T*>(y), P, C, relu, sums, save_mean, save_rstd, running_mean,
                                                               running_var, eps, momentum);
   }
@@ -595,15 +603,15 @@ extern "C" int fb_bn_nhwc_bwd(const void* dy, const void* x, const void* y, cons
   float* fold = scratch + static_cast<long long>(kBnMaxBlocks) * 2 * C;
   if (is_bf16) {
     using T = __nv_bfloat16;
-    bn_nhwc_bwd_reduce_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_nhwc_bwd_reduce_kernel<T>, dim3(grid), dim3(kBnThreads), smem, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                                 save_mean, save_rstd, scratch, counter, fold, dgamma, dbeta, accumulate, P, C, relu);
-    bn_nhwc_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
+    launch_pdl(bn_nhwc_bwd_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
                                                             save_mean, save_rstd, fold, static_cast<T*>(dx), static_cast<T*>(dresidual), P, C, relu);
   } else {
     using T = float;
-    bn_nhwc_bwd_reduce_kernel<T><<<grid, kBnThreads, smem, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_nhwc_bwd_reduce_kernel<T>, dim3(grid), dim3(kBnThreads), smem, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                                 save_mean, save_rstd, scratch, counter, fold, dgamma, dbeta, accumulate, P, C, relu);
-    bn_nhwc_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
+    launch_pdl(bn_nhwc_bwd_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y), gamma,
                                                             save_mean, save_rstd, fold, static_cast<T*>(dx), static_cast<T*>(dresidual), P, C, relu);
   }
   return static_cast<int>(cudaGetLastError());
@@ -621,14 +629,14 @@ extern "C" int fb_bn_fwd(const void* x, const void* residual, const float* gamma
   dim3 grid(C, kBnSplits);
   if (is_bf16) {
     using T = __nv_bfloat16;
-    if (training) bn_stats_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), scratch, N, C, HW);
-    bn_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, scratch,
+    if (training) launch_pdl(bn_stats_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), scratch, N, C, HW);
+    launch_pdl(bn_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, scratch,
                                                     running_mean, running_var, save_mean, save_rstd, static_cast<T*>(y), N, C, HW,
                                                     eps, momentum, relu, training);
   } else {
     using T = float;
-    if (training) bn_stats_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), scratch, N, C, HW);
-    bn_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, scratch,
+    if (training) launch_pdl(bn_stats_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), scratch, N, C, HW);
+    launch_pdl(bn_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(x), static_cast<const T*>(residual), gamma, beta, scratch,
                                                     running_mean, running_var, save_mean, save_rstd, static_cast<T*>(y), N, C, HW,
                                                     eps, momentum, relu, training);
   }
@@ -644,16 +652,16 @@ extern "C" int fb_bn_bwd(const void* dy, const void* x, const void* y, const flo
   dim3 grid(C, kBnSplits);
   if (is_bf16) {
     using T = __nv_bfloat16;
-    bn_bwd_reduce_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_bwd_reduce_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                          save_mean, save_rstd, scratch, N, C, HW, relu);
-    bn_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_bwd_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                         gamma, save_mean, save_rstd, scratch, static_cast<T*>(dx),
                                                         static_cast<T*>(dresidual), dgamma, dbeta, accumulate, N, C, HW, relu);
   } else {
     using T = float;
-    bn_bwd_reduce_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_bwd_reduce_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                          save_mean, save_rstd, scratch, N, C, HW, relu);
-    bn_bwd_apply_kernel<T><<<grid, kBnThreads, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
+    launch_pdl(bn_bwd_apply_kernel<T>, dim3(grid), dim3(kBnThreads), 0, st, static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(y),
                                                         gamma, save_mean, save_rstd, scratch, static_cast<T*>(dx),
                                                         static_cast<T*>(dresidual), dgamma, dbeta, accumulate, N, C, HW, relu);
   }

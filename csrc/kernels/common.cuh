@@ -169,6 +169,13 @@ __device__ __forceinline__ float dgelu_tanh_fast(float x) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// First statements of every kernel launched through `launch_pdl`: wait for the predecessor, then let the
+// successor's blocks be scheduled as this grid's blocks retire.
+__device__ __forceinline__ void pdl_entry() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
 // Host switch: FLODL_B200_PDL=0 turns the launch attribute off everywhere.
 inline bool pdl_enabled() {
   static const bool on = [] {
@@ -176,6 +183,28 @@ inline bool pdl_enabled() {
     return !(e && e[0] == '0');
   }();
   return on;
+}
+
+
+// `kern<<<grid, block, smem, stream>>>(args...)` with the programmatic-serialization attribute: the
+// launch latency and block ramp-up of this kernel overlap the tail of the one before it in the stream
+// (which matters when a training step is hundreds of kernels of a few microseconds each). The kernel
+// must start with `pdl_entry()`.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 }  // namespace fb

@@ -36,6 +36,7 @@ __device__ __forceinline__ float gelu_bwd_f(float x, int tanh_approx) {
 
 template <typename T>
 __global__ void gelu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, int tanh_approx) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * V;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
@@ -54,6 +55,7 @@ __global__ void gelu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long
 template <typename T>
 __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
                                 long long n, int tanh_approx) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * V;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V; i < n; i += stride) {
@@ -75,6 +77,7 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
 template <typename T>
 __global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, float p,
                                unsigned long long seed_in, const unsigned long long* __restrict__ seed_dev) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const unsigned long long seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   const float inv_keep = 1.f / (1.f - p);
@@ -101,7 +104,9 @@ __global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, long 
 // out[c] (+)= sum_r x[r][c]; a 32x32 tile per block so reads stay coalesced.
 template <typename T>
 __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, int cols,
-                              long long ld, int rows_per_block) {
+                              long long ld, int rows_per_block, const int* __restrict__ rows_dyn) {
+  pdl_entry();
+  if (rows_dyn) rows = min(rows, *rows_dyn);
   __shared__ float tile[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   const int r0 = blockIdx.y * rows_per_block;
@@ -123,7 +128,10 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
 // a block different rows; partials meet in shared memory, one atomicAdd per column per block.
 template <typename T>
 __global__ void __launch_bounds__(256)
-colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, int cols, long long ld, int rows_per_block) {
+colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, int cols, long long ld, int rows_per_block,
+                  const int* __restrict__ rows_dyn) {
+  pdl_entry();
+  if (rows_dyn) rows = min(rows, *rows_dyn);
   constexpr int V = VecIO<T>::kVec;
   __shared__ float red[8][32 * V + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -161,10 +169,106 @@ colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, int rows, in
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Row compaction for losses that ignore most rows (masked-LM: ~15 % of the positions carry a label).
+// The vocabulary projection, the softmax and their backward GEMMs then run on the active rows only;
+// ignored rows contribute neither loss nor gradient, so the result is the same as for the full matrix.
+// Counts stay on the device, buffers keep their full static size: the sequence is graph-capturable.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+compact_targets_kernel(const long long* __restrict__ targets, int rows, long long ignore_index, int* __restrict__ idx,
+                       long long* __restrict__ targets_c, int* __restrict__ counts) {
+  pdl_entry();
+  __shared__ int warp_tot[32];
+  __shared__ int base_sh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) base_sh = 0;
+  __syncthreads();
+  for (int r0 = 0; r0 < rows; r0 += 1024) {
+    const int r = r0 + threadIdx.x;
+    const long long t = (r < rows) ? targets[r] : ignore_index;
+    const bool act = (r < rows) && t != ignore_index;
+    const unsigned m = __ballot_sync(0xffffffffu, act);
+    const int before = __popc(m & ((1u << lane) - 1u));
+    if (lane == 0) warp_tot[warp] = __popc(m);
+    __syncthreads();
+    int woff = 0, tot = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = warp_tot[w];
+      if (w < warp) woff += c;
+      tot += c;
+    }
+    const int base = base_sh;
+    if (act) {
+      const int o = base + woff + before;
+      idx[o] = r;
+      targets_c[o] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) base_sh = base + tot;
+    __syncthreads();
+  }
+  const int n = base_sh;
+  int n_pad = (n + 255) / 256 * 256;
+  if (n_pad > rows) n_pad = rows;
+  for (int i = n + threadIdx.x; i < rows; i += 1024) {   // the tail: no row, no label
+    idx[i] = 0;
+    targets_c[i] = ignore_index;
+  }
+  if (threadIdx.x == 0) {
+    counts[0] = n;
+    counts[1] = n_pad;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const T* __restrict__ x, long long ld, const int* __restrict__ idx, const int* __restrict__ counts,
+                   T* __restrict__ xc, long long ldc, int cols) {
+  pdl_entry();
+  const int i = blockIdx.x;
+  const int n = counts[0], n_pad = counts[1];
+  if (i >= n_pad) return;
+  constexpr int V = VecIO<T>::kVec;
+  T* dst = xc + static_cast<long long>(i) * ldc;
+  const T* src = x + static_cast<long long>(i < n ? idx[i] : 0) * ld;
+  const bool vec = (cols % V == 0) && (ld % V == 0) && (ldc % V == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(xc) & 15) == 0);
+  if (vec) {
+    for (int c = threadIdx.x * V; c < cols; c += blockDim.x * V) {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (i < n) v = *reinterpret_cast<const uint4*>(src + c);
+      *reinterpret_cast<uint4*>(dst + c) = v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) VecIO<T>::put(dst + c, i < n ? VecIO<T>::get(src + c) : 0.f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+scatter_rows_kernel(const T* __restrict__ dxc, long long ldc, const int* __restrict__ idx, const int* __restrict__ counts,
+                    T* __restrict__ dx, long long ld, int cols) {
+  pdl_entry();
+  const int i = blockIdx.x;
+  if (i >= counts[0]) return;
+  constexpr int V = VecIO<T>::kVec;
+  const T* src = dxc + static_cast<long long>(i) * ldc;
+  T* dst = dx + static_cast<long long>(idx[i]) * ld;
+  const bool vec = (cols % V == 0) && (ld % V == 0) && (ldc % V == 0) && ((reinterpret_cast<uintptr_t>(dx) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(dxc) & 15) == 0);
+  if (vec) {
+    for (int c = threadIdx.x * V; c < cols; c += blockDim.x * V) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) VecIO<T>::put(dst + c, VecIO<T>::get(src + c));
+  }
+}
+
 // dW[ids[t]][:] += dy[t][:] for an embedding table (fp32 accumulation, rows equal to padding_idx skipped).
 template <typename T>
 __global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long long* __restrict__ ids, float* __restrict__ dw,
                                      long long tokens, int dim, long long vocab, long long padding_idx) {
+  pdl_entry();
   const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
   const long long id = ids[t];
@@ -176,6 +280,7 @@ __global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long long* 
 
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long long n, float scale) {
+  pdl_entry();
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     VecIO<TO>::put(y + i, VecIO<TI>::get(x + i) * scale);
@@ -194,10 +299,9 @@ extern "C" int fb_gelu_fwd(const void* x, void* y, long long n, int tanh_approx,
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    fb::gelu_fwd_kernel<__nv_bfloat16><<<fb::grid_for(n, 8, 256), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, tanh_approx);
+    fb::launch_pdl(fb::gelu_fwd_kernel<__nv_bfloat16>, dim3(fb::grid_for(n, 8, 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, tanh_approx);
   else
-    fb::gelu_fwd_kernel<float><<<fb::grid_for(n, 4, 256), 256, 0, st>>>(static_cast<const float*>(x),
+    fb::launch_pdl(fb::gelu_fwd_kernel<float>, dim3(fb::grid_for(n, 4, 256)), dim3(256), 0, st, static_cast<const float*>(x),
                                                                         static_cast<float*>(y), n, tanh_approx);
   return static_cast<int>(cudaGetLastError());
 }
@@ -207,12 +311,10 @@ extern "C" int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n,
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    fb::gelu_bwd_kernel<__nv_bfloat16><<<fb::grid_for(n, 8, 256), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+    fb::launch_pdl(fb::gelu_bwd_kernel<__nv_bfloat16>, dim3(fb::grid_for(n, 8, 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
         static_cast<__nv_bfloat16*>(dx), n, tanh_approx);
   else
-    fb::gelu_bwd_kernel<float><<<fb::grid_for(n, 4, 256), 256, 0, st>>>(
-        static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<float*>(dx), n, tanh_approx);
+    fb::launch_pdl(fb::gelu_bwd_kernel<float>, dim3(fb::grid_for(n, 4, 256)), dim3(256), 0, st, static_cast<const float*>(dy), static_cast<const float*>(x), static_cast<float*>(dx), n, tanh_approx);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -221,16 +323,20 @@ extern "C" int fb_dropout(const void* x, void* y, long long n, float p, unsigned
   if (n <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    fb::dropout_kernel<__nv_bfloat16><<<fb::grid_for(n, 8, 256), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, p, seed, seed_dev);
+    fb::launch_pdl(fb::dropout_kernel<__nv_bfloat16>, dim3(fb::grid_for(n, 8, 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, p, seed, seed_dev);
   else
-    fb::dropout_kernel<float><<<fb::grid_for(n, 4, 256), 256, 0, st>>>(static_cast<const float*>(x),
+    fb::launch_pdl(fb::dropout_kernel<float>, dim3(fb::grid_for(n, 4, 256)), dim3(256), 0, st, static_cast<const float*>(x),
                                                                        static_cast<float*>(y), n, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
 // `out` (fp32, `cols` long) is added to: zero it first for a plain column sum.
 extern "C" int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream) {
+  return fb_colsum_dyn(x, out, rows, cols, ld, is_bf16, nullptr, stream);
+}
+
+extern "C" int fb_colsum_dyn(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, const int* rows_dyn,
+                             void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vec = is_bf16 ? 8 : 4;
@@ -238,18 +344,18 @@ extern "C" int fb_colsum(const void* x, float* out, int rows, int cols, long lon
     const int rpbv = 64;
     dim3 gridv((cols + 32 * vec - 1) / (32 * vec), (rows + rpbv - 1) / rpbv);
     if (is_bf16)
-      fb::colsum_vec_kernel<__nv_bfloat16><<<gridv, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld, rpbv);
+      fb::launch_pdl(fb::colsum_vec_kernel<__nv_bfloat16>, dim3(gridv), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld, rpbv, rows_dyn);
     else
-      fb::colsum_vec_kernel<float><<<gridv, 256, 0, st>>>(static_cast<const float*>(x), out, rows, cols, ld, rpbv);
+      fb::launch_pdl(fb::colsum_vec_kernel<float>, dim3(gridv), dim3(256), 0, st, static_cast<const float*>(x), out, rows, cols, ld, rpbv, rows_dyn);
     return static_cast<int>(cudaGetLastError());
   }
   int rpb = 256;
   dim3 grid((cols + 31) / 32, (rows + rpb - 1) / rpb);
   dim3 block(32, 32);
   if (is_bf16)
-    fb::colsum_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld, rpb);
+    fb::launch_pdl(fb::colsum_kernel<__nv_bfloat16>, dim3(grid), dim3(block), 0, st, static_cast<const __nv_bfloat16*>(x), out, rows, cols, ld, rpb, rows_dyn);
   else
-    fb::colsum_kernel<float><<<grid, block, 0, st>>>(static_cast<const float*>(x), out, rows, cols, ld, rpb);
+    fb::launch_pdl(fb::colsum_kernel<float>, dim3(grid), dim3(block), 0, st, static_cast<const float*>(x), out, rows, cols, ld, rpb, rows_dyn);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -258,13 +364,13 @@ extern "C" int fb_cast(const void* x, void* y, long long n, float scale, int in_
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int g = fb::grid_for(n, 4, 256);
   if (in_bf16 && !out_bf16)
-    fb::cast_kernel<__nv_bfloat16, float><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<float*>(y), n, scale);
+    fb::launch_pdl(fb::cast_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<float*>(y), n, scale);
   else if (!in_bf16 && out_bf16)
-    fb::cast_kernel<float, __nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y), n, scale);
+    fb::launch_pdl(fb::cast_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, st, static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y), n, scale);
   else if (in_bf16)
-    fb::cast_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, scale);
+    fb::launch_pdl(fb::cast_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(g), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), n, scale);
   else
-    fb::cast_kernel<float, float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), n, scale);
+    fb::launch_pdl(fb::cast_kernel<float, float>, dim3(g), dim3(256), 0, st, static_cast<const float*>(x), static_cast<float*>(y), n, scale);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -276,10 +382,40 @@ extern "C" int fb_embedding_bwd(const void* dy, const long long* ids, float* dw,
   const int warps = 8;
   const long long grid = (tokens + warps - 1) / warps;
   if (is_bf16)
-    fb::embedding_bwd_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(dy), ids, dw, tokens, dim, vocab, padding_idx);
+    fb::launch_pdl(fb::embedding_bwd_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, static_cast<const __nv_bfloat16*>(dy), ids, dw, tokens, dim, vocab, padding_idx);
   else
-    fb::embedding_bwd_kernel<float><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(static_cast<const float*>(dy), ids, dw,
+    fb::launch_pdl(fb::embedding_bwd_kernel<float>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, static_cast<const float*>(dy), ids, dw,
                                                                                         tokens, dim, vocab, padding_idx);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_compact_targets(const long long* targets, int rows, long long ignore_index, int* idx, long long* targets_c,
+                                  int* counts, void* stream) {
+  if (rows <= 0) return 0;
+  fb::launch_pdl(fb::compact_targets_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), targets, rows, ignore_index, idx, targets_c, counts);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_gather_rows(const void* x, long long ld, const int* idx, const int* counts, void* xc, long long ldc, int rows,
+                              int cols, int is_bf16, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    fb::launch_pdl(fb::gather_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(x), ld, idx, counts,
+                                                                static_cast<__nv_bfloat16*>(xc), ldc, cols);
+  else
+    fb::launch_pdl(fb::gather_rows_kernel<float>, dim3(rows), dim3(128), 0, st, static_cast<const float*>(x), ld, idx, counts, static_cast<float*>(xc), ldc, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int fb_scatter_rows(const void* dxc, long long ldc, const int* idx, const int* counts, void* dx, long long ld, int rows,
+                               int cols, int is_bf16, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    fb::launch_pdl(fb::scatter_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(dxc), ldc, idx, counts,
+                                                                 static_cast<__nv_bfloat16*>(dx), ld, cols);
+  else
+    fb::launch_pdl(fb::scatter_rows_kernel<float>, dim3(rows), dim3(128), 0, st, static_cast<const float*>(dxc), ldc, idx, counts, static_cast<float*>(dx), ld, cols);
   return static_cast<int>(cudaGetLastError());
 }

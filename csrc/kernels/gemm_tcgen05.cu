@@ -58,6 +58,11 @@ struct GemmParams {
   int aux_tma;     // the GELU pre-activation goes out through its own staged TMA store
   int* status;
   long long* ts;   // optional per-CTA timeline (8 slots each), for tuning
+  // Optional device-side problem sizes (produced by an earlier kernel of the stream): the kernel
+  // works on min(M, *m_dyn) rows / min(K, *k_dyn) of the reduction. Buffers and tensor maps keep
+  // their full static size, so a captured graph can replay with a different count every step.
+  const int* m_dyn;
+  const int* k_dyn;
 };
 
 template <int kCG, int kBN>
@@ -358,12 +363,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int group = blockIdx.x / kCG;          // CTA (pair) index
   const int num_groups = gridDim.x / kCG;
 
-  const int num_m = (p.M + BM * kCG - 1) / (BM * kCG);
-  const int num_n = (p.N + kBN - 1) / kBN;
-  const int num_kb = (p.K + BK - 1) / BK;
-  const int kb_per = (num_kb + p.split_k - 1) / p.split_k;
-  const int num_units = num_m * num_n * p.split_k;
-
   if (p.ts && threadIdx.x == 0) {
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
@@ -403,6 +402,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 7] = clock64();
   pdl_wait();
   pdl_launch_dependents();
+
+  int m_eff = p.M, k_eff = p.K;
+  if (p.m_dyn) m_eff = max(0, min(p.M, *p.m_dyn));
+  if (p.k_dyn) k_eff = max(0, min(p.K, *p.k_dyn));
+  const int num_m = (m_eff + BM * kCG - 1) / (BM * kCG);
+  const int num_n = (p.N + kBN - 1) / kBN;
+  const int num_kb = (k_eff + BK - 1) / BK;
+  const int kb_per = (num_kb + p.split_k - 1) / p.split_k;
+  const int num_units = (num_kb > 0) ? num_m * num_n * p.split_k : 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -728,6 +736,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 
 extern "C" int fb_gemm_bf16_ts(const void*, const void*, void*, int, int, int, long long, long long, long long, int, int, int, const void*, int,
                                int, void*, long long, const float*, int, int, int, int*, long long*, void*);
+extern "C" int fb_gemm_bf16_dyn(const void*, const void*, void*, int, int, int, long long, long long, long long, int, int, int, const void*, int,
+                                int, void*, long long, const float*, int, int, int, int*, long long*, const int*, const int*, void*);
 
 extern "C" int fb_gemm_pick_config(int M, int N, int K, int split_k) {
   // Score = SM occupancy of the last wave x a per-tile efficiency prior (bigger tiles re-use
@@ -767,6 +777,15 @@ extern "C" int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int
                                long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias,
                                int bias_fp32, int epi, void* aux, long long ldaux, const float* alpha,
                                int accumulate, int split_k, int config, int* status, long long* ts, void* stream_) {
+  return fb_gemm_bf16_dyn(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, c_fp32, bias, bias_fp32, epi, aux, ldaux, alpha, accumulate, split_k,
+                          config, status, ts, nullptr, nullptr, stream_);
+}
+
+extern "C" int fb_gemm_bf16_dyn(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, const void* bias,
+                                int bias_fp32, int epi, void* aux, long long ldaux, const float* alpha,
+                                int accumulate, int split_k, int config, int* status, long long* ts, const int* m_dyn,
+                                const int* k_dyn, void* stream_) {
   using namespace fb;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -817,6 +836,7 @@ extern "C" int fb_gemm_bf16_ts(const void* A, const void* B, void* C, int M, int
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
   p.bias = bias; p.bias_fp32 = bias_fp32; p.epi = epi; p.aux = aux; p.ldaux = ldaux; p.alpha = alpha;
   p.accumulate = accumulate; p.split_k = split_k; p.status = status; p.ts = ts;
+  p.m_dyn = m_dyn; p.k_dyn = k_dyn;
   switch (config) {
     case 0: return launch_gemm<2, 256>(ta, tb, tc, tx, p, stream);
     case 1: return launch_gemm<1, 256>(ta, tb, tc, tx, p, stream);

@@ -45,6 +45,7 @@ ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const flo
               const float* __restrict__ beta, T* __restrict__ y, T* __restrict__ pre_out,
               float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols, float eps,
               float p_drop, uint64_t seed_in, const unsigned long long* __restrict__ seed_dev) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const uint64_t seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,6 +127,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* 
               const float* __restrict__ rstd, const float* __restrict__ gamma, T* __restrict__ dpre,
               T* __restrict__ dx_drop, float* __restrict__ partial, int rows, int cols, float p_drop,
               uint64_t seed_in, const unsigned long long* __restrict__ seed_dev) {
+  pdl_entry();
   constexpr int V = VecIO<T>::kVec;
   const uint64_t seed = seed_in + (seed_dev ? *seed_dev : 0ull);
   __shared__ float red[kLnWarps][32 * VPL * V + 1];
@@ -222,6 +224,7 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const float* 
 __global__ void __launch_bounds__(256)
 ln_bwd_finalize_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta, int nblocks,
                        int cols, int accumulate) {
+  pdl_entry();
   // block = 32 columns x 8 row-groups; each row-group strides over the partial rows
   __shared__ float rg[8][33], rb[8][33];
   const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
@@ -268,8 +271,7 @@ static int ln_fwd_launch(const void* x, const void* res, const float* gamma, con
                          void* pre, float* mean, float* rstd, int rows, int cols, float eps, float p,
                          uint64_t seed, const unsigned long long* seed_dev, cudaStream_t st) {
   const int grid = (rows + kLnWarps - 1) / kLnWarps;
-  ln_fwd_kernel<T, VPL><<<grid, kLnWarps * 32, 0, st>>>(
-      static_cast<const T*>(x), static_cast<const T*>(res), gamma, beta, static_cast<T*>(y),
+  launch_pdl(ln_fwd_kernel<T, VPL>, dim3(grid), dim3(kLnWarps * 32), 0, st, static_cast<const T*>(x), static_cast<const T*>(res), gamma, beta, static_cast<T*>(y),
       static_cast<T*>(pre), mean, rstd, rows, cols, eps, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
@@ -278,8 +280,7 @@ template <typename T, int VPL>
 static int ln_bwd_launch(const void* dy, const void* pre, const float* mean, const float* rstd,
                          const float* gamma, void* dpre, void* dxd, float* partial, int grid, int rows,
                          int cols, float p, uint64_t seed, const unsigned long long* seed_dev, cudaStream_t st) {
-  ln_bwd_kernel<T, VPL><<<grid, kLnWarps * 32, 0, st>>>(
-      static_cast<const T*>(dy), static_cast<const T*>(pre), mean, rstd, gamma, static_cast<T*>(dpre),
+  launch_pdl(ln_bwd_kernel<T, VPL>, dim3(grid), dim3(kLnWarps * 32), 0, st, static_cast<const T*>(dy), static_cast<const T*>(pre), mean, rstd, gamma, static_cast<T*>(dpre),
       static_cast<T*>(dxd), partial, rows, cols, p, seed, seed_dev);
   return static_cast<int>(cudaGetLastError());
 }
@@ -343,7 +344,7 @@ extern "C" int fb_layernorm_bwd(const void* dy, const void* pre, const float* me
   if (r) return r;
   if (partial && (dgamma || dbeta)) {
     const dim3 fgrid((cols + 31) / 32, accumulate ? 8 : 1);
-    fb::ln_bwd_finalize_kernel<<<fgrid, 256, 0, st>>>(partial, dgamma, dbeta, grid, cols, accumulate);
+    fb::launch_pdl(fb::ln_bwd_finalize_kernel, dim3(fgrid), dim3(256), 0, st, partial, dgamma, dbeta, grid, cols, accumulate);
     return static_cast<int>(cudaGetLastError());
   }
   return 0;

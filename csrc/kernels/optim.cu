@@ -27,9 +27,10 @@ __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
             __nv_bfloat16* __restrict__ p16, long long n, const float* __restrict__ hyper, float b1, float b2,
             float eps, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
+  pdl_entry();
   // `skip`: a device-visible word that a collective sets when it gave up; the update is then left out
   // and the parameters stay as they were, so the host can raise before anything diverged.
-  if (skip && *reinterpret_cast<const volatile int*>(skip) != 0) return;
+  if (skip && __ldg(skip) != 0) return;
   const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], wd = hyper[3];
   const float gs = grad_scale ? *grad_scale : 1.f;
   const float step_size = lr / bc1;
@@ -88,7 +89,8 @@ template <typename TG>
 __global__ void __launch_bounds__(256)
 sgd_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ buf, __nv_bfloat16* __restrict__ p16,
            long long n, const float* __restrict__ hyper, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
-  if (skip && *reinterpret_cast<const volatile int*>(skip) != 0) return;
+  pdl_entry();
+  if (skip && __ldg(skip) != 0) return;
   const float lr = hyper[0], mu = hyper[1], wd = hyper[2];
   const bool first = hyper[3] != 0.f;
   const float gs = grad_scale ? *grad_scale : 1.f;
@@ -110,6 +112,7 @@ sgd_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(256)
 sumsq_partial_kernel(const T* __restrict__ x, long long n, float* __restrict__ partial) {
+  pdl_entry();
   __shared__ float scratch[32];
   constexpr int V = VecIO<T>::kVec;
   float s = 0.f;
@@ -134,6 +137,7 @@ sumsq_partial_kernel(const T* __restrict__ x, long long n, float* __restrict__ p
 // out = {norm, clip coefficient = min(1, max_norm / (norm + 1e-6)) or 1 when max_norm <= 0}
 __global__ void sumsq_finalize_kernel(const float* __restrict__ partial, int nparts, float max_norm,
                                       float extra_scale, float* __restrict__ out) {
+  pdl_entry();
   __shared__ float scratch[32];
   float s = 0.f;
   for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += partial[i];
@@ -158,10 +162,9 @@ extern "C" int fb_adam_step(float* p, const void* g, float* m, float* v, void* p
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   if (g_bf16)
-    fb::adam_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
-        p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale, skip);
+    fb::launch_pdl(fb::adam_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale, skip);
   else
-    fb::adam_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(p, static_cast<const float*>(g), m, v,
+    fb::launch_pdl(fb::adam_kernel<float>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const float*>(g), m, v,
                                                                      static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2,
                                                                      eps, grad_scale, skip);
   return static_cast<int>(cudaGetLastError());
@@ -174,10 +177,9 @@ extern "C" int fb_sgd_step(float* p, const void* g, float* buf, void* p16, long 
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (g_bf16)
-    fb::sgd_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
-        p, static_cast<const __nv_bfloat16*>(g), buf, static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale, skip);
+    fb::launch_pdl(fb::sgd_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const __nv_bfloat16*>(g), buf, static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale, skip);
   else
-    fb::sgd_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(p, static_cast<const float*>(g), buf,
+    fb::launch_pdl(fb::sgd_kernel<float>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const float*>(g), buf,
                                                                     static_cast<__nv_bfloat16*>(p16), n, hyper, grad_scale, skip);
   return static_cast<int>(cudaGetLastError());
 }
@@ -196,10 +198,10 @@ extern "C" int fb_grad_norm(const void* g, long long n, float* partial, float ma
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int parts = fb_grad_norm_parts(n);
   if (is_bf16)
-    fb::sumsq_partial_kernel<__nv_bfloat16><<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(g), n, partial);
+    fb::launch_pdl(fb::sumsq_partial_kernel<__nv_bfloat16>, dim3(parts), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(g), n, partial);
   else
-    fb::sumsq_partial_kernel<float><<<parts, 256, 0, st>>>(static_cast<const float*>(g), n, partial);
-  fb::sumsq_finalize_kernel<<<1, 256, 0, st>>>(partial, parts, max_norm, extra_scale, out);
+    fb::launch_pdl(fb::sumsq_partial_kernel<float>, dim3(parts), dim3(256), 0, st, static_cast<const float*>(g), n, partial);
+  fb::launch_pdl(fb::sumsq_finalize_kernel, dim3(1), dim3(256), 0, st, partial, parts, max_norm, extra_scale, out);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -248,10 +250,10 @@ extern "C" int fb_grad_norm_noalloc(const void* g, long long n, float max_norm, 
   if (parts > kNormScratchFloats) return -4;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_bf16)
-    fb::sumsq_partial_kernel<__nv_bfloat16><<<parts, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(g), n, partial);
+    fb::launch_pdl(fb::sumsq_partial_kernel<__nv_bfloat16>, dim3(parts), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(g), n, partial);
   else
-    fb::sumsq_partial_kernel<float><<<parts, 256, 0, st>>>(static_cast<const float*>(g), n, partial);
-  fb::sumsq_finalize_kernel<<<1, 256, 0, st>>>(partial, parts, max_norm, extra_scale, out);
+    fb::launch_pdl(fb::sumsq_partial_kernel<float>, dim3(parts), dim3(256), 0, st, static_cast<const float*>(g), n, partial);
+  fb::launch_pdl(fb::sumsq_finalize_kernel, dim3(1), dim3(256), 0, st, partial, parts, max_norm, extra_scale, out);
   return static_cast<int>(cudaGetLastError());
 }
 

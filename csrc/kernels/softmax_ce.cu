@@ -26,10 +26,15 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 ce_fwd_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ targets, int rows,
               int V, long long ignore_index, T* __restrict__ dlogits, long long ldd,
-              const float* __restrict__ count_inv, float* __restrict__ row_loss) {
+              const float* __restrict__ count_inv, float* __restrict__ row_loss, const int* __restrict__ counts) {
+  pdl_entry();
   constexpr int VEC = VecIO<T>::kVec;
   __shared__ float scratch[32];
   const int row = blockIdx.x;
+  if (counts && row >= counts[1]) {      // compacted input: nothing lives past the padded count
+    if (row_loss && threadIdx.x == 0) row_loss[row] = 0.f;
+    return;
+  }
   const long long t = targets[row];
   const T* lr = logits + static_cast<long long>(row) * ld;
   T* dr = dlogits ? dlogits + static_cast<long long>(row) * ldd : nullptr;
@@ -108,6 +113,7 @@ ce_fwd_kernel(const T* __restrict__ logits, long long ld, const long long* __res
 // loss = sum(row_loss) / max(count, 1), in a fixed order (deterministic).
 __global__ void ce_finalize_kernel(const float* __restrict__ row_loss, int rows, const float* __restrict__ count_inv,
                                    float* __restrict__ loss) {
+  pdl_entry();
   __shared__ float scratch[32];
   float s = 0.f;
   for (int i = threadIdx.x; i < rows; i += blockDim.x) s += row_loss[i];
@@ -118,6 +124,7 @@ __global__ void ce_finalize_kernel(const float* __restrict__ row_loss, int rows,
 // x[r][c] *= *scalar (device scalar); rows of length `cols` with leading dimension `ld`.
 template <typename T>
 __global__ void scale_rows_kernel(T* __restrict__ x, long long ld, int rows, int cols, const float* __restrict__ scalar) {
+  pdl_entry();
   const float a = *scalar;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     T* xr = x + static_cast<long long>(r) * ld;
@@ -128,21 +135,27 @@ __global__ void scale_rows_kernel(T* __restrict__ x, long long ld, int rows, int
 }  // namespace fb
 
 // count_inv: 2 floats, row_loss: `rows` floats, loss: 1 float (all device memory, caller-owned).
+extern "C" int fb_softmax_ce_dyn(const void* logits, long long ld, const long long* targets, int rows, int V,
+                                 long long ignore_index, void* dlogits, long long ldd, float* count_inv,
+                                 float* row_loss, float* loss, int is_bf16, const int* counts, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  fb::launch_pdl(fb::ce_count_kernel, dim3(1), dim3(1024), 0, st, targets, rows, ignore_index, count_inv);
+  if (is_bf16)
+    fb::launch_pdl(fb::ce_fwd_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(logits), ld, targets, rows,
+                                                           V, ignore_index, static_cast<__nv_bfloat16*>(dlogits), ldd,
+                                                           count_inv, row_loss, counts);
+  else
+    fb::launch_pdl(fb::ce_fwd_kernel<float>, dim3(rows), dim3(256), 0, st, static_cast<const float*>(logits), ld, targets, rows, V,
+                                                   ignore_index, static_cast<float*>(dlogits), ldd, count_inv, row_loss, counts);
+  if (loss) fb::launch_pdl(fb::ce_finalize_kernel, dim3(1), dim3(1024), 0, st, row_loss, rows, count_inv, loss);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int fb_softmax_ce(const void* logits, long long ld, const long long* targets, int rows, int V,
                              long long ignore_index, void* dlogits, long long ldd, float* count_inv,
                              float* row_loss, float* loss, int is_bf16, void* stream) {
-  if (rows <= 0) return 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  fb::ce_count_kernel<<<1, 1024, 0, st>>>(targets, rows, ignore_index, count_inv);
-  if (is_bf16)
-    fb::ce_fwd_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, targets, rows,
-                                                           V, ignore_index, static_cast<__nv_bfloat16*>(dlogits), ldd,
-                                                           count_inv, row_loss);
-  else
-    fb::ce_fwd_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(logits), ld, targets, rows, V,
-                                                   ignore_index, static_cast<float*>(dlogits), ldd, count_inv, row_loss);
-  if (loss) fb::ce_finalize_kernel<<<1, 1024, 0, st>>>(row_loss, rows, count_inv, loss);
-  return static_cast<int>(cudaGetLastError());
+  return fb_softmax_ce_dyn(logits, ld, targets, rows, V, ignore_index, dlogits, ldd, count_inv, row_loss, loss, is_bf16, nullptr, stream);
 }
 
 extern "C" int fb_scale_rows(void* x, long long ld, int rows, int cols, const float* scalar, int is_bf16, void* stream) {
@@ -150,8 +163,8 @@ extern "C" int fb_scale_rows(void* x, long long ld, int rows, int cols, const fl
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   if (is_bf16)
-    fb::scale_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(x), ld, rows, cols, scalar);
+    fb::launch_pdl(fb::scale_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, static_cast<__nv_bfloat16*>(x), ld, rows, cols, scalar);
   else
-    fb::scale_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(x), ld, rows, cols, scalar);
+    fb::launch_pdl(fb::scale_rows_kernel<float>, dim3(grid), dim3(256), 0, st, static_cast<float*>(x), ld, rows, cols, scalar);
   return static_cast<int>(cudaGetLastError());
 }

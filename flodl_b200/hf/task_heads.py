@@ -66,7 +66,7 @@ class TiedDecoder(Linear):
     def forward(self, x):
         if self._labels is not None:
             return Variable.wrap(_ops.linear_cross_entropy(x.t, self.weight.t, None if self.bias is None else self.bias.t,
-                                                           self._labels.reshape(-1), self.ignore_index))
+                                                           self._labels.reshape(-1), self.ignore_index, sparse_targets=True))
         return super().forward(x)
 
 

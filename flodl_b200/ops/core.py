@@ -198,34 +198,38 @@ _EPI = {None: 0, "gelu": 1, "gelu_tanh": 3}
 _DEPI = {"gelu": 2, "gelu_tanh": 4}
 
 
-def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=None):
+def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, alpha=None, k_dyn=None, k_hint: Optional[int] = None):
     """dW[N,K] = dy2^T x2 on the tensor cores (both operands MN-major). Accumulates straight into
-    the flat gradient buffer when the parameter has a slot there, else returns a tensor."""
+    the flat gradient buffer when the parameter has a slot there, else returns a tensor.
+    `k_dyn` (device int32): only that many rows of the operands take part (compacted rows);
+    `k_hint` is the host's estimate of it for choosing the split."""
     C = _C()
     N, K = dy2.shape[1], x2.shape[1]
     slot = _grad_slot(w)
-    cfg, sk = _pick_dw_plan(N, K, dy2.shape[0])
+    cfg, sk = _pick_dw_plan(N, K, dy2.shape[0] if k_hint is None else k_hint)
+    if k_dyn is not None:
+        sk = 1          # the split is over the static reduction length; a dynamic one runs unsplit
     if slot is not None:
-        C.gemm(dy2, x2, slot.view(N, K), True, True, alpha=alpha, accumulate=True, split_k=sk, config=cfg)
+        C.gemm(dy2, x2, slot.view(N, K), True, True, alpha=alpha, accumulate=True, split_k=sk, config=cfg, k_dyn=k_dyn)
         _launched()
         _touched(w)
         return None
     out = torch.zeros(N, K, dtype=torch.float32, device=dy2.device) if sk > 1 else torch.empty(N, K, dtype=torch.float32, device=dy2.device)
-    C.gemm(dy2, x2, out, True, True, alpha=alpha, accumulate=sk > 1, split_k=sk, config=cfg)
+    C.gemm(dy2, x2, out, True, True, alpha=alpha, accumulate=sk > 1, split_k=sk, config=cfg, k_dyn=k_dyn)
     _launched()
     return out.to(w.dtype)
 
 
-def _bias_grad(dy2: torch.Tensor, b: torch.Tensor, alpha=None):
+def _bias_grad(dy2: torch.Tensor, b: torch.Tensor, alpha=None, rows_dyn=None):
     C = _C()
     slot = _grad_slot(b)
     if slot is not None and alpha is None:
-        C.colsum(dy2, slot.view(-1))
+        C.colsum(dy2, slot.view(-1), rows_dyn)
         _launched()
         _touched(b)
         return None
     tmp = torch.zeros(dy2.shape[1], dtype=torch.float32, device=dy2.device)
-    C.colsum(dy2, tmp)
+    C.colsum(dy2, tmp, rows_dyn)
     _launched()
     if alpha is not None:
         tmp = tmp * alpha
@@ -519,47 +523,68 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
     buffer with the upstream scalar as their `alpha`."""
 
     @staticmethod
-    def forward(ctx, x, w, b, target, ignore_index):
+    def forward(ctx, x, w, b, target, ignore_index, compact):
         C = _C()
         K = x.shape[-1]
         x2 = _as_operand(x.reshape(-1, K))
         w16 = _as_operand(_shadow(w))
         V = w.shape[0]
-        logits = _new_rows(x2.shape[0], V, BF16, x.device)
-        C.gemm(x2, w16, logits, False, False, bias=None if b is None else b.detach())
-        loss, dl, _ = C.softmax_ce(logits, target.reshape(-1).contiguous(), ignore_index, True, True)
+        rows = x2.shape[0]
+        tgt = target.reshape(-1).contiguous()
+        idx = counts = None
+        if compact:
+            # Rows whose target is `ignore_index` add nothing to the loss or to any gradient. Pack the
+            # others to the front (device-side count, static buffer sizes), run the projection, the
+            # softmax and the three backward GEMMs on those rows only, and scatter dX back.
+            idx, tgt, counts = C.compact_targets(tgt, ignore_index)
+            xc = _new_rows(rows, K, BF16, x.device)
+            C.gather_rows(x2, idx, counts, xc)
+            x2 = xc
+            _launched(2)
+        logits = _new_rows(rows, V, BF16, x.device)
+        C.gemm(x2, w16, logits, False, False, bias=None if b is None else b.detach(), m_dyn=None if counts is None else counts[0:1])
+        loss, dl, _ = C.softmax_ce(logits, tgt, ignore_index, True, True, counts)
         _launched(4)
-        ctx.save_for_backward(x2, w16, dl)
+        ctx.save_for_backward(x2, w16, dl, idx, counts)
         ctx.w, ctx.b, ctx.xshape = w, b, x.shape
         return loss
 
     @staticmethod
     def backward(ctx, g):
         C = _C()
-        x2, w16, dl = ctx.saved_tensors
+        x2, w16, dl, idx, counts = ctx.saved_tensors
         w, b = ctx.w, ctx.b
         alpha = g.detach().float().reshape(1)
+        n_dyn = None if counts is None else counts[0:1]
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx2 = _new_rows(x2.shape[0], x2.shape[1], BF16, dl.device)
-            C.gemm(dl, w16, dx2, False, True, alpha=alpha)
+            C.gemm(dl, w16, dx2, False, True, alpha=alpha, m_dyn=n_dyn)
             _launched()
+            if counts is not None:
+                full = torch.zeros_like(dx2)
+                C.scatter_rows(dx2, idx, counts, full)
+                _launched(2)
+                dx2 = full
             dx = dx2.view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            dw = _weight_grad(dl, x2, w, alpha=alpha)
+            dw = _weight_grad(dl, x2, w, alpha=alpha, k_dyn=n_dyn, k_hint=None if counts is None else max(64, x2.shape[0] // 6))
         if b is not None and ctx.needs_input_grad[2]:
-            db = _bias_grad(dl, b, alpha=alpha)
-        return dx, dw, db, None, None
+            db = _bias_grad(dl, b, alpha=alpha, rows_dyn=n_dyn)
+        return dx, dw, db, None, None, None
 
 
-def linear_cross_entropy(x, weight, bias, target, ignore_index: int = -100) -> torch.Tensor:
+def linear_cross_entropy(x, weight, bias, target, ignore_index: int = -100, sparse_targets: bool = False) -> torch.Tensor:
     """Vocabulary projection + mean cross-entropy in one op (the masked-LM / LM head hot path:
     `masked_lm_loss`, flodl-hf/src/task_heads.rs:170-183, over the tied decoder of
-    flodl-hf/src/models/bert.rs:707-752)."""
+    flodl-hf/src/models/bert.rs:707-752). `sparse_targets=True` says most targets are
+    `ignore_index` (masked-LM): the projection and its gradients are then computed for the
+    labelled rows only, which gives the same loss and the same gradients."""
     if _gemm_eligible(x, weight) and target.dtype == torch.int64:
         if x.dtype != BF16:
             x = x.to(BF16)
-        return _LinearCrossEntropyFn.apply(x, weight, bias, target, int(ignore_index))
+        rows = x.numel() // x.shape[-1]
+        return _LinearCrossEntropyFn.apply(x, weight, bias, target, int(ignore_index), bool(sparse_targets) and rows >= 512)
     logits = linear(x, weight, bias)
     return cross_entropy(logits.reshape(-1, logits.shape[-1]), target.reshape(-1), ignore_index)
 

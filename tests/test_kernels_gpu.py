@@ -476,3 +476,98 @@ def test_eager_adam_on_unflattened_parameters_matches_torch(C):
         ropt.step()
     for p, r in zip(ours, ref):
         assert (p.t.detach() - r.detach()).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("config", [0, 2])
+def test_gemm_device_side_row_and_reduction_counts(C, config):
+    """`m_dyn` / `k_dyn`: the kernel works on the device-side counts, buffers keep their static size."""
+    torch.manual_seed(11)
+    M, N, K, m_act = 1024, 512, 256, 300
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    cnt = torch.tensor([m_act], device="cuda", dtype=torch.int32)
+    C.clear_status(0)
+    C.gemm(a, b, out, False, False, config=config, m_dyn=cnt)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0
+    ref = a.float() @ b.float().t()
+    assert (out[:m_act].float() - ref[:m_act]).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.05
+    tile_m = 256 if config == 0 else 128
+    first_untouched = (m_act + tile_m - 1) // tile_m * tile_m
+    assert torch.all(out[first_untouched:] == 7.0), "tiles past the dynamic row count must not be written"
+    # reduction length: dW[n, k] = sum_t dy[t, n] x[t, k] over the first k_act rows only (rows up to the
+    # next multiple of 64 are zero, as the producers of such operands guarantee)
+    T, k_act = 1024, 200
+    dy = torch.randn(T, 384, device="cuda").bfloat16()
+    x = torch.randn(T, 256, device="cuda").bfloat16()
+    dy[k_act:256] = 0
+    x[k_act:256] = 0
+    dw = torch.zeros(384, 256, device="cuda")
+    kc = torch.tensor([k_act], device="cuda", dtype=torch.int32)
+    C.gemm(dy, x, dw, True, True, config=config, accumulate=True, k_dyn=kc)
+    torch.cuda.synchronize()
+    assert C.read_status(0) == 0
+    ref = dy[:k_act].float().t() @ x[:k_act].float()
+    assert (dw - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.05
+    # a zero count leaves the output alone
+    dw2 = torch.full((384, 256), 3.0, device="cuda")
+    C.gemm(dy, x, dw2, True, True, config=config, accumulate=True, k_dyn=torch.zeros(1, device="cuda", dtype=torch.int32))
+    torch.cuda.synchronize()
+    assert torch.all(dw2 == 3.0)
+
+
+def test_row_compaction_kernels(C):
+    torch.manual_seed(5)
+    rows, cols = 3000, 136
+    tgt = torch.randint(0, 50, (rows,), device="cuda")
+    tgt[torch.rand(rows, device="cuda") < 0.8] = -100
+    idx, tc, counts = C.compact_targets(tgt, -100)
+    n, n_pad = counts.tolist()
+    act = (tgt != -100).nonzero().flatten()
+    assert n == act.numel() and n_pad == min(rows, (n + 255) // 256 * 256)
+    assert torch.equal(idx[:n].long(), act) and torch.equal(tc[:n], tgt[act]) and torch.all(tc[n:] == -100)
+    x = torch.randn(rows, cols, device="cuda").bfloat16()
+    xc = torch.full_like(x, 9.0)
+    C.gather_rows(x, idx, counts, xc)
+    assert torch.equal(xc[:n], x[act]) and torch.all(xc[n:n_pad] == 0) and torch.all(xc[n_pad:] == 9.0)
+    dx = torch.zeros_like(x)
+    C.scatter_rows(xc, idx, counts, dx)
+    ref = torch.zeros_like(x)
+    ref[act] = x[act]
+    assert torch.equal(dx, ref)
+    # nothing active
+    idx, tc, counts = C.compact_targets(torch.full((700,), -100, device="cuda"), -100)
+    assert counts.tolist() == [0, 0]
+
+
+def test_masked_lm_loss_on_labelled_rows_only_matches_full_projection():
+    """The masked-LM head projects only the labelled rows; loss and every gradient must agree with the
+    projection of all rows (ignored rows contribute nothing to either)."""
+    from flodl_b200 import ops
+    torch.manual_seed(9)
+    rows, K, V = 2048, 256, 3000
+    x0 = (torch.randn(rows, K, device="cuda") * 0.5).bfloat16()
+    w0 = (torch.randn(V, K, device="cuda") * 0.05)
+    b0 = torch.randn(V, device="cuda") * 0.1
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    tgt[torch.rand(rows, device="cuda") < 0.85] = -100
+    res = []
+    for sparse in (False, True):
+        x, w, b = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+        loss = ops.linear_cross_entropy(x, w, b, tgt, -100, sparse_targets=sparse)
+        (loss * 1.5).backward()
+        torch.cuda.synchronize()
+        res.append((loss.item(), x.grad.float(), w.grad.float(), b.grad.float()))
+    (l0, dx0, dw0, db0), (l1, dx1, dw1, db1) = res
+    assert abs(l0 - l1) < 1e-4 * max(1.0, abs(l0)), (l0, l1)
+    assert torch.equal(dx1[tgt == -100], torch.zeros_like(dx1[tgt == -100]))
+    for a, b_, name in ((dx0, dx1, "dx"), (dw0, dw1, "dw"), (db0, db1, "db")):
+        scale = a.abs().max().item() + 1e-12
+        assert (a - b_).abs().max().item() <= 2e-2 * scale, (name, (a - b_).abs().max().item(), scale)
+    # against fp32 PyTorch
+    xr, wr, br = x0.float().requires_grad_(True), w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    ref = F.cross_entropy(F.linear(xr, wr.bfloat16().float(), br), tgt, ignore_index=-100)
+    (ref * 1.5).backward()
+    assert abs(ref.item() - l1) < 2e-2
+    assert (wr.grad - dw1).abs().max().item() <= 3e-2 * wr.grad.abs().max().item() + 1e-4
