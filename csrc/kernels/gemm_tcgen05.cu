@@ -80,6 +80,8 @@ struct GemmCfg {
   // epilogue staging: 4 KB (32 rows x 128 B, swizzled) per epilogue warp for C, the same again for aux
   static constexpr int EPI_BYTES = 2 * kEpiWarps * 4096;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert((2 * STAGES + 4) * 8 + 8 <= 512, "barrier block");
   static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
 };
 
@@ -150,6 +152,16 @@ __device__ __forceinline__ void add_bias32(const GemmParams& p, int col0, int nv
   }
 }
 
+// The bias of the up to 128 columns an epilogue warp owns lives in registers, four consecutive
+// columns per lane (fetched while the tensor cores were still working on the tile, so the
+// global-memory latency is off the critical path). v[0..32) += bias of columns [cc, cc+32) of the
+// warp's range: the owner lane of column cc+i is (cc+i)/4.
+__device__ __forceinline__ void add_bias32_regs(const float (&breg)[4], int cc, float (&v)[32]) {
+  const int lane0 = cc >> 2;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] += __shfl_sync(0xffffffffu, breg[i & 3], lane0 + (i >> 2));
+}
+
 // Epilogue for 32 consecutive columns of one output row. Every loop over the 32 values is fully
 // unrolled with compile-time indices (tails are handled by predicates), so the values stay in
 // registers: a dynamically indexed copy would be demoted to local memory and every access to it
@@ -158,7 +170,7 @@ __device__ __forceinline__ void add_bias32(const GemmParams& p, int col0, int nv
 // pre-activation (only meaningful for the GELU epilogues). Rows/cols outside the problem yield
 // harmless values; the caller's store clips them.
 __device__ __forceinline__ void epilogue_compute32(const GemmParams& p, const uint32_t (&acc)[32], int row, int col0,
-                                                   bool add_bias, float (&v)[32], float (&pre)[32]) {
+                                                   bool add_bias, float (&v)[32], float (&pre)[32], const float (&breg)[4], int bias_cc) {
   if (p.alpha) {
     const float alpha = __ldg(p.alpha);
 #pragma unroll
@@ -168,7 +180,10 @@ __device__ __forceinline__ void epilogue_compute32(const GemmParams& p, const ui
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
   }
   const int nvalid = (col0 + 32 <= p.N) ? 32 : (p.N > col0 ? p.N - col0 : 0);
-  if (p.bias && add_bias) add_bias32(p, col0, nvalid, v);
+  if (p.bias && add_bias) {
+    if (bias_cc >= 0) add_bias32_regs(breg, bias_cc, v);
+    else add_bias32(p, col0, nvalid, v);
+  }
   if (p.epi == FB_EPI_GELU_ERF) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) { pre[i] = v[i]; v[i] = gelu_erf_f(v[i]); }
@@ -514,6 +529,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int half = (warp - 2) >> 2;       // which half of the tile's columns
     constexpr int kSplit = Cfg::EPI_SPLIT;
     int it = 0;
+    uint32_t chunk_ix = 0;     // staged stores issued by this warp so far: picks the staging tile in turn
     bool ok = true;
     for (int u = group; u < num_units && ok; u += num_groups, ++it) {
       const int ks = u % p.split_k;
@@ -521,6 +537,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = (t % num_m) * BM * kCG + static_cast<int>(rank) * BM;
       const int n0 = (t / num_m) * kBN;
       const int acc = it & 1;
+      // This warp's slice of the bias is fetched now, while the tensor cores are still working on the
+      // tile: by the time the accumulator is ready the global-memory latency has been paid.
+      const bool stage_bias = p.bias != nullptr && ks == 0 && p.c_mode != 0;
+      float breg[4] = {0.f, 0.f, 0.f, 0.f};
+      if (stage_bias) {
+        const int wcols = half ? kBN - Cfg::EPI_SPLIT : Cfg::EPI_SPLIT;
+        const int cbase = n0 + half * Cfg::EPI_SPLIT + lane * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = cbase + j;
+          if (lane * 4 + j < wcols && col < p.N)
+            breg[j] = p.bias_fp32 ? __ldg(static_cast<const float*>(p.bias) + col) : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+        }
+      }
       ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, abort_flag, p.status, kStatusWaitAccum);
       if (!ok) break;
       tc_fence_after_sync();
@@ -543,10 +573,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t sx = smem_u32(epi_smem + (kEpiWarps + warp - 2) * 4096);
         if (!p.c_fp32) {
           // bf16 output: 64 columns (128 bytes per row) per staged store
+          // Without an aux store the second staging tile is free: the two take turns, so a chunk only
+          // waits for the store issued two chunks ago.
+          const bool pingpong = !p.aux_tma;
 #pragma unroll 1
           for (int c = 0; c < COLS_PER_WARP; c += 64) {
             if (ncol0 + c >= p.N) break;
-            if (lane == 0) tma_store_wait_read();   // the previous chunk's store has read the staging tile
+            const bool odd = pingpong && (chunk_ix & 1);
+            ++chunk_ix;
+            const uint32_t sc_cur = odd ? sx : sc;
+            uint8_t* sc_ptr = epi_smem + ((odd ? kEpiWarps : 0) + warp - 2) * 4096;
+            if (lane == 0) {
+              if (pingpong) tma_store_wait_read_but_one();
+              else tma_store_wait_read();           // the previous chunk's store has read the staging tile
+            }
             __syncwarp();
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {          // two 32-column halves, one at a time (register pressure)
@@ -554,10 +594,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tmem_ld32(taddr + c + 32 * hh, r0);
               tmem_ld_wait();
               float v0[32], p0[32];
-              epilogue_compute32(p, r0, row, ncol0 + c + 32 * hh, ks == 0, v0, p0);
+              epilogue_compute32(p, r0, row, ncol0 + c + 32 * hh, ks == 0, v0, p0, breg, stage_bias ? c + 32 * hh : -1);
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                st_shared_v4(stage_addr(sc, lane, 4 * hh + j), pack_bf16x2(v0[8 * j], v0[8 * j + 1]), pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]),
+                st_shared_v4(stage_addr(sc_cur, lane, 4 * hh + j), pack_bf16x2(v0[8 * j], v0[8 * j + 1]), pack_bf16x2(v0[8 * j + 2], v0[8 * j + 3]),
                              pack_bf16x2(v0[8 * j + 4], v0[8 * j + 5]), pack_bf16x2(v0[8 * j + 6], v0[8 * j + 7]));
               if (p.aux_tma) {
 #pragma unroll
@@ -569,7 +609,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
+              tma_store_2d(&tmC, sc_ptr, ncol0 + c, row0);
               if (p.aux_tma) tma_store_2d(&tmAux, epi_smem + (kEpiWarps + warp - 2) * 4096, ncol0 + c, row0);
               tma_store_commit();
             }
@@ -583,18 +623,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld32(taddr + c, r0);
             tmem_ld_wait();
             float v0[32], p0[32];
-            epilogue_compute32(p, r0, row, ncol0 + c, ks == 0, v0, p0);
-            if (lane == 0) tma_store_wait_read();
+            epilogue_compute32(p, r0, row, ncol0 + c, ks == 0, v0, p0, breg, stage_bias ? c : -1);
+            const bool odd = chunk_ix & 1;           // the two staging tiles take turns
+            ++chunk_ix;
+            const uint32_t sc_cur = odd ? sx : sc;
+            uint8_t* sc_ptr = epi_smem + ((odd ? kEpiWarps : 0) + warp - 2) * 4096;
+            if (lane == 0) tma_store_wait_read_but_one();
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              st_shared_v4(stage_addr(sc, lane, j), __float_as_uint(v0[4 * j]), __float_as_uint(v0[4 * j + 1]),
+              st_shared_v4(stage_addr(sc_cur, lane, j), __float_as_uint(v0[4 * j]), __float_as_uint(v0[4 * j + 1]),
                            __float_as_uint(v0[4 * j + 2]), __float_as_uint(v0[4 * j + 3]));
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              if (p.c_mode == 2) tma_reduce_add_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
-              else tma_store_2d(&tmC, epi_smem + (warp - 2) * 4096, ncol0 + c, row0);
+              if (p.c_mode == 2) tma_reduce_add_2d(&tmC, sc_ptr, ncol0 + c, row0);
+              else tma_store_2d(&tmC, sc_ptr, ncol0 + c, row0);
               tma_store_commit();
             }
           }
@@ -608,13 +652,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         else mbar_arrive_cluster(&tempty_bar[acc], 0);
       }
     }
-    if (p.c_mode && lane == 0) tma_store_wait_all();   // staged stores must land before the CTA retires
+    // The staging tiles must have been read before the CTA (and its shared memory) goes away; the
+    // writes themselves complete with the grid, as every other global store does.
+    if (p.c_mode && lane == 0) tma_store_wait_read();
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 6] = clock64();
+  if (p.ts && threadIdx.x == 0) {
+    p.ts[blockIdx.x * 8 + 6] = clock64();
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    p.ts[blockIdx.x * 8 + 7] = static_cast<long long>(g);   // wall-clock end (slot 7 held the set-up time before the main loop starts)
+  }
   if constexpr (kCG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();

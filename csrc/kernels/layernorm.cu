@@ -323,9 +323,18 @@ extern "C" int fb_layernorm_fwd(const void* x, const void* residual, const float
   FB_LN_DISPATCH(ln_fwd_launch, x, residual, gamma, beta, y, pre_out, mean, rstd, rows, cols, eps, p_drop, seed, seed_dev, st);
 }
 
+// One resident wave: the backward kernel keeps its dgamma / dbeta partial sums in registers (about
+// 160 per thread), so three 128-thread blocks fit on an SM; more blocks than that would run as a
+// second, mostly empty wave.
 extern "C" int fb_layernorm_bwd_grid(int rows) {
+  static int cap = 0;
+  if (!cap) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cap = 3 * (sms > 0 ? sms : 148);
+  }
   int g = (rows + fb::kLnWarps - 1) / fb::kLnWarps;
-  return g < 592 ? g : 592;
+  return g < cap ? g : cap;
 }
 
 // `partial` must hold fb_layernorm_bwd_grid(rows) * 2 * cols floats.

@@ -166,6 +166,10 @@ __device__ __forceinline__ void tma_store_wait_all() {
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// As above, but the most recent store group may still be reading its source (two staging buffers in turn).
+__device__ __forceinline__ void tma_store_wait_read_but_one() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // Make generic-proxy smem writes visible to the async proxy (TMA store / tcgen05.mma reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -194,6 +194,49 @@ def _pick_dw_plan(m_out: int, n_out: int, k_red: int):
     return 2, max(1, min(4, k_red // 512))
 
 
+# ---- weight gradients beside the data gradient ------------------------------------------------------
+# dX and dW of a linear layer are independent products of the same upstream gradient. Issued on two
+# streams they share the GPU: the blocks of one fill the SMs the other leaves idle in its last
+# (partial) wave and behind its fixed latencies, and the small bias-gradient column sums vanish
+# behind the GEMMs. The side stream forks from the current stream and is joined before backward()
+# returns, so the saved activations outlive every kernel that reads them. FLODL_B200_SIDE_DW=0
+# keeps everything on one stream.
+_SIDE = {"on": os.environ.get("FLODL_B200_SIDE_DW", "1") not in ("0", "false", "off"), "streams": {}}
+
+
+class _Fork:
+    """`with fork: ...` runs the body on the side stream (after everything issued so far on the
+    current stream); `fork.join()` makes the current stream wait for it."""
+
+    def __init__(self, device: torch.device):
+        self.active = _SIDE["on"] and device.type == "cuda"
+        if self.active:
+            self.main = torch.cuda.current_stream(device)
+            key = (device.index, torch.cuda.is_current_stream_capturing())
+            side = _SIDE["streams"].get(key)
+            if side is None:
+                side = _SIDE["streams"][key] = torch.cuda.Stream(device)
+            self.side = side
+            self.used = False
+
+    def __enter__(self):
+        if self.active:
+            self.side.wait_stream(self.main)
+            self.ctx = torch.cuda.stream(self.side)
+            self.ctx.__enter__()
+            self.used = True
+        return self
+
+    def __exit__(self, *exc):
+        if self.active:
+            self.ctx.__exit__(*exc)
+        return False
+
+    def join(self) -> None:
+        if self.active and self.used:
+            self.main.wait_stream(self.side)
+
+
 _EPI = {None: 0, "gelu": 1, "gelu_tanh": 3}
 _DEPI = {"gelu": 2, "gelu_tanh": 4}
 
@@ -269,15 +312,18 @@ class _LinearFn(torch.autograd.Function):
             _launched()
         dy2 = _as_operand(dy2)
         dx = dw = db = None
+        fork = _Fork(dy.device)
+        with fork:
+            if ctx.needs_input_grad[1]:
+                dw = _weight_grad(dy2, x2, w)
+            if b is not None and ctx.needs_input_grad[2]:
+                db = _bias_grad(dy2, b)
         if ctx.needs_input_grad[0]:
             dx2 = _new_rows(x2.shape[0], x2.shape[1], BF16, dy.device)
             C.gemm(dy2, w16, dx2, False, True)
             _launched()
             dx = dx2.view(ctx.xshape)
-        if ctx.needs_input_grad[1]:
-            dw = _weight_grad(dy2, x2, w)
-        if b is not None and ctx.needs_input_grad[2]:
-            db = _bias_grad(dy2, b)
+        fork.join()
         return dx, dw, db, None
 
 
@@ -339,18 +385,22 @@ class _FeedForwardFn(torch.autograd.Function):
         dy2 = _as_operand(dy.reshape(-1, N))
         M, F1 = a.shape
         dpre = _new_rows(M, F1, BF16, dy.device)
+        fork = _Fork(dy.device)
+        with fork:       # the second layer's parameter gradients need only dy: beside the d(pre-activation) GEMM
+            dw2 = _weight_grad(dy2, a, w2) if ctx.needs_input_grad[3] else None
+            db2 = _bias_grad(dy2, b2) if (b2 is not None and ctx.needs_input_grad[4]) else None
         C.gemm(dy2, w2s, dpre, False, True, epi=_DEPI[ctx.act], aux=h_pre)
         _launched()
-        dw2 = _weight_grad(dy2, a, w2) if ctx.needs_input_grad[3] else None
-        db2 = _bias_grad(dy2, b2) if (b2 is not None and ctx.needs_input_grad[4]) else None
-        dw1 = _weight_grad(dpre, x2, w1) if ctx.needs_input_grad[1] else None
-        db1 = _bias_grad(dpre, b1) if (b1 is not None and ctx.needs_input_grad[2]) else None
+        with fork:       # the first layer's, beside the dX GEMM (the side stream waits for dpre here)
+            dw1 = _weight_grad(dpre, x2, w1) if ctx.needs_input_grad[1] else None
+            db1 = _bias_grad(dpre, b1) if (b1 is not None and ctx.needs_input_grad[2]) else None
         dx = None
         if ctx.needs_input_grad[0]:
             dx2 = _new_rows(M, x2.shape[1], BF16, dy.device)
             C.gemm(dpre, w1s, dx2, False, True)
             _launched()
             dx = dx2.view(ctx.xshape)
+        fork.join()
         return dx, dw1, db1, dw2, db2, None
 
 
@@ -557,6 +607,12 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         alpha = g.detach().float().reshape(1)
         n_dyn = None if counts is None else counts[0:1]
         dx = dw = db = None
+        fork = _Fork(dl.device)
+        with fork:
+            if ctx.needs_input_grad[1]:
+                dw = _weight_grad(dl, x2, w, alpha=alpha, k_dyn=n_dyn, k_hint=None if counts is None else max(64, x2.shape[0] // 6))
+            if b is not None and ctx.needs_input_grad[2]:
+                db = _bias_grad(dl, b, alpha=alpha, rows_dyn=n_dyn)
         if ctx.needs_input_grad[0]:
             dx2 = _new_rows(x2.shape[0], x2.shape[1], BF16, dl.device)
             C.gemm(dl, w16, dx2, False, True, alpha=alpha, m_dyn=n_dyn)
@@ -567,10 +623,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
                 _launched(2)
                 dx2 = full
             dx = dx2.view(ctx.xshape)
-        if ctx.needs_input_grad[1]:
-            dw = _weight_grad(dl, x2, w, alpha=alpha, k_dyn=n_dyn, k_hint=None if counts is None else max(64, x2.shape[0] // 6))
-        if b is not None and ctx.needs_input_grad[2]:
-            db = _bias_grad(dl, b, alpha=alpha, rows_dyn=n_dyn)
+        fork.join()
         return dx, dw, db, None, None, None
 
 

@@ -569,5 +569,5 @@ def test_masked_lm_loss_on_labelled_rows_only_matches_full_projection():
     xr, wr, br = x0.float().requires_grad_(True), w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
     ref = F.cross_entropy(F.linear(xr, wr.bfloat16().float(), br), tgt, ignore_index=-100)
     (ref * 1.5).backward()
-    assert abs(ref.item() - l1) < 2e-2
+    assert abs(ref.item() - l1) < 5e-2      # bf16 logits against an fp32 projection
     assert (wr.grad - dw1).abs().max().item() <= 3e-2 * wr.grad.abs().max().item() + 1e-4
