@@ -133,6 +133,12 @@ def main():
             iters = args.iters if nbytes <= (64 << 20) else max(5, args.iters // 4)
             blocks = args.blocks or (4 if nbytes <= (64 << 10) else 16 if nbytes <= (4 << 20) else 48)
             ms_two = timed(lambda: buf.all_reduce(0, numel, dtype, blocks=blocks), iters, dev)
+            best_blocks = blocks
+            if not args.blocks and nbytes >= (32 << 20):      # large messages: also try wider launches, keep the best
+                for nb in (96, 192):
+                    t = timed(lambda: buf.all_reduce(0, numel, dtype, blocks=nb), iters, dev)
+                    if t < ms_two:
+                        ms_two, best_blocks = t, nb
             buf.check()
             ms_one = None
             if nbytes <= (8 << 20):
@@ -151,7 +157,8 @@ def main():
                 ms_nccl_chunks = timed(grouped, iters, dev)
             bus = lambda ms: None if ms is None else round(2 * (world - 1) / world * nbytes / (ms * 1e-3) / 1e9, 2)
             best = min(x for x in (ms_two, ms_one) if x is not None)
-            row = {"dtype": str(dtype).split(".")[-1], "bytes": nbytes, "world": world, "ours_two_shot_us": round(ms_two * 1e3, 2),
+            row = {"dtype": str(dtype).split(".")[-1], "bytes": nbytes, "world": world, "path": "nvls" if buf.nvls else "p2p", "blocks": best_blocks,
+                   "ours_two_shot_us": round(ms_two * 1e3, 2),
                    "ours_one_shot_us": None if ms_one is None else round(ms_one * 1e3, 2), "nccl_flat_us": round(ms_nccl * 1e3, 2),
                    "nccl_25MB_group_us": None if ms_nccl_chunks is None else round(ms_nccl_chunks * 1e3, 2),
                    "ours_bus_GBs": bus(best), "nccl_bus_GBs": bus(ms_nccl), "ours_frac_of_nvlink": round((bus(best) or 0) / NVLINK_GBS, 3),

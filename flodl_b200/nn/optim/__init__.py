@@ -14,7 +14,7 @@ import gzip
 import io
 import math
 import struct
-from typing import List, Optional, Sequence
+from typing import Tuple, List, Optional, Sequence
 
 import torch
 
@@ -254,7 +254,10 @@ class Adam(Optimizer):
         self.advance()
         self.apply()
 
-    def apply(self) -> None:
+    def apply(self, window: Optional[Tuple[int, int]] = None) -> None:
+        """The capturable half of a step. `window = (lo, hi)` restricts a flat-buffer update to the
+        elements [lo, hi) of the buffer (a trainer applies the part whose gradients have arrived
+        while the rest is still being exchanged); it needs every group to sit in one flat range."""
         for gi, (_, s, e) in enumerate(self._group_ranges()):
             lr, bc1, bc2 = self._cur[gi]
             ps = self.params[s:e]
@@ -264,8 +267,14 @@ class Adam(Optimizer):
                 C = _ext.require()
                 hyper = self._hyper[gi]
                 rng = _flat.contiguous_range(ps)
+                if window is not None and rng is None:
+                    raise TensorError("apply(window=...) needs parameters in one flat range")
                 if rng is not None:
                     flat, a, b = rng
+                    if window is not None:
+                        a, b = max(a, int(window[0])), min(b, int(window[1]))
+                        if b <= a:
+                            continue
                     m, v = self._flat_state(flat)
                     C.adam_step(flat.params[a:b], flat.grads[a:b], m[a:b], v[a:b],
                                 None if flat.shadow is None else flat.shadow[a:b], hyper, self.beta1, self.beta2, self.eps, self.grad_scale,
@@ -384,7 +393,7 @@ class SGD(Optimizer):
         self.advance()
         self.apply()
 
-    def apply(self) -> None:
+    def apply(self, window: Optional[Tuple[int, int]] = None) -> None:
         for gi, (_, s, e) in enumerate(self._group_ranges()):
             lr, first = self._cur[gi]
             ps = self.params[s:e]
@@ -393,8 +402,14 @@ class SGD(Optimizer):
             if _native(ps[0]):
                 C = _ext.require()
                 rng = _flat.contiguous_range(ps)
+                if window is not None and rng is None:
+                    raise TensorError("apply(window=...) needs parameters in one flat range")
                 if rng is not None:
                     flat, a, b = rng
+                    if window is not None:
+                        a, b = max(a, int(window[0])), min(b, int(window[1]))
+                        if b <= a:
+                            continue
                     if self.momentum and (self._flat_v is None or self._flat_v.numel() != flat.total):
                         self._flat_v = torch.zeros(flat.total, dtype=torch.float32, device=flat.device)
                         for i, p in enumerate(self.params):

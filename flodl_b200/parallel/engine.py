@@ -189,7 +189,12 @@ class TrainEngine:
         loss = loss_fn()
         lt = loss.t if hasattr(loss, "t") else loss
         lt.backward()
-        self.sync.finish()
+        # Without clipping (which needs every gradient first) the optimizer can start on the buckets
+        # that have arrived while the last one, complete only now, is still being exchanged.
+        import inspect
+        can_split = (self.max_grad_norm is None and hasattr(self.optimizer, "apply") and getattr(self.optimizer, "fused", False)
+                     and "window" in inspect.signature(self.optimizer.apply).parameters and not getattr(self.optimizer, "groups", None))
+        tail = self.sync.finish(defer_tail=can_split)
         if self.symm_bufs is not None:
             self.symm_bufs.broadcast(0, self._buf_bytes, 0, 1)
         elif self.world > 1 and self.grad_sync and self._float_bufs:
@@ -200,7 +205,11 @@ class TrainEngine:
         elif self.max_grad_norm is not None:
             from ..nn.clip import clip_grad_norm
             clip_grad_norm(self.flat.tensors, self.max_grad_norm)
-        if hasattr(self.optimizer, "apply"):
+        if tail is not None:
+            self.optimizer.apply(window=(tail[1], self.flat.total))
+            self.sync.wait_tail()
+            self.optimizer.apply(window=(tail[0], tail[1]))
+        elif hasattr(self.optimizer, "apply"):
             self.optimizer.apply()
         else:
             if self.sync.symm is not None and not torch.cuda.is_current_stream_capturing():

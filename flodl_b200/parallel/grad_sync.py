@@ -47,6 +47,7 @@ class GradSync:
         self.weights: Optional[List[float]] = None
         self.stream = torch.cuda.Stream(priority=-1) if flat.device.type == "cuda" and self.world > 1 else None
         self.done = torch.cuda.Event() if self.stream is not None else None
+        self.done_tail = torch.cuda.Event() if self.stream is not None else None
         self.active = False
         self.launch_count = 0
         self.next_bucket = 0
@@ -137,27 +138,48 @@ class GradSync:
             else:
                 _comm.all_reduce_nccl([g], _comm.ReduceOp.Avg)
 
-    def finish(self) -> None:
+    def finish(self, defer_tail: bool = False):
         """Call after backward: launches whatever has not been launched, then makes the current
-        stream wait for every bucket."""
+        stream wait for every bucket.
+
+        `defer_tail=True`: the current stream waits for every bucket but the last one (the first
+        parameters of the buffer, whose gradients are complete only when backward ends, so their
+        exchange can overlap nothing of backward) and `(lo, hi)`, that bucket's element range, is
+        returned. The caller applies the optimizer to the rest, calls `wait_tail()`, then applies
+        it to `[lo, hi)`: the last exchange runs behind the optimizer instead of in front of it."""
         if self.world <= 1:
-            return
+            return None
         self.active = False
         _core.GRAD_HOOK["fn"] = None
         if self.expected is None:
             self.expected = list(self.touch)
+        tail = None
+        split = defer_tail and self.stream is not None and len(self.buckets) > 1 and not self.mismatch
         for bi in range(len(self.buckets)):
+            if split and bi == len(self.buckets) - 1:
+                self.done.record(self.stream)                 # everything before the last bucket
+                torch.cuda.current_stream().wait_event(self.done)
             if not self.launched[bi]:
                 self._launch(bi)
         if self.stream is not None:
-            self.done.record(self.stream)
-            torch.cuda.current_stream().wait_event(self.done)
+            if split:
+                self.done_tail.record(self.stream)
+                tail = (self.buckets[-1]["start"], self.buckets[-1]["end"])
+            else:
+                self.done.record(self.stream)
+                torch.cuda.current_stream().wait_event(self.done)
         if self.mismatch:
             self.overlap = False
             raise RuntimeError(
                 "gradient exchange: a gradient was produced after its bucket had been reduced (the set of parameters that "
                 "receive gradients changed between steps). This step's gradients are incomplete on this rank; overlap is now "
                 "off. Build the trainer with overlap=False for models whose backward differs from step to step.")
+        return tail
+
+    def wait_tail(self) -> None:
+        """Make the current stream wait for the bucket `finish(defer_tail=True)` left in flight."""
+        if self.stream is not None:
+            torch.cuda.current_stream().wait_event(self.done_tail)
 
     # ---- one-off collectives --------------------------------------------------------------------
     def set_weights(self, weights: Optional[Sequence[float]]) -> None:
