@@ -73,7 +73,8 @@ def run(args):
     torch.manual_seed(1234)
     if args.model != "bert-base":
         if rank == 0:
-            print(json.dumps({"impl": "twin", "unavailable": f"twin for {args.model} is in baseline/twin_{args.model}.py"}))
+            print(json.dumps({"impl": "twin", "unavailable": f"the PyTorch restatement covers bert-base only; `--impl reference` runs {args.model} "
+                                                              "on the reference's own shim"}))
         return
     B, S, V = (args.batch or 32), 128, 30522
     model = BertMLM().to(dev).train()

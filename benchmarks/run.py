@@ -23,7 +23,13 @@ from .harness import BenchConfig, BenchResult, run_benchmark
 from .models import MODELS, TIER1, TIER2
 
 
-def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, runs: int = 0, epochs: int = 0, warmup: int = -1) -> BenchResult:
+def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, runs: int = 0, epochs: int = 0, warmup: int = -1,
+              mode: str = "captured") -> BenchResult:
+    """`mode` (flodl arm, CUDA only): "captured" runs the framework's standard training path, a
+    `TrainEngine` whose whole step (forward, backward, fused optimizer over the flat parameter
+    buffer) is one CUDA-graph launch; a model whose forward reads values on the host (data-dependent
+    loops) cannot be captured and runs the same engine step by step. "eager" is the plain
+    op-by-op loop with a per-tensor optimizer, the shape of the reference's benchmark loop."""
     build, cfg = MODELS[name]
     if quick:
         cfg = cfg.quick()
@@ -35,7 +41,33 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
     model, make_batch, loss_kind, lr = build(cfg, impl, dev, 8 if quick else 1)
     gen = torch.Generator().manual_seed(seed + 1)
     batches = [make_batch(dev, gen) for _ in range(cfg.batches_per_epoch)]
-    if impl == "flodl":
+    impl_label = impl
+    if impl == "flodl" and mode == "captured" and dev.type == "cuda":
+        from flodl_b200.parallel.engine import TrainEngine
+        model.train()
+        count = sum(p.t.numel() for p in model.parameters())
+        eng = TrainEngine(model, lambda ps: nn.Adam(ps, lr))
+
+        def step_fn(x, y):
+            pred = model.forward(Variable.wrap(x))
+            if loss_kind == "ce":
+                return nn.cross_entropy_loss(pred.reshape([-1, pred.t.shape[-1]]), Variable.wrap(y.reshape(-1)))
+            return nn.mse_loss(pred, Variable.wrap(y))
+        try:
+            eng.capture(step_fn, list(batches[0]), warmup=2)
+            one = lambda x, y: eng.replay([x, y])
+            impl_label = "flodl (one CUDA graph per step)"
+        except Exception:   # noqa: BLE001  (host-side control flow inside forward)
+            torch.cuda.synchronize()
+            one = lambda x, y: eng.step(lambda: step_fn(x, y))
+            impl_label = "flodl (engine, step by step)"
+
+        def epoch(_i, _warm):
+            total = 0.0
+            for x, y in batches:
+                total += one(x, y).item()
+            return total / len(batches)
+    elif impl == "flodl":
         model.train()
         params = model.parameters()
         count = sum(p.t.numel() for p in params)
@@ -70,7 +102,9 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
                 opt.step()
                 total += loss.item()
             return total / len(batches)
-    return run_benchmark(cfg, impl, count, epoch, dev)
+    res = run_benchmark(cfg, impl, count, epoch, dev)
+    res.impl = impl_label
+    return res
 
 
 def gpu_clocks() -> str:
@@ -83,13 +117,14 @@ def gpu_clocks() -> str:
 
 
 def report(results: Dict[str, Dict[str, BenchResult]]) -> str:
-    lines = ["| model | params | flodl_b200 ms/epoch | PyTorch ms/epoch | speed-up | flodl_b200 peak MB | PyTorch peak MB |", "|---|---|---|---|---|---|---|"]
+    lines = ["| model | params | flodl_b200 ms/epoch | PyTorch ms/epoch | speed-up | flodl_b200 peak MB | PyTorch peak MB | flodl_b200 path |",
+             "|---|---|---|---|---|---|---|---|"]
     for name, by in results.items():
         a, b = by.get("flodl"), by.get("torch")
         fmt = lambda r, f: "-" if r is None or f(r) is None else f"{f(r):.1f}"
         ratio = "-" if a is None or b is None else f"{b.median_epoch_ms / a.median_epoch_ms:.2f}x"
         lines.append(f"| {name} | {(a or b).param_count} | {fmt(a, lambda r: r.median_epoch_ms)} | {fmt(b, lambda r: r.median_epoch_ms)} | {ratio} | "
-                     f"{fmt(a, lambda r: r.peak_vram_mb)} | {fmt(b, lambda r: r.peak_vram_mb)} |")
+                     f"{fmt(a, lambda r: r.peak_vram_mb)} | {fmt(b, lambda r: r.peak_vram_mb)} | {a.impl if a is not None else '-'} |")
     return "\n".join(lines)
 
 
@@ -104,6 +139,8 @@ def main(argv=None) -> int:
     ap.add_argument("--runs", type=int, default=0, help="passes per model (default 4, the first is discarded)")
     ap.add_argument("--epochs", type=int, default=0, help="measured epochs per pass (default 20)")
     ap.add_argument("--warmup", type=int, default=-1, help="warm-up epochs per pass (default 3)")
+    ap.add_argument("--mode", default="captured", choices=["captured", "eager"],
+                    help="flodl arm on CUDA: whole-step CUDA graph through TrainEngine (default) or the op-by-op loop")
     args = ap.parse_args(argv)
     names = {"all": TIER1 + TIER2, "tier1": TIER1, "tier2": TIER2}.get(args.models) or [m for m in args.models.split(",") if m]
     impls = [i for i in args.impl.split(",") if i]
@@ -115,7 +152,7 @@ def main(argv=None) -> int:
     for _round in range(max(1, args.rounds)):
         for n in names:
             for impl in impls:           # interleaved: flodl, torch, flodl, torch, ...
-                r = run_model(n, impl, args.device, args.quick, 0, args.runs, args.epochs, args.warmup)
+                r = run_model(n, impl, args.device, args.quick, 0, args.runs, args.epochs, args.warmup, args.mode)
                 print(r.json(), flush=True)
                 if impl not in best[n] or r.median_epoch_ms < best[n][impl].median_epoch_ms:
                     best[n][impl] = r

@@ -547,8 +547,11 @@ __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
+#ifndef FB_TIMELINE
+#define FB_TIMELINE 0      // the timeline is a tuning aid, compiled in only with -DFB_TIMELINE=1
+#endif
 __device__ __forceinline__ void ts_mark(long long* ts, int slot) {
-  if (ts && blockIdx.x == 0 && slot < 64) {
+  if (FB_TIMELINE && ts && blockIdx.x == 0 && slot < 64) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     ts[slot] = static_cast<long long>(t);

@@ -33,6 +33,17 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+// The per-CTA timeline (`ts`) is a tuning aid: it is compiled in only with -DFB_TIMELINE=1
+// (FLODL_B200_TIMELINE=1 at build time); a regular build ignores the argument.
+#ifndef FB_TIMELINE
+#define FB_TIMELINE 0
+#endif
+#if FB_TIMELINE
+#define FB_TIMELINE_ONLY(stmt) stmt
+#else
+#define FB_TIMELINE_ONLY(stmt)
+#endif
+
 namespace fb {
 
 constexpr int BM = 128;  // rows of the tile held by ONE CTA
@@ -378,12 +389,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int group = blockIdx.x / kCG;          // CTA (pair) index
   const int num_groups = gridDim.x / kCG;
 
+#if FB_TIMELINE
   if (p.ts && threadIdx.x == 0) {
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
     p.ts[blockIdx.x * 8 + 0] = static_cast<long long>(g);
     p.ts[blockIdx.x * 8 + 1] = clock64();
   }
+#endif
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -414,7 +427,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // Programmatic dependent launch: everything above (barriers, descriptor prefetch, TMEM) touched
   // no global data and may run while the previous kernel of the stream drains; from here on this
   // kernel reads what that kernel wrote.
-  if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 7] = clock64();
+  FB_TIMELINE_ONLY(if (p.ts && threadIdx.x == 0) p.ts[blockIdx.x * 8 + 7] = clock64();)
   pdl_wait();
   pdl_launch_dependents();
 
@@ -504,7 +517,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, kStatusWaitFull);
           if (!ok) break;
           tc_fence_after_sync();
-          if (p.ts && it == 0 && kb == kb0) p.ts[blockIdx.x * 8 + 2] = clock64();
+          FB_TIMELINE_ONLY(if (p.ts && it == 0 && kb == kb0) p.ts[blockIdx.x * 8 + 2] = clock64();)
           const uint32_t sa = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
           const uint32_t sb = sa + Cfg::A_BYTES;
 #pragma unroll
@@ -520,7 +533,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         if constexpr (kCG == 1) umma_commit(&tfull_bar[acc]);
         else umma_commit_pair(&tfull_bar[acc], 3);
-        if (p.ts && it == 0) p.ts[blockIdx.x * 8 + 3] = clock64();
+        FB_TIMELINE_ONLY(if (p.ts && it == 0) p.ts[blockIdx.x * 8 + 3] = clock64();)
       }
     }
   } else {
@@ -554,7 +567,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, abort_flag, p.status, kStatusWaitAccum);
       if (!ok) break;
       tc_fence_after_sync();
-      if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 4] = clock64();
+      FB_TIMELINE_ONLY(if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 4] = clock64();)
       const int row = m0 + q * 32 + lane;
       const int row0 = m0 + q * 32;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN + half * kSplit;
@@ -646,7 +659,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 5] = clock64();
+      FB_TIMELINE_ONLY(if (p.ts && it == 0 && warp == 2 && lane == 0) p.ts[blockIdx.x * 8 + 5] = clock64();)
       if (lane == 0) {
         if (kCG == 1 || rank == 0) mbar_arrive(&tempty_bar[acc]);
         else mbar_arrive_cluster(&tempty_bar[acc], 0);
@@ -660,12 +673,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+#if FB_TIMELINE
   if (p.ts && threadIdx.x == 0) {
     p.ts[blockIdx.x * 8 + 6] = clock64();
     unsigned long long g;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
-    p.ts[blockIdx.x * 8 + 7] = static_cast<long long>(g);   // wall-clock end (slot 7 held the set-up time before the main loop starts)
+    p.ts[blockIdx.x * 8 + 7] = static_cast<long long>(g);   // wall-clock end
   }
+#endif
   if constexpr (kCG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();

@@ -133,9 +133,11 @@ struct ByteSource {
   gzFile gz = nullptr;
   const std::string* mem = nullptr;
   size_t pos = 0;
+  // Bytes that can still be read from an in-memory source (files: unknown, reported as "unbounded").
+  uint64_t remaining() const { return mem ? static_cast<uint64_t>(mem->size() - pos) : UINT64_MAX; }
   void read(void* p, size_t n) {
     if (mem) {
-      TORCH_CHECK(pos + n <= mem->size(), "checkpoint: unexpected end of data");
+      TORCH_CHECK(pos <= mem->size() && n <= mem->size() - pos, "checkpoint: unexpected end of data");
       std::memcpy(p, mem->data() + pos, n);
       pos += n;
       return;
@@ -146,6 +148,16 @@ struct ByteSource {
       TORCH_CHECK(gzread(gz, c, chunk) == (int)chunk, "checkpoint: unexpected end of file");
       c += chunk; n -= chunk;
     }
+  }
+  // Skip `n` payload bytes without materialising them.
+  void skip(uint64_t n) {
+    if (mem) {
+      TORCH_CHECK(pos <= mem->size() && n <= mem->size() - pos, "checkpoint: unexpected end of data");
+      pos += static_cast<size_t>(n);
+      return;
+    }
+    TORCH_CHECK(n <= static_cast<uint64_t>(INT64_MAX) && gzseek(gz, static_cast<z_off_t>(n), SEEK_CUR) >= 0,
+                "checkpoint: unexpected end of file");
   }
   template <typename T> T get() { T v; read(&v, sizeof(T)); return v; }
 };
@@ -182,15 +194,30 @@ void write_tensor_record(ByteSink& s, const Tensor& t_in) {
   s.put<uint64_t>(nbytes);
   if (nbytes) s.write(t.data_ptr(), nbytes);
 }
-Tensor read_tensor_record(ByteSource& s) {
+// The header of a record comes from an untrusted file: nothing is allocated until its dimensions are
+// non-negative, their product (checked for overflow) times the element size equals the stated byte
+// count, and - for in-memory sources - that many bytes are actually there. `skip_payload` moves past
+// the data instead of reading it (key listings).
+Tensor read_tensor_record(ByteSource& s, bool skip_payload = false) {
   const uint32_t ndim = s.get<uint32_t>();
   TORCH_CHECK(ndim <= 16, "checkpoint: implausible rank ", ndim);
   std::vector<int64_t> shape(ndim);
-  for (auto& d : shape) d = s.get<int64_t>();
+  uint64_t numel = 1;
+  for (auto& d : shape) {
+    d = s.get<int64_t>();
+    TORCH_CHECK(d >= 0, "checkpoint: negative dimension ", d);
+    TORCH_CHECK(d == 0 || numel <= (uint64_t(1) << 56) / static_cast<uint64_t>(d), "checkpoint: tensor size overflows");
+    numel *= static_cast<uint64_t>(d);
+  }
   const at::ScalarType st = tag_dtype(s.get<uint8_t>());
   const uint64_t nbytes = s.get<uint64_t>();
+  TORCH_CHECK(nbytes == numel * c10::elementSize(st), "checkpoint: byte count does not match shape");
+  TORCH_CHECK(nbytes <= s.remaining(), "checkpoint: record is longer than the data that follows");
+  if (skip_payload) {
+    s.skip(nbytes);
+    return Tensor();
+  }
   Tensor t = torch::empty(shape, torch::dtype(st));
-  TORCH_CHECK(nbytes == static_cast<uint64_t>(t.numel() * t.element_size()), "checkpoint: byte count does not match shape");
   if (nbytes) s.read(t.data_ptr(), nbytes);
   return t;
 }
@@ -259,7 +286,7 @@ py::tuple fdl_read_stream(ByteSource& s, bool keys_only) {
     TORCH_CHECK(nl < (1u << 20), "checkpoint: implausible name length");
     std::string name(nl, '\0');
     s.read(name.data(), nl);
-    Tensor t = read_tensor_record(s);
+    Tensor t = read_tensor_record(s, keys_only);
     if (keys_only) out.append(py::make_tuple(name, py::none()));
     else out.append(py::make_tuple(name, t));
   }

@@ -30,6 +30,10 @@ NVCC_FLAGS = [
 ]
 
 
+if os.environ.get("FLODL_B200_TIMELINE", "0") not in ("0", ""):
+    NVCC_FLAGS.append("-DFB_TIMELINE=1")      # per-CTA timestamps in the GEMM / convolution kernels (tuning builds only)
+
+
 def _sources():
     cu = sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
     cpp = sorted((CSRC / "runtime").glob("*.cpp")) + sorted((CSRC / "bindings").glob("*.cpp"))

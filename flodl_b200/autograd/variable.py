@@ -270,3 +270,9 @@ class Variable:
 
     def __repr__(self) -> str:
         return f"Variable(shape={list(self.t.shape)}, dtype={self.t.dtype}, device={self.t.device}, requires_grad={self.t.requires_grad})"
+
+
+# the comparison / query / math-extension ops of the reference's surface, by the reference's names
+from .. import tensor_ops as _tensor_ops  # noqa: E402
+
+_tensor_ops.install_variable_methods(Variable)

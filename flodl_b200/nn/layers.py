@@ -271,8 +271,9 @@ class RMSNorm(Module):
     def own_parameters(self): return [self.weight]
     def forward(self, x):
         t = x.t
-        ms = t.float().pow(2).mean(-1, keepdim=True)
-        return W((t.float() * torch.rsqrt(ms + self._eps)).to(t.dtype) * self.weight.t.to(t.dtype))
+        f = t if t.dtype == torch.float64 else t.float()      # statistics in fp32 at least (fp64 stays fp64)
+        ms = f.pow(2).mean(-1, keepdim=True)
+        return W((f * torch.rsqrt(ms + self._eps)).to(t.dtype) * self.weight.t.to(t.dtype))
 
 
 class GroupNorm(Module):

@@ -130,11 +130,6 @@ def conv2d(x, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
         if sums is not None:
             y._fb_bn_sums = sums.view(2, -1)
         return y if bias is None else y + bias.to(y.dtype).view(1, -1, 1, 1)
-    C = _ext.load() if x.is_cuda else None
-    if C is not None and core.FLAGS.native and hasattr(C, "conv2d_fwd"):
-        from . import conv_native
-        if conv_native.eligible(x, weight, stride, padding, dilation, groups):
-            return conv_native.conv2d(x, weight, bias, stride, padding)
     if x.dim() == 4 and x.is_cuda and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
         # channels-last activations: hand the filter over in the matching (KRSC) layout in the same
         # cast, so the library convolution runs its NHWC tensor-core kernels without transposes

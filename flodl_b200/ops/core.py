@@ -687,15 +687,22 @@ def attention(qkv: Optional[torch.Tensor] = None, q=None, k=None, v=None, mask=N
     Takes either a packed `qkv` [B, S, 3, H, D] (what a fused QKV projection produces) or separate
     `q`, `k`, `v` [B, S, H, D]; returns [B, S, H, D]. Counterpart of
     `autograd::scaled_dot_product_attention` (flodl/src/autograd/ops.rs:947-963)."""
-    if qkv is None:
-        qkv = torch.stack((q, k, v), dim=2)
-    B, S, _, H, D = qkv.shape
-    scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     p = p_drop if training else 0.0
-    ok, km = _key_mask(mask, B, S)
-    if _native_ok(qkv) and qkv.dtype == BF16 and D == 64 and ok and qkv.stride(4) == 1 and all(s % 8 == 0 for s in qkv.stride()[:4]):
-        return _AttnQKVFn.apply(qkv, km, scale, bool(causal), float(p), next_seed() if p > 0 else 0)
-    qh, kh, vh = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    if qkv is None and (q.shape != k.shape or k.shape != v.shape or not (_native_ok(q) and q.dtype == BF16 and q.shape[-1] == 64)):
+        # cross-attention (different query / key lengths) and everything the tensor-core kernel does
+        # not take: no packing, straight to the library op
+        D = q.shape[-1]
+        scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+        qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+    else:
+        if qkv is None:
+            qkv = torch.stack((q, k, v), dim=2)
+        B, S, _, H, D = qkv.shape
+        scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+        ok, km = _key_mask(mask, B, S)
+        if _native_ok(qkv) and qkv.dtype == BF16 and D == 64 and ok and qkv.stride(4) == 1 and all(s % 8 == 0 for s in qkv.stride()[:4]):
+            return _AttnQKVFn.apply(qkv, km, scale, bool(causal), float(p), next_seed() if p > 0 else 0)
+        qh, kh, vh = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     am = None
     if mask is not None:
         am = mask.to(qh.dtype)

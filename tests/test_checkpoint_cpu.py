@@ -159,3 +159,29 @@ def test_optimizer_state_file_roundtrip(tmp_path):
     opt.step()
     opt2.step()
     torch.testing.assert_close(p.t.detach(), q.t.detach())
+
+
+def test_corrupt_headers_are_rejected_before_anything_is_allocated():
+    """A damaged or hostile file must fail on its header: negative or overflowing dimensions, a byte
+    count that does not match the shape, or a record longer than the data that follows."""
+    import struct
+
+    from flodl_b200 import _ext
+    C = _ext.require()
+
+    def blob(shape, tag, nbytes, payload=b""):
+        out = b"FDLC" + struct.pack("<I", 2) + b"\0" * 32 + struct.pack("<I", 1)
+        name = b"w"
+        out += struct.pack("<I", len(name)) + name + struct.pack("<I", len(shape)) + b"".join(struct.pack("<q", d) for d in shape)
+        return out + struct.pack("<BQ", tag, nbytes) + payload
+
+    ok = blob([2, 2], 3, 16, b"\0" * 16)
+    assert C.fdl_load_bytes(ok, False)[2][0][1].shape == (2, 2)
+    for bad in (blob([-1, 4], 3, 16, b"\0" * 16),                      # negative dimension
+                blob([1 << 40, 1 << 40], 3, 16, b"\0" * 16),           # product overflows
+                blob([2, 2], 3, 12, b"\0" * 12),                       # byte count != shape
+                blob([1 << 20, 1 << 10], 3, 4 << 30, b"\0" * 16)):     # 4 GiB promised, 16 bytes present
+        with pytest.raises(RuntimeError):
+            C.fdl_load_bytes(bad, False)
+    # key listings skip the payloads instead of reading them
+    assert [k for k, _ in C.fdl_load_bytes(ok, True)[2]] == ["w"]
