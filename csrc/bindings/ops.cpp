@@ -90,6 +90,35 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, c
 
 int gemm_pick_config(int M, int N, int K, int split_k) { return fb_gemm_pick_config(M, N, K, split_k); }
 
+// Bounds-check record of the debug build (FLODL_BOUNDS_CHECK): one host-mapped int[4] = {site, index, limit, 0}.
+int* bounds_word(bool create) {
+  static int* host = nullptr;
+  if (!host && create) {
+    int* dev = nullptr;
+    TORCH_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host), 4 * sizeof(int), cudaHostAllocMapped) == cudaSuccess, "cudaHostAlloc");
+    host[0] = host[1] = host[2] = host[3] = 0;
+    TORCH_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev), host, 0) == cudaSuccess, "cudaHostGetDevicePointer");
+    check(fb_bounds_attach_elementwise(dev), "fb_bounds_attach_elementwise");
+    check(fb_bounds_attach_softmax_ce(dev), "fb_bounds_attach_softmax_ce");
+  }
+  return host;
+}
+bool bounds_check_build() {
+#ifdef FLODL_BOUNDS_CHECK
+  return FLODL_BOUNDS_CHECK != 0;
+#else
+  return false;
+#endif
+}
+// (site, index, limit) of the first recorded violation, or (0, 0, 0); `clear` re-arms the record.
+std::array<int, 3> bounds_report(bool clear) {
+  int* w = bounds_word(true);
+  cudaDeviceSynchronize();
+  std::array<int, 3> r = {w[0], w[1], w[2]};
+  if (clear) w[0] = w[1] = w[2] = 0;
+  return r;
+}
+
 int read_status(int device) {
   return status_word(device).item<int>();
 }
@@ -575,7 +604,7 @@ Tensor attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
 void bind_comm(py::module_& m);     // comm.cpp
 void bind_runtime(py::module_& m);  // runtime.cpp
 
-PYBIND11_MODULE(_C, m) {
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("bias") = py::none(), py::arg("epi") = 0, py::arg("aux") = py::none(), py::arg("alpha") = py::none(),
@@ -583,6 +612,8 @@ PYBIND11_MODULE(_C, m) {
         py::arg("m_dyn") = py::none(), py::arg("k_dyn") = py::none());
   m.def("gemm_pick_config", &gemm_pick_config);
   m.def("read_status", &read_status);
+  m.def("bounds_check_build", &bounds_check_build);
+  m.def("bounds_report", &bounds_report, py::arg("clear") = true);
   m.def("clear_status", &clear_status);
   m.def("layernorm_fwd", &layernorm_fwd, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("beta"), py::arg("eps"),
         py::arg("p_drop"), py::arg("seed"), py::arg("want_pre"), py::arg("seed_dev") = py::none());

@@ -196,6 +196,14 @@ int fb_grad_norm_noalloc(const void* g, long long n, float max_norm, float extra
                          void* stream);
 long long fb_grad_norm_noalloc_max(void);
 
+/* ---- bounds-checked debug build ----------------------------------------------------------------
+ * Built with FLODL_BOUNDS_CHECK=1, kernels range-check every index they read from device memory and
+ * record the first violation as {site, index, limit} instead of making the access. `dev_word` is a
+ * device-visible int[4] (host-mapped memory works); attach it once per translation unit. In a
+ * regular build the attach functions do nothing. */
+int fb_bounds_attach_elementwise(int* dev_word);
+int fb_bounds_attach_softmax_ce(int* dev_word);
+
 /* ---- collectives over peer-mapped buffers ---------------------------------------------------- */
 int fb_allreduce(const fb_symm_ctx* ctx, long long byte_off, long long n, int is_bf16, const float* weights,
                  int blocks, void* stream);

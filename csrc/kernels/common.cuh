@@ -160,6 +160,38 @@ __device__ __forceinline__ float dgelu_tanh_fast(float x) {
 }
 
 
+// ---- bounds-checked debug build -------------------------------------------------------------------
+// With -DFLODL_BOUNDS_CHECK=1 (FLODL_B200_BOUNDS_CHECK=1 at build time) every index that a kernel
+// takes from device memory (token ids, compaction tables, targets, row counts) is range-checked
+// before it is used. A violation never traps: the first one is recorded as {site, index, limit} in
+// a host-visible word that `fb_bounds_report` reads, and the access is skipped. This is the
+// stand-in for a memory checker on machines where none may be run. A regular build compiles the
+// checks away.
+#ifndef FLODL_BOUNDS_CHECK
+#define FLODL_BOUNDS_CHECK 0
+#endif
+#if FLODL_BOUNDS_CHECK
+static __device__ int* g_fb_bounds_word = nullptr;     // one per translation unit, all attached to the same record
+__device__ __forceinline__ bool fb_index_ok(long long i, long long n, int site) {
+  if (i >= 0 && i < n) return true;
+  int* w = g_fb_bounds_word;
+  if (w && atomicCAS(w, 0, site) == 0) {
+    w[1] = static_cast<int>(i < -2147483647LL ? -2147483647LL : (i > 2147483647LL ? 2147483647LL : i));
+    w[2] = static_cast<int>(n > 2147483647LL ? 2147483647LL : n);
+  }
+  return false;
+}
+#define FB_INDEX_OK(i, n, site) (::fb::fb_index_ok((i), (n), (site)))
+#define FB_BOUNDS_ATTACH(name)                                                                  \
+  extern "C" int fb_bounds_attach_##name(int* dev_word) {                                       \
+    return static_cast<int>(cudaMemcpyToSymbol(::fb::g_fb_bounds_word, &dev_word, sizeof(dev_word))); \
+  }
+#else
+#define FB_INDEX_OK(i, n, site) (true)
+#define FB_BOUNDS_ATTACH(name) \
+  extern "C" int fb_bounds_attach_##name(int*) { return 0; }
+#endif
+
 // ---- programmatic dependent launch -----------------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may start while its predecessor
 // in the stream is still running. `pdl_wait()` blocks until the predecessor grid has completed and

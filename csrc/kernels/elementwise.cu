@@ -231,6 +231,9 @@ gather_rows_kernel(const T* __restrict__ x, long long ld, const int* __restrict_
   if (i >= n_pad) return;
   constexpr int V = VecIO<T>::kVec;
   T* dst = xc + static_cast<long long>(i) * ldc;
+  const int rows_total = static_cast<int>(gridDim.x);
+  if (!FB_INDEX_OK(n, rows_total + 1, 102) || !FB_INDEX_OK(n_pad, rows_total + 1, 103)) return;
+  if (i < n && !FB_INDEX_OK(idx[i], rows_total, 104)) return;
   const T* src = x + static_cast<long long>(i < n ? idx[i] : 0) * ld;
   const bool vec = (cols % V == 0) && (ld % V == 0) && (ldc % V == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                    ((reinterpret_cast<uintptr_t>(xc) & 15) == 0);
@@ -252,6 +255,7 @@ scatter_rows_kernel(const T* __restrict__ dxc, long long ldc, const int* __restr
   pdl_entry();
   const int i = blockIdx.x;
   if (i >= counts[0]) return;
+  if (!FB_INDEX_OK(counts[0], static_cast<long long>(gridDim.x) + 1, 105) || !FB_INDEX_OK(idx[i], gridDim.x, 106)) return;
   constexpr int V = VecIO<T>::kVec;
   const T* src = dxc + static_cast<long long>(i) * ldc;
   T* dst = dx + static_cast<long long>(idx[i]) * ld;
@@ -272,7 +276,8 @@ __global__ void embedding_bwd_kernel(const T* __restrict__ dy, const long long* 
   const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
   const long long id = ids[t];
-  if (id == padding_idx || id < 0 || id >= vocab) return;
+  if (id == padding_idx) return;
+  if (!FB_INDEX_OK(id, vocab, 101) || id < 0 || id >= vocab) return;
   const T* src = dy + t * dim;
   float* dst = dw + id * dim;
   for (int c = threadIdx.x & 31; c < dim; c += 32) atomicAdd(dst + c, VecIO<T>::get(src + c));
@@ -419,3 +424,5 @@ extern "C" int fb_scatter_rows(const void* dxc, long long ldc, const int* idx, c
     fb::launch_pdl(fb::scatter_rows_kernel<float>, dim3(rows), dim3(128), 0, st, static_cast<const float*>(dxc), ldc, idx, counts, static_cast<float*>(dx), ld, cols);
   return static_cast<int>(cudaGetLastError());
 }
+
+FB_BOUNDS_ATTACH(elementwise)

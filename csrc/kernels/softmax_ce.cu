@@ -41,6 +41,8 @@ ce_fwd_kernel(const T* __restrict__ logits, long long ld, const long long* __res
   const int nvec = V / VEC;
   const bool aligned = ((reinterpret_cast<uintptr_t>(lr) & 15) == 0) && (!dr || (reinterpret_cast<uintptr_t>(dr) & 15) == 0);
 
+  if (t != ignore_index) (void)FB_INDEX_OK(t, V, 201);        // a label outside the vocabulary is recorded (and treated as ignored)
+  if (counts) (void)FB_INDEX_OK(counts[0], static_cast<long long>(rows) + 1, 202);
   if (t == ignore_index || t < 0 || t >= V) {
     if (row_loss && threadIdx.x == 0) row_loss[row] = 0.f;
     if (dr) {
@@ -168,3 +170,5 @@ extern "C" int fb_scale_rows(void* x, long long ld, int rows, int cols, const fl
     fb::launch_pdl(fb::scale_rows_kernel<float>, dim3(grid), dim3(256), 0, st, static_cast<float*>(x), ld, rows, cols, scalar);
   return static_cast<int>(cudaGetLastError());
 }
+
+FB_BOUNDS_ATTACH(softmax_ce)

@@ -30,6 +30,13 @@ NVCC_FLAGS = [
 ]
 
 
+BOUNDS_CHECK = os.environ.get("FLODL_B200_BOUNDS_CHECK", "0") not in ("0", "")
+if BOUNDS_CHECK:
+    # debug build: device-side index checks that record instead of faulting (see csrc/kernels/common.cuh);
+    # it goes to its own file so the regular library stays untouched
+    NVCC_FLAGS.append("-DFLODL_BOUNDS_CHECK=1")
+    BUILD = ROOT / "build_dbg"
+    TARGET = Path(__file__).resolve().parent / "_C_dbg.so"
 if os.environ.get("FLODL_B200_TIMELINE", "0") not in ("0", ""):
     NVCC_FLAGS.append("-DFB_TIMELINE=1")      # per-CTA timestamps in the GEMM / convolution kernels (tuning builds only)
 
@@ -64,7 +71,7 @@ def write_ninja() -> Path:
     torch_lib = str(Path(torch.__file__).parent / "lib")
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     cxx_flags = (
-        f"-O2 -std=c++17 -fPIC -fvisibility=default -DTORCH_EXTENSION_NAME=_C -D_GLIBCXX_USE_CXX11_ABI={abi} "
+        f"-O2 -std=c++17 -fPIC -fvisibility=default {'-DFLODL_BOUNDS_CHECK=1 ' if BOUNDS_CHECK else ''}-DTORCH_EXTENSION_NAME={'_C_dbg' if BOUNDS_CHECK else '_C'} -D_GLIBCXX_USE_CXX11_ABI={abi} "
         f"-DTORCH_API_INCLUDE_EXTENSION_H -Wno-deprecated-declarations -Wno-interference-size {inc_flags}"
     )
     lines = [

@@ -24,7 +24,9 @@ def load():
         from . import _build
         if _build.needs_build() and os.environ.get("FLODL_B200_NO_BUILD", "0") != "1":
             _build.build()
-        _C = importlib.import_module("flodl_b200._C")
+        # FLODL_B200_BOUNDS_CHECK=1 selects the debug library (`_C_dbg.so`: device-side index checks that
+        # record a violation instead of faulting); it is a separate file, the regular library is untouched
+        _C = importlib.import_module("flodl_b200._C_dbg" if _build.BOUNDS_CHECK else "flodl_b200._C")
     except Exception as e:  # pragma: no cover - surfaced by require()
         _ERR = e
         _C = None

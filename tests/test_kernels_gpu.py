@@ -571,3 +571,15 @@ def test_masked_lm_loss_on_labelled_rows_only_matches_full_projection():
     (ref * 1.5).backward()
     assert abs(ref.item() - l1) < 5e-2      # bf16 logits against an fp32 projection
     assert (wr.grad - dw1).abs().max().item() <= 3e-2 * wr.grad.abs().max().item() + 1e-4
+
+
+def test_bounds_checked_debug_build_records_instead_of_faulting():
+    """The debug library (`FLODL_B200_BOUNDS_CHECK=1`, built beside the regular one) range-checks every
+    index a kernel reads from device memory; see tests/_bounds_worker.py for the sweep."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, FLODL_B200_BOUNDS_CHECK="1")
+    res = subprocess.run([sys.executable, os.path.join(here, "_bounds_worker.py")], capture_output=True, text=True, timeout=900, env=env)
+    assert res.returncode == 0 and "BOUNDS_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-3000:]

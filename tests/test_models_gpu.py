@@ -101,3 +101,100 @@ def test_bert_mlm_native_vs_pytorch_loss_and_grads():
            for (n, _), a, b in zip(named, g_native, g_ref) if b.abs().max() > 0 and not n.endswith("key.bias")}
     worst = min(cos, key=cos.get)
     assert cos[worst] > 0.98, (worst, cos[worst])
+
+
+def _loss_curve(build, step_inputs, opt_factory, native: bool, steps: int = 40):
+    """Losses of `steps` training steps from a fixed seed, with the native kernels on or off."""
+    from flodl_b200 import nn, ops
+    from flodl_b200.parallel.engine import TrainEngine
+    torch.manual_seed(1234)
+    ops.manual_seed(7)
+    ops.set_native(native)
+    try:
+        model, loss_fn = build()
+        with nn.AutocastGuard(torch.bfloat16):
+            eng = TrainEngine(model, opt_factory)
+            out = []
+            for i in range(steps):
+                inp = step_inputs[i % len(step_inputs)]
+                out.append(eng.step(lambda: loss_fn(*inp)).item())
+        torch.cuda.synchronize()
+        return out
+    finally:
+        ops.set_native(True)
+
+
+def _assert_parity(a, b, what):
+    """Two bf16 trainings of the same model: the curves must track each other all the way (no drift
+    that compounds), and both must have learned."""
+    assert a[-1] < 0.8 * a[0] and b[-1] < 0.8 * b[0], (what, a[0], a[-1], b[0], b[-1])
+    worst = max(abs(x - y) / max(abs(y), 1e-3) for x, y in zip(a, b))
+    assert worst < 0.08, (what, worst, a[-5:], b[-5:])
+    tail = abs(sum(a[-10:]) - sum(b[-10:])) / abs(sum(b[-10:]))
+    assert tail < 0.04, (what, tail)
+
+
+def test_training_loss_parity_native_vs_pytorch_ops_bert_tiny():
+    from flodl_b200 import nn
+    from flodl_b200.hf.models.bert import BertConfig, BertForMaskedLM, build_extended_attention_mask
+    dev = torch.device("cuda", 0)
+    cfg = BertConfig(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=2, intermediate_size=256,
+                     max_position_embeddings=128, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    B, S = 8, 128
+    g = torch.Generator().manual_seed(3)
+    batches = []
+    for _ in range(4):
+        ids = torch.randint(0, 512, (B, S), generator=g)
+        labels = torch.full((B, S), -100, dtype=torch.long)
+        m = torch.rand(B, S, generator=g) < 0.15
+        labels[m] = ids[m]
+        batches.append((ids.to(dev), torch.arange(S, device=dev).expand(B, S).contiguous(), torch.zeros(B, S, dtype=torch.long, device=dev),
+                        build_extended_attention_mask(torch.ones(B, S, device=dev)), labels.to(dev)))
+
+    def build():
+        head = BertForMaskedLM.on_device(cfg, dev)
+        head.graph().set_training(True)
+        return head.graph(), lambda ids, pos, tt, am, lab: head.compute_loss([ids, pos, tt, am], lab)
+    opt = lambda ps: nn.AdamW(ps, 2e-3, 0.01)
+    _assert_parity(_loss_curve(build, batches, opt, True), _loss_curve(build, batches, opt, False), "bert-tiny")
+
+
+def test_training_loss_parity_native_vs_pytorch_ops_decoder_lm():
+    from flodl_b200 import nn
+    from flodl_b200.models.gpt import DecoderLM, DecoderLMConfig
+    dev = torch.device("cuda", 0)
+    cfg = DecoderLMConfig(vocab_size=512, d_model=128, n_layers=2, n_heads=2, d_ff=256, max_seq=128, dropout=0.0)
+    g = torch.Generator().manual_seed(4)
+    base = torch.randint(0, 512, (96,), generator=g)
+    stream = base.repeat(64)
+    batches = []
+    for i in range(4):
+        ids = torch.stack([stream[j * 31 + i:j * 31 + i + 129] for j in range(8)]).to(dev)
+        batches.append((ids[:, :-1].contiguous(), ids[:, 1:].contiguous()))
+
+    def build():
+        m = DecoderLM(cfg, dev)
+        m.set_training(True)
+        return m, lambda x, y: m.loss(x, y)
+    opt = lambda ps: nn.AdamW(ps, 2e-3, 0.0)
+    _assert_parity(_loss_curve(build, batches, opt, True), _loss_curve(build, batches, opt, False), "decoder-lm")
+
+
+def test_training_loss_parity_native_vs_pytorch_ops_resnet20():
+    from flodl_b200 import nn
+    from flodl_b200.autograd import Variable
+    from flodl_b200.models.resnet import resnet20
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 3, 32, 32, generator=g)
+    y = (x.mean((1, 2, 3)) * 40).long().clamp(-4, 5) + 4         # a learnable labelling of the images
+    batches = [(x.to(dev).bfloat16(), y.to(dev))]
+
+    def build():
+        m = resnet20(10, dev)
+        m.set_training(True)
+        return m, lambda a, b: nn.cross_entropy_loss(m.forward(Variable.wrap(a)), Variable.wrap(b))
+    opt = lambda ps: nn.SGD(ps, 0.05, 0.9, 1e-4)
+    a, b = _loss_curve(build, batches, opt, True, 30), _loss_curve(build, batches, opt, False, 30)
+    assert a[-1] < 0.8 * a[0] and b[-1] < 0.8 * b[0], (a[0], a[-1], b[0], b[-1])
+    assert abs(sum(a[-8:]) - sum(b[-8:])) / abs(sum(b[-8:])) < 0.15, (a[-8:], b[-8:])
