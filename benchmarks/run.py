@@ -53,12 +53,25 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
             if loss_kind == "ce":
                 return nn.cross_entropy_loss(pred.reshape([-1, pred.t.shape[-1]]), Variable.wrap(y.reshape(-1)))
             return nn.mse_loss(pred, Variable.wrap(y))
+        # A forward that reads device values on the host (a data-dependent loop count, an early exit)
+        # cannot be recorded into a graph. Find out with one eager forward + backward under PyTorch's
+        # sync detector rather than by letting a capture fail half-way.
+        capturable = True
+        torch.cuda.synchronize()
+        torch.cuda.set_sync_debug_mode("error")
         try:
+            step_fn(*batches[0]).t.backward()
+        except RuntimeError:
+            capturable = False
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+        torch.cuda.synchronize()
+        eng.flat.zero_grad()
+        if capturable:
             eng.capture(step_fn, list(batches[0]), warmup=2)
             one = lambda x, y: eng.replay([x, y])
             impl_label = "flodl (one CUDA graph per step)"
-        except Exception:   # noqa: BLE001  (host-side control flow inside forward)
-            torch.cuda.synchronize()
+        else:
             one = lambda x, y: eng.step(lambda: step_fn(x, y))
             impl_label = "flodl (engine, step by step)"
 

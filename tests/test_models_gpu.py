@@ -103,35 +103,50 @@ def test_bert_mlm_native_vs_pytorch_loss_and_grads():
     assert cos[worst] > 0.98, (worst, cos[worst])
 
 
-def _loss_curve(build, step_inputs, opt_factory, native: bool, steps: int = 40):
-    """Losses of `steps` training steps from a fixed seed, with the native kernels on or off."""
+def _loss_curve(build, step_inputs, opt_factory, native: bool, steps: int = 40, torch_opt=None):
+    """Losses of `steps` training steps from a fixed seed.
+
+    native=True : the product path - bf16 autocast, this library's kernels, `TrainEngine` with its flat
+                  buffers and fused optimizer.
+    native=False: the yardstick - the same modules through plain PyTorch fp32 ops (`ops.set_native(False)`,
+                  no autocast) and a stock `torch.optim` optimizer, nothing of the engine."""
     from flodl_b200 import nn, ops
     from flodl_b200.parallel.engine import TrainEngine
     torch.manual_seed(1234)
-    ops.manual_seed(7)
+    ops.core.manual_seed(7)
     ops.set_native(native)
     try:
         model, loss_fn = build()
-        with nn.AutocastGuard(torch.bfloat16):
-            eng = TrainEngine(model, opt_factory)
-            out = []
+        out = []
+        if native:
+            with nn.AutocastGuard(torch.bfloat16):
+                eng = TrainEngine(model, opt_factory)
+                for i in range(steps):
+                    inp = step_inputs[i % len(step_inputs)]
+                    out.append(eng.step(lambda: loss_fn(*inp)).item())
+        else:
+            opt = torch_opt([p.t for p in model.parameters()])
             for i in range(steps):
-                inp = step_inputs[i % len(step_inputs)]
-                out.append(eng.step(lambda: loss_fn(*inp)).item())
+                inp = [t.float() if t.is_floating_point() else t for t in step_inputs[i % len(step_inputs)]]
+                opt.zero_grad()
+                loss = loss_fn(*inp).t
+                loss.backward()
+                opt.step()
+                out.append(loss.item())
         torch.cuda.synchronize()
         return out
     finally:
         ops.set_native(True)
 
 
-def _assert_parity(a, b, what):
-    """Two bf16 trainings of the same model: the curves must track each other all the way (no drift
-    that compounds), and both must have learned."""
+def _assert_parity(a, b, what, step_tol=0.10, tail_tol=0.05):
+    """The bf16 product path against fp32 PyTorch: the curves must track each other all the way (no
+    drift that compounds), and both must have learned."""
     assert a[-1] < 0.8 * a[0] and b[-1] < 0.8 * b[0], (what, a[0], a[-1], b[0], b[-1])
-    worst = max(abs(x - y) / max(abs(y), 1e-3) for x, y in zip(a, b))
-    assert worst < 0.08, (what, worst, a[-5:], b[-5:])
+    worst = max(abs(x - y) / max(abs(y), 0.05) for x, y in zip(a, b))
+    assert worst < step_tol, (what, worst, a[-5:], b[-5:])
     tail = abs(sum(a[-10:]) - sum(b[-10:])) / abs(sum(b[-10:]))
-    assert tail < 0.04, (what, tail)
+    assert tail < tail_tol, (what, tail)
 
 
 def test_training_loss_parity_native_vs_pytorch_ops_bert_tiny():
@@ -155,8 +170,9 @@ def test_training_loss_parity_native_vs_pytorch_ops_bert_tiny():
         head = BertForMaskedLM.on_device(cfg, dev)
         head.graph().set_training(True)
         return head.graph(), lambda ids, pos, tt, am, lab: head.compute_loss([ids, pos, tt, am], lab)
-    opt = lambda ps: nn.AdamW(ps, 2e-3, 0.01)
-    _assert_parity(_loss_curve(build, batches, opt, True), _loss_curve(build, batches, opt, False), "bert-tiny")
+    a = _loss_curve(build, batches, lambda ps: nn.AdamW(ps, 2e-3, 0.01), True, 32)
+    b = _loss_curve(build, batches, None, False, 32, lambda ps: torch.optim.AdamW(ps, lr=2e-3, weight_decay=0.01))
+    _assert_parity(a, b, "bert-tiny")
 
 
 def test_training_loss_parity_native_vs_pytorch_ops_decoder_lm():
@@ -176,8 +192,9 @@ def test_training_loss_parity_native_vs_pytorch_ops_decoder_lm():
         m = DecoderLM(cfg, dev)
         m.set_training(True)
         return m, lambda x, y: m.loss(x, y)
-    opt = lambda ps: nn.AdamW(ps, 2e-3, 0.0)
-    _assert_parity(_loss_curve(build, batches, opt, True), _loss_curve(build, batches, opt, False), "decoder-lm")
+    a = _loss_curve(build, batches, lambda ps: nn.AdamW(ps, 2e-3, 0.0), True, 32)
+    b = _loss_curve(build, batches, None, False, 32, lambda ps: torch.optim.AdamW(ps, lr=2e-3, weight_decay=0.0))
+    _assert_parity(a, b, "decoder-lm", step_tol=0.15, tail_tol=0.08)
 
 
 def test_training_loss_parity_native_vs_pytorch_ops_resnet20():
@@ -194,7 +211,7 @@ def test_training_loss_parity_native_vs_pytorch_ops_resnet20():
         m = resnet20(10, dev)
         m.set_training(True)
         return m, lambda a, b: nn.cross_entropy_loss(m.forward(Variable.wrap(a)), Variable.wrap(b))
-    opt = lambda ps: nn.SGD(ps, 0.05, 0.9, 1e-4)
-    a, b = _loss_curve(build, batches, opt, True, 30), _loss_curve(build, batches, opt, False, 30)
+    a = _loss_curve(build, batches, lambda ps: nn.SGD(ps, 0.05, 0.9, 1e-4), True, 30)
+    b = _loss_curve(build, batches, None, False, 30, lambda ps: torch.optim.SGD(ps, lr=0.05, momentum=0.9, weight_decay=1e-4))
     assert a[-1] < 0.8 * a[0] and b[-1] < 0.8 * b[0], (a[0], a[-1], b[0], b[-1])
-    assert abs(sum(a[-8:]) - sum(b[-8:])) / abs(sum(b[-8:])) < 0.15, (a[-8:], b[-8:])
+    assert abs(sum(a[-8:]) - sum(b[-8:])) / abs(sum(b[-8:])) < 0.2, (a[-8:], b[-8:])
