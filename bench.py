@@ -38,6 +38,10 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's default)")
     ap.add_argument("--no-graph", action="store_true", help="eager steps instead of one CUDA graph per step")
     ap.add_argument("--comm", default="symm", choices=["symm", "nccl"])
+    ap.add_argument("--api", default="engine", choices=["engine", "trainer", "builder"],
+                    help="which public API drives the step: engine = TrainEngine (whole-step CUDA graph, the default and the headline); "
+                         "trainer = Trainer.setup_head + loss.backward() + graph.step() (the reference's synchronous path, bert-base); "
+                         "builder = Trainer.builder(...).run().join() with the coordinator in the loop (the reference's asynchronous path, lm)")
     return ap.parse_args()
 
 
@@ -289,6 +293,108 @@ def run_ours(args):
         comm.destroy_process_group()
 
 
+def run_trainer_api(args):
+    """The reference-shaped synchronous path (flodl/src/distributed/ddp.rs:900-923): `Trainer.setup_head`, then per batch
+    forward, `loss.backward()`, `graph.step()`; gradients are exchanged by `DistributedState` (bucketed, overlapped with
+    backward), nothing is captured into a CUDA graph."""
+    import torch
+    import torch.distributed as dist
+    from flodl_b200 import nn
+    from flodl_b200.parallel import comm
+    from flodl_b200.parallel.ddp import Trainer
+    comm.init_process_group()
+    world, rank, local = comm.world_size(), comm.rank(), comm.local_rank()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(1234)
+    guard = nn.AutocastGuard(torch.bfloat16)
+    graph, step_fn, batch, opt, B, desc, _ = make_bert(args, dev)
+    Trainer.setup_with(graph, None, opt, None, scatter=False)
+    gen = torch.Generator().manual_seed(100 + rank)
+    pool = [[t.pin_memory() for t in batch(gen)] for _ in range(8)]
+
+    def one(host):
+        inputs = [t.to(dev, non_blocking=True) for t in host]
+        if graph._ddp is not None:
+            graph._ddp.begin_batch(B)
+        loss = step_fn(*inputs)
+        loss.backward()
+        graph.step()
+        return loss
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for i in range(max(args.warmup, 3)):
+        one(pool[i % 8])
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last = 0.0
+    for i in range(args.steps):
+        last = one(pool[i % 8])
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "DDP samples/sec (max over ranks)", "api": "Trainer.setup_head + graph.step()", "impl": "ours", "value": round(world * B / (ms / 1e3), 2),
+                          "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+                          "config": dict(desc, per_gpu_batch=B, parallelism=f"dp{world}", step="eager, inputs copied from pinned host memory every step"),
+                          "final_loss": round(float(last.item()), 4)}), flush=True)
+    guard.release()
+    if world > 1:
+        dist.barrier()
+        comm.destroy_process_group()
+
+
+def run_builder_api(args):
+    """The reference-shaped asynchronous path (flodl/src/distributed/ddp_run/orchestrator.rs:1339-1359):
+    `Trainer.builder(...).run().join()`: one worker per rank, the coordinator on rank 0, parameters averaged every
+    AVG_EVERY batches (pinned cadence). Throughput comes from the coordinator's own epoch clock."""
+    import torch
+    from flodl_b200 import nn
+    from flodl_b200.data import TensorDataSet
+    from flodl_b200.models.gpt import DecoderLM, DecoderLMConfig
+    from flodl_b200.parallel import comm
+    from flodl_b200.parallel.ddp import Trainer
+    from flodl_b200.parallel.ddp_run import ApplyPolicy, AverageBackend
+    comm.init_process_group()
+    world, rank = comm.world_size(), comm.rank()
+    torch.cuda.set_device(comm.local_rank())
+    B, S = (args.batch or 32), 256
+    cfg = DecoderLMConfig(vocab_size=32000, d_model=512, n_layers=6, n_heads=8, d_ff=2048, max_seq=256, dropout=0.0)
+    batches_per_epoch = max(AVG_EVERY, (args.steps // AVG_EVERY) * AVG_EVERY)
+    n = batches_per_epoch * B * world
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (n, S + 1), generator=g)
+    ds = TensorDataSet(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+
+    def factory(d):
+        torch.manual_seed(11)
+        return DecoderLM(cfg, d)
+    epochs = 3
+    b = (Trainer.builder(factory, lambda ps: nn.AdamW(ps, 3e-4, 0.01), lambda m, batch: m.loss(batch[0], batch[1]))
+         .dataset(ds).batch_size(B).num_epochs(epochs).lr_scale_ratio(0.0).policy(ApplyPolicy.Cadence).backend(AverageBackend.Nccl)
+         .anchor(AVG_EVERY).max_anchor(AVG_EVERY))
+    with nn.AutocastGuard(torch.bfloat16):
+        h = b.run()
+        state = h.join()
+    if rank == 0:
+        ms = h.poll_metrics()
+        best = min(m.epoch_ms for m in ms[1:]) if len(ms) > 1 else ms[0].epoch_ms      # the first epoch pays for set-up and capture
+        print(json.dumps({"metric": "DDP samples/sec (coordinator epoch clock)", "api": "Trainer.builder(...).run().join()", "impl": "ours",
+                          "value": round(n / (best / 1e3), 2), "unit": "samples/s", "n_gpus": world, "epochs": epochs,
+                          "batches_per_epoch_per_rank": batches_per_epoch, "ms_per_step": round(best / batches_per_epoch, 4),
+                          "config": {"model": "decoder-lm (6x512, 8 heads, ffn 2048, vocab 32000, pre-LN, GELU)", "seq_len": S, "per_gpu_batch": B,
+                                     "grad_sync": f"parameter averaging every {AVG_EVERY} batches, coordinator in the loop"},
+                          "errors": [str(e) for e in h.errors()], "final_loss": round(ms[-1].avg_loss, 4), "trained": state is not None}), flush=True)
+    comm.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -301,6 +407,10 @@ def main():
         from baseline import twin
         twin.run(args)
         return
+    if args.api == "trainer":
+        return run_trainer_api(args)
+    if args.api == "builder":
+        return run_builder_api(args)
     run_ours(args)
 
 
