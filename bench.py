@@ -379,7 +379,7 @@ def run_builder_api(args):
     epochs = 3
     b = (Trainer.builder(factory, lambda ps: nn.AdamW(ps, 3e-4, 0.01), lambda m, batch: m.loss(batch[0], batch[1]))
          .dataset(ds).batch_size(B).num_epochs(epochs).lr_scale_ratio(0.0).policy(ApplyPolicy.Cadence).backend(AverageBackend.Nccl)
-         .anchor(AVG_EVERY).max_anchor(AVG_EVERY))
+         .anchor(AVG_EVERY).max_anchor(AVG_EVERY).cuda_graph(True))
     with nn.AutocastGuard(torch.bfloat16):
         h = b.run()
         state = h.join()

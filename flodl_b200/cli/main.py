@@ -11,7 +11,8 @@ from typing import List, Optional
 from .args import ArgError, FdlArgs, arg
 from .manifest import ManifestError, find_manifest, load_manifest, run_command
 
-BUILTINS = ["diagnose", "build", "bench", "export-hf", "api-ref", "schema", "completions", "config", "init", "help"]
+BUILTINS = ["diagnose", "setup", "install", "libtorch", "build", "bench", "export-hf", "api-ref", "schema", "completions", "config", "init", "add",
+            "skill", "help"]
 
 
 # ---- diagnose ---------------------------------------------------------------------------------------
@@ -232,7 +233,12 @@ def usage(manifest: Optional[str]) -> str:
              "  schema [command]        argument schemas as JSON",
              "  completions <shell>     shell completion script (bash, zsh, fish)",
              "  config show             the merged manifest with the origin of every value",
-             "  init <name>             scaffold a project"]
+             "  init <name>             scaffold a project",
+             "  add [dir]               add a training scaffold to an existing directory",
+             "  setup [--force]         check the machine and build the native library",
+             "  install [--check|--dev] build and verify the native library",
+             "  libtorch info|list|path which libtorch this process uses",
+             "  skill show|install      the assistant guide (condensed API and porting reference)"]
     if manifest:
         try:
             cmds = load_manifest(manifest)[0].get("commands") or {}
@@ -287,6 +293,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             return 2
         if cmd == "init":
             return init(rest)
+        if cmd in ("setup", "install", "libtorch", "add", "skill"):
+            from . import setup_cmds
+            return getattr(setup_cmds, cmd)(rest)
         if manifest is None:
             print(f"unknown command {cmd!r} and no fdl.yml found", file=sys.stderr)
             return 2

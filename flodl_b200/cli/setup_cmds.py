@@ -1,0 +1,291 @@
+"""`fdl setup`, `fdl libtorch`, `fdl install`, `fdl add`, `fdl skill` (flodl-cli/src/main.rs:111-181).
+
+In the reference these commands exist to get a matching libtorch onto the machine (download or
+build it, point `LIBTORCH_PATH` at it), to install the CLI itself, to add the framework to an
+existing project and to install the AI-assistant skill. Here libtorch arrives inside the installed
+`torch` wheel, so the same verbs answer the questions that remain:
+
+* `setup`     checks interpreter, torch, CUDA toolchain and GPUs against what the native library
+              needs (sm_100a, nvcc >= 12.8, torch with CUDA), builds the library, and prints what is
+              missing otherwise. `--non-interactive` never prompts (nothing here prompts), `--force`
+              rebuilds even if the library is current.
+* `libtorch`  `info` prints which libtorch the process would load (version, CUDA, cuDNN, NCCL, arch
+              list, library directory); `list` shows every torch installation on `sys.path`;
+              `path` prints the directory a C++ build should link against.
+* `install`   builds the native library in-tree and verifies it loads (`--check`: verify only;
+              `--dev`: also build the bounds-checked debug library).
+* `add`       adds a training scaffold (`train.py`, `fdl.yml`) to an existing directory without
+              touching files that are already there; `--playground` adds a small script that
+              exercises the graph builder.
+* `skill`     `install [dir]` writes the assistant guide (a condensed API and porting reference) into
+              `<dir>/.fdl/skills/flodl_b200/SKILL.md`; `show` prints it.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from dataclasses import dataclass
+from typing import List
+
+from .args import FdlArgs, arg
+
+
+@dataclass
+class SetupArgs(FdlArgs):
+    """Check the machine and build the native library."""
+    non_interactive: bool = arg(False, help="never prompt (accepted for compatibility: nothing prompts)")
+    force: bool = arg(False, help="rebuild the native library even if it is up to date")
+
+
+@dataclass
+class InstallArgs(FdlArgs):
+    """Build and verify the native library."""
+    check: bool = arg(False, help="only verify that the library is built and loads")
+    dev: bool = arg(False, help="also build the bounds-checked debug library")
+
+
+@dataclass
+class AddArgs(FdlArgs):
+    """Add a training scaffold to an existing directory."""
+    target: str = arg(".", positional=True, help="directory to add the files to")
+    playground: bool = arg(False, help="also add playground.py (graph-builder tour)")
+    install: bool = arg(False, help="build the native library afterwards")
+
+
+def _requirements() -> List[dict]:
+    """One row per requirement: name, ok, found, needed."""
+    import shutil
+    import subprocess
+    rows = []
+    rows.append({"name": "python", "ok": sys.version_info >= (3, 10), "found": sys.version.split()[0], "needed": ">= 3.10"})
+    try:
+        import torch
+        rows.append({"name": "torch", "ok": True, "found": torch.__version__, "needed": "any 2.x with CUDA"})
+        rows.append({"name": "torch CUDA build", "ok": torch.version.cuda is not None, "found": str(torch.version.cuda), "needed": ">= 12.8"})
+        if torch.cuda.is_available():
+            caps = sorted({torch.cuda.get_device_capability(i) for i in range(torch.cuda.device_count())})
+            rows.append({"name": "GPU", "ok": any(c[0] == 10 for c in caps), "found": ", ".join(f"sm_{a}{b}" for a, b in caps), "needed": "sm_100 (B200)"})
+        else:
+            rows.append({"name": "GPU", "ok": None, "found": "none visible", "needed": "sm_100 (B200) to run; not needed to build"})
+    except Exception as e:  # noqa: BLE001
+        rows.append({"name": "torch", "ok": False, "found": f"import failed: {e}", "needed": "installed"})
+    nvcc = shutil.which("nvcc") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    found = "not found"
+    ok = False
+    try:
+        out = subprocess.run([nvcc, "--version"], capture_output=True, text=True, timeout=20).stdout
+        line = [l for l in out.splitlines() if "release" in l]
+        if line:
+            found = line[0].split("release")[-1].strip()
+            major, minor = (int(x) for x in found.split(",")[0].split(".")[:2])
+            ok = (major, minor) >= (12, 8)
+    except Exception:  # noqa: BLE001
+        pass
+    rows.append({"name": "nvcc", "ok": ok, "found": found, "needed": ">= 12.8 (sm_100a target)"})
+    rows.append({"name": "ninja", "ok": shutil.which("ninja") is not None, "found": shutil.which("ninja") or "not found", "needed": "on PATH"})
+    rows.append({"name": "g++", "ok": shutil.which("g++") is not None, "found": shutil.which("g++") or "not found", "needed": "C++17"})
+    return rows
+
+
+def setup(argv: List[str]) -> int:
+    a = SetupArgs.parse(argv, "fdl setup")
+    rows = _requirements()
+    for r in rows:
+        mark = "ok " if r["ok"] else ("-- " if r["ok"] is None else "NO ")
+        print(f"  [{mark}] {r['name']:<18} {r['found']:<34} (needs {r['needed']})")
+    blockers = [r["name"] for r in rows if r["ok"] is False]
+    if blockers:
+        print("setup: cannot build the native library until these are fixed: " + ", ".join(blockers), file=sys.stderr)
+        return 1
+    from .. import _build
+    if a.force or _build.needs_build():
+        print("building the native library for sm_100a ...")
+        _build.build()
+    from .. import _ext
+    if not _ext.available():
+        print("setup: the library was built but does not load", file=sys.stderr)
+        return 1
+    print(f"ready: {_build.TARGET}")
+    return 0
+
+
+def libtorch(argv: List[str]) -> int:
+    sub = argv[0] if argv else "info"
+    import importlib.util
+    if sub == "path":
+        import torch
+        print(os.path.join(os.path.dirname(torch.__file__), "lib"))
+        return 0
+    if sub == "list":
+        seen = []
+        for p in sys.path:
+            init = os.path.join(p, "torch", "version.py")
+            if os.path.isfile(init) and p not in seen:
+                seen.append(p)
+                ver = {}
+                try:
+                    exec(open(init).read(), ver)  # noqa: S102  (the wheel's own version file)
+                except Exception:  # noqa: BLE001
+                    pass
+                print(f"{ver.get('__version__', '?'):<18} cuda {ver.get('cuda', '?'):<8} {os.path.join(p, 'torch')}")
+        if not seen:
+            print("no torch installation on sys.path", file=sys.stderr)
+            return 1
+        return 0
+    if sub == "info":
+        if importlib.util.find_spec("torch") is None:
+            print("torch is not installed", file=sys.stderr)
+            return 1
+        import torch
+        info = {"version": torch.__version__, "cuda": torch.version.cuda, "cudnn": torch.backends.cudnn.version() if torch.backends.cudnn.is_available() else None,
+                "arch_list": torch.cuda.get_arch_list() if torch.cuda.is_available() else [], "lib_dir": os.path.join(os.path.dirname(torch.__file__), "lib"),
+                "cxx11_abi": bool(torch._C._GLIBCXX_USE_CXX11_ABI)}
+        try:
+            info["nccl"] = ".".join(map(str, torch.cuda.nccl.version()))
+        except Exception:  # noqa: BLE001
+            info["nccl"] = None
+        print(json.dumps(info, indent=2) if "--json" in argv else "\n".join(f"  {k}: {v}" for k, v in info.items()))
+        return 0
+    print("usage: libtorch [info [--json] | list | path]", file=sys.stderr)
+    return 2
+
+
+def install(argv: List[str]) -> int:
+    a = InstallArgs.parse(argv, "fdl install")
+    from .. import _build, _ext
+    if not a.check:
+        _build.build()
+        if a.dev:
+            import subprocess
+            r = subprocess.run([sys.executable, "-c", "from flodl_b200 import _build; print(_build.build())"],
+                               env=dict(os.environ, FLODL_B200_BOUNDS_CHECK="1"), capture_output=True, text=True)
+            if r.returncode != 0:
+                print(r.stderr[-2000:], file=sys.stderr)
+                return 1
+            print(f"debug library: {r.stdout.strip().splitlines()[-1]}")
+    ok = (not _build.needs_build()) and _ext.available()
+    print(f"{'ok' if ok else 'NOT READY'}: {_build.TARGET}")
+    return 0 if ok else 1
+
+
+_TRAIN = '''"""Training entry point."""
+import torch
+from flodl_b200 import nn
+from flodl_b200.autograd import Variable
+from flodl_b200.graph import FlowBuilder
+from flodl_b200.parallel.ddp import Trainer
+
+dev = "cuda" if torch.cuda.is_available() else "cpu"
+model = (FlowBuilder.from_(nn.Linear(2, 16, True, dev)).through(nn.GELU()).through(nn.LayerNorm(16, device=dev))
+         .also(nn.Linear(16, 16, True, dev)).through(nn.Linear(16, 2, True, dev)).build())
+Trainer.setup(model, None, lambda ps: nn.Adam(ps, 1e-2))      # one rank or many: the same three lines below
+for step in range(200):
+    x = torch.randn(32, 2, device=dev)
+    y = torch.stack([x[:, 0].sin(), x[:, 1].cos()], 1)
+    loss = nn.mse_loss(model.forward(Variable.wrap(x)), Variable.wrap(y))
+    loss.backward()
+    model.step()
+    if step % 50 == 0:
+        print(step, loss.item())
+'''
+
+_PLAYGROUND = '''"""A tour of the graph builder: fork / merge / tag / observe."""
+import torch
+from flodl_b200 import nn
+from flodl_b200.autograd import Variable
+from flodl_b200.graph import FlowBuilder
+
+g = (FlowBuilder.from_(nn.Linear(8, 16)).tag("stem").through(nn.GELU())
+     .also(nn.Linear(16, 16)).tag("residual").through(nn.LayerNorm(16)).through(nn.Linear(16, 4)).build())
+print(g.to_dot())
+print(g.forward(Variable.wrap(torch.randn(3, 8))).t.shape)
+'''
+
+_MANIFEST = '''description: {name}
+
+commands:
+  train:
+    description: Train the model
+    run: python train.py
+  test:
+    description: Run the tests
+    run: python -m pytest -q
+'''
+
+
+def add(argv: List[str]) -> int:
+    a = AddArgs.parse(argv, "fdl add")
+    root = os.path.abspath(a.target)
+    if not os.path.isdir(root):
+        print(f"fdl add: {root} is not a directory", file=sys.stderr)
+        return 1
+    files = {"train.py": _TRAIN, "fdl.yml": _MANIFEST.format(name=os.path.basename(root) or "project")}
+    if a.playground:
+        files["playground.py"] = _PLAYGROUND
+    for name, text in files.items():
+        path = os.path.join(root, name)
+        if os.path.exists(path):
+            print(f"kept    {path} (already there)")
+            continue
+        with open(path, "w") as f:
+            f.write(text)
+        print(f"created {path}")
+    return install([]) if a.install else 0
+
+
+SKILL = '''# flodl_b200: assistant guide
+
+A Blackwell-native (sm_100a) deep-learning framework with floDl's API shape, in Python over PyTorch tensors
+with hand-written CUDA kernels for the hot ops and its own NVLink collectives.
+
+## Five things to know
+1. `Variable` wraps a `torch.Tensor` (`.t`); modules take and return `Variable`s; method names follow floDl
+   (`mul_scalar`, `sum_dim`, `narrow`, ...). `flodl_b200.tensor_ops` holds the rest of the tensor surface.
+2. Models are graphs: `FlowBuilder.from_(m).through(m2).also(res).split(...).merge(...).tag("name").build()`.
+   Loops: `.loop_body(b).for_n(3)`; routing: `.switch(router, branches)`, `.gate(router, experts)`.
+3. Training: `Trainer.setup(model, None, lambda ps: nn.Adam(ps, lr))`, then `loss.backward(); model.step()`.
+   The same code runs on 1 or N GPUs (`torchrun --nproc-per-node N`); gradients are exchanged by this
+   library's NVLink kernels, overlapped with backward.
+4. Fast path: `TrainEngine(model, opt_factory)` + `capture(step_fn, example_inputs)` + `replay(inputs)`:
+   the whole step (forward, backward, all-reduce, optimizer) is one CUDA graph; bf16 autocast with
+   `nn.AutocastGuard(torch.bfloat16)` puts GEMMs, attention, LayerNorm, cross-entropy on the tcgen05 kernels.
+5. Asynchronous / Local SGD: `Trainer.builder(factory, opt_factory, train_fn).dataset(ds).batch_size(b)
+   .num_epochs(e).policy(ApplyPolicy.Cadence).backend(AverageBackend.Nccl).run().join()`.
+
+## Porting from floDl (Rust)
+| floDl | here |
+|---|---|
+| `Tensor::randn(&[2,3], opts)?` | `torch.randn(2, 3, device=...)` |
+| `Variable::new(t, true)` | `Variable(t, requires_grad=True)` |
+| `x.matmul(&w)?.add(&b)?` | `x.matmul(w).add(b)` |
+| `Linear::on_device(i, o, dev)?` | `nn.Linear.on_device(i, o, dev)` |
+| `FlowBuilder::from(a).through(b).build()?` | `FlowBuilder.from_(a).through(b).build()` |
+| `Adam::new(&params, 1e-3)` | `nn.Adam(params, 1e-3)` |
+| `clip_grad_norm(&params, 1.0)?` | `nn.clip_grad_norm(params, 1.0)` |
+| `Ddp::setup(&model, builder, opt)?` | `Trainer.setup(model, builder, opt)` |
+| `save_checkpoint_file(path, ...)` | `nn.save_checkpoint_file(path, ...)` (same `.fdl` v2 format) |
+| `AutoModel::from_pretrained(id)` | `hf.AutoModel.from_pretrained(local_dir)` |
+Errors are `TensorError` exceptions instead of `Result`.
+
+## Commands
+`python -m flodl_b200.cli diagnose | setup | install | bench | api-ref | export-hf`, `python bench.py --gpus N`.
+'''
+
+
+def skill(argv: List[str]) -> int:
+    sub = argv[0] if argv else "show"
+    if sub == "show":
+        print(SKILL)
+        return 0
+    if sub == "install":
+        root = os.path.abspath(argv[1] if len(argv) > 1 else ".")
+        d = os.path.join(root, ".fdl", "skills", "flodl_b200")
+        os.makedirs(d, exist_ok=True)
+        path = os.path.join(d, "SKILL.md")
+        with open(path, "w") as f:
+            f.write(SKILL)
+        print(f"installed {path}")
+        return 0
+    print("usage: skill [show | install [dir]]", file=sys.stderr)
+    return 2

@@ -124,3 +124,21 @@ def test_api_ref_lists_public_names(capsys):
     assert main(["api-ref", "--json"]) == 0
     names = {r["name"] for r in json.loads(capsys.readouterr().out)}
     assert {"FlowBuilder", "Trainer", "Adam", "DataLoader", "CpuWorker", "record_scalar"} <= names
+
+
+def test_setup_install_add_libtorch_skill(tmp_path, capsys):
+    from flodl_b200.cli.main import main
+    assert main(["add", str(tmp_path), "--playground"]) == 0
+    for f in ("train.py", "fdl.yml", "playground.py"):
+        assert (tmp_path / f).exists()
+    (tmp_path / "train.py").write_text("# mine")
+    assert main(["add", str(tmp_path)]) == 0                      # existing files are kept
+    assert (tmp_path / "train.py").read_text() == "# mine"
+    assert main(["skill", "install", str(tmp_path)]) == 0
+    assert "Porting from floDl" in (tmp_path / ".fdl" / "skills" / "flodl_b200" / "SKILL.md").read_text()
+    assert main(["libtorch", "info", "--json"]) == 0
+    assert main(["libtorch", "path"]) == 0
+    assert main(["install", "--check"]) == 0
+    assert main(["setup"]) == 0
+    out = capsys.readouterr().out
+    assert "nvcc" in out and "ready:" in out and "lib_dir" in out

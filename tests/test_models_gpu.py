@@ -213,5 +213,7 @@ def test_training_loss_parity_native_vs_pytorch_ops_resnet20():
         return m, lambda a, b: nn.cross_entropy_loss(m.forward(Variable.wrap(a)), Variable.wrap(b))
     a = _loss_curve(build, batches, lambda ps: nn.SGD(ps, 0.05, 0.9, 1e-4), True, 30)
     b = _loss_curve(build, batches, None, False, 30, lambda ps: torch.optim.SGD(ps, lr=0.05, momentum=0.9, weight_decay=1e-4))
-    assert a[-1] < 0.8 * a[0] and b[-1] < 0.8 * b[0], (a[0], a[-1], b[0], b[-1])
-    assert abs(sum(a[-8:]) - sum(b[-8:])) / abs(sum(b[-8:])) < 0.2, (a[-8:], b[-8:])
+    # one batch is memorised within a dozen steps: compare the descent itself, then the (tiny) end values
+    assert a[-1] < 0.1 * a[0] and b[-1] < 0.1 * b[0], (a[0], a[-1], b[0], b[-1])
+    assert abs(sum(a[:10]) - sum(b[:10])) / abs(sum(b[:10])) < 0.15, (a[:10], b[:10])
+    assert abs(a[-1] - b[-1]) < 0.05, (a[-1], b[-1])
