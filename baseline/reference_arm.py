@@ -38,6 +38,7 @@ import ctypes as C
 import json
 import math
 import os
+from typing import Optional
 import subprocess
 import sys
 import time
@@ -697,13 +698,18 @@ def unavailable(reason: str):
         print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
 
 
-def run(args, clock_sampler_cls=None, device: str = "cuda"):
-    """Run K timed steps of the reference's training step and print the JSON line (rank 0)."""
+def run(args, clock_sampler_cls=None, device: str = "cuda", shim_path: Optional[str] = None):
+    """Run K timed steps of the reference's training step and print the JSON line (rank 0).
+    `shim_path` (a library exporting the same `flodl_*` C interface) replaces the reference's own shim:
+    the same host call sequence then measures that library; the line is tagged `"impl": "abi"`."""
     import numpy as np
-    try:
-        path = build_shim()
-    except Exception as e:  # noqa: BLE001
-        return unavailable(f"{type(e).__name__}: {str(e)[:200]}")
+    if shim_path is None:
+        try:
+            path = build_shim()
+        except Exception as e:  # noqa: BLE001
+            return unavailable(f"{type(e).__name__}: {str(e)[:200]}")
+    else:
+        path = shim_path
     shim = Shim(path)
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -882,6 +888,10 @@ def run(args, clock_sampler_cls=None, device: str = "cuda"):
             "reference_build": "flodl-sys/shim.cpp compiled unmodified (g++ -std=c++17 -DFLODL_BUILD_CUDA=1) into baseline/_ref/libflodl_shim.so; "
                                "host loop restated over the C ABI",
         }
+        if shim_path is not None:
+            calls = shim.fn("flodl_b200_native_calls", [], C.c_longlong)()
+            out.update(impl="abi", native_calls=int(calls), reference_build=None, shim=os.path.basename(shim_path))
+            out["config"]["step"] = "eager (the reference host's call sequence over this repository's drop-in flodl_* C library)"
         print(json.dumps(out), flush=True)
     o.autocast_del(guard)
     if comm is not None:

@@ -33,7 +33,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "twin"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "twin", "abi"])
     ap.add_argument("--model", default="bert-base", choices=["bert-base", "resnet20", "lm"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's default)")
     ap.add_argument("--no-graph", action="store_true", help="eager steps instead of one CUDA graph per step")
@@ -402,6 +402,12 @@ def main():
         # nothing of this repository's package or kernels is imported on this path
         from baseline import reference_arm
         reference_arm.run(args, ClockSampler)
+        return
+    if args.impl == "abi":
+        # the same host call sequence as the reference arm, over this repository's drop-in `flodl_*` C library
+        from baseline import reference_arm
+        shim = os.path.join(os.path.dirname(os.path.abspath(__file__)), "flodl_b200", "libflodl_b200_shim.so")
+        reference_arm.run(args, ClockSampler, shim_path=shim)
         return
     if args.impl == "twin":
         from baseline import twin

@@ -173,6 +173,9 @@ int fb_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, 
  * collectives raise such a word when a bounded wait gave up, so un-reduced gradients are never applied. */
 int fb_adam_step(float* p, const void* g, float* m, float* v, void* p16, long long n, const float* hyper, float b1,
                  float b2, float eps, const float* grad_scale, int g_bf16, const int* skip, void* stream);
+/* fb_adam_step with hyper = {lr, 1-b1^t, 1-b2^t, weight_decay} read from HOST memory at launch (no bf16 shadow, no skip word). */
+int fb_adam_step_host(float* p, const void* g, float* m, float* v, long long n, const float* hyper_host, float b1, float b2,
+                      float eps, int g_bf16, void* stream);
 int fb_sgd_step(float* p, const void* g, float* buf, void* p16, long long n, const float* hyper,
                 const float* grad_scale, int g_bf16, const int* skip, void* stream);
 int fb_grad_norm_parts(long long n);

@@ -26,12 +26,13 @@ template <typename TG>
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ p, const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
             __nv_bfloat16* __restrict__ p16, long long n, const float* __restrict__ hyper, float b1, float b2,
-            float eps, const float* __restrict__ grad_scale, const int* __restrict__ skip) {
+            float eps, const float* __restrict__ grad_scale, const int* __restrict__ skip, float4 hv) {
   pdl_entry();
   // `skip`: a device-visible word that a collective sets when it gave up; the update is then left out
   // and the parameters stay as they were, so the host can raise before anything diverged.
   if (skip && __ldg(skip) != 0) return;
-  const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], wd = hyper[3];
+  // hyper-parameters from device memory (a captured graph replays with fresh values) or, when `hyper` is null, by value
+  const float lr = hyper ? hyper[0] : hv.x, bc1 = hyper ? hyper[1] : hv.y, bc2 = hyper ? hyper[2] : hv.z, wd = hyper ? hyper[3] : hv.w;
   const float gs = grad_scale ? *grad_scale : 1.f;
   const float step_size = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
@@ -162,11 +163,32 @@ extern "C" int fb_adam_step(float* p, const void* g, float* m, float* v, void* p
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   if (g_bf16)
-    fb::launch_pdl(fb::adam_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale, skip);
+    fb::launch_pdl(fb::adam_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const __nv_bfloat16*>(g), m, v, static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2, eps, grad_scale, skip, make_float4(0.f, 0.f, 0.f, 0.f));
   else
     fb::launch_pdl(fb::adam_kernel<float>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const float*>(g), m, v,
                                                                      static_cast<__nv_bfloat16*>(p16), n, hyper, b1, b2,
-                                                                     eps, grad_scale, skip);
+                                                                     eps, grad_scale, skip, make_float4(0.f, 0.f, 0.f, 0.f));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The same update with the hyper-parameters {lr, 1-b1^t, 1-b2^t, weight_decay} passed from the host (eager callers
+// that have them at hand and do not replay the launch from a graph).
+extern "C" int fb_adam_step_host(float* p, const void* g, float* m, float* v, long long n, const float* hyper_host, float b1, float b2,
+                                 float eps, int g_bf16, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  const float4 hv = make_float4(hyper_host[0], hyper_host[1], hyper_host[2], hyper_host[3]);
+  if (g_bf16)
+    fb::launch_pdl(fb::adam_kernel<__nv_bfloat16>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const __nv_bfloat16*>(g), m, v,
+                   static_cast<__nv_bfloat16*>(nullptr), n, static_cast<const float*>(nullptr), b1, b2, eps, static_cast<const float*>(nullptr),
+                   static_cast<const int*>(nullptr), hv);
+  else
+    fb::launch_pdl(fb::adam_kernel<float>, dim3(static_cast<int>(blocks)), dim3(256), 0, st, p, static_cast<const float*>(g), m, v,
+                   static_cast<__nv_bfloat16*>(nullptr), n, static_cast<const float*>(nullptr), b1, b2, eps, static_cast<const float*>(nullptr),
+                   static_cast<const int*>(nullptr), hv);
   return static_cast<int>(cudaGetLastError());
 }
 

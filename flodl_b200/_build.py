@@ -23,6 +23,8 @@ ROOT = Path(__file__).resolve().parent.parent
 CSRC = ROOT / "csrc"
 BUILD = ROOT / "build"
 TARGET = Path(__file__).resolve().parent / "_C.so"
+# The drop-in C library (`csrc/abi`): the `flodl_*` functions of the reference's C interface, no Python in it.
+SHIM_TARGET = Path(__file__).resolve().parent / "libflodl_b200_shim.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
@@ -47,6 +49,19 @@ def _sources():
     return cu, cpp
 
 
+def _abi_sources():
+    return sorted((CSRC / "abi").glob("*.cpp"))
+
+
+def _nccl_flags():
+    """(include flag, link flags) for the NCCL that torch itself runs on, else the system one."""
+    import torch
+    root = Path(torch.__file__).parent.parent / "nvidia" / "nccl"
+    if (root / "lib" / "libnccl.so.2").is_file():
+        return f"-I{root / 'include'}", f"-L{root / 'lib'} -Wl,-rpath,{root / 'lib'} -l:libnccl.so.2"
+    return "", "-lnccl"
+
+
 def _newest_mtime(paths):
     return max((p.stat().st_mtime for p in paths), default=0.0)
 
@@ -56,6 +71,8 @@ def needs_build() -> bool:
         return True
     cu, cpp = _sources()
     hdrs = list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list(CSRC.rglob("*.hpp"))
+    if not BOUNDS_CHECK and (not SHIM_TARGET.exists() or _newest_mtime(cu + _abi_sources() + hdrs) > SHIM_TARGET.stat().st_mtime):
+        return True
     return _newest_mtime(cu + cpp + hdrs) > TARGET.stat().st_mtime
 
 
@@ -95,6 +112,20 @@ def write_ninja() -> Path:
         "-ltorch -ltorch_cpu -ltorch_cuda -lc10 -lc10_cuda -ltorch_python -lcudart -lz -ldl -lpthread",
         "  description = LINK $out",
     ]
+    nccl_inc, nccl_link = _nccl_flags()
+    lines += [
+        "rule cxx_abi",
+        f"  command = $cxx -O2 -std=c++17 -fPIC -fvisibility=hidden -D_GLIBCXX_USE_CXX11_ABI={abi} -Wno-deprecated-declarations "
+        f"-Wno-interference-size {' '.join('-I' + p for p in ce.include_paths() + [cuda_home + '/include', str(CSRC / 'include')])} {nccl_inc} "
+        "-MMD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "  description = CXX $in",
+        "rule link_abi",
+        f"  command = $cxx -shared $in -o $out -L{torch_lib} -L{cuda_home}/lib64 -Wl,-rpath,{torch_lib} -Wl,--no-undefined "
+        f"-ltorch -ltorch_cpu -ltorch_cuda -lc10 -lc10_cuda -lcudart {nccl_link} -ldl -lpthread",
+        "  description = LINK $out",
+    ]
     objs = []
     for s in cu:
         o = BUILD / (s.stem + ".cu.o")
@@ -105,14 +136,24 @@ def write_ninja() -> Path:
         lines.append(f"build {o}: cxx {s}")
         objs.append(str(o))
     lines.append(f"build {TARGET}: link {' '.join(objs)}")
-    lines.append(f"default {TARGET}")
+    defaults = [str(TARGET)]
+    if not BOUNDS_CHECK:
+        # the drop-in C library shares the kernel objects; the comm kernels stay out (it does its collectives with NCCL)
+        abi_objs = [o for o, src in zip(objs, cu) if src.parent.name == "kernels"]
+        for s in _abi_sources():
+            o = BUILD / (s.stem + ".abi.o")
+            lines.append(f"build {o}: cxx_abi {s}")
+            abi_objs.append(str(o))
+        lines.append(f"build {SHIM_TARGET}: link_abi {' '.join(abi_objs)}")
+        defaults.append(str(SHIM_TARGET))
+    lines.append(f"default {' '.join(defaults)}")
     path = BUILD / "build.ninja"
     path.write_text("\n".join(lines) + "\n")
     return path
 
 
 def build(verbose: bool = False) -> Path:
-    """Compile every native source for sm_100a and link `_C.so` (incremental)."""
+    """Compile every native source for sm_100a and link `_C.so` and `libflodl_b200_shim.so` (incremental)."""
     ninja_file = write_ninja()
     cmd = ["ninja", "-f", str(ninja_file), "-j", str(max(2, os.cpu_count() or 2))]
     if verbose:
