@@ -163,6 +163,11 @@ class Variable:
     __truediv__ = lambda self, o: self.div(o) if isinstance(o, (Variable, torch.Tensor)) else self.div_scalar(o)
     __neg__ = neg
     __matmul__ = matmul
+    __radd__ = lambda self, o: Variable.wrap(_t(o) + self.t)
+    __rsub__ = lambda self, o: Variable.wrap(_t(o) - self.t)
+    __rmul__ = lambda self, o: Variable.wrap(_t(o) * self.t)
+    __rtruediv__ = lambda self, o: Variable.wrap(_t(o) / self.t)
+    __pow__ = lambda self, e: Variable.wrap(self.t.pow(_t(e)))
 
     # ---- activations ----------------------------------------------------------------------------
     def relu(self): return Variable.wrap(torch.relu(self.t))

@@ -23,7 +23,7 @@ shim = R.Shim({shim!r})
 o = R.Ops(shim, R.CUDA, 0)
 o.set_device(0)
 o.manual_seed(7)
-guard = o.autocast_new(o.dt, R.BF16)
+guard = o.autocast_new(o.dt, R.BF16) if {autocast} else None
 B, S, V = 8, 64, 512
 model = R.BertMLM(o, V=V, H=128, L=2, heads=2, I_=256, P=S, p={p})
 opt = R.AdamW(o, model.params(), 1e-3, 0.01)
@@ -46,22 +46,29 @@ print("RESULT " + json.dumps({{"losses": losses, "native_calls": int(calls)}}))
 """
 
 
-def _run(native: bool, p: float):
+def _run(native: bool, p: float, autocast: bool = True):
     env = dict(os.environ, FLODL_B200_NATIVE="1" if native else "0")
-    res = subprocess.run([sys.executable, "-c", _CHILD.format(root=ROOT, shim=SHIM, p=p)], capture_output=True, text=True, timeout=900, env=env)
+    res = subprocess.run([sys.executable, "-c", _CHILD.format(root=ROOT, shim=SHIM, p=p, autocast=autocast)], capture_output=True, text=True, timeout=900, env=env)
     assert res.returncode == 0, res.stderr[-3000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
 
 
-def test_native_paths_track_the_aten_fallbacks():
-    a, b = _run(True, 0.0), _run(False, 0.0)
+def test_native_bf16_paths_track_fp32_aten():
+    """The oracle is the same host sequence over plain fp32 ATen ops (no autocast, natives off)."""
+    a, b = _run(True, 0.0), _run(False, 0.0, autocast=False)
     assert a["native_calls"] > 100 and b["native_calls"] == 0
     la, lb = a["losses"], b["losses"]
     assert all(math.isfinite(v) for v in la + lb)
     assert abs(la[0] - lb[0]) <= 2e-2 * abs(lb[0])
     assert la[-1] < 0.8 * la[0] and lb[-1] < 0.8 * lb[0]
     assert abs(la[-1] - lb[-1]) <= 0.1 * abs(lb[0])
+
+
+def test_aten_fallbacks_under_autocast_still_train():
+    b = _run(False, 0.0)
+    assert b["native_calls"] == 0
+    assert all(math.isfinite(v) for v in b["losses"]) and b["losses"][-1] < b["losses"][0]
 
 
 def test_native_dropout_trains():
