@@ -1,8 +1,10 @@
-"""`from_pretrained`: resolve a repo id to local files and build + load the model
-(flodl-hf/src/hub/). Nothing here opens a network connection: files are looked up, in this order,
-in `<HF_HOME>/flodl-converted/<repo>/`, in the HuggingFace hub cache layout
-(`<HF_HOME>/hub/models--org--name/snapshots/*/`), or in `repo_id` itself when it is a directory.
-A repo that is not on disk is reported with the paths that were tried."""
+"""`from_pretrained`: resolve a repo id to files and build + load the model (flodl-hf/src/hub/mod.rs).
+Files are looked up, in this order, in `repo_id` itself when it is a directory, in
+`<HF_HOME>/flodl-converted/<repo>/` (where `python -m flodl_b200.hf.convert` writes), and in the HuggingFace hub
+cache layout (`<HF_HOME>/hub/models--org--name/snapshots/*/`). What is not on disk is fetched from the hub
+(`fetch_file`: `<HF_ENDPOINT or https://huggingface.co>/<repo>/resolve/<revision>/<file>`, bearer token from `HF_TOKEN`)
+into that cache layout, unless `HF_HUB_OFFLINE=1`; a repo that can be neither found nor fetched is reported with
+the paths and the URL that were tried."""
 from __future__ import annotations
 
 import glob
@@ -30,8 +32,50 @@ def candidate_dirs(repo_id: str) -> List[str]:
     return out
 
 
-def resolve_files(repo_id: str) -> Tuple[str, str, Optional[str]]:
-    """(config.json, model.safetensors, tokenizer.json or None)."""
+def offline() -> bool:
+    return os.environ.get("HF_HUB_OFFLINE", "0") not in ("0", "", "false", "False")
+
+
+def endpoint() -> str:
+    return (os.environ.get("HF_ENDPOINT") or "https://huggingface.co").rstrip("/")
+
+
+def snapshot_dir(repo_id: str, revision: str = "main") -> str:
+    return os.path.join(hf_home(), "hub", "models--" + repo_id.replace("/", "--"), "snapshots", revision)
+
+
+def fetch_file(repo_id: str, filename: str, revision: str = "main", timeout_s: float = 30.0) -> str:
+    """Download one file of a hub repo into the cache layout and return its path (an existing copy is reused).
+    The body is streamed to `<name>.part` and renamed when complete, so an interrupted download leaves no
+    half-written file under the final name."""
+    import shutil
+    import urllib.error
+    import urllib.request
+    dst = os.path.join(snapshot_dir(repo_id, revision), filename)
+    if os.path.exists(dst):
+        return dst
+    if offline():
+        raise TensorError(f"fetch_file({repo_id}, {filename}): HF_HUB_OFFLINE is set and {dst} does not exist")
+    url = f"{endpoint()}/{repo_id}/resolve/{revision}/{filename}"
+    req = urllib.request.Request(url, headers={"User-Agent": "flodl_b200"})
+    token = os.environ.get("HF_TOKEN") or os.environ.get("HUGGING_FACE_HUB_TOKEN")
+    if token:
+        req.add_header("Authorization", f"Bearer {token}")
+    os.makedirs(os.path.dirname(dst), exist_ok=True)
+    part = dst + ".part"
+    try:
+        with urllib.request.urlopen(req, timeout=timeout_s) as r, open(part, "wb") as f:
+            shutil.copyfileobj(r, f, 1 << 20)
+    except (urllib.error.URLError, OSError) as e:
+        if os.path.exists(part):
+            os.remove(part)
+        raise TensorError(f"fetch_file: GET {url} failed: {e}") from e
+    os.replace(part, dst)
+    return dst
+
+
+def resolve_files(repo_id: str, revision: str = "main") -> Tuple[str, str, Optional[str]]:
+    """(config.json, model.safetensors, tokenizer.json or None); fetches what is missing when allowed."""
     tried = candidate_dirs(repo_id)
     cfg = st = tok = None
     for d in tried:
@@ -39,9 +83,22 @@ def resolve_files(repo_id: str) -> Tuple[str, str, Optional[str]]:
         cfg = cfg or (c if os.path.exists(c) else None)
         st = st or (s if os.path.exists(s) else None)
         tok = tok or (t if os.path.exists(t) else None)
+    errors = []
+    if (cfg is None or st is None) and not os.path.isdir(repo_id) and not offline():
+        try:
+            cfg = cfg or fetch_file(repo_id, "config.json", revision)
+            st = st or fetch_file(repo_id, "model.safetensors", revision)
+        except TensorError as e:
+            errors.append(str(e))
+        if tok is None and cfg is not None and st is not None:
+            try:
+                tok = fetch_file(repo_id, "tokenizer.json", revision)
+            except TensorError:
+                tok = None                    # optional: many repos ship only vocab.txt
     if cfg is None or st is None:
-        raise TensorError(f"from_pretrained({repo_id}): config.json / model.safetensors not found locally (no network access is attempted); "
-                          f"looked in: {tried}. If the repo ships only `pytorch_model.bin`, convert it to safetensors first.")
+        raise TensorError(f"from_pretrained({repo_id}): config.json / model.safetensors not found; looked in: {tried}"
+                          + (f"; {'; '.join(errors)}" if errors else "; HF_HUB_OFFLINE is set" if offline() else "")
+                          + ". If the repo ships only `pytorch_model.bin`, run `python -m flodl_b200.hf.convert <repo or file>` first.")
     return cfg, st, tok
 
 

@@ -169,9 +169,11 @@ def bert_legacy_layernorm_rename(key: str) -> str:
 
 def bert_legacy_key_rename(key: str) -> str:
     """Old TF-style names (`LayerNorm.gamma/beta`) and the MLM decoder bias stored beside the
-    decoder (`cls.predictions.bias`, `lm_head.bias`)."""
+    decoder (`cls.predictions.bias`, `lm_head.bias`, ALBERT's `predictions.bias`)."""
     if key == "cls.predictions.bias":
         return "cls.predictions.decoder.bias"
+    if key == "predictions.bias":
+        return "predictions.decoder.bias"
     if key == "lm_head.bias":
         return "lm_head.decoder.bias"
     return bert_legacy_layernorm_rename(key)

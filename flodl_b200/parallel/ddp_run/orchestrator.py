@@ -267,10 +267,19 @@ class DdpBuilder:
 
     def _worker_thread(self, wcfg: WorkerConfig, transport, collective: bool, stop: threading.Event, results: dict,
                        lr_factor: float, registry: List[GpuWorker], name: str) -> threading.Thread:
+        # Autocast state is per thread (PyTorch's and this package's): the workers inherit the state of the thread
+        # that calls run(), so `with AutocastGuard(bf16): builder.run().join()` trains in bf16.
+        from ... import ops as _ops_mod
+        inherited = _ops_mod.FLAGS.autocast
+
         def body():
+            guard = None
             try:
                 if wcfg.device.type == "cuda":
                     torch.cuda.set_device(wcfg.device)
+                if inherited is not None:
+                    from ...nn.amp import AutocastGuard
+                    guard = AutocastGuard(inherited, wcfg.device.type)
                 w = GpuWorker(wcfg, self.model_factory, self.optim_factory, self._dataset, transport, self._checkpoint_fn, collective)
                 registry.append(w)
                 sched = self._scheduler_fn(wcfg.world_size) if self._scheduler_fn is not None else None
@@ -291,6 +300,9 @@ class DdpBuilder:
                 except Exception:
                     pass
                 stop.set()
+            finally:
+                if guard is not None:
+                    guard.release()
         return threading.Thread(target=body, name=name, daemon=True)
 
     def _coord_thread(self, coord: Coordinator, stop: threading.Event, results: dict) -> threading.Thread:

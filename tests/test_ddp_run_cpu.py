@@ -454,6 +454,27 @@ def test_single_device_run():
     assert len(h.poll_metrics()) == 2 and len(st.params) == 4
 
 
+def test_workers_inherit_the_launching_threads_autocast_state():
+    """Autocast state is per thread; `with AutocastGuard(...): builder.run()` must reach the worker threads."""
+    from flodl_b200 import ops
+    x, y = _data(32)
+    seen = []
+
+    def fn(m, batch):
+        seen.append((ops.FLAGS.autocast, torch.is_autocast_enabled("cpu")))
+        return _train_fn(m, batch)
+    with nn.AutocastGuard(torch.bfloat16, "cpu"):
+        h = (Trainer.builder(_model, lambda ps: nn.SGD(ps, 0.05), fn).dataset(TensorDataSet(x, y)).batch_size(8)
+             .num_epochs(1).devices(["cpu"]).run())
+        h.join()
+    assert seen and all(a == torch.bfloat16 and b for a, b in seen)
+    seen.clear()
+    h = (Trainer.builder(_model, lambda ps: nn.SGD(ps, 0.05), fn).dataset(TensorDataSet(x, y)).batch_size(8)
+         .num_epochs(1).devices(["cpu"]).run())
+    h.join()
+    assert seen and all(a is None and not b for a, b in seen)
+
+
 def test_thread_worker_error_is_reported():
     x, y = _data(64)
 
