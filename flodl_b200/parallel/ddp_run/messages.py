@@ -223,4 +223,5 @@ def make_partition(offset: int, size: int, total: int, epoch: int, seed: int) ->
     partitions of one epoch never overlap (ddp_run/mod.rs:751-783)."""
     perm = _ext.require().Rng(int(seed) + int(epoch)).permutation(int(total))
     end = min(int(offset) + int(size), int(total))
-    return list(perm[int(offset):end])
+    part = perm[int(offset):end]
+    return part.tolist() if hasattr(part, "tolist") else [int(i) for i in part]

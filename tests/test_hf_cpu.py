@@ -256,7 +256,7 @@ def test_auto_classes_export_and_local_from_pretrained(tmp_path, monkeypatch):
     assert not any(n.startswith("classifier") for n, _ in backbone.named_parameters())
     with pytest.raises(Exception) as e:
         hf.from_pretrained("acme/not-there")
-    assert "not found locally" in str(e.value)
+    assert "not found; looked in" in str(e.value)
     assert classify_architecture("BertForMaskedLM") == "mlm" and classify_architecture("BertModel") == "base"
     assert parse_head("token-classification") == "tokcls"
     with pytest.raises(Exception):
@@ -301,3 +301,84 @@ def test_tokenizer_wrapper_builds_graph_inputs(tmp_path):
     assert "hello world" in t.decode([2, 4, 5, 3]) and t.token_to_id("world") == 5 and t.id_to_token(4) == "hello"
     with pytest.raises(Exception):
         t.encode([])
+
+
+# ---- hub fetch, converter, parity matrix ------------------------------------------------------------------
+def _serve(directory):
+    """A throw-away HTTP server on 127.0.0.1 that plays the hub: GET /<repo>/resolve/<rev>/<file>."""
+    import functools
+    import http.server
+    import threading
+
+    class Quiet(http.server.SimpleHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), functools.partial(Quiet, directory=str(directory)))
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv
+
+
+def _tiny_bert_files(dst):
+    hc = transformers.BertConfig(vocab_size=50, hidden_size=32, num_hidden_layers=1, num_attention_heads=4, intermediate_size=64,
+                                 max_position_embeddings=16, architectures=["BertModel"])
+    torch.manual_seed(0)
+    hf = transformers.BertModel(hc).eval()
+    dst.mkdir(parents=True, exist_ok=True)
+    (dst / "config.json").write_text(hc.to_json_string())
+    (dst / "model.safetensors").write_bytes(hf_state_bytes(hf))
+    return hf
+
+
+def test_from_pretrained_fetches_missing_files_into_the_cache_layout(tmp_path, monkeypatch):
+    from flodl_b200.hf import hub
+    from flodl_b200.tensor import TensorError
+    _tiny_bert_files(tmp_path / "www" / "acme" / "tiny-bert" / "resolve" / "main")
+    srv = _serve(tmp_path / "www")
+    try:
+        monkeypatch.setenv("HF_HOME", str(tmp_path / "home"))
+        monkeypatch.setenv("HF_ENDPOINT", f"http://127.0.0.1:{srv.server_address[1]}")
+        monkeypatch.delenv("HF_HUB_OFFLINE", raising=False)
+        cfg, weights, tok = hub.resolve_files("acme/tiny-bert")
+        snap = tmp_path / "home" / "hub" / "models--acme--tiny-bert" / "snapshots" / "main"
+        assert cfg == str(snap / "config.json") and weights == str(snap / "model.safetensors") and tok is None
+        assert not list(snap.glob("*.part"))
+        g = hub.from_pretrained("acme/tiny-bert")
+        assert g is not None
+        # a second resolve is served from the cache: it still works with the server gone and offline mode on
+        srv.shutdown()
+        monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+        assert hub.resolve_files("acme/tiny-bert")[0] == cfg
+        with pytest.raises(TensorError, match="HF_HUB_OFFLINE"):
+            hub.resolve_files("acme/not-there")
+        monkeypatch.delenv("HF_HUB_OFFLINE")
+        with pytest.raises(TensorError, match="GET http://127.0.0.1"):
+            hub.resolve_files("acme/not-there")
+    finally:
+        srv.shutdown()
+
+
+def test_convert_bin_to_safetensors_round_trip(tmp_path, monkeypatch):
+    from flodl_b200.hf import convert, hub
+    src = tmp_path / "repo"
+    hf = _tiny_bert_files(src)
+    (src / "model.safetensors").unlink()
+    torch.save(hf.state_dict(), src / "pytorch_model.bin")
+    monkeypatch.setenv("HF_HOME", str(tmp_path / "home"))
+    monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+    assert convert.main([str(src)]) == 0
+    out = tmp_path / "home" / "flodl-converted" / "repo"
+    back = st.read_safetensors((out / "model.safetensors").read_bytes())
+    sd = hf.state_dict()
+    assert set(back) == {k for k, v in sd.items()} and all(torch.equal(back[k], sd[k]) for k in back)
+    assert (out / "config.json").exists()
+    g = hub.from_pretrained("repo")                       # found under flodl-converted
+    assert g is not None
+    assert convert.main([str(tmp_path / "nothing-here")]) == 1
+
+
+def test_parity_matrix_tool_covers_every_family_and_head():
+    from flodl_b200.hf import parity
+    res = parity.run(["bert", "distilbert"], ["base", "mlm", "qa"], "cpu", 2e-4)
+    assert all(v is not None and v <= 2e-4 for v, _ in res.values()), res
+    table = parity.render(res, ["bert", "distilbert"], ["base", "mlm", "qa"], 2e-4)
+    assert "| bert |" in table and "FAIL" not in table and "n/a" not in table
