@@ -31,8 +31,8 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "twin", "abi"])
     ap.add_argument("--model", default="bert-base", choices=["bert-base", "resnet20", "lm"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's default)")
@@ -69,7 +69,7 @@ class ClockSampler(threading.Thread):
                 for bit, name in names.items():
                     if isinstance(bit, int) and bit and mask & bit and bit & (bit - 1) == 0:
                         self.reasons.add(name.replace("nvmlClocksEventReason", "").replace("nvmlClocksThrottleReason", ""))
-                time.sleep(0.05)
+                time.sleep(0.01)
         except Exception as e:  # NVML missing: report that instead of numbers
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
@@ -78,7 +78,7 @@ class ClockSampler(threading.Thread):
         self.join(timeout=2)
         s = sorted(self.samples)
         rs = sorted(r for r in self.reasons if r not in ("None", "GpuIdle", "ApplicationsClocksSetting"))
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz or None, "reasons": rs}
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz or None, "reasons": rs, "samples": len(s)}
 
 
 # ---------------------------------------------------------------------------------------- workloads
@@ -90,6 +90,17 @@ def make_bert(args, dev):
     B, S = (args.batch or 32), 128
     head = BertForMaskedLM.on_device(cfg, dev)
     head.graph().set_training(True)
+    # BERT's own initialisation (normal(0, initializer_range = 0.02) matrices and embeddings, zero biases, unit
+    # LayerNorm gains), as the reference arm uses: the first loss is then ln(vocab) ~ 10.3
+    with torch.no_grad():
+        for name, p in head.graph().named_parameters():
+            t = p.t if hasattr(p, "t") else p
+            if t.dim() >= 2:
+                t.normal_(0.0, 0.02)
+            elif name.endswith("LayerNorm.weight"):
+                t.fill_(1.0)
+            else:
+                t.zero_()
 
     def batch(gen):
         ids = torch.randint(0, cfg.vocab_size, (B, S), generator=gen)

@@ -30,6 +30,20 @@ constexpr int kBlk = 128;      // rows per query / key block
 constexpr int kAttnThreads = 160;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Per-CTA timeline of the single-block kernels (a tuning aid, compiled in only with -DFB_TIMELINE=1): 8 clock64
+// stamps per CTA for the first 1024 CTAs of a launch (forward) / 16 per CTA (backward), read back with fb_attn_timeline.
+#ifndef FB_TIMELINE
+#define FB_TIMELINE 0
+#endif
+#if FB_TIMELINE
+__device__ long long g_attn_ts[16 * 1024];
+#define FB_ATTN_TS(slot) do { const int cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); if (cta_ < 1024) { \
+    long long v_ = clock64(); if ((slot) >= 14) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); v_ = static_cast<long long>(g_); } \
+    g_attn_ts[cta_ * 16 + (slot)] = v_; } } while (0)
+#else
+#define FB_ATTN_TS(slot) do { } while (0)
+#endif
+
 int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
                       uint32_t box_inner, uint32_t box_outer);  // gemm_tcgen05.cu
 void ensure_thread_context();                                    // gemm_tcgen05.cu
@@ -100,30 +114,36 @@ struct AttnParams {
 };
 
 // ===================================================================================== forward
-// Shared-memory layout of the forward kernel for `st` K/V stages (1 when the sequence is a single
-// key block: 82 KB, so two CTAs share an SM; 2 otherwise).
+// Shared-memory layout of the forward kernel. Several key blocks: two K/V stages and P panels of their own
+// (114 KB, two CTAs per SM). A single key block (S <= 128, the encoder shapes): Q and K are dead once S = Q K^T
+// has completed, so the probabilities are written over them (49 KB); with the output accumulator taking over the
+// TMEM columns of S as well (128 columns per CTA) and no running accumulator in registers, four CTAs share an
+// SM and hide one another's load / MMA / softmax latencies, which is what bounds a 128 x 128 x 64 problem.
 struct FwdSmem {
   int Q, K, V, P, MASK, BARS, TOTAL;
-  __host__ __device__ explicit FwdSmem(int st) {
+  __host__ __device__ explicit FwdSmem(bool single) {
+    const int st = single ? 1 : 2;
     Q = 0;                       // 16 KB
     K = 16384;                   // st x 16 KB
     V = K + st * 16384;          // st x 16 KB
-    P = V + st * 16384;          // 2 panels x 16 KB
-    MASK = P + 2 * 16384;        // 128 floats
+    P = single ? 0 : V + st * 16384;          // 2 panels x 16 KB
+    MASK = single ? V + 16384 : P + 2 * 16384;        // 128 floats
     BARS = MASK + 512;
     TOTAL = BARS + 256;
   }
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+template <bool kSingle>
+__global__ void __launch_bounds__(kAttnThreads, kSingle ? 4 : 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ o, float* __restrict__ lse,
                 const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int n_kv_all = (p.S + kBlk - 1) / kBlk;
-  const int kv_stages = n_kv_all > 1 ? 2 : 1;
-  const FwdSmem L(kv_stages);
+  constexpr int kv_stages = kSingle ? 1 : 2;
+  constexpr int kTmemCols = kSingle ? 128 : 256;
+  const FwdSmem L(kSingle);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.BARS);
   uint64_t* q_full = bars + 0;
   uint64_t* kv_full = bars + 1;     // [2]
@@ -139,6 +159,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qb * kBlk;
+  if (kSingle && threadIdx.x == 0) { FB_ATTN_TS(0); FB_ATTN_TS(14); }
   const int n_kv = p.causal ? min(n_kv_all, qb + 1) : n_kv_all;
   const unsigned long long seed = p.seed + (p.seed_dev ? *p.seed_dev : 0ull);
 
@@ -153,7 +174,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_fence_init();
   }
   if (warp == 4) {
-    tmem_alloc<1>(tmem_slot, 256);
+    tmem_alloc<1>(tmem_slot, kTmemCols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
@@ -161,7 +182,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base;
-  const uint32_t tmem_O = tmem_base + 128;
+  pdl_entry();       // barriers, TMEM and descriptors are set up; everything below reads the predecessor's output
+  if (kSingle && threadIdx.x == 0) FB_ATTN_TS(1);
+  // single key block: every softmax thread has read its row of S before P V is issued (p_ready), so O reuses S's columns
+  const uint32_t tmem_O = kSingle ? tmem_base : tmem_base + 128;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -186,6 +210,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = mbar_wait(&kv_full[st], use & 1, abort_flag, p.status, kStatusWaitFull);
         if (!ok) break;
         tc_fence_after_sync();
+        if (kSingle) FB_ATTN_TS(2);
         // S = Q K^T (the softmax threads have drained S of block j-1: they arrived on p_ready)
 #pragma unroll
         for (int k4 = 0; k4 < kHD / 16; ++k4)
@@ -224,9 +249,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float sc = p.scale * kLog2e;
     const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
     float m_run = -INFINITY, l_run = 0.f;
-    float acc[kHD];
+    float acc[kSingle ? 1 : kHD];      // running output row; not needed when there is one key block
 #pragma unroll
-    for (int i = 0; i < kHD; ++i) acc[i] = 0.f;
+    for (int i = 0; i < (kSingle ? 1 : kHD); ++i) acc[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int kv0 = j * kBlk;
@@ -241,6 +266,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(s_full, j & 1, abort_flag, p.status, kStatusWaitAccum);
       if (!ok) break;
       tc_fence_after_sync();
+      if (kSingle && t == 0) FB_ATTN_TS(3);
       // pass 1: row maximum
       float m_blk = -INFINITY;
 #pragma unroll 1
@@ -249,10 +275,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld32(tmem_S + lane_base + c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * sc + mask_s[c + i];
-          if (p.causal && kv0 + c + i > q) s = -INFINITY;
-          m_blk = fmaxf(m_blk, s);
+        for (int i4 = 0; i4 < 32; i4 += 4) {
+          const float4 mk = *reinterpret_cast<const float4*>(mask_s + c + i4);     // one 16-byte shared load per 4 keys
+          const float mk4[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i4 + k;
+            float s = __uint_as_float(v[i]) * sc + mk4[k];
+            if (p.causal && kv0 + c + i > q) s = -INFINITY;
+            m_blk = fmaxf(m_blk, s);
+          }
         }
       }
       const float m_new = fmaxf(m_run, m_blk);
@@ -267,11 +299,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_wait();
         float pr[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * sc + mask_s[c + i];
-          if (p.causal && kv0 + c + i > q) s = -INFINITY;
-          pr[i] = exp2f(s - m_use);
-          l_blk += pr[i];
+        for (int i4 = 0; i4 < 32; i4 += 4) {
+          const float4 mk = *reinterpret_cast<const float4*>(mask_s + c + i4);
+          const float mk4[4] = {mk.x - m_use, mk.y - m_use, mk.z - m_use, mk.w - m_use};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i4 + k;
+            float s = __uint_as_float(v[i]) * sc + mk4[k];      // score - row maximum in one FMA
+            if (p.causal && kv0 + c + i > q) s = -INFINITY;
+            pr[i] = exp2f(s);
+            l_blk += pr[i];
+          }
         }
         if (p.p_drop > 0.f) {
           const unsigned long long base = ((static_cast<unsigned long long>(b) * p.H + h) * p.S + q) * p.S + kv0 + c;
@@ -289,67 +327,117 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
+      if (kSingle && t == 0) FB_ATTN_TS(4);
       mbar_arrive(p_ready);
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
       ok = mbar_wait(o_full, j & 1, abort_flag, p.status, kStatusWaitAccum);
       if (!ok) break;
       tc_fence_after_sync();
+      if (kSingle && t == 0) FB_ATTN_TS(5);
+      if constexpr (kSingle) {
+        // the only block: normalise and store straight from TMEM
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
 #pragma unroll
-      for (int c = 0; c < kHD; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_O + lane_base + c, v);
-        tmem_ld_wait();
+        for (int c = 0; c < kHD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_O + lane_base + c, v);
+          tmem_ld_wait();
+          if (q < p.S) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * alpha + __uint_as_float(v[i]);
+            for (int g = 0; g < 4; ++g) {
+              float tmp[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) tmp[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
+              *reinterpret_cast<uint4*>(orow + c + g * 8) = pack8(tmp);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kHD; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_O + lane_base + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * alpha + __uint_as_float(v[i]);
+        }
       }
       tc_fence_before_sync();
       mbar_arrive(o_done);
     }
     if (ok && q < p.S) {
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
+      if constexpr (!kSingle) {
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
 #pragma unroll
-      for (int g = 0; g < kHD / 8; ++g) {
-        float tmp[8];
+        for (int g = 0; g < kHD / 8; ++g) {
+          float tmp[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) tmp[i] = acc[g * 8 + i] * inv_l;
-        *reinterpret_cast<uint4*>(orow + g * 8) = pack8(tmp);
+          for (int i = 0; i < 8; ++i) tmp[i] = acc[g * 8 + i] * inv_l;
+          *reinterpret_cast<uint4*>(orow + g * 8) = pack8(tmp);
+        }
       }
       // natural-log LSE of the scaled, masked scores
       lse[(static_cast<long long>(b) * p.H + h) * p.S + q] = (l_run > 0.f) ? (m_run + log2f(l_run)) / kLog2e : -INFINITY;
     }
   }
+  if (kSingle && threadIdx.x == 0) FB_ATTN_TS(6);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 4) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, 256);
+    tmem_dealloc<1>(tmem_base, kTmemCols);
   }
+  if (kSingle && threadIdx.x == 0) { FB_ATTN_TS(7); FB_ATTN_TS(15); }
 }
 
 // ==================================================================================== backward
+// Several key blocks: every tile has a buffer of its own and every accumulator its own TMEM columns (129 KB, 512
+// columns: one CTA per SM). A single key block (S <= 128): V is dead once dP = dO V^T has completed, so the first
+// dS panel takes its place (112.75 KB), and dV / dK / dQ accumulate in the columns S and dP occupied until the
+// softmax threads had read them (256 columns): two CTAs share an SM.
 struct BwdSmem {
-  static constexpr int Q = 0;
-  static constexpr int DO = 16384;
-  static constexpr int K = 2 * 16384;
-  static constexpr int V = 3 * 16384;
-  static constexpr int P = 4 * 16384;       // 2 panels
-  static constexpr int DS = 6 * 16384;      // 2 panels
-  static constexpr int MASK = 8 * 16384;
-  static constexpr int BARS = MASK + 512;
-  static constexpr int TOTAL = BARS + 256;
+  int Q, DO, K, V, P, DS, MASK, BARS, TOTAL;
+  __host__ __device__ explicit BwdSmem(bool single) {
+    Q = 0;
+    DO = 16384;
+    K = 2 * 16384;
+    if (single) {
+      P = 3 * 16384;           // 2 panels
+      V = 5 * 16384;
+      DS = 5 * 16384;          // 2 panels, the first one over V
+      MASK = 7 * 16384;
+    } else {
+      V = 3 * 16384;
+      P = 4 * 16384;           // 2 panels
+      DS = 6 * 16384;          // 2 panels
+      MASK = 8 * 16384;
+    }
+    BARS = MASK + 512;
+    TOTAL = BARS + 256;
+  }
 };
 
-__global__ void __launch_bounds__(kAttnThreads, 1)
+template <bool kSingle>
+__global__ void __launch_bounds__(kAttnThreads, kSingle ? 2 : 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                 const float* __restrict__ lse, __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk,
                 __nv_bfloat16* __restrict__ dv, float* __restrict__ dq_accum, const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // The single-block layout leaves no room for alignment slack (two CTAs must fit in one SM): it relies on the
+  // 1024-byte alignment of the dynamic shared-memory window and reports instead of computing if that does not hold.
+  uint8_t* smem = kSingle ? smem_raw : reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (kSingle && (smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, static_cast<int>(kStatusBadArg));
+    return;
+  }
+  const BwdSmem L(kSingle);
+  constexpr int kTmemCols = kSingle ? 256 : 512;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.BARS);
   uint64_t* kv_full = bars + 0;
   uint64_t* q_full = bars + 1;
   uint64_t* sdp_full = bars + 2;
@@ -358,11 +446,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* tile_done = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* mask_s = reinterpret_cast<float*>(smem + BwdSmem::MASK);
+  float* mask_s = reinterpret_cast<float*>(smem + L.MASK);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x, b = blockIdx.y;
   const int nblk = (p.S + kBlk - 1) / kBlk;
+  if (kSingle && threadIdx.x == 0) FB_ATTN_TS(8);
   const unsigned long long seed = p.seed + (p.seed_dev ? *p.seed_dev : 0ull);
 
   if (threadIdx.x == 0) {
@@ -376,23 +465,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_fence_init();
   }
   if (warp == 4) {
-    tmem_alloc<1>(tmem_slot, 512);
+    tmem_alloc<1>(tmem_slot, kTmemCols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 320, tDQ = tmem_base + 384;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128;
+  pdl_entry();
+  // single key block: S and dP have been read by every softmax thread (pds_ready) before the gradient MMAs are issued
+  const uint32_t tDV = tmem_base + (kSingle ? 0 : 256), tDK = tmem_base + (kSingle ? 64 : 320), tDQ = tmem_base + (kSingle ? 128 : 384);
 
   if (warp == 4) {
     if (lane == 0) {
       const uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);      // S, dP: both operands K-major
       const uint32_t idesc_mn = make_idesc_bf16(128, kHD, 1, 1);      // dV, dK: A^T (MN-major) x MN-major
       const uint32_t idesc_kn = make_idesc_bf16(128, kHD, 0, 1);      // dQ: K-major x MN-major
-      const uint32_t sQ = smem_u32(smem + BwdSmem::Q), sDO = smem_u32(smem + BwdSmem::DO);
-      const uint32_t sK = smem_u32(smem + BwdSmem::K), sV = smem_u32(smem + BwdSmem::V);
-      const uint32_t sP = smem_u32(smem + BwdSmem::P), sDS = smem_u32(smem + BwdSmem::DS);
+      const uint32_t sQ = smem_u32(smem + L.Q), sDO = smem_u32(smem + L.DO);
+      const uint32_t sK = smem_u32(smem + L.K), sV = smem_u32(smem + L.V);
+      const uint32_t sP = smem_u32(smem + L.P), sDS = smem_u32(smem + L.DS);
       int it = 0;
       bool ok = true;
       for (int j = 0; j < nblk && ok; ++j) {
@@ -402,16 +494,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!ok) break;
         }
         mbar_expect_tx(kv_full, 32768);
-        tma_load_4d(smem + BwdSmem::K, &tmK, kv_full, 0, j * kBlk, h, b);
-        tma_load_4d(smem + BwdSmem::V, &tmV, kv_full, 0, j * kBlk, h, b);
+        tma_load_4d(smem + L.K, &tmK, kv_full, 0, j * kBlk, h, b);
+        tma_load_4d(smem + L.V, &tmV, kv_full, 0, j * kBlk, h, b);
         for (int i = i0; i < nblk && ok; ++i, ++it) {
           if (i > i0) {
             ok = mbar_wait(tile_done, (it - 1) & 1, abort_flag, p.status, kStatusWaitEpi);
             if (!ok) break;
           }
           mbar_expect_tx(q_full, 32768);
-          tma_load_4d(smem + BwdSmem::Q, &tmQ, q_full, 0, i * kBlk, h, b);
-          tma_load_4d(smem + BwdSmem::DO, &tmDO, q_full, 0, i * kBlk, h, b);
+          tma_load_4d(smem + L.Q, &tmQ, q_full, 0, i * kBlk, h, b);
+          tma_load_4d(smem + L.DO, &tmDO, q_full, 0, i * kBlk, h, b);
           if (i == i0) {
             ok = mbar_wait(kv_full, j & 1, abort_flag, p.status, kStatusWaitFull);
             if (!ok) break;
@@ -455,7 +547,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else {
     const int t = threadIdx.x;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t sP = smem_u32(smem + BwdSmem::P), sDS = smem_u32(smem + BwdSmem::DS);
+    const uint32_t sP = smem_u32(smem + L.P), sDS = smem_u32(smem + L.DS);
     const float sc = p.scale * kLog2e;
     const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
     int it = 0;
@@ -486,9 +578,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           lse_q = lse[(static_cast<long long>(b) * p.H + h) * p.S + q] * kLog2e;
         }
+        if (kSingle && t == 0) FB_ATTN_TS(9);
         ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
         if (!ok) break;
         tc_fence_after_sync();
+        if (kSingle && t == 0) FB_ATTN_TS(10);
 #pragma unroll 1
         for (int c = 0; c < kBlk; c += 32) {
           uint32_t sv[32], dpv[32];
@@ -510,14 +604,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
             for (int e = 0; e < 32; ++e) z[e] = 1.f;
           }
+          const bool row_live = q_ok && lse_q != -INFINITY;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float s = __uint_as_float(sv[e]) * sc + mask_s[c + e];
-            if (p.causal && kv0 + c + e > q) s = -INFINITY;
-            const float pe = (q_ok && lse_q != -INFINITY) ? exp2f(s - lse_q) : 0.f;
-            const float dpe = __uint_as_float(dpv[e]) * z[e];
-            pr[e] = pe * z[e];
-            ds[e] = pe * (dpe - Dq) * p.scale;
+          for (int e4 = 0; e4 < 32; e4 += 4) {
+            const float4 mk = *reinterpret_cast<const float4*>(mask_s + c + e4);
+            const float mk4[4] = {mk.x - lse_q, mk.y - lse_q, mk.z - lse_q, mk.w - lse_q};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int e = e4 + k;
+              float s = __uint_as_float(sv[e]) * sc + mk4[k];   // score - log-sum-exp in one FMA
+              if (p.causal && kv0 + c + e > q) s = -INFINITY;
+              const float pe = row_live ? exp2f(s) : 0.f;
+              const float dpe = __uint_as_float(dpv[e]) * z[e];
+              pr[e] = pe * z[e];
+              ds[e] = pe * (dpe - Dq) * p.scale;
+            }
           }
           const uint32_t pp = sP + (c >> 6) * 16384, dp = sDS + (c >> 6) * 16384;
 #pragma unroll
@@ -528,10 +629,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_before_sync();
         fence_proxy_async_smem();
+        if (kSingle && t == 0) FB_ATTN_TS(11);
         mbar_arrive(pds_ready);
         ok = mbar_wait(grads_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
         if (!ok) break;
         tc_fence_after_sync();
+        if (kSingle && t == 0) FB_ATTN_TS(12);
         // ---- dQ tile: single key block -> write bf16; otherwise accumulate in the fp32 scratch
         {
           const int j_first = 0;
@@ -592,11 +695,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   }
+  if (kSingle && threadIdx.x == 0) FB_ATTN_TS(13);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 4) {
     tc_fence_after_sync();
-    tmem_dealloc<1>(tmem_base, 512);
+    tmem_dealloc<1>(tmem_base, kTmemCols);
   }
 }
 
@@ -617,6 +721,12 @@ static bool strides_ok(const void* ptr, long long sb, long long ss, long long sh
 
 }  // namespace fb
 
+#if FB_TIMELINE
+extern "C" int fb_attn_timeline(long long* host_out, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, fb::g_attn_ts, sizeof(long long) * static_cast<size_t>(count)));
+}
+#endif
+
 extern "C" int fb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const float* mask, int B, int H,
                            int S, const long long* qkv_strides, const long long* o_strides, float scale, int causal,
                            float p_drop, unsigned long long seed, const unsigned long long* seed_dev, int* status,
@@ -634,16 +744,24 @@ extern "C" int fb_attn_fwd(const void* q, const void* k, const void* v, void* o,
   if ((r = make_tmap_bshd(&tv, v, B, H, S, sb, ss, sh))) return r;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem(2).TOTAL + 1024);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem(false).TOTAL + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem(true).TOTAL + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int smem_bytes = FwdSmem(S > kBlk ? 2 : 1).TOTAL + 1024;
+  const bool single = S <= kBlk;
+  const int smem_bytes = FwdSmem(single).TOTAL + 1024;
   AttnParams p = make_params(B, H, S, qkv_strides, o_strides, o_strides, mask, scale, causal, p_drop, seed, seed_dev, status);
   dim3 grid((S + kBlk - 1) / kBlk, H, B);
-  attn_fwd_kernel<<<grid, kAttnThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-      tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, p);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le;
+  if (single)
+    le = launch_pdl(attn_fwd_kernel<true>, grid, dim3(kAttnThreads), smem_bytes, static_cast<cudaStream_t>(stream), tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, p);
+  else
+    le = launch_pdl(attn_fwd_kernel<false>, grid, dim3(kAttnThreads), smem_bytes, static_cast<cudaStream_t>(stream), tq, tk, tv, static_cast<__nv_bfloat16*>(o), lse, p);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }
 
 // dq_accum: fp32 scratch [B, H, S, 64]; only touched when a query block meets more than one key block
@@ -670,14 +788,22 @@ extern "C" int fb_attn_bwd(const void* q, const void* k, const void* v, const vo
   if ((r = make_tmap_bshd(&tdo, d_o, B, H, S, o_strides[0], o_strides[1], o_strides[2]))) return r;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL + 1024);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem(false).TOTAL + 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem(true).TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   AttnParams p = make_params(B, H, S, qkv_strides, o_strides, g_strides, mask, scale, causal, p_drop, seed, seed_dev, status);
   dim3 grid(H, B);
-  attn_bwd_kernel<<<grid, kAttnThreads, BwdSmem::TOTAL + 1024, static_cast<cudaStream_t>(stream)>>>(
-      tq, tk, tv, tdo, static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse,
-      static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), dq_accum, p);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t le;
+  if (S <= kBlk)
+    le = launch_pdl(attn_bwd_kernel<true>, grid, dim3(kAttnThreads), static_cast<size_t>(BwdSmem(true).TOTAL), static_cast<cudaStream_t>(stream),
+                    tq, tk, tv, tdo, static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse,
+                    static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), dq_accum, p);
+  else
+    le = launch_pdl(attn_bwd_kernel<false>, grid, dim3(kAttnThreads), static_cast<size_t>(BwdSmem(false).TOTAL + 1024), static_cast<cudaStream_t>(stream),
+                    tq, tk, tv, tdo, static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse,
+                    static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), dq_accum, p);
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
 }

@@ -259,7 +259,9 @@ def _attn_ref(q, k, v, mask, scale, causal):
     return (p @ vh).permute(0, 2, 1, 3)
 
 
-@pytest.mark.parametrize("B,H,S,causal,use_mask", [(2, 3, 128, False, True), (2, 2, 256, True, False), (1, 2, 256, False, True), (2, 2, 384, True, False), (1, 1, 200, False, False)])
+@pytest.mark.parametrize("B,H,S,causal,use_mask", [(2, 3, 128, False, True), (2, 2, 256, True, False), (1, 2, 256, False, True), (2, 2, 384, True, False), (1, 1, 200, False, False),
+                                                        # one key block: the kernels that share an SM between four / two CTAs
+                                                        (4, 12, 128, True, False), (3, 2, 77, False, True), (2, 4, 64, True, False), (32, 12, 128, False, True)])
 def test_attention_fwd_bwd(C, B, H, S, causal, use_mask):
     torch.manual_seed(5)
     D = 64
