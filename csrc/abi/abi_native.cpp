@@ -38,6 +38,15 @@ bool natives_on() {
   }();
   return on;
 }
+// FLODL_B200_NATIVE_OPS=linear,layer_norm,gelu,sdpa,cross_entropy,dropout restricts the native paths to the listed ops
+// (for bisecting a numerical difference); unset = all.
+bool op_on(const char* name) {
+  static const std::string list = [] {
+    const char* e = std::getenv("FLODL_B200_NATIVE_OPS");
+    return e ? "," + std::string(e) + "," : std::string();
+  }();
+  return list.empty() || list.find("," + std::string(name) + ",") != std::string::npos;
+}
 bool autocast_bf16() { return at::autocast::is_autocast_enabled(at::kCUDA) && at::autocast::get_autocast_dtype(at::kCUDA) == at::kBFloat16; }
 bool is_bf16(const Tensor& t) { return t.scalar_type() == at::kBFloat16; }
 // bf16 is the compute type of an op on `x`
@@ -147,7 +156,7 @@ Tensor weight_grad(const Tensor& dy2, const Tensor& x2, at::ScalarType want, con
   return want == at::kFloat ? out : out.to(want);
 }
 Tensor bias_grad(const Tensor& dy2, at::ScalarType want) {
-  Tensor out = torch::empty({dy2.size(1)}, torch::dtype(torch::kFloat).device(dy2.device()));
+  Tensor out = torch::zeros({dy2.size(1)}, torch::dtype(torch::kFloat).device(dy2.device()));   // the kernel adds into it
   check(fb_colsum(dy2.data_ptr(), out.data_ptr<float>(), static_cast<int>(dy2.size(0)), static_cast<int>(dy2.size(1)), dy2.stride(0), is_bf16(dy2),
                   stream_of(dy2)),
         "fb_colsum");
@@ -213,10 +222,11 @@ struct LayerNormFn : public torch::autograd::Function<LayerNormFn> {
           "fb_layernorm_fwd");
     ctx->save_for_backward({x, mean, rstd, gamma});
     ctx->saved_data["has_beta"] = beta.defined();
-    ctx->mark_non_differentiable({mean, rstd});
     std::vector<int64_t> stat_shape = x.sizes().vec();
     stat_shape.back() = 1;
-    return {y, mean.view(stat_shape), rstd.view(stat_shape)};
+    Tensor mean_out = mean.view(stat_shape), rstd_out = rstd.view(stat_shape);
+    ctx->mark_non_differentiable({mean_out, rstd_out});
+    return {y, mean_out, rstd_out};
   }
   static variable_list backward(AutogradContext* ctx, variable_list grads) {
     auto saved = ctx->get_saved_variables();
@@ -394,7 +404,7 @@ struct CrossEntropyFn : public torch::autograd::Function<CrossEntropyFn> {
 void note_mutation() { g_epoch.fetch_add(1, std::memory_order_relaxed); }
 
 bool native_linear(const Tensor& x, const Tensor& w, const Tensor& b, Tensor* out) {
-  if (!bf16_compute(x) || w.dim() != 2 || !w.is_cuda() || x.dim() < 1 || x.size(-1) != w.size(1) || x.size(-1) % 8 != 0) return false;
+  if (!op_on("linear") || !bf16_compute(x) || w.dim() != 2 || !w.is_cuda() || x.dim() < 1 || x.size(-1) != w.size(1) || x.size(-1) % 8 != 0) return false;
   if (!(w.scalar_type() == at::kFloat || is_bf16(w))) return false;
   if (b.defined() && !(b.is_cuda() && (b.scalar_type() == at::kFloat || is_bf16(b)) && b.numel() == w.size(0))) return false;
   if (x.numel() / x.size(-1) >= (1ll << 31) || w.size(0) >= (1ll << 31)) return false;
@@ -404,7 +414,7 @@ bool native_linear(const Tensor& x, const Tensor& w, const Tensor& b, Tensor* ou
 }
 
 bool native_layer_norm(const Tensor& x, const Tensor& w, const Tensor& b, int64_t size, double eps, Tensor* out, Tensor* mean, Tensor* rstd) {
-  if (!natives_on() || !x.defined() || !x.is_cuda() || x.numel() == 0 || x.size(-1) != size) return false;
+  if (!op_on("layer_norm") || !natives_on() || !x.defined() || !x.is_cuda() || x.numel() == 0 || x.size(-1) != size) return false;
   if (!(is_bf16(x) || x.scalar_type() == at::kFloat)) return false;
   if (size > 1024 || size % (is_bf16(x) ? 8 : 4) != 0) return false;
   auto affine_ok = [&](const Tensor& t) { return !t.defined() || (t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == size); };
@@ -418,14 +428,14 @@ bool native_layer_norm(const Tensor& x, const Tensor& w, const Tensor& b, int64_
 }
 
 bool native_gelu(const Tensor& x, bool tanh_approx, Tensor* out) {
-  if (!natives_on() || !x.defined() || !x.is_cuda() || x.numel() == 0 || !(is_bf16(x) || x.scalar_type() == at::kFloat)) return false;
+  if (!op_on("gelu") || !natives_on() || !x.defined() || !x.is_cuda() || x.numel() == 0 || !(is_bf16(x) || x.scalar_type() == at::kFloat)) return false;
   *out = GeluFn::apply(x, tanh_approx);
   g_native_calls.fetch_add(1, std::memory_order_relaxed);
   return true;
 }
 
 bool native_dropout(const Tensor& x, double p, bool training, Tensor* out) {
-  if (!training || p <= 0.0 || p >= 1.0) return false;
+  if (!training || p <= 0.0 || p >= 1.0 || !op_on("dropout")) return false;
   if (!natives_on() || !x.defined() || !x.is_cuda() || x.numel() == 0 || !(is_bf16(x) || x.scalar_type() == at::kFloat)) return false;
   *out = DropoutFn::apply(x, p);
   g_native_calls.fetch_add(1, std::memory_order_relaxed);
@@ -433,7 +443,7 @@ bool native_dropout(const Tensor& x, double p, bool training, Tensor* out) {
 }
 
 bool native_sdpa(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& mask, double p, bool causal, double scale, Tensor* out) {
-  if (!bf16_compute(q) || q.dim() != 4 || q.size(3) != 64) return false;
+  if (!op_on("sdpa") || !bf16_compute(q) || q.dim() != 4 || q.size(3) != 64) return false;
   if (k.sizes() != q.sizes() || v.sizes() != q.sizes() || !k.is_cuda() || !v.is_cuda()) return false;
   Tensor m;
   if (mask.defined()) {
@@ -453,7 +463,7 @@ bool native_sdpa(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor
 }
 
 bool native_cross_entropy(const Tensor& logits, const Tensor& target, int64_t reduction, int64_t ignore_index, double smoothing, Tensor* out) {
-  if (!natives_on() || !logits.defined() || !logits.is_cuda() || logits.dim() != 2 || logits.numel() == 0) return false;
+  if (!op_on("cross_entropy") || !natives_on() || !logits.defined() || !logits.is_cuda() || logits.dim() != 2 || logits.numel() == 0) return false;
   if (reduction != 1 || smoothing != 0.0 || !(is_bf16(logits) || logits.scalar_type() == at::kFloat)) return false;
   if (!target.is_cuda() || target.scalar_type() != at::kLong || target.dim() != 1 || target.size(0) != logits.size(0)) return false;
   if (logits.size(0) >= (1ll << 31) || logits.size(1) >= (1ll << 31)) return false;

@@ -102,6 +102,7 @@ int fb_gelu_fwd(const void* x, void* y, long long n, int tanh_approx, int is_bf1
 int fb_gelu_bwd(const void* dy, const void* x, void* dx, long long n, int tanh_approx, int is_bf16, void* stream);
 int fb_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, const unsigned long long* seed_dev,
                int is_bf16, void* stream);
+/* out[c] += sum over rows of x[r][c] (the caller zeroes `out`, or passes a gradient slot to accumulate into). */
 int fb_colsum(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, void* stream);
 /* As fb_colsum over the first min(rows, *rows_dyn) rows (device-side count). */
 int fb_colsum_dyn(const void* x, float* out, int rows, int cols, long long ld, int is_bf16, const int* rows_dyn, void* stream);

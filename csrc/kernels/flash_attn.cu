@@ -99,6 +99,74 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
   return r;
 }
 
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// Row-per-thread data (the TMEM register layout: thread = row, 64 bf16 = 128 bytes per row) to and from global rows
+// that are `row_stride` elements apart. A thread touching its own row would make every load / store instruction hit 32
+// different 128-byte lines; instead each warp moves its 32 rows through a 4 KB staging area of shared memory
+// (chunks XOR-swizzled by row, so both sides are free of bank conflicts) and eight lanes share one row in global
+// memory. Only the warp's own rows are involved: __syncwarp is all the synchronisation needed.
+//
+// stage_half: thread `lane` deposits 32 consecutive columns [col0, col0 + 32) of its row.
+__device__ __forceinline__ void stage_half(uint32_t stage, int lane, int col0, const float* v32) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) st_shared_v4(stage + lane * 128 + ((((col0 >> 3) + g) ^ (lane & 7)) << 4), pack8(v32 + 8 * g));
+}
+// flush_rows: after both halves were staged, writes rows [row0, row0 + 32) (those below `row_limit`) of a [*, 64] bf16 tensor.
+__device__ __forceinline__ void flush_rows(uint32_t stage, int lane, __nv_bfloat16* base, long long row_stride, int row0, int row_limit) {
+  __syncwarp();
+  const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + sub;
+    const uint4 val = ld_shared_v4(stage + r * 128 + ((ch ^ (r & 7)) << 4));
+    if (row0 + r < row_limit) *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + r) * row_stride + ch * 8) = val;
+  }
+  __syncwarp();
+}
+// D[row] = sum_c a[row][c] * b[row][c] over 64 columns for the warp's 32 rows, eight lanes per row; lane l gets row l's sum.
+__device__ __forceinline__ float row_dot64(const __nv_bfloat16* a, const __nv_bfloat16* b, long long row_stride, int row0, int row_limit, int lane) {
+  const int sub = lane >> 3, ch = lane & 7;
+  float mine = 0.f;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    // all loads of four iterations first (the shuffles below would otherwise serialise one memory latency per iteration)
+    uint4 xa[4], xb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int r = (half * 4 + k) * 4 + sub;
+      xa[k] = xb[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (row0 + r < row_limit) {
+        xa[k] = __ldg(reinterpret_cast<const uint4*>(a + static_cast<long long>(row0 + r) * row_stride + ch * 8));
+        xb[k] = __ldg(reinterpret_cast<const uint4*>(b + static_cast<long long>(row0 + r) * row_stride + ch * 8));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int it = half * 4 + k;
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&xa[k]);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&xb[k]);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(ha[e]), fb2 = __bfloat1622float2(hb[e]);
+        d += fa.x * fb2.x + fa.y * fb2.y;
+      }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      // row it*4 + g now sits in lanes 8g .. 8g+7; lane l wants row l = it*4 + g  <=>  it == l / 4, g == l % 4
+      const float got = __shfl_sync(0xffffffffu, d, (lane & 3) * 8);
+      if ((lane >> 2) == it) mine = got;
+    }
+  }
+  return mine;
+}
+
 struct AttnParams {
   int B, H, S;
   long long sb, ss, sh;      // element strides of q/k/v
@@ -331,29 +399,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(p_ready);
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
-      ok = mbar_wait(o_full, j & 1, abort_flag, p.status, kStatusWaitAccum);
+      ok = __all_sync(0xffffffffu, mbar_wait(o_full, j & 1, abort_flag, p.status, kStatusWaitAccum));   // warp-uniform: the staged stores below use __syncwarp
       if (!ok) break;
       tc_fence_after_sync();
       if (kSingle && t == 0) FB_ATTN_TS(5);
       if constexpr (kSingle) {
-        // the only block: normalise and store straight from TMEM
+        // the only block: normalise, then out through the warp's staging area (P is dead: P V has completed)
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
+        const uint32_t stage = smem_u32(smem + L.P) + warp * 4096;
 #pragma unroll
         for (int c = 0; c < kHD; c += 32) {
           uint32_t v[32];
           tmem_ld32(tmem_O + lane_base + c, v);
           tmem_ld_wait();
-          if (q < p.S) {
+          float f[32];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float tmp[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) tmp[i] = __uint_as_float(v[g * 8 + i]) * inv_l;
-              *reinterpret_cast<uint4*>(orow + c + g * 8) = pack8(tmp);
-            }
-          }
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]) * inv_l;
+          stage_half(stage, lane, c, f);
         }
+        flush_rows(stage, lane, o + static_cast<long long>(b) * p.osb + static_cast<long long>(h) * p.osh, p.oss, q0 + warp * 32, p.S);
       } else {
 #pragma unroll
         for (int c = 0; c < kHD; c += 32) {
@@ -367,18 +431,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       mbar_arrive(o_done);
     }
-    if (ok && q < p.S) {
-      if constexpr (!kSingle) {
+    if constexpr (!kSingle) {
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {      // every MMA has completed: the P panels serve as staging area
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow = o + static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
+        const uint32_t stage = smem_u32(smem + L.P) + warp * 4096;
 #pragma unroll
-        for (int g = 0; g < kHD / 8; ++g) {
-          float tmp[8];
+        for (int c = 0; c < kHD; c += 32) {
+          float f[32];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) tmp[i] = acc[g * 8 + i] * inv_l;
-          *reinterpret_cast<uint4*>(orow + g * 8) = pack8(tmp);
+          for (int i = 0; i < 32; ++i) f[i] = acc[c + i] * inv_l;
+          stage_half(stage, lane, c, f);
         }
+        flush_rows(stage, lane, o + static_cast<long long>(b) * p.osb + static_cast<long long>(h) * p.osh, p.oss, q0 + warp * 32, p.S);
       }
+    }
+    if (ok && q < p.S) {
       // natural-log LSE of the scaled, masked scores
       lse[(static_cast<long long>(b) * p.H + h) * p.S + q] = (l_run > 0.f) ? (m_run + log2f(l_run)) / kLog2e : -INFINITY;
     }
@@ -474,6 +542,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 128;
   pdl_entry();
+  if (kSingle && threadIdx.x == 0) FB_ATTN_TS(7);
   // single key block: S and dP have been read by every softmax thread (pds_ready) before the gradient MMAs are issued
   const uint32_t tDV = tmem_base + (kSingle ? 0 : 256), tDK = tmem_base + (kSingle ? 64 : 320), tDQ = tmem_base + (kSingle ? 128 : 384);
 
@@ -511,6 +580,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kStatusWaitFull);
           if (!ok) break;
           tc_fence_after_sync();
+          if (kSingle) FB_ATTN_TS(5);
 #pragma unroll
           for (int k4 = 0; k4 < kHD / 16; ++k4) {
             umma_bf16<1>(tS, make_smem_desc(sQ + k4 * 32, 16, 1024), make_smem_desc(sK + k4 * 32, 16, 1024), idesc_kk, k4 > 0);
@@ -552,32 +622,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float inv_keep = p.p_drop > 0.f ? 1.f / (1.f - p.p_drop) : 1.f;
     int it = 0;
     bool ok = true;
+    // D = rowsum(dO * O) (eight lanes per row, coalesced) and the LSE of a query row
+    auto load_row_stats = [&](int i, float& Dq, float& lse_q) {
+      const int q = i * kBlk + t;
+      lse_q = q < p.S ? __ldg(lse + (static_cast<long long>(b) * p.H + h) * p.S + q) * kLog2e : 0.f;
+      Dq = row_dot64(o + static_cast<long long>(b) * p.osb + static_cast<long long>(h) * p.osh,
+                     d_o + static_cast<long long>(b) * p.osb + static_cast<long long>(h) * p.osh, p.oss, i * kBlk + warp * 32, p.S, lane);
+    };
+    float D_first = 0.f, lse_first = 0.f;
     for (int j = 0; j < nblk && ok; ++j) {
       const int kv0 = j * kBlk;
       const int i0 = p.causal ? j : 0;
       asm volatile("bar.sync 1, 128;");
       {
         const int kv = kv0 + t;
-        mask_s[t] = (kv < p.S) ? (p.mask ? p.mask[static_cast<long long>(b) * p.S + kv] * kLog2e : 0.f) : -INFINITY;
+        // the mask load, and with a single key block the row statistics too, are in flight together
+        const float mraw = (kv < p.S && p.mask) ? __ldg(p.mask + static_cast<long long>(b) * p.S + kv) : 0.f;
+        if constexpr (kSingle) load_row_stats(0, D_first, lse_first);
+        mask_s[t] = (kv < p.S) ? mraw * kLog2e : -INFINITY;
       }
       asm volatile("bar.sync 1, 128;");
+      if (kSingle && t == 0) FB_ATTN_TS(6);
       for (int i = i0; i < nblk && ok; ++i, ++it) {
         const int q = i * kBlk + t;
         const bool q_ok = q < p.S;
-        // D = rowsum(dO * O), LSE for this row
-        float Dq = 0.f, lse_q = 0.f;
-        if (q_ok) {
-          const long long off = static_cast<long long>(b) * p.osb + static_cast<long long>(q) * p.oss + static_cast<long long>(h) * p.osh;
-#pragma unroll
-          for (int g = 0; g < kHD / 8; ++g) {
-            float a[8], c[8];
-            VecIO<__nv_bfloat16>::load(o + off + g * 8, a);
-            VecIO<__nv_bfloat16>::load(d_o + off + g * 8, c);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) Dq += a[e] * c[e];
-          }
-          lse_q = lse[(static_cast<long long>(b) * p.H + h) * p.S + q] * kLog2e;
-        }
+        float Dq = D_first, lse_q = lse_first;
+        if constexpr (!kSingle) load_row_stats(i, Dq, lse_q);
         if (kSingle && t == 0) FB_ATTN_TS(9);
         ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
         if (!ok) break;
@@ -631,63 +701,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         fence_proxy_async_smem();
         if (kSingle && t == 0) FB_ATTN_TS(11);
         mbar_arrive(pds_ready);
-        ok = mbar_wait(grads_full, it & 1, abort_flag, p.status, kStatusWaitAccum);
+        ok = __all_sync(0xffffffffu, mbar_wait(grads_full, it & 1, abort_flag, p.status, kStatusWaitAccum));   // warp-uniform: staged stores below
         if (!ok) break;
         tc_fence_after_sync();
         if (kSingle && t == 0) FB_ATTN_TS(12);
-        // ---- dQ tile: single key block -> write bf16; otherwise accumulate in the fp32 scratch
+        // ---- dQ tile: last key block of this query block -> bf16 rows through the staging area (the P panels are dead:
+        //      every MMA of this tile has completed); otherwise accumulate in the fp32 scratch
+        const uint32_t stage = sP + warp * 4096;
         {
           const int j_first = 0;
           const int j_last = p.causal ? min(i, nblk - 1) : nblk - 1;
-          const long long off = static_cast<long long>(b) * p.gsb + static_cast<long long>(q) * p.gss + static_cast<long long>(h) * p.gsh;
           float* acc_row = dq_accum ? dq_accum + ((static_cast<long long>(b) * p.H + h) * p.S + q) * kHD : nullptr;
 #pragma unroll
           for (int c = 0; c < kHD; c += 32) {
             uint32_t v[32];
             tmem_ld32(tDQ + lane_base + c, v);
             tmem_ld_wait();
-            if (q_ok) {
+            float f[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
+            if (q_ok && j != j_first) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 4) {
+                float4 old = *reinterpret_cast<const float4*>(acc_row + c + e);
+                f[e] += old.x; f[e + 1] += old.y; f[e + 2] += old.z; f[e + 3] += old.w;
+              }
+            }
+            if (j == j_last) {
+              stage_half(stage, lane, c, f);
+            } else if (q_ok) {
+#pragma unroll
+              for (int e = 0; e < 32; e += 4)
+                *reinterpret_cast<float4*>(acc_row + c + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+            }
+          }
+          if (j == j_last)
+            flush_rows(stage, lane, dq + static_cast<long long>(b) * p.gsb + static_cast<long long>(h) * p.gsh, p.gss, i * kBlk + warp * 32, p.S);
+        }
+        // ---- last query block of this key block: drain dK, dV the same way
+        if (i == nblk - 1) {
+          __nv_bfloat16* const bases[2] = {dk + static_cast<long long>(b) * p.gsb + static_cast<long long>(h) * p.gsh,
+                                            dv + static_cast<long long>(b) * p.gsb + static_cast<long long>(h) * p.gsh};
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+#pragma unroll
+            for (int c = 0; c < kHD; c += 32) {
+              uint32_t v[32];
+              tmem_ld32((which == 0 ? tDK : tDV) + lane_base + c, v);
+              tmem_ld_wait();
               float f[32];
 #pragma unroll
               for (int e = 0; e < 32; ++e) f[e] = __uint_as_float(v[e]);
-              if (j != j_first) {
-#pragma unroll
-                for (int e = 0; e < 32; e += 4) {
-                  float4 old = *reinterpret_cast<const float4*>(acc_row + c + e);
-                  f[e] += old.x; f[e + 1] += old.y; f[e + 2] += old.z; f[e + 3] += old.w;
-                }
-              }
-              if (j == j_last) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(dq + off + c + g * 8) = pack8(f + 8 * g);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 32; e += 4)
-                  *reinterpret_cast<float4*>(acc_row + c + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
-              }
+              stage_half(stage, lane, c, f);
             }
-          }
-        }
-        // ---- last query block of this key block: drain dK, dV
-        if (i == nblk - 1) {
-          const int kv = kv0 + t;
-          const long long off = static_cast<long long>(b) * p.gsb + static_cast<long long>(kv) * p.gss + static_cast<long long>(h) * p.gsh;
-#pragma unroll
-          for (int c = 0; c < kHD; c += 32) {
-            uint32_t v[32], w[32];
-            tmem_ld32(tDK + lane_base + c, v);
-            tmem_ld32(tDV + lane_base + c, w);
-            tmem_ld_wait();
-            if (kv < p.S) {
-              float f[32], g2[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) { f[e] = __uint_as_float(v[e]); g2[e] = __uint_as_float(w[e]); }
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                *reinterpret_cast<uint4*>(dk + off + c + g * 8) = pack8(f + 8 * g);
-                *reinterpret_cast<uint4*>(dv + off + c + g * 8) = pack8(g2 + 8 * g);
-              }
-            }
+            flush_rows(stage, lane, bases[which], p.gss, kv0 + warp * 32, p.S);
           }
         }
         tc_fence_before_sync();
