@@ -176,7 +176,7 @@ def run_ours(args):
     from flodl_b200.parallel import comm
     from flodl_b200.parallel.engine import TrainEngine
 
-    comm.init_process_group()
+    comm.init_process_group(timeout_s=180.0)
     world, rank = comm.world_size(), comm.rank()
     local = comm.local_rank()
     torch.cuda.set_device(local)
@@ -313,7 +313,7 @@ def run_trainer_api(args):
     from flodl_b200 import nn
     from flodl_b200.parallel import comm
     from flodl_b200.parallel.ddp import Trainer
-    comm.init_process_group()
+    comm.init_process_group(timeout_s=180.0)
     world, rank, local = comm.world_size(), comm.rank(), comm.local_rank()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -373,7 +373,7 @@ def run_builder_api(args):
     from flodl_b200.parallel import comm
     from flodl_b200.parallel.ddp import Trainer
     from flodl_b200.parallel.ddp_run import ApplyPolicy, AverageBackend
-    comm.init_process_group()
+    comm.init_process_group(timeout_s=180.0)
     world, rank = comm.world_size(), comm.rank()
     torch.cuda.set_device(comm.local_rank())
     B, S = (args.batch or 32), 256

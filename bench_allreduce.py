@@ -116,7 +116,7 @@ def main():
     ap.add_argument("--also", default="", help="comma-separated extras: param_average, broadcast")
     ap.add_argument("--skip-sweep", action="store_true", help="only run the --also benchmarks")
     args = ap.parse_args()
-    comm.init_process_group()
+    comm.init_process_group(timeout_s=180.0)
     rank, world = comm.rank(), comm.world_size()
     dev = torch.device("cuda", comm.local_rank())
     torch.cuda.set_device(dev)

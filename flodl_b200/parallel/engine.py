@@ -69,9 +69,12 @@ class TrainEngine:
         if use_symm and param_staging:
             self.symm_stage = _comm.SymmetricBuffer(self.flat.total * 4, self.device.index, comm_timeout_s)
         _core_ops.set_eager_min_numel(0)      # flat buffers and direct gradient slots: native kernels for every size
+        # launch shape of the gradient exchange (tuning knobs; the defaults come from measurements on B200)
         comm_blocks = int(os.environ.get("FLODL_B200_COMM_BLOCKS", comm_blocks))
+        bucket_mb = float(os.environ.get("FLODL_B200_BUCKET_MB", bucket_mb))
+        tail_blocks = int(os.environ.get("FLODL_B200_COMM_TAIL_BLOCKS", 96))
         self.sync = GradSync(self.flat, self.symm_grads, int(bucket_mb * 1024 * 1024), overlap, comm_blocks, comm_backend,
-                             world=None if self.grad_sync else 1)
+                             world=None if self.grad_sync else 1, tail_blocks=tail_blocks)
         # Buffers (BatchNorm running statistics) follow rank 0 after every step, as in the reference
         # (one ncclBroadcast per buffer per step, flodl/src/distributed/ddp.rs:150-157). Here they are
         # re-homed into one peer-mapped block and refreshed by ONE pull-broadcast launch per step.
