@@ -69,24 +69,36 @@ class LocalTransport:
 
 
 class _StoreBox(Mailbox):
+    """Message n of a box lives under `<box>/<n>`: a small header (the number of chunks) written LAST, and the
+    pickled payload in chunks `<box>/<n>/c<k>` of at most `CHUNK` bytes (the store's server refuses requests above
+    8 MB; parameter snapshots are hundreds of megabytes)."""
+    CHUNK = 4 << 20
+
     def __init__(self, store, name: str):
         self.store, self.name = store, name
         self.tx = 0
         self.rx = 0
 
     def send(self, msg) -> None:
-        self.store.set(f"{self.name}/{self.tx}", pickle.dumps(msg, protocol=pickle.HIGHEST_PROTOCOL))
+        data = pickle.dumps(msg, protocol=pickle.HIGHEST_PROTOCOL)
+        key = f"{self.name}/{self.tx}"
+        n = max(1, (len(data) + self.CHUNK - 1) // self.CHUNK)
+        for k in range(n):
+            self.store.set(f"{key}/c{k}", data[k * self.CHUNK:(k + 1) * self.CHUNK])
+        self.store.set(key, str(n).encode())          # the receiver looks for this key: every chunk is there by now
         self.tx += 1
 
     def try_recv(self):
         key = f"{self.name}/{self.rx}"
         if not self.store.check([key]):
             return None
-        raw = self.store.get(key)
-        try:
-            self.store.delete_key(key)
-        except Exception:
-            pass
+        n = int(bytes(self.store.get(key)).decode())
+        raw = b"".join(bytes(self.store.get(f"{key}/c{k}")) for k in range(n))
+        for k in [key] + [f"{key}/c{k}" for k in range(n)]:
+            try:
+                self.store.delete_key(k)
+            except Exception:
+                pass
         self.rx += 1
         return pickle.loads(raw)
 

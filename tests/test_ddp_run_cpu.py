@@ -335,6 +335,23 @@ def test_store_transport_is_fifo_and_cleans_up():
     assert b.box("ctl0").recv(timeout=0.01) is None
 
 
+def test_store_transport_splits_large_messages():
+    """Parameter snapshots are far above the store's 8 MB request limit: they travel in chunks."""
+    class LimitedStore(FakeStore):
+        def set(self, k, v):
+            assert len(v) <= 8 << 20, "request above the store's limit"
+            super().set(k, v)
+    store = LimitedStore()
+    a, b = StoreTransport(store, "y"), StoreTransport(store, "y")
+    big = torch.arange(5_000_000, dtype=torch.float32)            # 20 MB
+    a.box("fin0").send(ParamSnapshot(0, [big], [], 7))
+    a.box("fin0").send(ParamSnapshot(0, [torch.ones(3)], [], 8))
+    got = b.box("fin0").try_recv()
+    assert got.batch_count == 7 and torch.equal(got.params[0], big)
+    assert b.box("fin0").try_recv().batch_count == 8
+    assert store.d == {}
+
+
 # ---- workers ----------------------------------------------------------------------------------------
 def _model(dev=None):
     torch.manual_seed(3)
