@@ -495,6 +495,14 @@ class Ddp:
     def builder(model_factory, optim_factory, train_fn): return Trainer.builder(model_factory, optim_factory, train_fn)
 
 
+def _native_ready() -> bool:
+    from .. import ops as _ops
+    try:
+        return bool(_ops.native_enabled())
+    except Exception:
+        return False
+
+
 class Trainer:
     """One-call training setup (ddp.rs:742-952). Works for one rank or many: with a single
     process nothing is distributed and `model.step()` is a plain optimizer step."""
@@ -506,7 +514,11 @@ class Trainer:
     @staticmethod
     def setup_with(model, builder: Optional[Callable], optimizer: Callable, config: Optional[DdpConfig], **kw) -> None:
         Ddp.print_device_summary()
-        if _comm.world_size() > 1:
+        # One rank on a GPU still takes the distributed state: it moves parameters and gradients into the flat
+        # buffers, so every op runs this library's kernels (gradients straight into their slots, one fused
+        # optimizer launch); its collectives are no-ops in a world of one.
+        on_gpu = any(p.t.is_cuda for p in model.parameters()[:1]) and _native_ready()
+        if _comm.world_size() > 1 or on_gpu:
             model.distribute(builder, **kw)
             st: DistributedState = model._ddp
             if config is not None:
