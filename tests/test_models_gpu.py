@@ -217,3 +217,27 @@ def test_training_loss_parity_native_vs_pytorch_ops_resnet20():
     assert a[-1] < 0.1 * a[0] and b[-1] < 0.1 * b[0], (a[0], a[-1], b[0], b[-1])
     assert abs(sum(a[:10]) - sum(b[:10])) / abs(sum(b[:10])) < 0.15, (a[:10], b[:10])
     assert abs(a[-1] - b[-1]) < 0.05, (a[-1], b[-1])
+
+
+@pytest.mark.parametrize("opt_name", ["RMSprop", "Adagrad", "RAdam", "NAdam"])
+def test_bf16_weight_copy_follows_every_optimizer(opt_name):
+    """The forward GEMMs read a bf16 copy of the parameters. Only Adam / AdamW / SGD refresh it inside their fused
+    kernel; every other optimizer must leave it equal to the updated fp32 values too, or training would keep using the
+    initial weights."""
+    from flodl_b200 import nn
+    from flodl_b200.models.gpt import DecoderLM, DecoderLMConfig
+    from flodl_b200.parallel.engine import TrainEngine
+    torch.manual_seed(0)
+    cfg = DecoderLMConfig(vocab_size=128, d_model=64, n_layers=1, n_heads=1, d_ff=128, max_seq=32, dropout=0.0)
+    model = DecoderLM(cfg, "cuda")
+    model.set_training(True)
+    ids = torch.randint(0, 128, (4, 33), device="cuda")
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    with nn.AutocastGuard(torch.bfloat16):
+        eng = TrainEngine(model, lambda ps: getattr(nn, opt_name)(ps, 1e-2))
+        before = eng.flat.params.clone()
+        losses = [float(eng.step(lambda: model.loss(x, y))) for _ in range(6)]
+    torch.cuda.synchronize()
+    assert not torch.equal(eng.flat.params, before)
+    assert torch.equal(eng.flat.shadow, eng.flat.params.to(torch.bfloat16)), "the bf16 copy was not refreshed after the step"
+    assert losses[-1] < losses[0]
