@@ -6,12 +6,12 @@ import json
 from typing import Optional
 
 from ...tensor import TensorError
-from . import albert, bert, deberta_v2, distilbert, roberta
+from . import albert, bert, deberta_v2, distilbert, roberta, xlm_roberta
 
 _FAMILIES = {
     "bert": (bert.BertConfig, "BertModel", bert),
     "roberta": (roberta.RobertaConfig, "RobertaModel", roberta),
-    "xlm-roberta": (roberta.XlmRobertaConfig, "XLMRobertaModel", roberta),
+    "xlm-roberta": (xlm_roberta.XlmRobertaConfig, "XLMRobertaModel", xlm_roberta),
     "distilbert": (distilbert.DistilBertConfig, "DistilBertModel", distilbert),
     "albert": (albert.AlbertConfig, "AlbertModel", albert),
     "deberta-v2": (deberta_v2.DebertaV2Config, "DebertaV2Model", deberta_v2),

@@ -86,20 +86,6 @@ class RobertaConfig:
                 Variable.wrap(build_extended_attention_mask(enc.attention_mask))]
 
 
-@dataclass
-class XlmRobertaConfig(RobertaConfig):
-    """Same fields as RoBERTa; a type of its own so `model_type: "xlm-roberta"` survives a round trip."""
-    vocab_size: int = 250002
-
-    MODEL_TYPE = "xlm-roberta"
-    FAMILY_NAME = "XlmRoberta"
-    BASE_ARCH = "XLMRobertaModel"
-
-    @classmethod
-    def xlm_roberta_base(cls) -> "XlmRobertaConfig":
-        return cls()
-
-
 class RobertaEmbeddings(Module):
     def __init__(self, config: RobertaConfig, device=None):
         self.word_embeddings = Embedding(config.vocab_size, config.hidden_size, config.pad_token_id, device)
@@ -241,5 +227,3 @@ def _family(prefix: str, config_cls):
 
 (RobertaModel, RobertaForSequenceClassification, RobertaForTokenClassification, RobertaForQuestionAnswering,
  RobertaForMaskedLM) = _family("Roberta", RobertaConfig)
-(XlmRobertaModel, XlmRobertaForSequenceClassification, XlmRobertaForTokenClassification, XlmRobertaForQuestionAnswering,
- XlmRobertaForMaskedLM) = _family("XLMRoberta", XlmRobertaConfig)

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from flodl_b200.hf import safetensors_io as st
-from flodl_b200.hf.models import albert, bert, deberta_v2, distilbert, roberta
+from flodl_b200.hf.models import albert, bert, deberta_v2, distilbert, roberta, xlm_roberta
 from flodl_b200.hf.path import HfPath, hf_key_from_flodl_key
 
 transformers = pytest.importorskip("transformers")
@@ -143,7 +143,7 @@ def test_bert_key_map_matches_hf_names():
 
 
 def test_config_round_trips_and_presets():
-    for cfg in (bert.BertConfig.bert_base_uncased(), roberta.RobertaConfig.roberta_base(), roberta.XlmRobertaConfig.xlm_roberta_base(),
+    for cfg in (bert.BertConfig.bert_base_uncased(), roberta.RobertaConfig.roberta_base(), xlm_roberta.XlmRobertaConfig.xlm_roberta_base(),
                 distilbert.DistilBertConfig.distilbert_base_uncased(), albert.AlbertConfig.albert_base_v2(),
                 deberta_v2.DebertaV2Config.deberta_v3_base()):
         s = cfg.to_json_str()
@@ -264,7 +264,7 @@ def test_auto_classes_export_and_local_from_pretrained(tmp_path, monkeypatch):
     with pytest.raises(Exception):
         hf.AutoConfig.from_json_str('{"model_type": "gpt2"}')
     for mt, c in (("bert", bert.BertConfig), ("distilbert", distilbert.DistilBertConfig), ("albert", albert.AlbertConfig),
-                  ("deberta-v2", deberta_v2.DebertaV2Config), ("xlm-roberta", roberta.XlmRobertaConfig)):
+                  ("deberta-v2", deberta_v2.DebertaV2Config), ("xlm-roberta", xlm_roberta.XlmRobertaConfig)):
         assert hf.AutoConfig.from_json_str(c().to_json_str()).model_type() == mt
 
 
