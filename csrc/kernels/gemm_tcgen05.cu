@@ -811,9 +811,15 @@ extern "C" int fb_gemm_pick_config(int M, int N, int K, int split_k) {
   const int sms = 148;
   // Single-CTA tiles read A and the whole B tile from shared memory for every MMA and run close to
   // the shared-memory bandwidth limit; the pair configs (each CTA reads half of B) do not, hence
-  // their higher prior. The 256x192 pair needs a K-major B (its 96-column half tile is not a whole
+  // their higher prior. (Back to back in isolation the single-CTA 128x192 tile is the fastest shape for N = 768, 9.2 against
+  // 9.9 / 10.4 us, but inside a BERT-base step, where these GEMMs share the GPU with the weight-gradient stream, preferring it
+  // made the step 1.7 % slower: 6.01 against 5.90 ms in an A/B within one run. The prior stays at 0.80.) The 256x192 pair needs a K-major B (its 96-column half tile is not a whole
   // number of 64-column panels), so fb_gemm_bf16 falls back to 256x256 when B is MN-major.
-  const struct { int cg, bn; float prior; } cand[6] = {{2, 256, 1.00f}, {1, 256, 0.85f}, {1, 128, 0.70f}, {1, 64, 0.50f}, {1, 192, 0.80f}, {2, 192, 0.98f}};
+  static const float prior192 = [] {      // tuning knob: FLODL_B200_GEMM_PRIOR192 overrides the 128x192 tile's prior
+    const char* e = std::getenv("FLODL_B200_GEMM_PRIOR192");
+    return e ? static_cast<float>(std::atof(e)) : 0.80f;
+  }();
+  const struct { int cg, bn; float prior; } cand[6] = {{2, 256, 1.00f}, {1, 256, 0.85f}, {1, 128, 0.70f}, {1, 64, 0.50f}, {1, 192, prior192}, {2, 192, 0.98f}};
   int best = 2;
   float best_score = -1.f;
   for (int i = 0; i < 6; ++i) {
