@@ -14,6 +14,7 @@ weights get several) is learned on the first step, which runs without overlap.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -31,6 +32,10 @@ class GradSync:
         # left to overlap with, so it may use most of the GPU instead of the few blocks that keep the
         # overlapped buckets out of the GEMMs' way.
         self.tail_blocks = max(int(tail_blocks), int(blocks))
+        # How many of the last buckets (the first parameters of the buffer: embeddings and the first layers, whose
+        # gradients are complete only as backward ends) the optimizer leaves for a second pass, see finish().
+        self.tail_buckets = max(1, int(os.environ.get("FLODL_B200_TAIL_BUCKETS", "1")))
+        self._done_recorded = False
         self.world = _comm.world_size() if world is None else int(world)   # world=1: no gradient exchange (Local SGD)
         self.backend = backend if self.world > 1 else "none"
         self.overlap = overlap and self.world > 1
@@ -73,6 +78,7 @@ class GradSync:
             self.touch[i] = 0
         self.next_bucket = 0
         self.mismatch = False
+        self._done_recorded = False
         for bi, b in enumerate(self.buckets):
             self.launched[bi] = False
             self.pending[bi] = sum(1 for i in b["members"] if self.expected is not None and self.expected[i] > 0)
@@ -121,10 +127,21 @@ class GradSync:
         cur = torch.cuda.current_stream()
         ev = torch.cuda.Event()
         ev.record(cur)
+        self._mark_rest_done(bi)
         self.stream.wait_event(ev)
         with torch.cuda.stream(self.stream):
             self._reduce_range(b["start"], b["end"], self.tail_blocks if tail else self.blocks)
         self.launch_count += 1
+
+    def _first_tail(self) -> int:
+        return max(0, len(self.buckets) - self.tail_buckets)
+
+    def _mark_rest_done(self, bi: int) -> None:
+        """Called before bucket `bi` is put on the exchange stream: `done` is recorded in front of the first tail
+        bucket, so waiting for it means "every bucket before the tail has been exchanged" and nothing more."""
+        if self.stream is not None and not self._done_recorded and bi >= self._first_tail():
+            self.done.record(self.stream)
+            self._done_recorded = True
 
     def _reduce_range(self, start: int, end: int, blocks: Optional[int] = None) -> None:
         n = end - start
@@ -142,11 +159,11 @@ class GradSync:
         """Call after backward: launches whatever has not been launched, then makes the current
         stream wait for every bucket.
 
-        `defer_tail=True`: the current stream waits for every bucket but the last one (the first
-        parameters of the buffer, whose gradients are complete only when backward ends, so their
-        exchange can overlap nothing of backward) and `(lo, hi)`, that bucket's element range, is
-        returned. The caller applies the optimizer to the rest, calls `wait_tail()`, then applies
-        it to `[lo, hi)`: the last exchange runs behind the optimizer instead of in front of it."""
+        `defer_tail=True`: the current stream waits for every bucket but the last `tail_buckets` ones (the first
+        parameters of the buffer: their gradients are complete only as backward ends, so their exchange can
+        overlap little or nothing of it) and `(lo, hi)`, the element range of those buckets, is returned. The
+        caller applies the optimizer to the rest, calls `wait_tail()`, then applies it to `[lo, hi)`: the last
+        exchanges run behind the optimizer instead of in front of it."""
         if self.world <= 1:
             return None
         self.active = False
@@ -156,18 +173,19 @@ class GradSync:
         tail = None
         split = defer_tail and self.stream is not None and len(self.buckets) > 1 and not self.mismatch
         for bi in range(len(self.buckets)):
-            if split and bi == len(self.buckets) - 1:
-                self.done.record(self.stream)                 # everything before the last bucket
-                torch.cuda.current_stream().wait_event(self.done)
             if not self.launched[bi]:
                 self._launch(bi)
         if self.stream is not None:
             if split:
-                self.done_tail.record(self.stream)
-                tail = (self.buckets[-1]["start"], self.buckets[-1]["end"])
-            else:
-                self.done.record(self.stream)
+                # `done` sits in front of the first tail bucket (see _mark_rest_done): the optimizer may start on
+                # everything behind the tail while the tail buckets are still being exchanged
+                self._mark_rest_done(len(self.buckets))
                 torch.cuda.current_stream().wait_event(self.done)
+                self.done_tail.record(self.stream)
+                tail = (self.buckets[-1]["start"], self.buckets[self._first_tail()]["end"])
+            else:
+                self.done_tail.record(self.stream)
+                torch.cuda.current_stream().wait_event(self.done_tail)
         if self.mismatch:
             self.overlap = False
             raise RuntimeError(
