@@ -50,7 +50,8 @@ class GradSync:
         self.pending = [0] * len(self.buckets)
         self.launched = [False] * len(self.buckets)
         self.weights: Optional[List[float]] = None
-        self.stream = torch.cuda.Stream(priority=-1) if flat.device.type == "cuda" and self.world > 1 else None
+        self.stream = (torch.cuda.Stream(priority=int(os.environ.get("FLODL_B200_COMM_PRIORITY", "-1")))
+                       if flat.device.type == "cuda" and self.world > 1 else None)
         self.done = torch.cuda.Event() if self.stream is not None else None
         self.done_tail = torch.cuda.Event() if self.stream is not None else None
         self.active = False
