@@ -59,6 +59,9 @@ class GradSync:
         self.next_bucket = 0
         self.mismatch = False
         self._hooks = []
+        # per-bucket exchange timing (eager steps only: timing events cannot be recorded into a CUDA graph)
+        self._timing = False
+        self._timing_events: List[tuple] = []
         if self.world > 1:
             for t in flat.tensors:
                 if t.requires_grad:
@@ -130,8 +133,15 @@ class GradSync:
         ev.record(cur)
         self._mark_rest_done(bi)
         self.stream.wait_event(ev)
+        timed = self._timing and not torch.cuda.is_current_stream_capturing()
         with torch.cuda.stream(self.stream):
+            if timed:
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(self.stream)
             self._reduce_range(b["start"], b["end"], self.tail_blocks if tail else self.blocks)
+            if timed:
+                t1.record(self.stream)
+                self._timing_events.append((bi, t0, t1))
         self.launch_count += 1
 
     def _first_tail(self) -> int:
@@ -194,6 +204,32 @@ class GradSync:
                 "receive gradients changed between steps). This step's gradients are incomplete on this rank; overlap is now "
                 "off. Build the trainer with overlap=False for models whose backward differs from step to step.")
         return tail
+
+    # ---- diagnostics ------------------------------------------------------------------------------
+    def enable_timing(self, on: bool = True) -> None:
+        """Bracket every bucket exchange of the following eager steps with CUDA events (`bucket_report`)."""
+        self._timing = bool(on)
+        self._timing_events.clear()
+
+    def bucket_report(self, link_gbs: float = 900.0) -> List[dict]:
+        """Per bucket, over the steps timed so far: payload, mean device time of the exchange kernel (which includes
+        waiting for the peers at its barriers), bus bandwidth 2 (W - 1) / W x bytes / time and that as a fraction
+        of `link_gbs` (NVLink per direction per GPU). Synchronises the device."""
+        if self.stream is not None:
+            torch.cuda.synchronize()
+        acc: Dict[int, List[float]] = {}
+        for bi, t0, t1 in self._timing_events:
+            acc.setdefault(bi, []).append(t0.elapsed_time(t1))
+        out = []
+        w = max(1, self.world)
+        for bi in sorted(acc):
+            b = self.buckets[bi]
+            nbytes = (b["end"] - b["start"]) * 4
+            ms = sum(acc[bi]) / len(acc[bi])
+            bus = 2.0 * (w - 1) / w * nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+            out.append({"bucket": bi, "bytes": nbytes, "launches": len(acc[bi]), "ms": round(ms, 4), "bus_GBs": round(bus, 1),
+                        "frac_of_link": round(bus / link_gbs, 3), "tail": bi >= self._first_tail()})
+        return out
 
     def wait_tail(self) -> None:
         """Make the current stream wait for the bucket `finish(defer_tail=True)` left in flight."""

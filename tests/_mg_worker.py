@@ -151,6 +151,7 @@ def main():
             eng = TrainEngine(head.graph(), lambda ps: nn.AdamW(ps, 1e-3, 0.0), bucket_mb=0.25)
             p0 = gather_all(eng.flat.params.clone())
             assert all(torch.equal(p0[0], a) for a in p0), "parameters not synchronised after broadcast"
+            eng.sync.enable_timing()
             for step in range(4):
                 eng.step(lambda: head.compute_loss([ids, pos, tt, mask], labels))
                 torch.cuda.synchronize()
@@ -160,6 +161,9 @@ def main():
                 ps = gather_all(eng.flat.params.clone())
                 assert all(torch.equal(ps[0], a) for a in ps), f"parameters diverged at step {step}"
             assert len(eng.sync.buckets) > 1 and eng.sync.launch_count >= 4 * len(eng.sync.buckets)
+            rep = eng.sync.bucket_report()
+            assert [r["bucket"] for r in rep] == list(range(len(eng.sync.buckets))) and all(r["ms"] > 0 and r["launches"] == 4 for r in rep), rep
+            assert sum(r["bytes"] for r in rep) == eng.flat.total * 4
     elif mode == "giveup":
         # A rank that is late by more than the collectives' time limit: the others must not apply
         # un-reduced gradients. The fused optimizer is predicated on the exchange's status word, so

@@ -116,3 +116,10 @@ def test_world_of_one_is_inert():
     gs.begin_step()
     gs._on_touch(params[0])
     assert gs.finish() is None and gs.launch_count == 0
+
+
+def test_bucket_report_is_empty_without_timed_launches():
+    params, flat, gs, calls = make()
+    gs.enable_timing()
+    step(gs, params, [5, 4, 3, 2, 1, 0])            # CPU: exchanges run in line, nothing is timed
+    assert gs.bucket_report() == []
