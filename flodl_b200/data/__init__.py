@@ -8,6 +8,6 @@
   stream, `PrefetchWorker`); chosen from free device memory unless forced.
 """
 from .dataset import Batch, BatchDataSet, DataSet, DataSetAdapter, TensorDataSet  # noqa: F401
-from .loader import DataLoader, DataLoaderBuilder, prefetch_depth_from_vram  # noqa: F401
+from .loader import DataLoader, DataLoaderBuilder, DistributedEpochIterator, EpochIterator, prefetch_depth_from_vram  # noqa: F401
 from .prefetch import PrefetchWorker  # noqa: F401
 from .sampler import RandomSampler, Sampler, SequentialSampler  # noqa: F401

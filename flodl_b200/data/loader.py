@@ -186,13 +186,14 @@ class DataLoader:
         return b - a
 
     # ---- iteration ------------------------------------------------------------------------------
-    def epoch(self, epoch: int) -> Iterator[Batch]:
+    def epoch(self, epoch: int) -> "EpochIterator":
         order = self._sampler.indices(epoch)
         a, b = self._shard_bounds(len(order))
         order = order[a:b]
-        if self._resident is not None:
-            return self._iter_resident(order)
-        return self._iter_streaming(order)
+        gen = self._iter_resident(order) if self._resident is not None else self._iter_streaming(order)
+        if self._world > 1:
+            return DistributedEpochIterator(gen, self.num_batches(), self._rank, self._world, (a, b))
+        return EpochIterator(gen, self.num_batches())
 
     def _iter_resident(self, order: List[int]) -> Iterator[Batch]:
         idx_all = torch.as_tensor(order, dtype=torch.long).to(self._device)
@@ -219,3 +220,50 @@ class DataLoader:
                 yield Batch(batch, self._names)
         finally:
             self._worker.stop()
+
+
+class EpochIterator:
+    """The batches of one epoch (`DataLoader.epoch`), already on the loader's device. Knows how many
+    batches are left (`len(it)`, `size_hint()`); dropping or `close()`-ing it mid-epoch stops the
+    prefetch worker of a streaming loader (flodl/src/data/loader.rs:861-900)."""
+
+    def __init__(self, gen, num_batches: int):
+        self._gen, self._remaining = gen, int(num_batches)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> Batch:
+        try:
+            batch = next(self._gen)
+        except StopIteration:
+            self._remaining = 0
+            raise
+        self._remaining = max(0, self._remaining - 1)
+        return batch
+
+    def __len__(self) -> int:
+        return self._remaining
+
+    def size_hint(self):
+        return self._remaining, self._remaining
+
+    def close(self) -> None:
+        self._gen.close()
+        self._remaining = 0
+
+    def __del__(self):
+        try:
+            self._gen.close()
+        except Exception:
+            pass
+
+
+class DistributedEpochIterator(EpochIterator):
+    """Epoch iterator of a loader that was sharded with `DataLoader.distributed(rank, world)`: this
+    rank's slice `[lo, hi)` of the epoch's global permutation, cut by the current shard ratios
+    (flodl/src/data/loader.rs:1180-1275; one process per GPU here, so each rank iterates its own)."""
+
+    def __init__(self, gen, num_batches: int, rank: int, world: int, bounds):
+        super().__init__(gen, num_batches)
+        self.rank, self.world_size, self.shard_bounds = rank, world, tuple(bounds)

@@ -10,4 +10,4 @@ from .render import format_duration  # noqa: F401
 from .snapshot import ModelSnapshot, snapshot_cpu  # noqa: F401
 from .tree import PathKind  # noqa: F401
 from .trend import Trend, TrendGroup  # noqa: F401
-from .distributed import GraphEpochIterator, LossContext  # noqa: F401
+from .distributed import ActiveGraphEpochIterator, GraphEpochIterator, LossContext  # noqa: F401

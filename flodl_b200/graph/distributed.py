@@ -18,23 +18,57 @@ class LossContext:
 
 
 class GraphEpochIterator:
-    """Iterator over the bound loader's batches for one epoch. With a loss function bound
+    """Handle on one epoch of the bound loader (`Graph.epoch(n)`); iteration starts with `activate()`
+    or with the first `next()` (flodl/src/graph/graph.rs:1150-1230). With a loss function bound
     (`set_loss_fn`) each item has already been run: forward on the batch's input field, loss,
     backward; the item is then `(batch, loss)`. Without one the item is the `Batch`."""
 
     def __init__(self, graph, epoch: int):
         self.graph, self.epoch_index = graph, epoch
-        loader, self.input_name = graph._data_binding
-        self._it = iter(loader.epoch(epoch))
+        self._active = None
 
-    def activate(self) -> "GraphEpochIterator":
-        return self
+    def activate(self) -> "ActiveGraphEpochIterator":
+        if self._active is None:
+            self._active = ActiveGraphEpochIterator(self.graph, self.epoch_index)
+        return self._active
+
+    def __iter__(self):
+        return self.activate()
+
+    def __next__(self):
+        return next(self.activate())
+
+    def __len__(self) -> int:
+        return len(self.activate())
+
+
+class ActiveGraphEpochIterator:
+    """The running form of `GraphEpochIterator`. Knows how many batches are left. When it ends (or is
+    closed) on an El Che cadence with gradients accumulated and not yet combined, it calls
+    `graph.step()` so that the epoch's last batches are not lost (graph.rs:1232-1250)."""
+
+    def __init__(self, graph, epoch: int):
+        self.graph, self.epoch_index = graph, epoch
+        loader, self.input_name = graph._data_binding
+        self._it = loader.epoch(epoch)
+        self._done = False
 
     def __iter__(self):
         return self
 
+    def __len__(self) -> int:
+        return len(self._it) if hasattr(self._it, "__len__") else 0
+
+    def size_hint(self):
+        n = len(self)
+        return n, n
+
     def __next__(self):
-        batch = next(self._it)
+        try:
+            batch = next(self._it)
+        except StopIteration:
+            self.close()
+            raise
         g = self.graph
         if g._loss_fn is None:
             return batch
@@ -46,6 +80,16 @@ class GraphEpochIterator:
         loss = g._loss_fn(LossContext(out, batch, tags, {}))
         loss.backward()
         return batch, loss
+
+    def close(self) -> None:
+        if self._done:
+            return
+        self._done = True
+        if hasattr(self._it, "close"):
+            self._it.close()
+        g = self.graph
+        if g.has_el_che() and getattr(g._ddp, "_acc_batches", 0) > 0 and g._optimizer is not None:
+            g.step()
 
 
 class DistributedMixin:

@@ -196,9 +196,11 @@ class FlowBuilder:
             self._resolve_pending(name, ref)
         return self
 
-    def using(self, refs: Sequence[str]) -> "FlowBuilder":
+    def using(self, refs, *more: str) -> "FlowBuilder":
         """Feed tagged values to the preceding node as named refs (`forward_named`). A name that
-        is not tagged yet becomes a forward reference: the value of the PREVIOUS forward call."""
+        is not tagged yet becomes a forward reference: the value of the PREVIOUS forward call.
+        Takes a list of names, or the names themselves: `using(["a", "b"])`, `using("a", "b")`."""
+        refs = ([refs] if isinstance(refs, str) else list(refs)) + list(more)
         if self.err is not None or not refs:
             return self
         if self.on_target is not None:

@@ -405,6 +405,12 @@ class Graph(Module, TreeMixin, ObserveMixin, ProfileMixin, RenderMixin, Distribu
     def clear_source_config(self) -> None:
         self._source_config = None
 
+    def snapshot_cpu(self):
+        """Host copies of every named parameter and buffer, to be written later off the training
+        thread (`ModelSnapshot.save_file`; flodl/src/graph/snapshot.rs:90-120)."""
+        from .snapshot import snapshot_cpu
+        return snapshot_cpu(self)
+
     def save_checkpoint(self, path: str) -> None:
         """`.fdl` (gzip if the path ends in .gz) + `<stem>.config.json` sidecar when a source config
         is attached (graph.rs:891-907, :1046-1054)."""

@@ -68,6 +68,9 @@ class Linear(Module):
 
 # ------------------------------------------------------------------------------------------- conv
 class _ConvBuilder:
+    """`Conv2d.configure(in, out, k).with_stride(2).with_padding(1).without_bias().on_device(d).done()`
+    (flodl/src/nn/conv2d.rs:40-110; the 1-D and 3-D builders are the same shape)."""
+
     def __init__(self, cls, in_c, out_c, k):
         self.cls, self.a = cls, dict(in_channels=in_c, out_channels=out_c, kernel_size=k)
 
@@ -79,6 +82,9 @@ class _ConvBuilder:
     def without_bias(self): self.a["bias"] = False; return self
     def on_device(self, device): self.a["device"] = device; return self
     def done(self): return self.cls(**self.a)
+
+
+Conv1dBuilder = Conv2dBuilder = Conv3dBuilder = _ConvBuilder
 
 
 class _ConvNd(Module):

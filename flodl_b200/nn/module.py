@@ -215,6 +215,26 @@ def walk_modules(root: Module) -> List[Module]:
     return out
 
 
+def walk_modules_visited(module: Module, visited: set, f) -> None:
+    """Call `f` on `module` and everything below it, skipping what `visited` (a set the caller owns,
+    of `id()`s) already holds: share one set over several roots to see a shared sub-module once
+    (flodl/src/nn/mod.rs:408-420)."""
+    if id(module) in visited:
+        return
+    visited.add(id(module))
+    f(module)
+    for child in module.sub_modules():
+        walk_modules_visited(child, visited, f)
+
+
+def collect_parameters(mods) -> list:
+    """Parameters of several modules, concatenated without de-duplication (flodl/src/nn/mod.rs:422-436)."""
+    out = []
+    for m in mods:
+        out.extend(m.parameters())
+    return out
+
+
 def modules(*mods: Module) -> List[Module]:
     """`modules![a, b, c]` (flodl/src/lib.rs:47-52)."""
     return list(mods)
@@ -229,8 +249,43 @@ class LoopBodyEmit:
     def __call__(self, name: str, value: Variable) -> None:
         self.values.setdefault(name, []).append(value)
 
+    publish = __call__
+
+    @classmethod
+    def discard(cls) -> "LoopBodyEmit":
+        """An emitter whose values nobody reads (what `forward_via_step` hands to `step`)."""
+        return cls()
+
 
 TraceEmit = LoopBodyEmit
+
+
+class NamedInputModule(Module):
+    """A module that takes extra named inputs wired by `FlowBuilder.using()`: implement
+    `forward_named(input, refs)` with `refs` a dict from tag name to the tag's current value
+    (flodl/src/nn/mod.rs:281-290). Any module with a `forward_named` method is accepted by the
+    builder; this base states the contract and defaults `forward` to empty refs."""
+
+    def forward_named(self, input: Variable, refs: Dict[str, Variable]) -> Variable:
+        raise NotImplementedError
+
+    def forward(self, x):
+        return self.forward_named(x, {})
+
+
+class LoopBody(Module):
+    """A loop body with named per-iteration traces: implement `step(input, refs, emit)` and call
+    `emit.publish(name, value)`; the loop collects them under `Graph.traces_named(name)`
+    (flodl/src/nn/mod.rs:374-384). `forward` runs one step with a discarding emitter."""
+
+    def step(self, input: Variable, refs: Dict[str, Variable], emit: LoopBodyEmit) -> Variable:
+        raise NotImplementedError
+
+    def as_loop_body(self):
+        return self
+
+    def forward(self, x):
+        return forward_via_step(self, x)
 
 
 def forward_via_step(body: Module, input: Variable) -> Variable:

@@ -189,11 +189,19 @@ def _native(p: torch.Tensor) -> bool:
 
 
 class _GroupBuilder:
+    """Fluent construction of an optimizer: hyper-parameters by name, then one `group(params, lr)` per
+    learning-rate group (or the `(params, lr)` given to `Opt.builder`), then `build()`."""
+    KNOBS = ()
+
     def __init__(self, cls, **kw):
         self.cls, self.kw, self.gs = cls, kw, []
 
     def group(self, params, lr):
         self.gs.append((list(params), lr))
+        return self
+
+    def _set(self, key, value):
+        self.kw[key] = value
         return self
 
     def build(self):
@@ -202,6 +210,38 @@ class _GroupBuilder:
             opt._add_group(ps, lr)
         opt._init_state()
         return opt
+
+
+class AdamBuilder(_GroupBuilder):
+    """`Adam.with_groups().betas(0.9, 0.98).eps(1e-6).group(ps, lr).build()` (adam.rs:58-100)."""
+    def betas(self, beta1, beta2): return self._set("betas", (beta1, beta2))
+    def eps(self, eps): return self._set("eps", eps)
+
+
+class AdamWBuilder(AdamBuilder):
+    """`AdamW.with_groups(weight_decay)`, same knobs as `AdamBuilder` (adam.rs:268-310)."""
+    def weight_decay(self, wd): return self._set("weight_decay", wd)
+
+
+class SGDBuilder(_GroupBuilder):
+    """`SGD.with_groups(momentum).weight_decay(wd).group(ps, lr).build()` (sgd.rs:62-110)."""
+    def momentum(self, m): return self._set("momentum", m)
+    def weight_decay(self, wd): return self._set("weight_decay", wd)
+
+
+class RMSpropBuilder(_GroupBuilder):
+    """`RMSprop.builder(ps, lr).alpha(a).eps(e).weight_decay(wd).momentum(m).build()` (rmsprop.rs:100-125)."""
+    def alpha(self, a): return self._set("alpha", a)
+    def eps(self, eps): return self._set("eps", eps)
+    def weight_decay(self, wd): return self._set("weight_decay", wd)
+    def momentum(self, m): return self._set("momentum", m)
+
+
+class AdagradBuilder(_GroupBuilder):
+    """`Adagrad.builder(ps, lr).eps(e).weight_decay(wd).lr_decay(d).build()` (adagrad.rs:30-50)."""
+    def eps(self, eps): return self._set("eps", eps)
+    def weight_decay(self, wd): return self._set("weight_decay", wd)
+    def lr_decay(self, d): return self._set("lr_decay", d)
 
 
 # -------------------------------------------------------------------------------------------- Adam
@@ -218,7 +258,7 @@ class Adam(Optimizer):
     @classmethod
     def new(cls, params, lr): return cls(params, lr)
     @classmethod
-    def with_groups(cls, **kw): return _GroupBuilder(cls, **kw)
+    def with_groups(cls, **kw): return AdamBuilder(cls, **kw)
 
     def _init_state(self):
         self.m: List[Optional[torch.Tensor]] = [None] * len(self.params)
@@ -350,9 +390,8 @@ class AdamW(Adam):
 
     @classmethod
     def new(cls, params, lr, weight_decay): return cls(params, lr, weight_decay)
-
-
-AdamBuilder = AdamWBuilder = _GroupBuilder
+    @classmethod
+    def with_groups(cls, weight_decay=0.01, **kw): return AdamWBuilder(cls, weight_decay=weight_decay, **kw)
 
 
 # --------------------------------------------------------------------------------------------- SGD
@@ -368,7 +407,7 @@ class SGD(Optimizer):
     @classmethod
     def new(cls, params, lr, momentum=0.0): return cls(params, lr, momentum)
     @classmethod
-    def with_groups(cls, **kw): return _GroupBuilder(cls, **kw)
+    def with_groups(cls, momentum=0.0, **kw): return SGDBuilder(cls, momentum=momentum, **kw)
     def with_weight_decay(self, wd): self.weight_decay = wd; return self
 
     def _init_state(self):
@@ -486,7 +525,9 @@ class RMSprop(Optimizer):
         self._init_state()
 
     @classmethod
-    def with_groups(cls, **kw): return _GroupBuilder(cls, **kw)
+    def with_groups(cls, **kw): return RMSpropBuilder(cls, **kw)
+    @classmethod
+    def builder(cls, params, lr): return RMSpropBuilder(cls).group(params, lr)
 
     def _init_state(self):
         self.sq = [None] * len(self.params)
@@ -534,7 +575,6 @@ class RMSprop(Optimizer):
         self._load_groups(r)
 
 
-RMSpropBuilder = _GroupBuilder
 
 
 # ----------------------------------------------------------------------------------------- Adagrad
@@ -549,7 +589,9 @@ class Adagrad(Optimizer):
         self._init_state()
 
     @classmethod
-    def with_groups(cls, **kw): return _GroupBuilder(cls, **kw)
+    def with_groups(cls, **kw): return AdagradBuilder(cls, **kw)
+    @classmethod
+    def builder(cls, params, lr): return AdagradBuilder(cls).group(params, lr)
 
     def _init_state(self):
         self.ss = [None] * len(self.params)
@@ -588,7 +630,6 @@ class Adagrad(Optimizer):
         self._load_groups(r)
 
 
-AdagradBuilder = _GroupBuilder
 
 
 # ------------------------------------------------------------------------------------ RAdam / NAdam

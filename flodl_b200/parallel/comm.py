@@ -14,6 +14,7 @@ API and are bound to a multicast object, so the kernels can let the switch do th
 from __future__ import annotations
 
 import atexit
+import enum
 import os
 import socket
 import threading
@@ -90,6 +91,9 @@ class CudaStream:
     def __init__(self, device=None, high_priority: bool = False):
         self.s = torch.cuda.Stream(device=device, priority=-1 if high_priority else 0)
 
+    def is_complete(self) -> bool: return self.s.query()
+    def device(self): return self.s.device
+
     @classmethod
     def new(cls, device=None, high_priority=False): return cls(device, high_priority)
     def synchronize(self) -> None: self.s.synchronize()
@@ -102,12 +106,27 @@ class CudaStream:
 StreamGuard = lambda stream: stream.guard()  # noqa: E731  (`StreamGuard::new(stream)`)
 
 
+class CudaEventFlags(enum.IntEnum):
+    """`Default` records timestamps (needed by `CudaEvent.elapsed_time`), `DisableTiming` is the
+    cheaper synchronisation-only event (flodl/src/distributed/cuda_event.rs:32-37)."""
+    Default = 0
+    DisableTiming = 1
+
+
 class CudaEvent:
-    def __init__(self, timing: bool = False):
-        self.e = torch.cuda.Event(enable_timing=timing)
+    def __init__(self, timing=False):
+        if isinstance(timing, CudaEventFlags):
+            timing = timing == CudaEventFlags.Default
+        self.e = torch.cuda.Event(enable_timing=bool(timing))
 
     @classmethod
     def new(cls, timing=False): return cls(timing)
+
+    @staticmethod
+    def elapsed_time(start: "CudaEvent", end: "CudaEvent") -> float:
+        """Milliseconds between two recorded timing events."""
+        return start.e.elapsed_time(end.e)
+
     def record(self) -> None: self.e.record()
     def record_on(self, stream: CudaStream) -> None: self.e.record(stream.s)
     def synchronize(self) -> None: self.e.synchronize()

@@ -503,6 +503,19 @@ def _native_ready() -> bool:
         return False
 
 
+def _graph_of(head):
+    g = getattr(head, "graph", None)
+    return g() if callable(g) else head        # a bare Graph stands for itself
+
+
+class HasGraph:
+    """Anything that wraps a training graph and hands it out with `.graph()`: what `Trainer.setup_head`
+    accepts (the task heads of `flodl_b200.hf`; ddp.rs:974-981). A `Graph` is its own graph."""
+
+    def graph(self):
+        raise NotImplementedError
+
+
 class Trainer:
     """One-call training setup (ddp.rs:742-952). Works for one rank or many: with a single
     process nothing is distributed and `model.step()` is a plain optimizer step."""
@@ -531,11 +544,11 @@ class Trainer:
     @staticmethod
     def setup_head(head, builder: Optional[Callable], optimizer: Callable) -> None:
         """`head`: an object with `.graph()` (the task heads of `flodl_b200.hf`), ddp.rs:900-923."""
-        Trainer.setup_with(head.graph(), builder, optimizer, None)
+        Trainer.setup_with(_graph_of(head), builder, optimizer, None)
 
     @staticmethod
     def setup_head_with(head, builder: Optional[Callable], optimizer: Callable, config: DdpConfig) -> None:
-        Trainer.setup_with(head.graph(), builder, optimizer, config)
+        Trainer.setup_with(_graph_of(head), builder, optimizer, config)
 
     @staticmethod
     def builder(model_factory: Callable, optim_factory: Callable, train_fn: Callable):

@@ -342,3 +342,31 @@ def cuda_devices() -> List["DeviceInfo"]:
 
 def cuda_peak_reserved_bytes(index: int = 0) -> int:
     return int(torch.cuda.max_memory_reserved(index)) if cuda_available() else 0
+
+
+def _alloc_stat(index: int, key: str) -> int:
+    return int(torch.cuda.memory_stats(index).get(key, 0)) if cuda_available() else 0
+
+
+def cuda_active_bytes(index: Optional[int] = None) -> int:
+    """Bytes in blocks the caching allocator has handed out and not yet taken back (what
+    `CUDACachingAllocator::getDeviceStats` calls active; ops_nn.cpp:560-600), current device."""
+    return _alloc_stat(current_cuda_device() if index is None else index, "active_bytes.all.current")
+
+
+def cuda_peak_active_bytes(index: Optional[int] = None) -> int:
+    return _alloc_stat(current_cuda_device() if index is None else index, "active_bytes.all.peak")
+
+
+# `*_idx(i)`: the same queries for an explicit device index (flodl/src/tensor/cuda.rs:30-110)
+def cuda_memory_info_idx(index: int): return cuda_memory_info(index)
+def cuda_allocated_bytes_idx(index: int) -> int: return cuda_allocated_bytes(index)
+def cuda_active_bytes_idx(index: int) -> int: return cuda_active_bytes(index)
+def cuda_peak_active_bytes_idx(index: int) -> int: return cuda_peak_active_bytes(index)
+def cuda_peak_reserved_bytes_idx(index: int) -> int: return cuda_peak_reserved_bytes(index)
+def cuda_reset_peak_stats_idx(index: int) -> None: cuda_reset_peak_stats(index)
+def cuda_utilization_idx(index: int): return cuda_utilization(index)
+def cuda_device_name_idx(index: int) -> str: return cuda_device_name(index)
+
+
+Result = object     # Rust's `Result<T>`: calls here return the value or raise `TensorError`
