@@ -7,6 +7,10 @@ import torch
 class NoGradGuard:
     """RAII-style guard: gradient recording is off while the object is alive / inside `with`."""
 
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
     def __init__(self):
         self._prev = torch.is_grad_enabled()
         torch.set_grad_enabled(False)

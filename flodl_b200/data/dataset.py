@@ -96,6 +96,9 @@ class Batch:
     def get(self, index: int) -> torch.Tensor:
         return self._tensors[index]
 
+    def len(self) -> int:
+        return len(self._tensors)
+
     def get_named(self, name: str) -> Optional[torch.Tensor]:
         i = self._index.get(name)
         return None if i is None else self._tensors[i]

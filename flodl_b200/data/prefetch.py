@@ -27,9 +27,14 @@ class PrefetchWorker:
         self._thread: Optional[threading.Thread] = None
         self._q: Optional["queue.Queue"] = None
         self._stop = threading.Event()
+        self._cmd: Optional["queue.Queue"] = None          # distributed mode: index lists, one per requested batch
         if isinstance(dataset, TensorDataSet) and all(t.device.type == "cpu" for t in dataset.tensors()) and _ext.available():
             srcs = [t.contiguous() for t in dataset.tensors()]
             self._native = _ext.require().PrefetchWorker(srcs, self.device.index if self.device.type == "cuda" else -1, self.depth)
+
+    @classmethod
+    def new(cls, dataset: BatchDataSet, device, prefetch_depth: int = 4) -> "PrefetchWorker":
+        return cls(dataset, device, prefetch_depth)
 
     def prefetch_depth(self) -> int:
         return self.depth
@@ -78,9 +83,65 @@ class PrefetchWorker:
         self._thread = threading.Thread(target=work, name="prefetch", daemon=True)
         self._thread.start()
 
+    def _load(self, indices, stream):
+        batch = self.dataset.get_batch(indices)
+        ev = None
+        if stream is not None:
+            with torch.cuda.stream(stream):
+                batch = [t.pin_memory().to(self.device, non_blocking=True) if t.device.type == "cpu" else t for t in batch]
+                ev = torch.cuda.Event()
+                ev.record(stream)
+        return batch, ev
+
+    def start_distributed_epoch(self) -> "queue.Queue":
+        """Open an epoch whose batches are asked for one at a time with `load_batch(indices)` (the
+        shard sizes of a heterogeneous run change from batch to batch, so the order cannot be
+        handed over up front). Results come back in request order from `next()`, or from the
+        returned queue as `(tensors, ready_event)` items (prefetch.rs:108-123)."""
+        self.stop()
+        self._q = queue.Queue(maxsize=self.depth)
+        self._cmd = queue.Queue()
+        self._stop = threading.Event()
+        q, cmd, stop = self._q, self._cmd, self._stop
+        stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+
+        def work():
+            try:
+                while not stop.is_set():
+                    try:
+                        indices = cmd.get(timeout=0.05)
+                    except queue.Empty:
+                        continue
+                    if indices is None:
+                        break
+                    item = self._load(indices, stream)
+                    while not stop.is_set():
+                        try:
+                            q.put(item, timeout=0.05)
+                            break
+                        except queue.Full:
+                            continue
+                q.put(None)
+            except BaseException as e:
+                q.put(e)
+
+        self._thread = threading.Thread(target=work, name="prefetch-dist", daemon=True)
+        self._thread.start()
+        return q
+
+    def load_batch(self, indices: Sequence[int]) -> None:
+        """Request one batch (distributed mode); `end_distributed_epoch()` after the last one."""
+        if self._cmd is None:
+            raise RuntimeError("PrefetchWorker.load_batch: call start_distributed_epoch() first")
+        self._cmd.put(list(indices))
+
+    def end_distributed_epoch(self) -> None:
+        if self._cmd is not None:
+            self._cmd.put(None)
+
     def next(self) -> Optional[List[torch.Tensor]]:
         """Next batch on the device, or None at the end of the epoch."""
-        if self._native is not None:
+        if self._native is not None and self._cmd is None:
             return self._native.next()
         if self._q is None:
             return None
@@ -97,9 +158,10 @@ class PrefetchWorker:
         return batch
 
     def stop(self) -> None:
-        if self._native is not None:
+        if self._native is not None and self._cmd is None:
             self._native.stop()
             return
+        self._cmd = None
         self._stop.set()
         if self._thread is not None:
             if self._q is not None:

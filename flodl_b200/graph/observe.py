@@ -36,6 +36,8 @@ class ObserveMixin:
         return self.tagged_outputs.get(tag)
 
     def tag_names_list(self) -> List[str]:
+        """All tag names of this graph (`Graph::tag_names()`, observe.rs:44-47; the attribute
+        `tag_names` is the name -> node map)."""
         return list(self.tag_names.keys())
 
     def _expand_groups(self, tags: Sequence[str]) -> List[str]:

@@ -23,6 +23,9 @@ class Trend:
     def __init__(self, values: Sequence[float]):
         self._v = [float(x) for x in values]
 
+    @classmethod
+    def new(cls, values: Sequence[float]) -> "Trend": return cls(values)
+
     def __len__(self): return len(self._v)
     def len(self): return len(self._v)
     def is_empty(self): return not self._v

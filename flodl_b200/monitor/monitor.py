@@ -34,8 +34,42 @@ class EpochRecord:
     gpu_metrics: List[GpuMetrics] = field(default_factory=list)
 
 
+class Metrics:
+    """What `Monitor.log` takes as its `metrics` argument (flodl/src/monitor/mod.rs:68-125): a list of
+    `(name, value)` pairs, a dict, a `Graph` (the latest flushed epoch of its observed tags, plus the per-GPU
+    shares of a distributed graph), a `(graph, extra_pairs)` tuple, a DDP `EpochMetrics`, or any object
+    that implements this interface."""
+
+    def into_metrics(self) -> List[Tuple[str, float]]:
+        raise NotImplementedError
+
+    def gpu_metrics(self) -> List["GpuMetrics"]:
+        return []
+
+
+def _graph_gpu_metrics(graph) -> List["GpuMetrics"]:
+    if not (hasattr(graph, "is_distributed") and graph.is_distributed()):
+        return []
+    ratios, tp, shards = graph.chunk_ratios(), graph.throughput(), graph.shard_sizes()
+    out = []
+    for i, dev in enumerate(graph.devices()):
+        idx = getattr(dev, "index", None)
+        out.append(GpuMetrics(i if idx is None else int(idx), float(tp[i]) if i < len(tp) else 0.0, float(ratios[i]) if i < len(ratios) else 0.0,
+                              {"shard_size": float(shards[i])} if i < len(shards) else {}))
+    return out
+
+
 def _metric_pairs(metrics) -> Tuple[List[Tuple[str, float]], List[GpuMetrics]]:
-    """Accepts a list of (name, value), a dict, or a DDP `EpochMetrics`."""
+    """Normalise the accepted forms (see `Metrics`) to (pairs, per-GPU rows)."""
+    if isinstance(metrics, tuple) and len(metrics) == 2 and hasattr(metrics[0], "latest_metrics"):
+        pairs, gm = _metric_pairs(metrics[0])
+        extra, _ = _metric_pairs(metrics[1])
+        return pairs + extra, gm
+    if hasattr(metrics, "latest_metrics"):
+        return [(k, float(v)) for k, v in metrics.latest_metrics()], _graph_gpu_metrics(metrics)
+    if hasattr(metrics, "into_metrics"):
+        gm = metrics.gpu_metrics() if hasattr(metrics, "gpu_metrics") else []
+        return [(k, float(v)) for k, v in metrics.into_metrics()], list(gm)
     if hasattr(metrics, "scalars") and hasattr(metrics, "avg_loss"):
         pairs = [("loss", float(metrics.avg_loss))] + [(k, float(v)) for k, v in sorted(metrics.scalars.items()) if k != "loss"]
         gm = [GpuMetrics(dev, tp, sh, dict(sc)) for dev, tp, sh, sc in

@@ -22,6 +22,67 @@ EVENT_KINDS = ("EpochStart", "EpochEnd", "SyncStart", "SyncEnd", "CpuAvgStart", 
                "Custom")
 
 
+class EventKind:
+    """One of the event variants, with its fields: `EventKind.SyncEnd(duration_ms=3.1)`,
+    `EventKind.AnchorChanged(8, 12)`, `EventKind.Custom("eval")` (flodl/src/monitor/timeline.rs:77-98).
+    `Timeline.event` takes one of these, or the kind's name and the fields as keywords."""
+
+    def __init__(self, kind: str, **fields):
+        if kind not in EVENT_KINDS:
+            raise ValueError(f"unknown timeline event kind {kind!r}")
+        self.kind, self.fields = kind, fields
+
+    def __repr__(self) -> str:
+        return f"EventKind.{self.kind}({', '.join(f'{k}={v!r}' for k, v in self.fields.items())})"
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, EventKind) and (self.kind, self.fields) == (other.kind, other.fields)
+
+    @classmethod
+    def EpochStart(cls, epoch: int): return cls("EpochStart", epoch=int(epoch))
+    @classmethod
+    def EpochEnd(cls, epoch: int, loss: float): return cls("EpochEnd", epoch=int(epoch), loss=float(loss))
+    @classmethod
+    def SyncStart(cls): return cls("SyncStart")
+    @classmethod
+    def SyncEnd(cls, duration_ms: float): return cls("SyncEnd", duration_ms=float(duration_ms))
+    @classmethod
+    def CpuAvgStart(cls): return cls("CpuAvgStart")
+    @classmethod
+    def CpuAvgEnd(cls, duration_ms: float): return cls("CpuAvgEnd", duration_ms=float(duration_ms))
+    @classmethod
+    def AnchorChanged(cls, from_: int, to: int): return cls("AnchorChanged", **{"from": int(from_), "to": int(to)})
+    @classmethod
+    def Throttle(cls, rank: int): return cls("Throttle", rank=int(rank))
+    @classmethod
+    def Idle(cls, device: int, duration_ms: float): return cls("Idle", device=int(device), duration_ms=float(duration_ms))
+    @classmethod
+    def Custom(cls, label: str): return cls("Custom", label=str(label))
+
+
+@dataclass
+class GpuTimelineSample:
+    """One GPU inside a `TimelineSample` (timeline.rs:36-49); `TimelineSample.gpu_samples()` gives these."""
+    device: int
+    compute_util: Optional[float]
+    vram_used_bytes: Optional[int]
+    vram_allocated_bytes: Optional[int]
+    vram_total_bytes: Optional[int] = None
+    sm_mhz: Optional[int] = None
+    power_w: Optional[float] = None
+
+
+@dataclass
+class TimelineBroadcast:
+    """What a subscriber's queue receives every broadcast interval: the samples and events since the last one,
+    as dicts ready for JSON (timeline.rs:125-132). Indexable by "samples" / "events" as well."""
+    samples: List[dict]
+    events: List[dict]
+
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+
 @dataclass
 class TimelineEvent:
     t_ms: int
@@ -41,6 +102,10 @@ class TimelineSample:
 
     def to_dict(self) -> dict:
         return {"t_ms": self.t_ms, "cpu_percent": self.cpu_percent, "ram_used_bytes": self.ram_used_bytes, "gpus": self.gpus}
+
+    def gpu_samples(self) -> List[GpuTimelineSample]:
+        return [GpuTimelineSample(g.get("index"), g.get("util"), g.get("vram_used"), g.get("vram_allocated"), g.get("vram_total"),
+                                  g.get("sm_mhz"), g.get("power_w")) for g in self.gpus]
 
 
 @dataclass
@@ -121,7 +186,9 @@ class Timeline:
             self._samples.append(s)
 
     # ---- events -------------------------------------------------------------------------------
-    def event(self, kind: str, **fields) -> None:
+    def event(self, kind, **fields) -> None:
+        if isinstance(kind, EventKind):
+            kind, fields = kind.kind, {**kind.fields, **fields}
         ev = TimelineEvent(self.elapsed_ms(), kind, fields)
         with self._lock:
             self._events.append(ev)
@@ -144,7 +211,7 @@ class Timeline:
             subs = list(self._subs)
         if not (new_s or new_e):
             return
-        msg = {"samples": [s.to_dict() for s in new_s], "events": [e.to_dict() for e in new_e]}
+        msg = TimelineBroadcast([s.to_dict() for s in new_s], [e.to_dict() for e in new_e])
         for q in subs:
             q.put(msg)
 

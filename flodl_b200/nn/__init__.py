@@ -12,7 +12,7 @@ from .cuda_graph import CaptureMode, CudaGraph, MemPoolId, cuda_graph_capture, c
 from .init import (kaiming_normal, kaiming_uniform, normal, orthogonal, trunc_normal, uniform, uniform_bias,  # noqa: F401
                    xavier_normal, xavier_uniform)
 from .layers import (GRU, LSTM, AdaptiveAvgPool2d, AdaptiveMaxPool2d, AlphaDropout, AvgPool1d, AvgPool2d, BatchNorm,  # noqa: F401
-                     BatchNorm2d, Bilinear, Conv1d, Conv1dBuilder, Conv2d, Conv2dBuilder, Conv3d, Conv3dBuilder, ConvTranspose1d, ConvTranspose2d, ConvTranspose3d,
+                     BatchNorm2d, Bilinear, Conv1d, Conv1dBuilder, Conv2d, Conv2dBuilder, Conv3d, Conv3dBuilder, ConvTranspose1d, ConvTranspose1dBuilder, ConvTranspose2dBuilder, ConvTranspose3dBuilder, ConvTranspose2d, ConvTranspose3d,
                      Dropout, Dropout2d, Embedding, EmbeddingBag, Fold, GaussianBlur, GroupNorm, GRUCell, InstanceNorm,
                      LayerNorm, Linear, LSTMCell, MaxPool1d, MaxPool2d, MultiheadAttention, PixelShuffle, PixelUnshuffle,
                      ReflectionPad2d, RMSNorm, Unfold, Upsample, ZeroPad2d, gaussian_blur_2d)

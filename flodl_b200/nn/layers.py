@@ -85,6 +85,7 @@ class _ConvBuilder:
 
 
 Conv1dBuilder = Conv2dBuilder = Conv3dBuilder = _ConvBuilder
+ConvTranspose1dBuilder = ConvTranspose2dBuilder = ConvTranspose3dBuilder = _ConvBuilder
 
 
 class _ConvNd(Module):
@@ -155,28 +156,40 @@ class ConvTranspose3d(_ConvNd): ND, NAME, TRANSPOSED = 3, "conv_transpose3d", Tr
 
 
 # ---------------------------------------------------------------------------------------- pooling
-class MaxPool2d(Module):
+class _PoolKnobs:
+    """Builder-style setters shared by the pooling layers: `MaxPool2d.new(3).padding(1).ceil_mode(True)`,
+    `AvgPool2d.with_stride(3, 2)` (flodl/src/nn/pooling.rs:45-90, 138-180)."""
+
+    @classmethod
+    def with_stride(cls, kernel_size, stride): return cls(kernel_size, stride)
+    def padding(self, p): self.p = p; return self
+    def dilation(self, d): self.d = d; return self
+    def ceil_mode(self, on: bool): self.c = bool(on); return self
+    def count_include_pad(self, on: bool): self.i = bool(on); return self
+
+
+class MaxPool2d(_PoolKnobs, Module):
     def __init__(self, kernel_size, stride=None, padding=0, dilation=1, ceil_mode=False):
         self.k, self.s, self.p, self.d, self.c = kernel_size, stride or kernel_size, padding, dilation, ceil_mode
     def name(self): return "maxpool2d"
     def forward(self, x): return A.max_pool2d(x, self.k, self.s, self.p, self.d, self.c)
 
 
-class AvgPool2d(Module):
+class AvgPool2d(_PoolKnobs, Module):
     def __init__(self, kernel_size, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
         self.k, self.s, self.p, self.c, self.i = kernel_size, stride or kernel_size, padding, ceil_mode, count_include_pad
     def name(self): return "avgpool2d"
     def forward(self, x): return A.avg_pool2d(x, self.k, self.s, self.p, self.c, self.i)
 
 
-class MaxPool1d(Module):
+class MaxPool1d(_PoolKnobs, Module):
     def __init__(self, kernel_size, stride=None, padding=0, dilation=1, ceil_mode=False):
         self.k, self.s, self.p, self.d, self.c = kernel_size, stride or kernel_size, padding, dilation, ceil_mode
     def name(self): return "maxpool1d"
     def forward(self, x): return A.max_pool1d(x, self.k, self.s, self.p, self.d, self.c)
 
 
-class AvgPool1d(Module):
+class AvgPool1d(_PoolKnobs, Module):
     def __init__(self, kernel_size, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
         self.k, self.s, self.p, self.c, self.i = kernel_size, stride or kernel_size, padding, ceil_mode, count_include_pad
     def name(self): return "avgpool1d"
@@ -208,33 +221,76 @@ class PixelUnshuffle(Module):
 
 
 class Upsample(Module):
+    """Resize the spatial dimensions. `Upsample(scale_factor=2)` / `Upsample(size=(H, W), mode="bilinear")` in
+    the PyTorch spelling, or the reference's `Upsample.new([H, W], mode)` with mode 0 = nearest, 1 = bilinear,
+    2 = bicubic, 3 = trilinear, then `.align_corners(True)` (flodl/src/nn/pooling.rs:549-580)."""
+    MODES = ("nearest", "bilinear", "bicubic", "trilinear")
+
     def __init__(self, scale_factor=None, size=None, mode="nearest", align_corners=None):
-        self.sf, self.size, self.mode, self.ac = scale_factor, size, mode, align_corners
+        self.sf, self.size, self.ac = scale_factor, size, align_corners
+        self.mode = self.MODES[mode] if isinstance(mode, int) else mode
+
+    @classmethod
+    def new(cls, output_size, mode=0):
+        return cls(size=tuple(output_size), mode=mode)
+
+    def align_corners(self, on: bool):
+        self.ac = bool(on)
+        return self
+
     def name(self): return "upsample"
+
     def forward(self, x):
-        return W(F.interpolate(x.t, size=self.size, scale_factor=self.sf, mode=self.mode, align_corners=self.ac))
+        ac = self.ac if self.mode != "nearest" else None
+        return W(F.interpolate(x.t, size=self.size, scale_factor=self.sf, mode=self.mode, align_corners=ac))
 
 
-class Unfold(Module):
+class _FoldKnobs:
+    def dilation(self, d): self._set(dilation=d); return self
+    def padding(self, p): self._set(padding=p); return self
+    def stride(self, s): self._set(stride=s); return self
+
+
+class Unfold(_FoldKnobs, Module):
+    """im2col: `Unfold(k, dilation, padding, stride)`, or `Unfold.new(3).padding([1, 1]).stride([2, 2])`,
+    `Unfold.with_kernel([3, 5])` (flodl/src/nn/pooling.rs:634-660)."""
+
     def __init__(self, kernel_size, dilation=1, padding=0, stride=1): self.a = (kernel_size, dilation, padding, stride)
+    @classmethod
+    def with_kernel(cls, kernel_size): return cls(tuple(kernel_size))
+    def _set(self, **kw):
+        k, d, p, s = self.a
+        self.a = (k, kw.get("dilation", d), kw.get("padding", p), kw.get("stride", s))
     def name(self): return "unfold"
     def forward(self, x): return A.im2col(x, *self.a)
 
 
-class Fold(Module):
+class Fold(_FoldKnobs, Module):
+    """col2im, the inverse of `Unfold` (flodl/src/nn/pooling.rs:712-740)."""
+
     def __init__(self, output_size, kernel_size, dilation=1, padding=0, stride=1): self.a = (output_size, kernel_size, dilation, padding, stride)
+    @classmethod
+    def with_kernel(cls, output_size, kernel_size): return cls(tuple(output_size), tuple(kernel_size))
+    def _set(self, **kw):
+        o, k, d, p, s = self.a
+        self.a = (o, k, kw.get("dilation", d), kw.get("padding", p), kw.get("stride", s))
     def name(self): return "fold"
     def forward(self, x): return A.col2im(x, *self.a)
 
 
 class ZeroPad2d(Module):
+    """Zero padding of `[B, C, H, W]`: one amount for all sides, or `asymmetric(left, right, top, bottom)`."""
     def __init__(self, padding): self.p = _tuple(padding, 4)
+    @classmethod
+    def asymmetric(cls, left, right, top, bottom): return cls((left, right, top, bottom))
     def name(self): return "zero_pad2d"
     def forward(self, x): return W(F.pad(x.t, self.p))
 
 
 class ReflectionPad2d(Module):
     def __init__(self, padding): self.p = _tuple(padding, 4)
+    @classmethod
+    def asymmetric(cls, left, right, top, bottom): return cls((left, right, top, bottom))
     def name(self): return "reflection_pad2d"
     def forward(self, x): return W(F.pad(x.t, self.p, mode="reflect"))
 
@@ -579,6 +635,7 @@ class Bilinear(Module):
     def name(self): return "bilinear"
     def own_parameters(self): return [self.weight] + ([self.bias] if self.bias is not None else [])
     def forward_pair(self, a, b): return A.bilinear(a, b, self.weight.variable, None if self.bias is None else self.bias.variable)
+    forward_bilinear = forward_pair                                   # the reference's name (bilinear.rs:77)
     def forward(self, x): return self.forward_pair(x, x)
 
 

@@ -31,6 +31,10 @@ class Parameter:
             self.variable = Variable(data, requires_grad=True)
         self.name = name
 
+    @classmethod
+    def new(cls, data, name: str) -> "Parameter":
+        return cls(data, name)
+
     @property
     def t(self) -> torch.Tensor:
         return self.variable.t
@@ -75,6 +79,10 @@ class Buffer:
         self._t = tensor.detach()
         self.name = name
 
+    @classmethod
+    def new(cls, tensor: torch.Tensor, name: str) -> "Buffer":
+        return cls(tensor, name)
+
     def get(self) -> torch.Tensor:
         return self._t
 
@@ -108,6 +116,17 @@ class Module:
     """Base class of every layer, activation, container and `Graph`."""
 
     training: bool = True
+
+    # ---- the reference's constructor spellings: `X::new(args)` and `X::on_device(args, device)` ------
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
+    @classmethod
+    def on_device(cls, *args, **kw):
+        """Like `new`, with the device as the last argument (classes whose constructor takes `device=`)."""
+        *rest, device = args
+        return cls(*rest, device=device, **kw)
 
     # ---- to be provided by subclasses -----------------------------------------------------------
     def forward(self, input: Variable) -> Variable:  # pragma: no cover - abstract

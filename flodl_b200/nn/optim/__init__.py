@@ -76,6 +76,10 @@ def read_tensor_state(r, device) -> Optional[torch.Tensor]:
 
 
 class Optimizer(Stateful):
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
     def __init__(self, params: Sequence, lr: float):
         self.params: List[torch.Tensor] = [_pt(p) for p in params]
         self._lr = float(lr)

@@ -6,6 +6,10 @@ from typing import Sequence
 
 
 class Scheduler:
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
     def lr(self, step: int) -> float:  # pragma: no cover - interface
         raise NotImplementedError
 
@@ -36,6 +40,10 @@ class WarmupScheduler(Scheduler):
 
 class PlateauScheduler:
     """Lower-is-better metric; after `patience` non-improving observations lr *= factor (>= min_lr)."""
+    @classmethod
+    def new(cls, base_lr: float, patience: int, factor: float, min_lr: float) -> "PlateauScheduler":
+        return cls(base_lr, patience, factor, min_lr)
+
     def __init__(self, base_lr: float, patience: int, factor: float, min_lr: float):
         self.patience, self.factor, self.min_lr = patience, factor, min_lr
         self.current_lr, self.best, self.wait = base_lr, math.inf, 0

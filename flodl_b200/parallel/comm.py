@@ -103,7 +103,33 @@ class CudaStream:
     def guard(self): return torch.cuda.stream(self.s)
 
 
-StreamGuard = lambda stream: stream.guard()  # noqa: E731  (`StreamGuard::new(stream)`)
+class StreamGuard:
+    """Makes `stream` the current stream of its device until the guard is closed: `with StreamGuard(s): ...`,
+    or `g = StreamGuard.new(s)` ... `g.close()` (flodl/src/distributed/cuda_stream.rs:120-150)."""
+
+    def __init__(self, stream: CudaStream, enter: bool = False):
+        self._ctx = stream.guard()
+        self._open = False
+        if enter:
+            self.__enter__()
+
+    @classmethod
+    def new(cls, stream: CudaStream) -> "StreamGuard":
+        return cls(stream, enter=True)
+
+    def __enter__(self):
+        self._ctx.__enter__()
+        self._open = True
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
+
+    def close(self) -> None:
+        if self._open:
+            self._open = False
+            self._ctx.__exit__(None, None, None)
 
 
 class CudaEventFlags(enum.IntEnum):
@@ -497,11 +523,16 @@ class NcclAbortHandle:
 
     def __init__(self, buffers: Optional[List["SymmetricBuffer"]] = None):
         self.buffers = list(buffers or [])
+        self._aborted = False
+
+    def is_aborted(self) -> bool:
+        return self._aborted
 
     def register(self, buf: "SymmetricBuffer") -> None:
         self.buffers.append(buf)
 
     def abort(self) -> None:
+        self._aborted = True
         for b in self.buffers:
             b.abort()
         if dist.is_initialized():

@@ -420,6 +420,16 @@ class DistributedState:
             return (self.step_count - self.calibration_steps) % self.rebalance_interval == 0
         return False
 
+    def update_balance(self) -> bool:
+        """Count the step, read the last forward's timing into the throughput estimate and, when a
+        rebalance is due, recompute the chunk ratios; true when they changed (ddp.rs:227-270).
+        `Graph.step()` does the same through `after_step()`."""
+        self.step_count += 1
+        self._read_timing()
+        if self.world_size <= 1 or self.el_che is not None or not self.update_balance_due():
+            return False
+        return self.rebalance()
+
     def rebalance(self) -> bool:
         """Exchange the per-rank throughput estimates and recompute the chunk ratios."""
         got = self._all_gather_floats([self._local_ema])

@@ -8,6 +8,10 @@ from typing import List, Optional, Tuple
 
 
 class ChunkPool:
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
     def __init__(self, epoch: int, total_samples: int, world_size: int):
         self.epoch = epoch
         self.total_samples = int(total_samples)

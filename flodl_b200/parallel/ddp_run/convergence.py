@@ -62,6 +62,10 @@ class ConvergenceGuard:
     """Keeps the last five divergences. `Sync` never acts; `Cadence`/`Async` suppress anchor growth
     when the last three values rise strictly and the newest exceeds `threshold`."""
 
+    @classmethod
+    def new(cls, *args, **kw):
+        return cls(*args, **kw)
+
     def __init__(self, policy: ApplyPolicy, enabled: bool = True, threshold: float = 0.05):
         self.policy, self.enabled, self.threshold = policy, bool(enabled), float(threshold)
         self._history: deque = deque(maxlen=5)

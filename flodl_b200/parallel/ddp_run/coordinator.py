@@ -134,6 +134,45 @@ def divergence_of(snapshots: Sequence[ParamSnapshot], averaged: AveragedParams) 
     return DivergenceReport(deltas, pre, post)
 
 
+class CoordinatorBuilder:
+    """Collects the optional settings of a `Coordinator` by name; `build()` makes it."""
+
+    def __init__(self, transport, policy, backend, world_size, total_samples, el_che):
+        self._args = (transport, policy, backend, world_size, total_samples, el_che)
+        self._kw: Dict[str, object] = {}
+
+    def _set(self, **kw):
+        self._kw.update(kw)
+        return self
+
+    def progressive(self, enabled: bool): return self._set(progressive=bool(enabled))
+    def batch_size(self, bs: int): return self._set(batch_size=int(bs))
+    def timeline(self, tl): return self._set(timeline=tl)
+    def divergence_threshold(self, t: float): return self._set(divergence_threshold=float(t))
+    def no_divergence_guard(self): return self._set(divergence_guard=False)
+    def checkpoint_every(self, n: int): return self._set(checkpoint_every=int(n))
+    def snapshot_timeout_secs(self, secs: float): return self._set(snapshot_timeout_secs=float(secs))
+    def epoch_metrics_tx(self, sink): return self._set(epoch_metrics_sink=sink)
+    def metrics_fn(self, f): return self._set(metrics_fn=f)
+    def device_indices(self, idx): return self._set(device_indices=list(idx))
+    def num_epochs(self, n: int): return self._set(num_epochs=int(n))
+    def partition_ratios(self, ratios): return self._set(partition_ratios=None if ratios is None else list(ratios))
+    def max_overshoot(self, n: int): return self._set(max_overshoot=int(n))
+    def fixed_cadence(self, k: Optional[int]): return self._set(fixed_cadence=k)
+    def overshoot_ceiling(self, n: int): return self._set(overshoot_ceiling=int(n))
+
+    def overhead_target(self, target: float):
+        self._args[5].with_overhead_target(float(target))          # the cadence controller owns these two
+        return self
+
+    def max_anchor(self, m: int):
+        self._args[5].with_max_anchor(int(m))
+        return self
+
+    def build(self) -> "Coordinator":
+        return Coordinator(*self._args, **self._kw)
+
+
 class Coordinator:
     """State machine driven by `tick()` (or `run()`), fed by the workers' mailboxes."""
 
@@ -201,6 +240,31 @@ class Coordinator:
         self.stop = threading.Event()
         self.error: Optional[BaseException] = None
         self.failed_ranks: List[int] = []
+
+    @staticmethod
+    def builder(transport, policy: ApplyPolicy, backend: AverageBackend, world_size: int, total_samples: int, el_che: ElChe) -> "CoordinatorBuilder":
+        """Fluent construction: `Coordinator.builder(...).batch_size(32).num_epochs(3).progressive(True).build()`
+        (coordinator/mod.rs:178-300, 389-425)."""
+        return CoordinatorBuilder(transport, policy, backend, world_size, total_samples, el_che)
+
+    def drain_timing_blocking(self, timeout_s: float) -> bool:
+        """Wait up to `timeout_s` for a timing message, then take everything else that is queued.
+        False once the run is being wound down (a rank failed or `stop` is set), true otherwise
+        (coordinator/mod.rs:904-915)."""
+        deadline = time.monotonic() + max(0.0, float(timeout_s))
+        while self.drain_timing() == 0 and time.monotonic() < deadline and not self.stop.is_set():
+            time.sleep(0.0005)
+        return not self.stop.is_set()
+
+    def debug_state_dump(self, tick: int) -> None:
+        """One line of coordinator state at debug verbosity (`-vv`)."""
+        if not log.enabled(log.Verbosity.Debug):
+            return
+        pools = ", ".join(f"e{e}(cur={p.cursor}/{p.total_samples} [" + " ".join(f"{r}:{p.completed[r]}/{p.dispatched[r]}" for r in range(self.world_size)) + "])"
+                          for e, p in self.chunk_pools.items())
+        log.debug(f"  ddp-state: tick={tick} steps={self.steps_since_avg} wall={[round(w, 1) for w in self.wall_ms_accum]} "
+                  f"throttled={self.throttled} nccl_ack={self.nccl_ack} rank_epoch={self.rank_epoch} active={self.active_count} "
+                  f"last_agg={self.last_aggregated_epoch} avg#={self.avg_count} pools=[{pools}]")
 
     # ---- small accessors ------------------------------------------------------------------------
     def is_calibrated(self) -> bool: return self.calibrated

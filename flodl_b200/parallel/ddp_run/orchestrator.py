@@ -54,6 +54,23 @@ class DdpHandle:
         self._broadcast_final = broadcast_final
         self._final: Optional[TrainedState] = None
 
+    # ---- constructors kept from the reference (orchestrator.rs:90-215); `Trainer.builder` is the entry point
+    @staticmethod
+    def builder(model_factory: Callable, optim_factory: Callable, train_fn: Callable) -> "DdpBuilder":
+        return DdpBuilder(model_factory, optim_factory, train_fn)
+
+    @staticmethod
+    def auto(model_factory, optim_factory, train_fn, dataset, batch_size: int, num_epochs: int,
+             policy: ApplyPolicy = ApplyPolicy.Cadence, backend: AverageBackend = AverageBackend.Nccl) -> "DdpHandle":
+        """Start a run with the default configuration (deprecated in the reference in favour of the builder)."""
+        return DdpHandle.auto_with(model_factory, optim_factory, train_fn, dataset, batch_size, num_epochs, policy, backend, DdpRunConfig())
+
+    @staticmethod
+    def auto_with(model_factory, optim_factory, train_fn, dataset, batch_size: int, num_epochs: int,
+                  policy: ApplyPolicy, backend: AverageBackend, config: DdpRunConfig) -> "DdpHandle":
+        return (DdpBuilder(model_factory, optim_factory, train_fn).dataset(dataset).batch_size(batch_size).num_epochs(num_epochs)
+                .policy(policy).backend(backend).config(config).run())
+
     def world_size(self) -> int: return len(self._devices)
     def devices(self) -> List: return list(self._devices)
     def architecture_svg(self) -> Optional[str]: return self._svg

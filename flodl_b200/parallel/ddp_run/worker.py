@@ -16,7 +16,7 @@ event that follows them has completed. The reference reads `loss.item()` every b
 from __future__ import annotations
 
 import time
-from collections import deque
+from collections import deque, namedtuple
 from typing import Callable, List, Optional, Sequence
 
 import torch
@@ -39,6 +39,10 @@ class _SchedAdapter:
 
     def lr(self, _step: int) -> float:
         return self.sched.lr(self.w.global_step + self.w.steps_since_avg)
+
+
+WorkerEndpoints = namedtuple("WorkerEndpoints", "timing_tx metrics_tx param_tx final_param_tx control_rx")
+WorkerChannels = namedtuple("WorkerChannels", "timing_rx metrics_rx param_rx final_param_rx control_tx")
 
 
 class GpuWorker:
@@ -89,6 +93,21 @@ class GpuWorker:
         self._loss_sum = 0.0
         self._loss_n = 0
         self._shutdown_seen = False
+
+    @classmethod
+    def new(cls, config: WorkerConfig, model_factory: Callable, optim_factory: Callable, dataset, transport, **kw) -> "GpuWorker":
+        return cls(config, model_factory, optim_factory, dataset, transport, **kw)
+
+    @staticmethod
+    def channels(transport, rank: int):
+        """The five mailboxes of worker `rank`, as (worker side, coordinator side): the worker sends on
+        `timing, metrics, params, final_params` and receives on `control`; the coordinator holds the
+        other ends. Both sides are views of the same named boxes of `transport`, which is how a worker
+        built later in its own thread (or process) finds them (worker.rs:157-173)."""
+        boxes = {k: transport.box(f"{k}{rank}") for k in ("tim", "met", "par", "fin", "ctl")}
+        worker_side = WorkerEndpoints(boxes["tim"], boxes["met"], boxes["par"], boxes["fin"], boxes["ctl"])
+        coord_side = WorkerChannels(boxes["tim"], boxes["met"], boxes["par"], boxes["fin"], boxes["ctl"])
+        return worker_side, coord_side
 
     # ---- accessors (worker.rs:371-436) ----------------------------------------------------------
     def rank(self) -> int: return self.rank_
@@ -316,6 +335,14 @@ class GpuWorker:
 
     def report_exiting(self) -> None:
         self.tim.send(TimingExiting(self.rank_))
+
+    def report_timing(self, batch_ms: float, param_norm: Optional[float], batch_loss: float, sync_divergence: Optional[float] = None) -> None:
+        """Send one batch's timing report to the coordinator now (worker.rs:776-791)."""
+        self.tim.send(TimingBatch(self.rank_, float(batch_ms), self.local_step_, param_norm, float(batch_loss), sync_divergence))
+
+    def abort_nccl(self) -> None:
+        """Reference name of `abort_collectives` (worker.rs:820-830)."""
+        self.abort_collectives()
 
     def abort_collectives(self) -> None:
         """Make any device-side wait of this rank's averaging kernels return at once."""

@@ -22,6 +22,14 @@ Tensor = torch.Tensor
 class TensorError(RuntimeError):
     """Error type of the framework (flodl/src/tensor/mod.rs `TensorError`)."""
 
+    @classmethod
+    def new(cls, msg: str) -> "TensorError":
+        return cls(msg)
+
+    def is_cuda_oom(self) -> bool:
+        """Whether the message reports that the device ran out of memory."""
+        return "out of memory" in str(self)
+
 
 class DType(Enum):
     """Element types with the C-ABI tags of flodl-sys/shim.h:920-925."""
@@ -331,6 +339,9 @@ class DeviceInfo:
         p = torch.cuda.get_device_properties(index)
         self.index, self.name, self.total_memory = index, p.name, int(p.total_memory)
         self.sm_major, self.sm_minor, self.multi_processor_count = p.major, p.minor, p.multi_processor_count
+
+    def sm_version(self) -> str:
+        return f"sm_{self.sm_major}{self.sm_minor}"
 
     def __repr__(self) -> str:
         return f"DeviceInfo({self.index}, {self.name!r}, {self.total_memory >> 30} GiB, sm_{self.sm_major}{self.sm_minor}, {self.multi_processor_count} SMs)"

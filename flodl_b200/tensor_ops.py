@@ -203,6 +203,10 @@ def install_variable_methods(cls) -> None:
 
 
 def surface() -> Dict[str, Callable]:
-    """Every public op of this module by name (used by the API reference and the tests)."""
-    return {k: v for k, v in globals().items() if callable(v) and not k.startswith("_") and getattr(v, "__module__", None) == __name__
-            and k not in ("install_variable_methods", "surface")}
+    """Every public op by name: this module's and `tensor_nn_ops`' (used by the API reference and the tests)."""
+    from . import tensor_nn_ops as nn_ops
+    out = {k: v for k, v in vars(nn_ops).items() if callable(v) and not k.startswith("_") and getattr(v, "__module__", None) == nn_ops.__name__
+           and not isinstance(v, type)}
+    out.update({k: v for k, v in globals().items() if callable(v) and not k.startswith("_") and getattr(v, "__module__", None) == __name__
+                and k not in ("install_variable_methods", "surface")})
+    return out

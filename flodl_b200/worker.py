@@ -44,6 +44,10 @@ class CpuWorker:
     def pending(self) -> int:
         return self._q.unfinished_tasks
 
+    def is_idle(self) -> bool:
+        """Nothing queued or running: submit the next checkpoint only then (worker.rs:57-63)."""
+        return self._q.unfinished_tasks == 0
+
     def errors(self) -> List[BaseException]:
         return list(self._errors)
 

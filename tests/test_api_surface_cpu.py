@@ -4,6 +4,7 @@ import os
 
 import pytest
 import torch
+import torch.nn.functional as F
 
 import flodl_b200
 from flodl_b200 import nn
@@ -185,3 +186,159 @@ def test_snapshot_cpu_method_and_has_graph(tmp_path):
     class Head(flodl_b200.HasGraph):
         def graph(self): return g
     assert _graph_of(Head()) is g and _graph_of(g) is g
+
+
+# ---- constructor spellings and fluent knobs of the reference's layers -------------------------------------
+def test_new_and_on_device_spellings_exist_on_every_module_class():
+    assert isinstance(nn.ReLU.new(), nn.ReLU) and isinstance(nn.LeakyReLU.new(0.2), nn.LeakyReLU)
+    assert nn.Softmax.new(-1).forward(Variable.wrap(torch.randn(2, 3))).t.sum().item() == pytest.approx(2.0, abs=1e-5)
+    cell = nn.GRUCell.on_device(3, 5, "cpu")
+    assert cell.parameters()[0].t.device.type == "cpu"
+    assert isinstance(nn.StepDecay.new(0.1, 10, 0.5), nn.StepDecay) and nn.PlateauScheduler.new(0.1, 2, 0.5, 1e-4).current_lr == 0.1
+    assert isinstance(nn.RAdam.new([_p(2)], 1e-3), nn.RAdam)
+    g = flodl_b200.NoGradGuard.new()
+    assert not torch.is_grad_enabled()
+    g.release()
+    assert torch.is_grad_enabled()
+
+
+def test_pooling_knobs():
+    x = Variable.wrap(torch.randn(1, 2, 9, 9))
+    a = nn.MaxPool2d.new(3).padding(1).ceil_mode(True).forward(x).t
+    assert torch.equal(a, F.max_pool2d(x.t, 3, 3, 1, 1, True))
+    b = nn.AvgPool2d.with_stride(3, 2).padding(1).count_include_pad(False).forward(x).t
+    torch.testing.assert_close(b, F.avg_pool2d(x.t, 3, 2, 1, False, False))
+    x1 = Variable.wrap(torch.randn(1, 2, 10))
+    assert torch.equal(nn.MaxPool1d.with_stride(3, 1).padding(1).forward(x1).t, F.max_pool1d(x1.t, 3, 1, 1))
+    torch.testing.assert_close(nn.AvgPool1d.new(2).forward(x1).t, F.avg_pool1d(x1.t, 2))
+
+
+def test_upsample_fold_unfold_and_padding_constructors():
+    x = Variable.wrap(torch.randn(1, 2, 4, 4))
+    up = nn.Upsample.new([8, 8], 1).align_corners(True).forward(x).t
+    torch.testing.assert_close(up, F.interpolate(x.t, size=(8, 8), mode="bilinear", align_corners=True))
+    assert nn.Upsample.new([8, 8], 0).align_corners(False).forward(x).t.shape == (1, 2, 8, 8)
+    cols = nn.Unfold.new(3).padding([1, 1]).stride([1, 1]).forward(x).t
+    assert cols.shape == (1, 18, 16)
+    back = nn.Fold.with_kernel([4, 4], [3, 3]).padding([1, 1]).forward(Variable.wrap(cols)).t
+    assert back.shape == (1, 2, 4, 4)
+    assert nn.Unfold.with_kernel([2, 4]).forward(x).t.shape == (1, 16, 3)
+    assert nn.ZeroPad2d.asymmetric(1, 2, 3, 4).forward(x).t.shape == (1, 2, 11, 7)
+    assert nn.ReflectionPad2d.asymmetric(1, 0, 2, 0).forward(x).t.shape == (1, 2, 6, 5)
+    bl = nn.Bilinear(3, 4, 5)
+    assert bl.forward_bilinear(Variable.wrap(torch.randn(2, 3)), Variable.wrap(torch.randn(2, 4))).t.shape == (2, 5)
+
+
+def test_tensor_error_and_device_info_helpers():
+    e = flodl_b200.TensorError.new("CUDA out of memory. Tried to allocate 2 GiB")
+    assert e.is_cuda_oom() and not flodl_b200.TensorError("shape mismatch").is_cuda_oom()
+    assert flodl_b200.NcclAbortHandle().is_aborted() is False
+
+
+# ---- timeline types ------------------------------------------------------------------------------------
+def test_event_kind_variants_and_broadcast_type():
+    from flodl_b200.monitor import EventKind, GpuTimelineSample, Timeline, TimelineBroadcast
+    tl = Timeline.new(1000)
+    tl.event(EventKind.SyncStart())
+    tl.event(EventKind.SyncEnd(2.5))
+    tl.event(EventKind.AnchorChanged(4, 8))
+    tl.event(EventKind.Custom("eval"))
+    tl.event("Throttle", rank=1)
+    kinds = [e.kind for e in tl.events()]
+    assert kinds == ["SyncStart", "SyncEnd", "AnchorChanged", "Custom", "Throttle"]
+    assert tl.events()[2].fields == {"from": 4, "to": 8} and tl.events()[1].fields["duration_ms"] == 2.5
+    assert EventKind.Throttle(1) == EventKind("Throttle", rank=1) and "Throttle" in repr(EventKind.Throttle(1))
+    with pytest.raises(ValueError):
+        EventKind("Nope")
+    sub = tl.subscribe()
+    tl.sample_once()
+    tl._broadcast()
+    msg = sub.get(timeout=1)
+    assert isinstance(msg, TimelineBroadcast) and len(msg.events) == 5 and msg["samples"] == msg.samples
+    assert tl.summary().sync_count == 1
+    gs = tl.drain()[0][0].gpu_samples()
+    assert all(isinstance(g, GpuTimelineSample) for g in gs)
+
+
+# ---- coordinator / worker construction helpers ----------------------------------------------------------
+def test_coordinator_builder_and_blocking_drain():
+    from flodl_b200.parallel.ddp_run.channel import LocalTransport
+    from flodl_b200.parallel.ddp_run.coordinator import Coordinator, CoordinatorBuilder
+    from flodl_b200.parallel.ddp_run.messages import ApplyPolicy, AverageBackend, TimingBatch
+    from flodl_b200.parallel.ddp_run.worker import GpuWorker
+    tr = LocalTransport()
+    el = flodl_b200.ElChe.new(2, 10)
+    b = Coordinator.builder(tr, ApplyPolicy.Cadence, AverageBackend.Cpu, 2, 640, el)
+    assert isinstance(b, CoordinatorBuilder)
+    c = (b.batch_size(32).num_epochs(3).progressive(False).divergence_threshold(0.1).no_divergence_guard().checkpoint_every(5)
+         .snapshot_timeout_secs(2).device_indices([0, 1]).partition_ratios([0.75, 0.25]).max_overshoot(3).overshoot_ceiling(9)
+         .overhead_target(0.2).max_anchor(50).build())
+    assert (c.batch_size, c.num_epochs, c.progressive, c.checkpoint_every, c.snapshot_timeout_secs) == (32, 3, False, 5, 2.0)
+    assert c.partition_ratios == [0.75, 0.25] and c.max_overshoot == 3 and c.overshoot_ceiling == 9
+    assert not c.convergence_guard.enabled and c.version == 0 and c.avg_count == 0 and c.abort_count == 0
+    worker_side, coord_side = GpuWorker.channels(tr, 1)
+    worker_side.timing_tx.send(TimingBatch(1, 12.5, 1, None, 0.7, None))
+    assert c.drain_timing_blocking(0.5) is True and c.last_batch_ms[1] == 12.5 and c.steps_since_avg[1] == 1
+    t0 = __import__("time").monotonic()
+    assert c.drain_timing_blocking(0.05) is True and __import__("time").monotonic() - t0 < 1.0      # nothing queued: times out
+    c.stop.set()
+    assert c.drain_timing_blocking(0.01) is False
+    coord_side.control_tx.send("x")
+    assert worker_side.control_rx.try_recv() == "x"
+    c.debug_state_dump(1)                                      # silent below debug verbosity
+
+
+def test_prefetch_worker_distributed_mode_serves_requests_in_order():
+    from flodl_b200.data import PrefetchWorker, TensorDataSet
+    ds = TensorDataSet(torch.arange(20.0).reshape(10, 2), torch.arange(10))
+    w = PrefetchWorker.new(ds, "cpu", 2)
+    w.start_distributed_epoch()
+    for idx in ([0, 1, 2], [7], [9, 8]):
+        w.load_batch(idx)
+    w.end_distributed_epoch()
+    got = []
+    while True:
+        b = w.next()
+        if b is None:
+            break
+        got.append(b[1].tolist())
+    assert got == [[0, 1, 2], [7], [9, 8]]
+    w.stop()
+    with pytest.raises(RuntimeError):
+        w.load_batch([1])
+    w.start_epoch(list(range(10)), 5)                          # the ordinary mode still works afterwards
+    assert w.next()[1].tolist() == [0, 1, 2, 3, 4]
+    w.stop()
+
+
+def test_monitor_log_accepts_a_graph_and_a_graph_with_extras():
+    from flodl_b200.monitor import Metrics, Monitor
+    g = FlowBuilder.from_(nn.Linear(2, 1)).tag("out").build()
+    g.record_scalar("loss", 0.5)
+    g.record_scalar("loss", 0.3)
+    g.flush([])
+    m = Monitor.new(2)
+    line = m.log(0, 1.0, g)
+    assert "loss=" in line and m.epochs[0].metrics[0][0] == "loss" and abs(m.epochs[0].metrics[0][1] - 0.4) < 1e-9
+    m.log(1, 1.0, (g, [("lr", 0.01)]))
+    assert [k for k, _ in m.epochs[1].metrics] == ["loss", "lr"]
+
+    class Mine(Metrics):
+        def into_metrics(self): return [("acc", 0.9)]
+    m2 = Monitor.new(1)
+    m2.log(0, 0.5, Mine())
+    assert m2.epochs[0].metrics == [("acc", 0.9)] and m2.epochs[0].gpu_metrics == []
+
+
+def test_ddp_handle_auto_runs_a_small_job_on_cpu():
+    from flodl_b200.data import TensorDataSet
+    from flodl_b200.parallel.ddp_run import ApplyPolicy, AverageBackend
+    torch.manual_seed(0)
+    x = torch.randn(64, 4)
+    ds = TensorDataSet(x, x.sum(1, keepdim=True))
+    h = flodl_b200.DdpHandle.auto(lambda dev: nn.Linear(4, 1, True, dev), lambda ps: nn.SGD(ps, 0.05),
+                                  lambda m, batch: nn.mse_loss(m.forward(Variable.wrap(batch[0])), Variable.wrap(batch[1])),
+                                  ds, 16, 2, ApplyPolicy.Sync, AverageBackend.Cpu)
+    state = h.join()
+    assert h.world_size() == 1 and len(state.params) == 2 and not h.errors()
+    assert isinstance(flodl_b200.DdpHandle.builder(lambda d: None, lambda p: None, lambda m, b: None), flodl_b200.DdpBuilder)
