@@ -102,6 +102,31 @@ def resolve_files(repo_id: str, revision: str = "main") -> Tuple[str, str, Optio
     return cfg, st, tok
 
 
+def resolve_tokenizer(repo_id: str, revision: str = "main") -> Optional[str]:
+    """Path of the repo's `tokenizer.json` (on disk, else fetched when allowed), or None."""
+    for d in candidate_dirs(repo_id):
+        t = os.path.join(d, "tokenizer.json")
+        if os.path.exists(t):
+            return t
+    if os.path.isdir(repo_id) or offline():
+        return None
+    try:
+        return fetch_file(repo_id, "tokenizer.json", revision)
+    except TensorError:
+        return None
+
+
+def fetch_config_str(repo_id: str, revision: str = "main") -> str:
+    """The text of the repo's `config.json` alone (cheap: decides the family and head before any weights move)."""
+    for d in candidate_dirs(repo_id):
+        c = os.path.join(d, "config.json")
+        if os.path.exists(c):
+            return open(c).read()
+    if os.path.isdir(repo_id) or offline():
+        raise TensorError(f"config.json of {repo_id} not found; looked in: {candidate_dirs(repo_id)}")
+    return open(fetch_file(repo_id, "config.json", revision)).read()
+
+
 def _rename_for(model_type: str):
     prefix = {"distilbert": "distilbert.", "albert": "albert.", "deberta-v2": "deberta.", "bert": "bert.", "roberta": "roberta.",
               "xlm-roberta": "roberta."}[model_type]
@@ -135,10 +160,16 @@ def from_pretrained(repo_id: str, device=None, head: Optional[str] = None):
     return g
 
 
-def _head_from_pretrained(auto_cls, repo_id: str, device=None):
+def _head_from_pretrained(auto_cls, repo_id: str, device=None, family: Optional[str] = None):
+    """`auto_cls`: an `AutoModelFor*` class (the family comes from config.json) or a family's own head class
+    (`family` then names the `model_type` the repo must have)."""
     cfg_path, st_path, tok_path = resolve_files(repo_id)
     cfg = AutoConfig.from_json_str(open(cfg_path).read())
-    h = auto_cls.from_config(cfg, device)
+    if family is not None:
+        _check_family(cfg, family, auto_cls.__name__, repo_id)
+        h = _AUTO_BY_SUFFIX[_suffix_of(auto_cls)].from_config(cfg, device)
+    else:
+        h = auto_cls.from_config(cfg, device)
     _load(h.graph(), open(st_path, "rb").read(), cfg.model_type(), False)
     h.graph().set_training(False)
     if tok_path is not None:
@@ -154,3 +185,100 @@ def sequence_classification_from_pretrained(repo_id: str, device=None): return _
 def token_classification_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForTokenClassification, repo_id, device)
 def question_answering_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForQuestionAnswering, repo_id, device)
 def masked_lm_from_pretrained(repo_id: str, device=None): return _head_from_pretrained(AutoModelForMaskedLM, repo_id, device)
+
+
+# ---- `X.from_pretrained(repo)` on every family class and on the Auto classes (flodl-hf/src/hub/{mod,auto}.rs) ------
+class HubExportHead:
+    """Which head `AutoModel.from_pretrained_for_export_with_head` builds (hub/auto.rs `HubExportHead`)."""
+    Base, SeqCls, TokCls, Qa, Mlm = "base", "seqcls", "tokcls", "qa", "mlm"
+
+    @staticmethod
+    def parse(s: str) -> str:
+        if s not in ("base", "seqcls", "tokcls", "qa", "mlm"):
+            raise TensorError(f"unsupported head `{s}`; expected one of auto|base|seqcls|tokcls|qa|mlm")
+        return s
+
+
+_AUTO_BY_SUFFIX = {"ForSequenceClassification": AutoModelForSequenceClassification, "ForTokenClassification": AutoModelForTokenClassification,
+                   "ForQuestionAnswering": AutoModelForQuestionAnswering, "ForMaskedLM": AutoModelForMaskedLM}
+_HEAD_OF_SUFFIX = {"ForSequenceClassification": HubExportHead.SeqCls, "ForTokenClassification": HubExportHead.TokCls,
+                   "ForQuestionAnswering": HubExportHead.Qa, "ForMaskedLM": HubExportHead.Mlm}
+
+
+def _suffix_of(cls) -> str:
+    for suf in _AUTO_BY_SUFFIX:
+        if cls.__name__.endswith(suf):
+            return suf
+    return "Model"
+
+
+def _check_family(cfg: AutoConfig, family: str, cls_name: str, repo_id: str) -> None:
+    if cfg.model_type() != family:
+        raise TensorError(f"{cls_name}.from_pretrained({repo_id}): config.json says model_type {cfg.model_type()!r}, this class loads {family!r}; "
+                          f"use the matching family class or AutoModel")
+
+
+def _backbone_from_pretrained(repo_id: str, device=None, family: Optional[str] = None, keep_pooler: bool = True, cls_name: str = "AutoModel"):
+    cfg_path, st_path, _ = resolve_files(repo_id)
+    cfg = AutoConfig.from_json_str(open(cfg_path).read())
+    if family is not None:
+        _check_family(cfg, family, cls_name, repo_id)
+    weights = open(st_path, "rb").read()
+    g = build_for_export(cfg, keep_pooler and weights_have_pooler(weights), device, "base")
+    _load(g, weights, cfg.model_type(), True)
+    # the sidecar of a later save_checkpoint names the class that was built, not the repo's pretraining class
+    g.set_source_config(cfg.into_normalized_config_json(cfg.base_class_name()))
+    return g
+
+
+def classify_for_hub_export(arch: str) -> str:
+    """`architectures[0]` of a repo -> the head to rebuild for export; pretraining classes fall back to the backbone."""
+    for suf, kind in _HEAD_OF_SUFFIX.items():
+        if arch.endswith(suf):
+            return kind
+    return HubExportHead.Base
+
+
+def _export_graph(repo_id: str, head: Optional[str], device=None):
+    if head is None:
+        archs = AutoConfig.from_json_str(fetch_config_str(repo_id)).architectures() or []
+        head = classify_for_hub_export(archs[0]) if archs else HubExportHead.Base
+    if head == HubExportHead.Base:
+        return _backbone_from_pretrained(repo_id, device, None, True)
+    auto = {v: _AUTO_BY_SUFFIX[k] for k, v in _HEAD_OF_SUFFIX.items()}[head]
+    return _head_from_pretrained(auto, repo_id, device).into_graph()
+
+
+def _install_from_pretrained() -> None:
+    from .models import auto as _auto
+    from .tokenizer import HfTokenizer  # noqa: F401  (HfTokenizer.from_pretrained resolves through this module)
+
+    def on(cls, name, fn):
+        setattr(cls, name, classmethod(fn) if not isinstance(fn, staticmethod) else fn)
+
+    for model_type, (_cfg_cls, _base_name, mod) in _auto._FAMILIES.items():
+        prefix = _auto._PREFIX[model_type]
+        base = getattr(mod, prefix + "Model")
+        on(base, "from_pretrained_on_device", lambda cls, repo_id, device=None, _f=model_type: _backbone_from_pretrained(repo_id, device, _f, True, cls.__name__))
+        on(base, "from_pretrained", lambda cls, repo_id: cls.from_pretrained_on_device(repo_id, None))
+        for suf in _AUTO_BY_SUFFIX:
+            head = getattr(mod, prefix + suf, None)
+            if head is None:
+                continue
+            on(head, "from_pretrained_on_device", lambda cls, repo_id, device=None, _f=model_type: _head_from_pretrained(cls, repo_id, device, _f))
+            on(head, "from_pretrained", lambda cls, repo_id: cls.from_pretrained_on_device(repo_id, None))
+    for auto_head in _AUTO_BY_SUFFIX.values():
+        on(auto_head, "from_pretrained_on_device", lambda cls, repo_id, device=None: _head_from_pretrained(cls, repo_id, device))
+        on(auto_head, "from_pretrained", lambda cls, repo_id: cls.from_pretrained_on_device(repo_id, None))
+    A = _auto.AutoModel
+    # uniform `[batch, seq, hidden]` output over all families: pooler-bearing ones are built without it
+    A.from_pretrained_on_device = staticmethod(lambda repo_id, device=None: _backbone_from_pretrained(repo_id, device, None, False))
+    A.from_pretrained = staticmethod(lambda repo_id: A.from_pretrained_on_device(repo_id, None))
+    A.from_pretrained_for_export_on_device = staticmethod(lambda repo_id, device=None: _export_graph(repo_id, None, device))
+    A.from_pretrained_for_export = staticmethod(lambda repo_id: _export_graph(repo_id, None, None))
+    A.from_pretrained_for_export_with_head_on_device = staticmethod(lambda repo_id, head, device=None: _export_graph(repo_id, parse_head(head), device))
+    A.from_pretrained_for_export_with_head = staticmethod(lambda repo_id, head: _export_graph(repo_id, parse_head(head), None))
+    _auto.AutoConfig.from_pretrained = classmethod(lambda cls, repo_id: cls.from_json_str(fetch_config_str(repo_id)))
+
+
+_install_from_pretrained()

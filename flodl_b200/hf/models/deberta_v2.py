@@ -223,6 +223,56 @@ class DebertaV2TransformerLayer(Module):
                                training=self.training)
 
 
+class DebertaV2SelfOutput(Module):
+    """Post-attention stage on its own: `LN(dropout(dense(x)) + residual)`, HF's `DebertaV2SelfOutput`
+    (deberta_transformer_layer.rs:382-415). `DebertaV2TransformerLayer` runs the same math as one fused
+    residual + dropout + LayerNorm op; this class is the stage as a separate module (`forward_pair(x, residual)`)."""
+
+    def __init__(self, c: DebertaV2LayerConfig, device=None, in_features: Optional[int] = None):
+        self.dense = Linear(in_features or c.hidden_size, c.hidden_size, True, device)
+        self.layer_norm = LayerNorm(c.hidden_size, c.layer_norm_eps, device)
+        self.p, self.eps = c.hidden_dropout_prob, c.layer_norm_eps
+
+    @classmethod
+    def on_device(cls, config: DebertaV2LayerConfig, device=None): return cls(config, device)
+    def name(self): return "deberta_v2_self_output"
+    def own_parameters(self):
+        return prefix_params("dense", self.dense.own_parameters()) + prefix_params("LayerNorm", self.layer_norm.own_parameters())
+
+    def forward_pair(self, x: Variable, residual: Variable) -> Variable:
+        a = _ops.linear(x.t, self.dense.weight.t, self.dense.bias.t)
+        return Variable.wrap(_ops.layer_norm(a, self.layer_norm.weight.t, self.layer_norm.bias.t, self.eps, residual=residual.t, p_drop=self.p,
+                                             training=self.training))
+
+    def forward(self, x: Variable) -> Variable:
+        return self.forward_pair(x, x)
+
+
+class DebertaV2Intermediate(Module):
+    """FFN up-projection `act(dense(H -> I))`, HF's `DebertaV2Intermediate` (deberta_transformer_layer.rs:417-440)."""
+
+    def __init__(self, c: DebertaV2LayerConfig, device=None):
+        self.dense = Linear(c.hidden_size, c.intermediate_size, True, device)
+        self.act = "gelu" if c.hidden_act == GeluApprox.Exact else "gelu_tanh"
+
+    @classmethod
+    def on_device(cls, config: DebertaV2LayerConfig, device=None): return cls(config, device)
+    def name(self): return "deberta_v2_intermediate"
+    def own_parameters(self): return prefix_params("dense", self.dense.own_parameters())
+    def forward(self, x: Variable) -> Variable:
+        return Variable.wrap(_ops.linear(x.t, self.dense.weight.t, self.dense.bias.t, self.act))
+
+
+class DebertaV2Output(DebertaV2SelfOutput):
+    """FFN down-projection + residual stage `LN(dropout(dense(I -> H)) + residual)`, HF's `DebertaV2Output`
+    (deberta_transformer_layer.rs:441-480)."""
+
+    def __init__(self, c: DebertaV2LayerConfig, device=None):
+        super().__init__(c, device, in_features=c.intermediate_size)
+
+    def name(self): return "deberta_v2_output"
+
+
 class DebertaV2Embeddings(Module):
     def __init__(self, config: DebertaV2Config, device=None):
         self.word_embeddings = Embedding(config.vocab_size, config.hidden_size, config.pad_token_id, device)

@@ -23,6 +23,7 @@ class HfPath:
         self.path = str(root)
 
     try_new = classmethod(lambda cls, root: cls(root))
+    new = classmethod(lambda cls, root: cls(root))
 
     def sub(self, segment) -> "HfPath":
         seg = str(segment)

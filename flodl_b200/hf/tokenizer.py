@@ -17,9 +17,11 @@ class EncodedBatch:
     attention_mask: torch.Tensor   # [B, S] float32, 1 = token, 0 = padding
     token_type_ids: torch.Tensor   # [B, S] int64
     position_ids: torch.Tensor     # [B, S] int64, 0..S-1
+    sequence_ids: Optional[torch.Tensor] = None   # [B, S] int64: 0 / 1 = first / second text of a pair, -1 = special token or padding
 
     def to(self, device) -> "EncodedBatch":
-        return EncodedBatch(*(t.to(device) for t in (self.input_ids, self.attention_mask, self.token_type_ids, self.position_ids)))
+        return EncodedBatch(*(None if t is None else t.to(device)
+                              for t in (self.input_ids, self.attention_mask, self.token_type_ids, self.position_ids, self.sequence_ids)))
 
 
 class HfTokenizer:
@@ -42,6 +44,16 @@ class HfTokenizer:
             return cls(Tokenizer.from_file(str(path)))
         except Exception as e:
             raise TensorError(f"tokenizer load {path}: {e}")
+
+    @classmethod
+    def from_pretrained(cls, repo_id: str) -> "HfTokenizer":
+        """The `tokenizer.json` of a hub repo or local directory (looked up like the weights: the directory
+        itself, the converted-models folder, the hub cache, then a download unless `HF_HUB_OFFLINE=1`)."""
+        from . import hub
+        path = hub.resolve_tokenizer(repo_id)
+        if path is None:
+            raise TensorError(f"HfTokenizer.from_pretrained({repo_id}): no tokenizer.json found (looked in {hub.candidate_dirs(repo_id)})")
+        return cls.from_file(path)
 
     @classmethod
     def from_inner(cls, inner) -> "HfTokenizer":
@@ -67,7 +79,8 @@ class HfTokenizer:
         mask = torch.tensor([e.attention_mask for e in encs], dtype=torch.float32)
         tt = torch.tensor([e.type_ids for e in encs], dtype=torch.long)
         pos = torch.arange(ids.shape[1]).unsqueeze(0).expand_as(ids).contiguous()
-        b = EncodedBatch(ids, mask, tt, pos)
+        seq = torch.tensor([[-1 if s is None else int(s) for s in e.sequence_ids] for e in encs], dtype=torch.long)
+        b = EncodedBatch(ids, mask, tt, pos, seq)
         return b if device is None else b.to(device)
 
     def encode(self, texts: Sequence[str]) -> EncodedBatch:

@@ -5,6 +5,7 @@ import json
 import pytest
 import torch
 
+from flodl_b200 import hf
 from flodl_b200.hf import safetensors_io as st
 from flodl_b200.hf.models import albert, bert, deberta_v2, distilbert, roberta, xlm_roberta
 from flodl_b200.hf.path import HfPath, hf_key_from_flodl_key
@@ -382,3 +383,158 @@ def test_parity_matrix_tool_covers_every_family_and_head():
     assert all(v is not None and v <= 2e-4 for v, _ in res.values()), res
     table = parity.render(res, ["bert", "distilbert"], ["base", "mlm", "qa"], 2e-4)
     assert "| bert |" in table and "FAIL" not in table and "n/a" not in table
+
+
+# ---- class-level from_pretrained and the text-level head methods ------------------------------------------------
+VOCAB = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "paris", "is", "the", "capital", "of", "france", "where", "what", "berlin", "germany", "."]
+
+
+def _word_tokenizer(path):
+    tokenizers = pytest.importorskip("tokenizers")
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel({w: i for i, w in enumerate(VOCAB)}, unk_token="[UNK]"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.post_processor = tokenizers.processors.TemplateProcessing(single="[CLS] $A [SEP]", pair="[CLS] $A [SEP] $B:1 [SEP]:1",
+                                                                  special_tokens=[("[CLS]", 2), ("[SEP]", 3)])
+    tok.add_special_tokens(["[MASK]"])                 # kept whole by the pre-tokenizer, as in real vocabularies
+    tok.save(str(path))
+
+
+def _tiny_repo(dst, hf_cls, arch, **extra):
+    hc = transformers.BertConfig(vocab_size=len(VOCAB), hidden_size=32, num_hidden_layers=1, num_attention_heads=4, intermediate_size=64,
+                                 max_position_embeddings=32, architectures=[arch], **extra)
+    torch.manual_seed(0)
+    model = hf_cls(hc).eval()
+    dst.mkdir(parents=True, exist_ok=True)
+    (dst / "config.json").write_text(hc.to_json_string())
+    (dst / "model.safetensors").write_bytes(hf_state_bytes(model))
+    _word_tokenizer(dst / "tokenizer.json")
+    return model
+
+
+def test_family_and_auto_classes_load_with_from_pretrained(tmp_path):
+    from flodl_b200.hf.hub import HubExportHead
+    from flodl_b200.hf.tokenizer import HfTokenizer
+    repo = tmp_path / "tiny-bert"
+    ref = _tiny_repo(repo, transformers.BertModel, "BertModel")
+    ids = torch.tensor([[2, 5, 6, 7, 8, 3]])
+    want = ref(ids).last_hidden_state
+    g = bert.BertModel.from_pretrained(str(repo))                       # keeps the pooler the weights carry
+    enc = HfTokenizer.from_pretrained(str(repo)).encode(["paris is the capital"])
+    assert enc.input_ids.tolist() == ids.tolist()
+    g.set_training(False)
+    with torch.no_grad():
+        out = g.forward_multi(bert.BertConfig.encoder_inputs(enc))
+    assert out.t.shape == (1, 32)                                        # pooled output
+    g2 = hf.AutoModel.from_pretrained(str(repo))                         # uniform [B, S, H] output
+    g2.set_training(False)
+    with torch.no_grad():
+        torch.testing.assert_close(g2.forward_multi(bert.BertConfig.encoder_inputs(enc)).t, want, atol=1e-4, rtol=1e-4)
+    assert json.loads(g2.source_config())["architectures"] == ["BertModel"]
+    assert hf.AutoConfig.from_pretrained(str(repo)).model_type() == "bert"
+    assert hf.AutoModel.from_pretrained_for_export(str(repo)).structural_hash() == g.structural_hash()
+    g3 = hf.AutoModel.from_pretrained_for_export_with_head(str(repo), HubExportHead.Base)
+    assert g3.structural_hash() == g.structural_hash()
+    with pytest.raises(Exception, match="model_type"):
+        roberta.RobertaModel.from_pretrained(str(repo))
+    with pytest.raises(Exception):
+        bert.BertModel.from_pretrained(str(tmp_path / "nope"))
+
+
+def test_sequence_classification_predicts_from_text(tmp_path):
+    repo = tmp_path / "cls"
+    ref = _tiny_repo(repo, transformers.BertForSequenceClassification, "BertForSequenceClassification", num_labels=3,
+                     id2label={0: "neg", 1: "neu", 2: "pos"}, label2id={"neg": 0, "neu": 1, "pos": 2})
+    for head in (bert.BertForSequenceClassification.from_pretrained(str(repo)), hf.AutoModelForSequenceClassification.from_pretrained(str(repo))):
+        assert head.labels() == ["neg", "neu", "pos"] and head.tokenizer is not None
+        got = head.predict(["paris is the capital of france", "berlin"])
+        assert len(got) == 2 and [k for k, _ in sorted(got[0])] == ["neg", "neu", "pos"]
+        ids = head.tokenizer.encode(["paris is the capital of france"])
+        want = torch.softmax(ref(ids.input_ids).logits, -1)[0]
+        assert abs(dict(got[0])["pos"] - float(want[2])) < 1e-4 and got[0][0][1] >= got[0][1][1] >= got[0][2][1]
+        assert head.classify(ids)[0][0][0] == got[0][0][0] and head.predict("berlin")[0][0][0] == got[1][0][0]
+    bare = bert.BertForSequenceClassification.on_device(bert.BertConfig.from_json_str((repo / "config.json").read_text()), 3)
+    with pytest.raises(Exception, match="needs a tokenizer"):
+        bare.predict(["paris"])
+
+
+def test_token_classification_returns_token_predictions(tmp_path):
+    from flodl_b200.hf.task_heads import TokenPrediction
+    repo = tmp_path / "tok"
+    _tiny_repo(repo, transformers.BertForTokenClassification, "BertForTokenClassification", num_labels=3)
+    head = hf.AutoModelForTokenClassification.from_pretrained(str(repo))
+    rows = head.predict(["paris is the capital", "berlin"])
+    assert len(rows) == 2 and len(rows[0]) == 6 and all(isinstance(p, TokenPrediction) for p in rows[0])
+    assert [p.token for p in rows[0]] == ["[CLS]", "paris", "is", "the", "capital", "[SEP]"]
+    assert [p.attends for p in rows[1]] == [True, True, True, False, False, False] and rows[0][1].label in ("LABEL_0", "LABEL_1", "LABEL_2")
+    assert 1 / 3 <= rows[0][1].score <= 1.0
+
+
+def test_question_answering_extracts_a_context_span(tmp_path):
+    from flodl_b200.hf.task_heads import Answer
+    repo = tmp_path / "qa"
+    ref = _tiny_repo(repo, transformers.BertForQuestionAnswering, "BertForQuestionAnswering")
+    head = bert.BertForQuestionAnswering.from_pretrained(str(repo))
+    a = head.answer("what is the capital of france", "paris is the capital of france .")
+    assert isinstance(a, Answer) and a.end >= a.start >= 8            # inside the context: [CLS] + 6 question tokens + [SEP]
+    enc = head.tokenizer.encode_pairs([("what is the capital of france", "paris is the capital of france .")])
+    assert enc.sequence_ids[0].tolist()[:9] == [-1, 0, 0, 0, 0, 0, 0, -1, 1]
+    with torch.no_grad():
+        o = ref(enc.input_ids, token_type_ids=enc.token_type_ids)
+    ps, pe = torch.softmax(o.start_logits, 1)[0], torch.softmax(o.end_logits, 1)[0]
+    ctx = [i for i, s in enumerate(enc.sequence_ids[0].tolist()) if s == 1]
+    best = max(((i, j) for i in ctx for j in ctx if j >= i), key=lambda ij: float(ps[ij[0]] + pe[ij[1]]))
+    assert (a.start, a.end) == best and abs(a.score - float(ps[best[0]] + pe[best[1]])) < 1e-4
+    assert a.text == head.tokenizer.decode(enc.input_ids[0, a.start:a.end + 1].tolist())
+    two = head.answer_batch([("where is paris", "paris is the capital of france"), ("what", "berlin germany")])
+    assert len(two) == 2 and head.extract(enc)[0] == a
+    single = head.tokenizer.encode(["paris"])
+    with pytest.raises(Exception, match="no context tokens"):
+        head.extract(single)
+
+
+def test_fill_mask_from_text(tmp_path):
+    repo = tmp_path / "mlm"
+    ref = _tiny_repo(repo, transformers.BertForMaskedLM, "BertForMaskedLM")
+    head = hf.AutoModelForMaskedLM.from_pretrained(str(repo))
+    out = head.fill_mask("paris is the [MASK] of [MASK]", 3)
+    assert len(out) == 2 and len(out[0]) == 3 and out[0][0][1] >= out[0][1][1] >= out[0][2][1] and out[0][0][0] in VOCAB
+    enc = head.tokenizer.encode(["paris is the [MASK] of [MASK]"])
+    with torch.no_grad():
+        want = torch.softmax(ref(enc.input_ids).logits, -1)[0, 4]
+    assert out[0][0][0] == VOCAB[int(want.argmax())] and abs(out[0][0][1] - float(want.max())) < 1e-4
+    with pytest.raises(Exception, match="no \\[MASK\\]"):
+        head.fill_mask("paris is", 2)
+    with pytest.raises(Exception, match="top_k"):
+        head.fill_mask("paris [MASK]", 0)
+    pairs = head.fill_mask([enc.input_ids, enc.position_ids, enc.token_type_ids, bert.build_extended_attention_mask(enc.attention_mask)], [(0, 4)], 2)
+    assert pairs[0][0][0] == int(want.argmax())
+    g = hf.AutoModel.from_pretrained_for_export(str(repo))
+    assert g.structural_hash() == head.graph().structural_hash()
+
+
+def test_generic_heads_dispatch_on_the_config_family_and_small_names():
+    from flodl_b200.hf.task_heads import ClassificationHead, MaskedLmHead, QaHead, TaggingHead
+    cfg = distilbert.DistilBertConfig(vocab_size=30, dim=16, hidden_dim=32, n_layers=1, n_heads=2, max_position_embeddings=8)
+    assert type(ClassificationHead.on_device(cfg, 2, None)).__name__ == "DistilBertForSequenceClassification"
+    assert type(TaggingHead.on_device(cfg, 2, None)).__name__ == "DistilBertForTokenClassification"
+    assert type(QaHead.on_device(cfg, None)).__name__ == "DistilBertForQuestionAnswering"
+    assert type(MaskedLmHead.on_device(cfg, None)).__name__ == "DistilBertForMaskedLM"
+    with pytest.raises(Exception, match="not a known family"):
+        QaHead.on_device(object())
+    assert HfPath.new("encoder").sub("layer").sub(3).path == "encoder.layer.3"
+
+
+def test_deberta_stage_modules_match_the_fused_layer():
+    from flodl_b200.autograd import Variable
+    c = deberta_v2.DebertaV2LayerConfig(hidden_size=16, num_attention_heads=2, intermediate_size=32, hidden_dropout_prob=0.0,
+                                        attention_probs_dropout_prob=0.0, layer_norm_eps=1e-7, position_buckets=8, max_relative_positions=16)
+    so, it, out = (deberta_v2.DebertaV2SelfOutput.on_device(c), deberta_v2.DebertaV2Intermediate.on_device(c), deberta_v2.DebertaV2Output.on_device(c))
+    x, r = Variable.wrap(torch.randn(2, 5, 16)), Variable.wrap(torch.randn(2, 5, 16))
+    want = torch.nn.functional.layer_norm(torch.nn.functional.linear(x.t, so.dense.weight.t, so.dense.bias.t) + r.t, [16],
+                                          so.layer_norm.weight.t, so.layer_norm.bias.t, 1e-7)
+    torch.testing.assert_close(so.forward_pair(x, r).t, want, atol=1e-5, rtol=1e-5)
+    up = it.forward(x)
+    torch.testing.assert_close(up.t, torch.nn.functional.gelu(torch.nn.functional.linear(x.t, it.dense.weight.t, it.dense.bias.t)), atol=1e-5, rtol=1e-5)
+    assert out.forward_pair(up, x).t.shape == (2, 5, 16)
+    assert [p.name for p in so.parameters()] == ["dense.weight", "dense.bias", "LayerNorm.weight", "LayerNorm.bias"]
+    assert [p.name for p in it.parameters()] == ["dense.weight", "dense.bias"] and out.dense.weight.t.shape == (16, 32)
