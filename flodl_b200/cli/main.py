@@ -9,10 +9,10 @@ from dataclasses import dataclass
 from typing import List, Optional
 
 from .args import ArgError, FdlArgs, arg
-from .manifest import ManifestError, find_manifest, load_manifest, run_command
+from .manifest import ManifestError, adopt_template, env_from_first_word, find_manifest, load_manifest, run_command
 
-BUILTINS = ["diagnose", "setup", "install", "libtorch", "build", "bench", "export-hf", "api-ref", "schema", "completions", "config", "init", "add",
-            "skill", "help"]
+BUILTINS = ["diagnose", "setup", "install", "libtorch", "build", "bench", "export-hf", "api-ref", "schema", "completions", "autocomplete", "config", "init",
+            "add", "skill", "help"]
 
 
 # ---- diagnose ---------------------------------------------------------------------------------------
@@ -178,26 +178,98 @@ def init(argv: List[str]) -> int:
     return 0
 
 
-def completions(shell: str, manifest: Optional[str]) -> int:
-    names = list(BUILTINS)
-    if manifest:
-        try:
-            names += list((load_manifest(manifest)[0].get("commands") or {}).keys())
-        except ManifestError:
-            pass
-    words = " ".join(sorted(set(names)))
+def completion_script(shell: str, manifest: Optional[str]) -> str:
+    """A completion script that knows the built-in commands, the project's commands of all three kinds with their
+    nested entries, and the values of options declared with `choices:`."""
+    from .manifest import completion_tree, flatten_completions
+    tree = completion_tree(manifest) if manifest else {"words": {}, "flags": {}}
+    for b in BUILTINS:
+        tree["words"].setdefault(b, {"words": {}, "flags": {}})
+    tree["words"]["libtorch"]["words"] = {k: {"words": {}, "flags": {}} for k in ("info", "list", "path", "activate", "download", "build", "remove")}
+    tree["words"]["schema"]["words"] = {k: {"words": {}, "flags": {}} for k in ("list", "clear", "refresh", "bench", "export-hf", "init")}
+    tree["words"]["skill"]["words"] = {k: {"words": {}, "flags": {}} for k in ("list", "show", "install")}
+    tree["words"]["completions"]["words"] = {k: {"words": {}, "flags": {}} for k in ("bash", "zsh", "fish")}
+    tree["words"]["config"]["words"] = {"show": {"words": {}, "flags": {}}}
+    rows = flatten_completions(tree)
+    if shell == "fish":
+        lines = []
+        for path, words, choices in rows:
+            parts = path.split()
+            cond = "__fish_use_subcommand" if not parts else "__fish_seen_subcommand_from " + parts[-1]
+            for w in words:
+                if w.startswith("--"):
+                    vals = choices.get(w)
+                    lines.append(f"complete -c fdl -f -n '{cond}' -l {w[2:]}" + (f" -x -a '{' '.join(vals)}'" if vals else ""))
+                else:
+                    lines.append(f"complete -c fdl -f -n '{cond}' -a {w}")
+        return "\n".join(lines)
+    cases, value_cases = [], []
+    for path, words, choices in rows:
+        cases.append(f'    "{path}") COMPREPLY=($(compgen -W "{" ".join(words)}" -- "$cur"));;')
+        for flag, vals in choices.items():
+            value_cases.append(f'    "{path}|{flag}") COMPREPLY=($(compgen -W "{" ".join(vals)}" -- "$cur")); return;;')
+    body = "\n".join([
+        "_fdl() {",
+        "  local cur prev path i w",
+        '  cur="${COMP_WORDS[COMP_CWORD]}"; prev="${COMP_WORDS[COMP_CWORD-1]}"; path=""',
+        "  for ((i=1; i<COMP_CWORD; i++)); do",
+        '    w="${COMP_WORDS[i]}"',
+        '    case "$w" in -*) ;; *) case "${COMP_WORDS[i-1]}" in --*) ;; *) path="$path $w";; esac;; esac',
+        "  done",
+        '  case "$path|$prev" in'] + value_cases + ["  esac", '  case "$path" in'] + cases + ["  esac", "}"])
     if shell == "zsh":
-        print(f"#compdef fdl\n_arguments '1: :({words})'")
-    elif shell == "fish":
-        for w in sorted(set(names)):
-            print(f"complete -c fdl -f -n '__fish_use_subcommand' -a {w}")
-    else:
-        print(f"complete -W \"{words}\" fdl")
+        return "#compdef fdl\nautoload -U +X bashcompinit && bashcompinit\n" + body + "\ncomplete -F _fdl fdl"
+    return body + "\ncomplete -F _fdl fdl"
+
+
+def completions(shell: str, manifest: Optional[str]) -> int:
+    if shell not in ("bash", "zsh", "fish"):
+        print(f"fdl completions: unknown shell {shell!r} (bash, zsh, fish)", file=sys.stderr)
+        return 2
+    print(completion_script(shell, manifest))
     return 0
 
 
-def schema(argv: List[str]) -> int:
+def autocomplete(manifest: Optional[str]) -> int:
+    """Detect the login shell and install the completion script where that shell looks for it."""
+    shell = os.path.basename(os.environ.get("SHELL", "bash"))
+    shell = shell if shell in ("bash", "zsh", "fish") else "bash"
+    home = os.path.expanduser("~")
+    dst = {"bash": os.path.join(home, ".local", "share", "bash-completion", "completions", "fdl"),
+           "zsh": os.path.join(home, ".zfunc", "_fdl"),
+           "fish": os.path.join(home, ".config", "fish", "completions", "fdl.fish")}[shell]
+    os.makedirs(os.path.dirname(dst), exist_ok=True)
+    with open(dst, "w") as f:
+        f.write(completion_script(shell, manifest) + "\n")
+    print(f"installed {shell} completions to {dst}" + ("; add `fpath+=~/.zfunc` before compinit in ~/.zshrc" if shell == "zsh" else ""))
+    return 0
+
+
+def schema(argv: List[str], manifest: Optional[str] = None, env: Optional[str] = None) -> int:
+    """`schema [bench|export-hf|init]`: the built-in commands' argument schemas. `schema list [--json] | clear [cmd] |
+    refresh [cmd]`: the cached `--fdl-schema` answers of the project's sub-commands."""
+    from .manifest import clear_caches, discover_caches, refresh_caches
     table = {"bench": BenchArgs, "export-hf": ExportArgs, "init": InitArgs}
+    if argv and argv[0] in ("list", "clear", "refresh"):
+        if manifest is None:
+            print("fdl schema: no fdl.yml found", file=sys.stderr)
+            return 1
+        only = next((a for a in argv[1:] if not a.startswith("-")), None)
+        if argv[0] == "list":
+            rows = discover_caches(manifest)
+            if "--json" in argv:
+                print(json.dumps(rows, indent=2))
+            else:
+                for r in rows:
+                    print(f"{r['command']:<20} {r['status']:<7} {r['path']}")
+                if not rows:
+                    print("no cached schemas")
+        elif argv[0] == "clear":
+            print(f"removed {clear_caches(manifest, only)} cached schema(s)")
+        else:
+            done = refresh_caches(manifest, only, env)
+            print("refreshed: " + (", ".join(done) if done else "nothing (no sub-command with an entry answered --fdl-schema)"))
+        return 0
     if not argv or argv[0] not in table:
         print(json.dumps({k: v.schema() for k, v in table.items()}, indent=2))
     else:
@@ -231,8 +303,10 @@ def usage(manifest: Optional[str]) -> str:
              "  export-hf <ckpt>        .fdl checkpoint -> HuggingFace directory",
              "  api-ref [--json]        list the public API",
              "  schema [command]        argument schemas as JSON",
-             "  completions <shell>     shell completion script (bash, zsh, fish)",
-             "  config show             the merged manifest with the origin of every value",
+             "  schema list|clear|refresh  cached --fdl-schema answers of the project's sub-commands",
+             "  completions <shell>     shell completion script (bash, zsh, fish), aware of the project and of option values",
+             "  autocomplete            install the completion script for the login shell",
+             "  config show [env]       the merged manifest with the origin of every value",
              "  init <name>             scaffold a project",
              "  add [dir]               add a training scaffold to an existing directory",
              "  setup [--force]         check the machine and build the native library",
@@ -265,6 +339,14 @@ def main(argv: Optional[List[str]] = None) -> int:
         else:
             dry, argv = True, argv[1:]
     manifest = find_manifest(os.getcwd())
+    if manifest is not None and manifest.endswith((".example", ".dist")):
+        manifest = adopt_template(manifest)              # a checkout ships the template; the copy is the user's to edit
+    if manifest is not None and env is None and argv and not os.environ.get("FDL_ENV") and argv[0] not in BUILTINS:
+        try:
+            env, argv = env_from_first_word(manifest, argv)      # `fdl ci test` = `fdl --env ci test`
+        except ManifestError as e:
+            print(f"fdl: {e}", file=sys.stderr)
+            return 2
     if not argv or argv[0] in ("help", "-h", "--help"):
         print(usage(manifest))
         return 0
@@ -283,13 +365,15 @@ def main(argv: Optional[List[str]] = None) -> int:
         if cmd == "api-ref":
             return api_ref("--json" in rest)
         if cmd == "schema":
-            return schema(rest)
+            return schema(rest, manifest, env)
         if cmd == "completions":
             return completions(rest[0] if rest else "bash", manifest)
+        if cmd == "autocomplete":
+            return autocomplete(manifest)
         if cmd == "config":
             if rest[:1] == ["show"]:
-                return config_show(manifest, env)
-            print("usage: config show", file=sys.stderr)
+                return config_show(manifest, rest[1] if len(rest) > 1 else env)
+            print("usage: config show [env]", file=sys.stderr)
             return 2
         if cmd == "init":
             return init(rest)

@@ -111,44 +111,9 @@ def setup(argv: List[str]) -> int:
 
 
 def libtorch(argv: List[str]) -> int:
-    sub = argv[0] if argv else "info"
-    import importlib.util
-    if sub == "path":
-        import torch
-        print(os.path.join(os.path.dirname(torch.__file__), "lib"))
-        return 0
-    if sub == "list":
-        seen = []
-        for p in sys.path:
-            init = os.path.join(p, "torch", "version.py")
-            if os.path.isfile(init) and p not in seen:
-                seen.append(p)
-                ver = {}
-                try:
-                    exec(open(init).read(), ver)  # noqa: S102  (the wheel's own version file)
-                except Exception:  # noqa: BLE001
-                    pass
-                print(f"{ver.get('__version__', '?'):<18} cuda {ver.get('cuda', '?'):<8} {os.path.join(p, 'torch')}")
-        if not seen:
-            print("no torch installation on sys.path", file=sys.stderr)
-            return 1
-        return 0
-    if sub == "info":
-        if importlib.util.find_spec("torch") is None:
-            print("torch is not installed", file=sys.stderr)
-            return 1
-        import torch
-        info = {"version": torch.__version__, "cuda": torch.version.cuda, "cudnn": torch.backends.cudnn.version() if torch.backends.cudnn.is_available() else None,
-                "arch_list": torch.cuda.get_arch_list() if torch.cuda.is_available() else [], "lib_dir": os.path.join(os.path.dirname(torch.__file__), "lib"),
-                "cxx11_abi": bool(torch._C._GLIBCXX_USE_CXX11_ABI)}
-        try:
-            info["nccl"] = ".".join(map(str, torch.cuda.nccl.version()))
-        except Exception:  # noqa: BLE001
-            info["nccl"] = None
-        print(json.dumps(info, indent=2) if "--json" in argv else "\n".join(f"  {k}: {v}" for k, v in info.items()))
-        return 0
-    print("usage: libtorch [info [--json] | list | path]", file=sys.stderr)
-    return 2
+    """`libtorch list | info | path | activate | remove | download | build` (see `cli/libtorch.py`)."""
+    from . import libtorch as lt
+    return lt.main(argv)
 
 
 def install(argv: List[str]) -> int:

@@ -1,6 +1,8 @@
 """Command line: typed argument parsing + schema, manifest commands, overlays, built-ins."""
 import json
 import os
+import subprocess
+import sys
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -79,7 +81,8 @@ settings:
 def test_manifest_commands_and_subcommands(tmp_path):
     m = _project(tmp_path)
     spec, rest, cwd = resolve_command(m, ["hello"])
-    assert build_shell_line(spec, rest) == "echo hello world" and build_shell_line(spec, ["you", "two words"]) == "echo hello you 'two words'"
+    assert build_shell_line(spec, rest) == "echo hello world"
+    assert build_shell_line(spec, ["you", "two words"]) == "echo hello you 'two words' world"      # run + forwarded + append
     spec, rest, cwd = resolve_command(m, ["sub", "inner", "x"])
     assert spec["run"] == "echo inner" and rest == ["x"] and cwd.endswith("sub")
     spec, _, cwd = resolve_command(m, ["bench", "quick"])
@@ -103,8 +106,10 @@ def test_overlay_deep_merge_keeps_origins(tmp_path):
 def test_main_dispatch(tmp_path, monkeypatch, capsys):
     _project(tmp_path)
     monkeypatch.chdir(tmp_path)
-    assert main(["--dry-run", "hello", "there"]) == 0
-    assert capsys.readouterr().out.strip() == "echo hello there"
+    assert main(["--dry-run", "hello", "--", "there"]) == 0
+    assert capsys.readouterr().out.strip() == "echo hello there world"
+    assert main(["--dry-run", "hello", "there"]) == 2                      # extra arguments only after `--`
+    assert "fdl hello -- there" in capsys.readouterr().err
     assert main(["hello"]) == 0
     assert main(["--env", "gpu", "config", "show"]) == 0
     out = capsys.readouterr().out
@@ -142,3 +147,245 @@ def test_setup_install_add_libtorch_skill(tmp_path, capsys):
     assert main(["setup"]) == 0
     out = capsys.readouterr().out
     assert "nvcc" in out and "ready:" in out and "lib_dir" in out
+
+
+# ---- the three command kinds, docker, presets, schema cache, first-word overlays ---------------------------------
+def _bench_project(tmp_path):
+    """A root manifest with a docker run command and a path-kind sub-command whose entry is a script that answers
+    `--fdl-schema` (the shape of the reference's `ddp-bench/` and `benchmarks/`)."""
+    from textwrap import dedent
+    (tmp_path / "fdl.yml").write_text(dedent("""\
+        description: demo
+        commands:
+          test:
+            description: Run the tests
+            run: pytest -q
+            append: -- --nocapture
+            docker: dev
+          lint:
+            run: ruff check .
+          suite:
+        """))
+    (tmp_path / "fdl.ci.yml").write_text("commands:\n  test:\n    run: pytest -q -x\n")
+    sub = tmp_path / "suite"
+    sub.mkdir()
+    (sub / "tool.py").write_text(dedent("""\
+        import json, sys
+        if "--fdl-schema" in sys.argv:
+            print(json.dumps({"options": {"model": {"type": "string", "short": "m", "description": "which model", "default": "all",
+                                                     "choices": ["mlp", "resnet", "all"]},
+                                          "epochs": {"type": "int", "description": "epochs"},
+                                          "validate": {"type": "bool", "description": "check baselines"}}, "strict": True}))
+            sys.exit(0)
+        print("ARGS", " ".join(sys.argv[1:]))
+        """))
+    (sub / "fdl.yml").write_text(dedent(f"""\
+        description: the suite
+        entry: {sys.executable} tool.py
+        training:
+          epochs: 5
+          seed: 42
+        ddp:
+          policy: cadence
+        commands:
+          quick:
+            description: Fast smoke test
+            training: {{epochs: 1}}
+            options: {{model: mlp, validate: true, batches: null}}
+          full:
+            options: {{model: all}}
+          helper:
+            run: echo helper
+        """))
+    return str(tmp_path / "fdl.yml")
+
+
+def test_run_kind_docker_wrap_forwarding_and_overlay_by_first_word(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli.manifest import compose, resolve
+    m = _bench_project(tmp_path)
+    assert compose(resolve(m, ["test"])) == "docker compose run --rm dev bash -c 'pytest -q -- --nocapture'"
+    assert compose(resolve(m, ["test", "--", "-k", "two words"])) == "docker compose run --rm dev bash -c 'pytest -q -k '\"'\"'two words'\"'\"' -- --nocapture'"
+    assert compose(resolve(m, ["lint"])) == "ruff check ."
+    with pytest.raises(Exception, match="fdl test -- -k x"):
+        compose(resolve(m, ["test", "-k", "x"]))
+    monkeypatch.chdir(tmp_path)
+    assert main(["--dry-run", "ci", "test"]) == 0                            # first word names fdl.ci.yml
+    assert "pytest -q -x -- --nocapture" in capsys.readouterr().out
+    assert main(["config", "show", "ci"]) == 0 and "# fdl.ci.yml" in capsys.readouterr().out
+    monkeypatch.setenv("FDL_ENV", "ci")
+    assert main(["--dry-run", "test"]) == 0 and "-x" in capsys.readouterr().out
+    monkeypatch.delenv("FDL_ENV")
+    (tmp_path / "fdl.lint.yml").write_text("description: clash\n")
+    assert main(["--dry-run", "lint"]) == 2 and "both a command and the overlay" in capsys.readouterr().err
+
+
+def test_presets_merge_sections_and_become_flags(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli.manifest import compose, config_to_args, resolve
+    m = _bench_project(tmp_path)
+    r = resolve(m, ["suite", "quick", "--report", "out"])
+    assert (r.kind, r.name, r.rest) == ("preset", "quick", ["--report", "out"])
+    line = compose(r)
+    assert line.endswith("tool.py --policy cadence --epochs 1 --seed 42 --model mlp --validate --report out")
+    assert compose(resolve(m, ["suite", "--model", "resnet"])).endswith("tool.py --policy cadence --epochs 5 --seed 42 --model resnet")
+    assert compose(resolve(m, ["suite", "helper"])) == "echo helper"
+    monkeypatch.chdir(tmp_path)
+    assert main(["suite", "full"]) == 0                                       # really runs the entry
+    args = config_to_args({"ddp": {"mode": "sync", "speed_hint": {"slow_rank": 1, "ratio": 0.5}, "partition_ratios": [0.7, 0.3], "timeline": True,
+                                   "progressive": False},
+                           "training": {"batches_per_epoch": 10, "lr": 0.1}, "output": {"dir": "runs/", "monitor": 3000},
+                           "options": {"data_dir": "d", "list": False, "tags": ["a", "b"]}})
+    assert args == ["--mode", "sync", "--progressive", "false", "--speed-hint", "1:0.5", "--partition-ratios", "0.7,0.3", "--timeline", "--batches", "10",
+                    "--lr", "0.1", "--output", "runs/", "--monitor", "3000", "--data-dir", "d", "--tags", "a,b"]
+
+
+def test_schema_probe_cache_validation_and_help(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli.manifest import cache_path, command_help, compose, discover_caches, resolve
+    m = _bench_project(tmp_path)
+    sub = str(tmp_path / "suite")
+    text = command_help(resolve(m, ["suite"]))                                # probes the script and caches the answer
+    assert os.path.isfile(cache_path(sub, "suite"))
+    assert "the suite" in text and "quick" in text and "Fast smoke test" in text and "helper" in text
+    assert "-m, --model <string>" in text and "one of: mlp, resnet, all" in text and "default: all" in text and "--validate" in text
+    assert [c["status"] for c in discover_caches(m)] == ["fresh"]
+    assert "--epochs 1" in command_help(resolve(m, ["suite", "quick"]))
+    bad = (tmp_path / "suite" / "fdl.yml").read_text().replace("model: mlp", "model: lenet")
+    (tmp_path / "suite" / "fdl.yml").write_text(bad)
+    with pytest.raises(Exception, match="not one of mlp, resnet, all"):
+        compose(resolve(m, ["suite", "quick"]))
+    (tmp_path / "suite" / "fdl.yml").write_text(bad.replace("model: lenet", "modle: mlp"))
+    with pytest.raises(Exception, match="does not declare"):
+        compose(resolve(m, ["suite", "quick"]))                               # strict schema: unknown option
+    monkeypatch.chdir(tmp_path)
+    assert main(["suite", "--help"]) == 0 and "Options:" in capsys.readouterr().out
+    assert main(["test", "--help"]) == 0 and "fdl test -- <args>" in capsys.readouterr().out
+    assert main(["schema", "list", "--json"]) == 0 and json.loads(capsys.readouterr().out)[0]["command"] == "suite"
+    assert main(["schema", "clear"]) == 0 and "removed 1" in capsys.readouterr().out and not os.path.isfile(cache_path(sub, "suite"))
+    assert main(["schema", "refresh", "suite"]) == 0 and "refreshed: suite" in capsys.readouterr().out
+    os.remove(tmp_path / "suite" / "fdl.yml")
+    (tmp_path / "suite" / "fdl.yml").write_text("commands:\n  x:\n    run: echo x\n")
+    assert discover_caches(m)[0]["status"] == "orphan"
+
+
+def test_manifest_load_time_checks_json_and_templates(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli.manifest import adopt_template, list_envs
+    (tmp_path / "a").mkdir()
+    (tmp_path / "a" / "fdl.json").write_text(json.dumps({"commands": {"hi": {"run": "echo hi"}}}))
+    spec, _, _ = resolve_command(str(tmp_path / "a" / "fdl.json"), ["hi"])
+    assert spec["run"] == "echo hi"
+    for body, needle in (("commands:\n  p:\n    path: ./x/\n    docker: dev\n", "`docker:` on command `p` needs `run:`"),
+                         ("commands:\n  p:\n    options: {a: 1}\n    append: x\n", "`append:` on command `p` needs `run:`"),
+                         ("commands:\n  p:\n    options: {a: 1}\n", "presets need an `entry:`"),
+                         ("commands:\n  p: echo\n", "must be a mapping"),
+                         ("commands:\n  p:\n    run: [a]\n", "must be a string")):
+        (tmp_path / "fdl.yml").write_text(body)
+        with pytest.raises(Exception) as e:
+            load_manifest(str(tmp_path / "fdl.yml"))
+        assert needle in str(e.value), body
+    os.remove(tmp_path / "fdl.yml")
+    (tmp_path / "fdl.yml.example").write_text("commands:\n  hi:\n    run: echo template\n")
+    (tmp_path / "fdl.dev.yml").write_text("{}\n")
+    assert list_envs(str(tmp_path / "fdl.yml.example")) == ["dev"]
+    monkeypatch.chdir(tmp_path)
+    assert main(["--dry-run", "hi"]) == 0 and "echo template" in capsys.readouterr().out
+    assert os.path.isfile(tmp_path / "fdl.yml")                               # the template was copied for local edits
+    assert adopt_template(str(tmp_path / "fdl.yml")) == str(tmp_path / "fdl.yml")
+
+
+def test_completion_scripts_know_nested_commands_and_choices(tmp_path, monkeypatch, capsys):
+    m = _bench_project(tmp_path)
+    monkeypatch.chdir(tmp_path)
+    assert main(["completions", "bash"]) == 0
+    out = capsys.readouterr().out
+    assert '" suite") COMPREPLY=($(compgen -W "full helper quick --epochs --model --validate"' in out
+    assert '" suite|--model") COMPREPLY=($(compgen -W "mlp resnet all"' in out and '" suite quick|--model")' in out
+    assert "complete -F _fdl fdl" in out and '" libtorch")' in out
+    assert subprocess.run(["bash", "-n"], input=out, text=True).returncode == 0        # the script parses
+    assert main(["completions", "zsh"]) == 0 and capsys.readouterr().out.startswith("#compdef fdl")
+    assert main(["completions", "fish"]) == 0 and "-l model -x -a 'mlp resnet all'" in capsys.readouterr().out
+    assert main(["completions", "tcsh"]) == 2
+    capsys.readouterr()
+    monkeypatch.setenv("HOME", str(tmp_path / "home"))
+    monkeypatch.setenv("SHELL", "/usr/bin/fish")
+    assert main(["autocomplete"]) == 0 and os.path.isfile(tmp_path / "home" / ".config" / "fish" / "completions" / "fdl.fish")
+
+
+# ---- libtorch variants -------------------------------------------------------------------------------------------
+def _fake_variant(root, name, archs="9.0 10.0", cuda="12.8"):
+    from flodl_b200.cli import libtorch as lt
+    vdir = os.path.join(root, "libtorch", name)
+    os.makedirs(os.path.join(vdir, "lib"))
+    lt.write_arch(vdir, "2.10.0", cuda, archs, "compiled" if name.startswith("builds/") else "precompiled")
+    return vdir
+
+
+def test_libtorch_variants_list_activate_info_remove(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli import libtorch as lt
+    monkeypatch.setenv("FLODL_HOME", str(tmp_path / "home"))
+    monkeypatch.chdir(tmp_path)                                    # no fdl.yml here: variants live under $FLODL_HOME
+    root = lt.root_dir(".")
+    assert root == str(tmp_path / "home")
+    _fake_variant(root, "precompiled/cu128")
+    _fake_variant(root, "builds/sm61-sm120", "6.1 12.0")
+    os.makedirs(os.path.join(root, "libtorch", "precompiled", "broken"))      # no lib/: not a variant
+    names = [v["name"] for v in lt.list_variants(root)]
+    assert names[0].startswith("wheel/") and names[1:] == ["precompiled/cu128", "builds/sm61-sm120"]
+    assert lt.active_variant(root)["name"].startswith("wheel/")              # nothing activated yet: the wheel's
+    assert main(["libtorch", "activate", "builds/sm61-sm120"]) == 0
+    assert lt.read_active(root) == "builds/sm61-sm120"
+    capsys.readouterr()
+    assert main(["libtorch", "info"]) == 0
+    out = capsys.readouterr().out
+    assert "Active:   builds/sm61-sm120" in out and "Archs:    6.1 12.0" in out and "Source:   compiled" in out
+    assert main(["libtorch", "list"]) == 0 and "builds/sm61-sm120 (active)" in capsys.readouterr().out
+    assert main(["libtorch", "list", "--json"]) == 0
+    rows = json.loads(capsys.readouterr().out)
+    assert [r["active"] for r in rows] == [False, False, True]
+    assert main(["libtorch", "path"]) == 0 and capsys.readouterr().out.strip().endswith("builds/sm61-sm120/lib")
+    assert main(["libtorch", "activate", "nope"]) == 1 and "no variant `nope`" in capsys.readouterr().err
+    assert main(["libtorch", "remove", "builds/sm61-sm120"]) == 0
+    assert lt.read_active(root) is None and not os.path.isdir(os.path.join(root, "libtorch", "builds", "sm61-sm120"))
+    assert main(["libtorch", "remove", names[0]]) == 1 and "pip" in capsys.readouterr().err
+    assert main(["libtorch", "activate"]) == 0 and "precompiled/cu128" in capsys.readouterr().out
+    assert lt.arch_compatible(10, 0, "9.0 10.0") and lt.arch_compatible(6, 1, "6.1;12.0") and not lt.arch_compatible(7, 5, "9.0 10.0")
+    assert main(["libtorch", "frobnicate"]) == 2
+
+
+def test_libtorch_download_plan_archive_install_and_build_plan(tmp_path, monkeypatch, capsys):
+    import zipfile
+    from flodl_b200.cli import libtorch as lt
+    monkeypatch.setenv("FLODL_HOME", str(tmp_path / "home"))
+    monkeypatch.chdir(tmp_path)
+    root = lt.root_dir(".")
+    assert lt.pick_variant([]) == "cpu" and lt.pick_variant(["10.0"]) == "cu128" and lt.pick_variant(["6.1", "12.0"]) == "cu126"
+    assert lt.download_url("cu128") == f"https://download.pytorch.org/libtorch/cu128/libtorch-shared-with-deps-{lt.LIBTORCH_VERSION}%2Bcu128.zip"
+    assert main(["libtorch", "download", "--cuda", "12.8", "--dry-run"]) == 0
+    out = capsys.readouterr().out
+    assert "precompiled/cu128" in out and "dry run" in out and not os.path.isdir(os.path.join(root, "libtorch"))
+    assert main(["libtorch", "download", "--cuda", "11.8"]) == 1 and "12.6 or 12.8" in capsys.readouterr().err
+    z = tmp_path / "lt.zip"
+    with zipfile.ZipFile(z, "w") as f:
+        f.writestr("libtorch/lib/libtorch.so", b"x")
+        f.writestr("libtorch/include/torch/torch.h", b"y")
+    vdir = str(tmp_path / "home" / "libtorch" / "precompiled" / "cpu")
+    os.makedirs(vdir)
+    lt.install_archive(str(z), vdir)
+    assert os.path.isfile(os.path.join(vdir, "lib", "libtorch.so")) and os.path.isfile(os.path.join(vdir, "include", "torch", "torch.h"))
+    with zipfile.ZipFile(z, "w") as f:
+        f.writestr("libtorch/../../escape.txt", b"x")
+    with pytest.raises(lt.LibtorchError, match="escapes"):
+        lt.install_archive(str(z), vdir)
+    assert lt.arch_dir_name("6.1;12.0") == "sm61-sm120"
+    monkeypatch.setattr(lt.shutil, "which", lambda t: "/usr/bin/" + t if t != "docker" else None)
+    plan = lt.build_plan(root, "9.0;10.0", 8, None)
+    assert plan["backend"] == "native" and plan["output"].endswith("builds/sm90-sm100") and 'TORCH_CUDA_ARCH_LIST="9.0;10.0" MAX_JOBS=8' in plan["commands"][2]
+    with pytest.raises(lt.LibtorchError, match="docker is not installed"):
+        lt.build_plan(root, "9.0", 6, "docker")
+    assert main(["libtorch", "build", "--archs", "10.0", "--dry-run"]) == 0 and "nothing built" in capsys.readouterr().out
+    monkeypatch.setattr(lt, "detect_gpu_archs", lambda: [])
+    assert main(["libtorch", "build", "--dry-run"]) == 1 and "no GPU detected" in capsys.readouterr().err
+    monkeypatch.setattr(lt.shutil, "which", lambda t: "/usr/bin/" + t)
+    calls = []
+    plan = lt.build_plan(root, "10.0", 4, "docker")
+    lt.build_docker(plan, run=lambda cmd: calls.append(cmd) or 0, capture=lambda cmd, text=True: "abc123\n")
+    assert calls[0][:2] == ["docker", "build"] and "TORCH_CUDA_ARCH_LIST=10.0" in calls[0] and calls[1][:2] == ["docker", "cp"]
+    assert calls[1][2] == "abc123:/opt/libtorch/." and calls[2] == ["docker", "rm", "abc123"]
