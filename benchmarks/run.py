@@ -18,6 +18,7 @@ import torch
 
 from flodl_b200 import nn
 from flodl_b200.autograd import Variable
+from flodl_b200.cli.args import answer_schema_probe
 
 from .harness import BenchConfig, BenchResult, run_benchmark
 from .models import MODELS, TIER1, TIER2
@@ -154,6 +155,7 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=-1, help="warm-up epochs per pass (default 3)")
     ap.add_argument("--mode", default="captured", choices=["captured", "eager"],
                     help="flodl arm on CUDA: whole-step CUDA graph through TrainEngine (default) or the op-by-op loop")
+    answer_schema_probe(ap, argv)
     args = ap.parse_args(argv)
     names = {"all": TIER1 + TIER2, "tier1": TIER1, "tier2": TIER2}.get(args.models) or [m for m in args.models.split(",") if m]
     impls = [i for i in args.impl.split(",") if i]

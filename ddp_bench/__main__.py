@@ -13,30 +13,38 @@ import sys
 
 import torch
 
+from flodl_b200.cli.args import answer_schema_probe
 from flodl_b200.parallel import comm
 
 from .config import ALL_MODES, DdpMode, RunOptions
 from .harness import run
 from .models import all_models, find_model
-from .report import write_report
+from .report import load_baselines, results_to_baselines, save_baselines, validate_results, write_report
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="ddp_bench")
-    ap.add_argument("--list", action="store_true")
-    ap.add_argument("--model", default="mlp")
-    ap.add_argument("--mode", default="solo-0")
-    ap.add_argument("--epochs", type=int)
-    ap.add_argument("--batches", type=int)
-    ap.add_argument("--batch-size", type=int)
-    ap.add_argument("--lr", type=float)
-    ap.add_argument("--seed", type=int, default=42)
-    ap.add_argument("--device", default="auto", choices=["auto", "cpu", "cuda"])
-    ap.add_argument("--output", default="")
+    ap.add_argument("--list", action="store_true", help="show the models and modes, then exit")
+    ap.add_argument("--model", "-m", default="mlp", choices=[m.name for m in all_models()] + ["all"], help="one model, or all")
+    ap.add_argument("--mode", default="solo-0", choices=list(ALL_MODES) + ["all"], help="one DDP mode, or all")
+    ap.add_argument("--epochs", type=int, help="epochs (default: the model's)")
+    ap.add_argument("--batches", type=int, help="batches per epoch (default: the model's)")
+    ap.add_argument("--batch-size", type=int, help="batch size per GPU")
+    ap.add_argument("--lr", type=float, help="learning rate (default: the model's)")
+    ap.add_argument("--seed", type=int, default=42, help="RNG seed")
+    ap.add_argument("--device", default="auto", choices=["auto", "cpu", "cuda"], help="where to train")
+    ap.add_argument("--output", default="", help="directory for results and timelines")
     ap.add_argument("--monitor", type=int, default=0, help="serve the live dashboard on this port (builder modes)")
     ap.add_argument("--tiny", action="store_true", help="smoke-test sizes")
     ap.add_argument("--report", default="", help="directory of results: print the report and exit")
     ap.add_argument("--report-out", default="")
+    ap.add_argument("--lr-scale", type=float, help="multiply every model's default learning rate")
+    ap.add_argument("--data-dir", default="data", help="dataset cache directory (the built-in tasks are synthetic and need none)")
+    ap.add_argument("--validate", action="store_true", help="check the final losses against the baselines")
+    ap.add_argument("--save-baseline", action="store_true", help="save this run's final losses as the new baselines")
+    ap.add_argument("--baseline", default="baselines/baseline.json", help="baseline JSON file")
+    ap.add_argument("--tolerance", type=float, default=0.15, help="relative loss tolerance of --validate")
+    answer_schema_probe(ap, argv)
     args = ap.parse_args(argv)
     if args.list:
         for m in all_models():
@@ -58,8 +66,10 @@ def main(argv=None) -> int:
     if distributed and not comm.is_initialized():
         use_cuda = args.device != "cpu" and torch.cuda.is_available()
         comm.init_process_group("nccl" if use_cuda else "gloo")
-    opts = RunOptions(args.epochs, args.batches, args.batch_size, args.lr, args.seed, args.device, args.output, args.monitor, args.tiny)
+    opts = RunOptions(args.epochs, args.batches, args.batch_size, args.lr, args.seed, args.device, args.output, args.monitor, args.tiny,
+                      args.lr_scale)
     rc = 0
+    finished = []
     for md in models:
         for mode in modes:
             if mode.requires_multi_gpu() and not distributed:
@@ -74,10 +84,23 @@ def main(argv=None) -> int:
             res = run(md, mode, opts)
             if res is not None:
                 print(res.json(), flush=True)
+                finished.append(res)
             if distributed:
                 comm.barrier()
     if distributed:
         comm.destroy_process_group()
+    if args.save_baseline and finished:
+        save_baselines(args.baseline, results_to_baselines(finished))
+        print(f"saved {len(finished)} baseline(s) to {args.baseline}", file=sys.stderr)
+    if args.validate and finished:
+        try:
+            ok, bad, lines = validate_results(finished, load_baselines(args.baseline), args.tolerance)
+        except ValueError as e:
+            print(f"--validate: {e}", file=sys.stderr)
+            return 2
+        print("\n".join(lines), file=sys.stderr)
+        print(f"validation: {ok} passed, {bad} failed", file=sys.stderr)
+        rc = rc or (1 if bad else 0)
     return rc
 
 

@@ -62,6 +62,7 @@ class RunOptions:
     output_dir: str = ""
     monitor_port: int = 0                   # > 0: serve the live dashboard while training
     tiny: bool = False                      # shrink data and model for smoke tests
+    lr_scale: Optional[float] = None        # multiplies the learning rate (given or default)
 
 
 def all_modes() -> List[DdpMode]:

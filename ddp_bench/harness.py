@@ -58,7 +58,7 @@ def _resolve(md: ModelDef, opts: RunOptions):
     epochs = opts.epochs or (2 if opts.tiny else d.epochs)
     bpe = opts.batches_per_epoch or (6 if opts.tiny else d.batches_per_epoch)
     bs = opts.batch_size or (16 if opts.tiny else d.batch_size)
-    return epochs, bpe, bs, opts.lr or d.lr
+    return epochs, bpe, bs, (opts.lr or d.lr) * (opts.lr_scale or 1.0)
 
 
 def _factory(md: ModelDef, opts: RunOptions):

@@ -6,6 +6,7 @@ from __future__ import annotations
 import glob
 import json
 import os
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 from .config import ALL_MODES
@@ -70,3 +71,66 @@ def write_report(directory: str, out_path: Optional[str] = None) -> str:
         with open(out_path, "w") as f:
             f.write(text)
     return text
+
+
+# ---- loss baselines (ddp-bench/src/report.rs:17-150) -----------------------------------------------------------------
+@dataclass
+class Baseline:
+    model: str
+    mode: str
+    loss: float
+    epochs: int = 0
+    batches: int = 0
+    batch_size: int = 0
+
+
+def load_baselines(path: str) -> List[Baseline]:
+    try:
+        data = json.load(open(path))
+    except OSError as e:
+        raise ValueError(f"cannot read {path}: {e}")
+    except ValueError as e:
+        raise ValueError(f"invalid JSON in {path}: {e}")
+    if not isinstance(data, list):
+        raise ValueError(f"{path}: expected a JSON array")
+    out = []
+    for item in data:
+        for key in ("model", "mode", "loss"):
+            if key not in item:
+                raise ValueError(f"{path}: entry without `{key}`")
+        out.append(Baseline(str(item["model"]), str(item["mode"]), float(item["loss"]), int(item.get("epochs", 0)), int(item.get("batches", 0)),
+                            int(item.get("batch_size", 0))))
+    return out
+
+
+def save_baselines(path: str, baselines: List[Baseline]) -> None:
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    rows = [f'  {{"model":"{b.model}","mode":"{b.mode}","loss":{b.loss:.6f},"epochs":{b.epochs},"batches":{b.batches},"batch_size":{b.batch_size}}}'
+            for b in baselines]
+    with open(path, "w") as f:
+        f.write("[\n" + ",\n".join(rows) + "\n]\n")
+
+
+def results_to_baselines(results) -> List[Baseline]:
+    """One baseline per finished run: its last epoch's loss with the run's shape."""
+    return [Baseline(r.model, r.mode, float(r.epoch_losses[-1]), r.epochs, r.batches_per_epoch, r.batch_size)
+            for r in results if r.epoch_losses and not r.error]
+
+
+def validate_results(results, baselines: List[Baseline], tolerance: float = 0.15):
+    """(passed, failed, lines): every run's final loss against the baseline of its model (relative difference, absolute
+    when the baseline is ~0); runs without a baseline are reported as skipped."""
+    lookup = {b.model: b for b in baselines}
+    ok = bad = 0
+    lines = []
+    for r in results:
+        loss = float(r.epoch_losses[-1]) if r.epoch_losses else float("nan")
+        b = lookup.get(r.model)
+        if b is None:
+            lines.append(f"  SKIP  {r.model:<16} {r.mode:<20} loss={loss:.6f} (no baseline)")
+            continue
+        diff = abs(loss - b.loss) / abs(b.loss) if abs(b.loss) > 1e-10 else abs(loss - b.loss)
+        good = diff <= tolerance and not r.error                  # NaN compares false: a diverged run fails
+        ok, bad = ok + good, bad + (not good)
+        lines.append(f"  {'PASS' if good else 'FAIL'}  {r.model:<16} {r.mode:<20} loss={loss:.6f} (baseline={b.loss:.6f}, diff={diff * 100:.1f}%)")
+    return ok, bad, lines

@@ -195,3 +195,39 @@ def _is_number(tok: str) -> bool:
         return True
     except ValueError:
         return False
+
+
+def argparse_schema(parser, strict: bool = True) -> Dict[str, Any]:
+    """The `--fdl-schema` description of an `argparse.ArgumentParser`: `{"options": {name: {type, short, description,
+    default, choices}}, "args": [{name, description, ...}], "strict": bool}`. A program that already parses with argparse
+    answers the probe with `answer_schema_probe(parser)` as its first line."""
+    import argparse
+    options: Dict[str, Any] = {}
+    args: List[Dict[str, Any]] = []
+    for a in parser._actions:
+        if isinstance(a, argparse._HelpAction):
+            continue
+        kind = ("bool" if isinstance(a, (argparse._StoreTrueAction, argparse._StoreFalseAction)) else
+                {int: "int", float: "float"}.get(a.type, "string"))
+        decl: Dict[str, Any] = {"type": kind, "description": a.help or ""}
+        if a.default not in (None, False, "", argparse.SUPPRESS) and kind != "bool":
+            decl["default"] = a.default
+        if a.choices:
+            decl["choices"] = list(a.choices)
+        longs = [o for o in a.option_strings if o.startswith("--")]
+        shorts = [o for o in a.option_strings if o.startswith("-") and not o.startswith("--")]
+        if not a.option_strings:
+            args.append({"name": a.dest, **decl, "variadic": a.nargs in ("*", "+")})
+            continue
+        if shorts:
+            decl["short"] = shorts[0][1:]
+        options[(longs[0] if longs else shorts[0]).lstrip("-")] = decl
+    return {"options": options, "args": args, "strict": strict}
+
+
+def answer_schema_probe(parser, argv: Optional[Sequence[str]] = None) -> None:
+    """Print the schema and exit 0 when the program was started with `--fdl-schema` (before any real work)."""
+    argv = sys.argv[1:] if argv is None else argv
+    if "--fdl-schema" in argv:
+        print(json.dumps(argparse_schema(parser), indent=2))
+        raise SystemExit(0)

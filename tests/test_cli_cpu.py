@@ -389,3 +389,20 @@ def test_libtorch_download_plan_archive_install_and_build_plan(tmp_path, monkeyp
     lt.build_docker(plan, run=lambda cmd: calls.append(cmd) or 0, capture=lambda cmd, text=True: "abc123\n")
     assert calls[0][:2] == ["docker", "build"] and "TORCH_CUDA_ARCH_LIST=10.0" in calls[0] and calls[1][:2] == ["docker", "cp"]
     assert calls[1][2] == "abc123:/opt/libtorch/." and calls[2] == ["docker", "rm", "abc123"]
+
+
+def test_the_repositorys_own_manifests_resolve(capsys):
+    """`fdl.yml.example` at the root and the sub-command manifests of `ddp_bench/` and `benchmarks/` load, their presets pass
+    the entries' own schemas, and the composed lines are what the docs promise."""
+    from flodl_b200.cli.manifest import compose, load_manifest as load, resolve
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "fdl.yml.example")
+    man, _ = load(root)
+    assert {"build", "test", "test-gpu", "bench", "ddp-bench", "bench-models"} <= set(man["commands"])
+    assert compose(resolve(root, ["test", "--", "-k", "ddp"])) == 'python -m pytest tests -q -m "not gpu" -k ddp -x'
+    for sub in ("ddp-bench", "bench-models"):
+        sub_man = resolve(root, [sub]).manifest
+        for preset in sub_man["commands"]:
+            line = compose(resolve(root, [sub, preset]))                     # raises if a preset sets an undeclared option
+            assert line.startswith("PYTHONPATH=.. python -m ")
+    assert compose(resolve(root, ["ddp-bench", "quick"])).endswith("--epochs 1 --seed 42 --output runs/ --model mlp --mode solo-0 --tiny")
+    assert "--output" not in compose(resolve(root, ["ddp-bench", "report"]))
