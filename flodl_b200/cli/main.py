@@ -107,6 +107,9 @@ class ExportArgs(FdlArgs):
 class InitArgs(FdlArgs):
     """Scaffold a small training project that uses this package."""
     name: str = arg(help="project directory to create", positional=True)
+    docker: bool = arg(False, help="commands run inside docker compose services (Dockerfile, Dockerfile.cuda, docker-compose.yml)")
+    native: bool = arg(False, help="no docker files; commands run on the host")
+    with_hf: bool = arg(False, help="also scaffold the flodl-hf playground")
 
 
 def _repo_root() -> str:
@@ -133,48 +136,19 @@ def export_hf(argv: List[str]) -> int:
     return 0
 
 
-_TEMPLATE_MAIN = '''"""Minimal training script: a small MLP on synthetic data."""
-import torch
-
-from flodl_b200 import Adam, FlowBuilder, GELU, LayerNorm, Linear, Variable, clip_grad_norm, mse_loss
-
-model = (FlowBuilder.from_(Linear(2, 16)).through(GELU()).through(LayerNorm(16)).also(Linear(16, 16)).through(Linear(16, 2)).build())
-opt = Adam(model.parameters(), 0.01)
-x = torch.randn(32, 2)
-y = torch.stack([torch.sin(x[:, 0]), torch.cos(x[:, 1])], dim=1)
-for step in range(200):
-    loss = mse_loss(model.forward(Variable.wrap(x)), Variable.wrap(y))
-    loss.backward()
-    clip_grad_norm(model.parameters(), 1.0)
-    opt.step()
-    opt.zero_grad()
-    if step % 50 == 0:
-        print(step, loss.item())
-'''
-
-_TEMPLATE_MANIFEST = '''description: {name}
-
-commands:
-  train:
-    description: Train the model
-    run: python train.py
-  test:
-    description: Run the tests
-    run: python -m pytest -q
-'''
-
-
 def init(argv: List[str]) -> int:
+    from .scaffold import project_files, write_files
     a = InitArgs.parse(argv, "fdl init")
+    if a.docker and a.native:
+        print("fdl init: --docker and --native exclude each other", file=sys.stderr)
+        return 2
     if os.path.exists(a.name):
         print(f"fdl init: {a.name} already exists", file=sys.stderr)
         return 1
-    os.makedirs(a.name)
-    with open(os.path.join(a.name, "train.py"), "w") as f:
-        f.write(_TEMPLATE_MAIN)
-    with open(os.path.join(a.name, "fdl.yml"), "w") as f:
-        f.write(_TEMPLATE_MANIFEST.format(name=a.name))
-    print(f"created {a.name}/train.py and {a.name}/fdl.yml")
+    import shutil
+    mode = "docker" if a.docker else "native" if a.native else ("docker" if shutil.which("docker") else "native")
+    written = write_files(a.name, project_files(os.path.basename(os.path.normpath(a.name)), mode, a.with_hf))
+    print(f"created {a.name}/ ({mode} mode): " + ", ".join(sorted(written)))
     return 0
 
 

@@ -48,7 +48,7 @@ class InstallArgs(FdlArgs):
 @dataclass
 class AddArgs(FdlArgs):
     """Add a training scaffold to an existing directory."""
-    target: str = arg(".", positional=True, help="directory to add the files to")
+    target: str = arg(".", positional=True, help="directory to add the files to, or `flodl-hf` (alias `hf`) for the Hugging Face playground")
     playground: bool = arg(False, help="also add playground.py (graph-builder tour)")
     install: bool = arg(False, help="build the native library afterwards")
 
@@ -181,6 +181,16 @@ commands:
 
 def add(argv: List[str]) -> int:
     a = AddArgs.parse(argv, "fdl add")
+    if a.target in ("flodl-hf", "hf"):
+        from .scaffold import add_flodl_hf
+        try:
+            for rel in add_flodl_hf(os.getcwd()):
+                print(f"created {rel}")
+        except FileExistsError as e:
+            print(f"fdl add: {e}", file=sys.stderr)
+            return 1
+        print("try: python -m flodl_b200.cli flodl-hf classify")
+        return 0
     root = os.path.abspath(a.target)
     if not os.path.isdir(root):
         print(f"fdl add: {root} is not a directory", file=sys.stderr)

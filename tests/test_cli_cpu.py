@@ -406,3 +406,44 @@ def test_the_repositorys_own_manifests_resolve(capsys):
             assert line.startswith("PYTHONPATH=.. python -m ")
     assert compose(resolve(root, ["ddp-bench", "quick"])).endswith("--epochs 1 --seed 42 --output runs/ --model mlp --mode solo-0 --tiny")
     assert "--output" not in compose(resolve(root, ["ddp-bench", "report"]))
+
+
+def test_init_modes_and_add_flodl_hf(tmp_path, monkeypatch, capsys):
+    from flodl_b200.cli.manifest import compose, resolve
+    monkeypatch.chdir(tmp_path)
+    assert main(["init", "dk", "--docker", "--with-hf"]) == 0
+    files = {os.path.relpath(os.path.join(d, f), tmp_path / "dk") for d, _, fs in os.walk(tmp_path / "dk") for f in fs}
+    assert {"train.py", "fdl.yml.example", ".gitignore", "README.md", "requirements.txt", "Dockerfile", "Dockerfile.cuda", "docker-compose.yml",
+            "flodl-hf/classify.py", "flodl-hf/fill_mask.py", "flodl-hf/fdl.yml", "flodl-hf/README.md"} == files
+    m = str(tmp_path / "dk" / "fdl.yml.example")
+    assert compose(resolve(m, ["train"])) == "docker compose run --rm dev bash -c 'python train.py'"
+    assert compose(resolve(m, ["cuda-train"])).startswith("docker compose run --rm cuda ")
+    assert compose(resolve(m, ["flodl-hf", "classify"])) == "docker compose run --rm dev bash -c 'python classify.py'"
+    import yaml
+    assert set(yaml.safe_load(open(tmp_path / "dk" / "docker-compose.yml"))["services"]) == {"dev", "cuda"}
+    for script in ("train.py", "flodl-hf/classify.py", "flodl-hf/fill_mask.py"):
+        compile(open(tmp_path / "dk" / script).read(), script, "exec")
+    assert main(["init", "nt", "--native"]) == 0
+    files = set(os.listdir(tmp_path / "nt"))
+    assert "Dockerfile" not in files and "docker-compose.yml" not in files and "flodl-hf" not in files
+    m = str(tmp_path / "nt" / "fdl.yml.example")
+    assert compose(resolve(m, ["train"])) == "python train.py" and "shell" not in open(m).read()
+    assert main(["init", "x", "--docker", "--native"]) == 2
+    capsys.readouterr()
+    monkeypatch.chdir(tmp_path / "nt")
+    assert main(["add", "hf"]) == 0 and "created flodl-hf/classify.py" in capsys.readouterr().out
+    assert "docker:" not in open(tmp_path / "nt" / "flodl-hf" / "fdl.yml").read()         # native project: no docker lines
+    assert main(["add", "flodl-hf"]) == 1 and "already exists" in capsys.readouterr().err
+    (tmp_path / "bare").mkdir()
+    monkeypatch.chdir(tmp_path / "bare")
+    assert main(["add", "flodl-hf"]) == 1 and "initialised flodl project" in capsys.readouterr().err
+
+
+def test_scaffolded_training_script_runs(tmp_path):
+    from flodl_b200.cli.scaffold import TRAIN
+    script = tmp_path / "train.py"
+    script.write_text(TRAIN.replace("range(200)", "range(3)"))
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, str(script)], cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert os.path.isfile(tmp_path / "model.fdl") and out.stdout.startswith("0 ")
