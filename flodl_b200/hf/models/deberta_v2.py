@@ -74,6 +74,9 @@ class DebertaV2Config:
             kinds = sorted(pat.split("|") if isinstance(pat, str) else list(pat))
             if kinds != ["c2p", "p2c"]:
                 raise TensorError(f"DebertaV2Config: pos_att_type {pat!r} is not supported — expected c2p|p2c")
+        if cj.optional_bool(v, "legacy", False):
+            raise TensorError("DebertaV2Config: legacy = true is not supported: the masked-LM head here is the non-legacy one "
+                              "(`lm_predictions.lm_head`: dense(H, H), GELU, LayerNorm, tied decoder), not `cls.predictions`.")
         if str(v.get("norm_rel_ebd", "layer_norm")) != "layer_norm":
             raise TensorError("DebertaV2Config: norm_rel_ebd must be \"layer_norm\"")
         mrp = cj.optional_i64(v, "max_relative_positions", -1)
@@ -98,7 +101,7 @@ class DebertaV2Config:
              "position_buckets": self.position_buckets, "max_relative_positions": self.max_relative_positions,
              "hidden_act": cj.emit_hidden_act(self.hidden_act), "pooler_hidden_act": cj.emit_hidden_act(self.pooler_hidden_act),
              "pooler_hidden_size": self.hidden_size, "relative_attention": True, "share_att_key": True, "position_biased_input": False,
-             "pos_att_type": ["p2c", "c2p"], "norm_rel_ebd": "layer_norm", "type_vocab_size": 0}
+             "pos_att_type": ["p2c", "c2p"], "norm_rel_ebd": "layer_norm", "type_vocab_size": 0, "legacy": False}
         if self.pad_token_id is not None:
             m["pad_token_id"] = self.pad_token_id
         return json.dumps(emit_labels(m, self), indent=2)
@@ -110,13 +113,19 @@ class DebertaV2Config:
 
 # ---- relative positions ----------------------------------------------------------------------------
 def make_log_bucket_position(rel_pos: torch.Tensor, bucket_size: int, max_position: int) -> torch.Tensor:
-    """Distances below bucket_size/2 keep their value; larger ones share logarithmically spaced buckets."""
+    """Distances up to bucket_size/2 keep their value; larger ones share logarithmically spaced buckets, `mid .. 2 mid - 1`
+    at `max_position - 1`. A distance beyond `max_position - 1` (a sequence longer than the model's relative range) maps
+    past the last bucket, as in the Transformers implementation; the index clamp of the attention then folds it onto the
+    outermost embedding row of its side. The ratio is snapped to 1 within rounding error so that the distance
+    `max_position - 1` itself lands exactly on the last bucket."""
     mid = bucket_size // 2
     rp = rel_pos.float()
     sign = torch.sign(rp)
     near = (rp < mid) & (rp > -mid)
     abs_pos = torch.where(near, torch.full_like(rp, float(mid - 1)), rp.abs())
-    log_pos = torch.ceil(torch.clamp(torch.log(abs_pos / mid) / math.log((max_position - 1) / mid), 0.0, 1.0) * (mid - 1)) + mid
+    ratio = torch.log(abs_pos / mid) / math.log((max_position - 1) / mid)
+    ratio = torch.where((ratio - 1.0).abs() < 1e-5, torch.ones_like(ratio), ratio).clamp_min(0.0)
+    log_pos = torch.ceil(ratio * (mid - 1)) + mid
     return torch.where(rp.abs() <= mid, rp, log_pos * sign).long()
 
 

@@ -89,14 +89,31 @@ def _outputs(out, head: str) -> List[torch.Tensor]:
     return [out.logits]
 
 
-def compare(family: str, head: str, device: str = "cpu", seed: int = 0) -> Tuple[float, Optional[str]]:
-    """(largest |difference|, note). Raises ImportError when `transformers` is missing."""
+def compare(family: str, head: str, device: str = "cpu", seed: int = 0, stress: bool = False, seq_len: int = 12) -> Tuple[float, Optional[str]]:
+    """(largest |difference|, note). Raises ImportError when `transformers` is missing.
+
+    `stress` redraws the reference model's matrices with a standard deviation of 0.3 instead of the initialiser's 0.02.
+    With the small default weights every attention score is close to zero and whole terms of a layer (DeBERTa's
+    position-to-content bias, for one) can be wrong without moving the output beyond the tolerance; with weights of
+    ordinary trained size they cannot. `seq_len` beyond the tiny model's relative-position range exercises the
+    out-of-range buckets."""
     import transformers as tf
     hc, prefix, key_prefix = _tiny(tf, family)
     if head == "qa":
         hc.num_labels = 2                              # start / end logits
+    if seq_len + 2 > hc.max_position_embeddings:
+        hc.max_position_embeddings = seq_len + 2
     torch.manual_seed(seed)
     hf = getattr(tf, prefix + _HF_SUFFIX[head])(hc).eval().to(device)
+    if stress:
+        with torch.no_grad():
+            for n, p in hf.named_parameters():
+                if p.dim() >= 2 and "embeddings" not in n:
+                    p.normal_(0, 0.3)
+                elif n.endswith("bias"):
+                    p.normal_(0, 0.1)
+        if hasattr(hf, "tie_weights"):
+            hf.tie_weights()
     cfg = AutoConfig.from_json_str(hc.to_json_string())
     if head == "base":
         graph = AutoModel.from_config(cfg, torch.device(device), with_pooler=False)
@@ -108,8 +125,8 @@ def compare(family: str, head: str, device: str = "cpu", seed: int = 0) -> Tuple
     st.load_safetensors_into_graph_with_rename_allow_unused(graph, _state_bytes(hf), rename)
     pad = int(getattr(hc, "pad_token_id", 0) or 0)
     g = torch.Generator().manual_seed(seed + 1)
-    ids = torch.randint(5, hc.vocab_size, (2, 12), generator=g)
-    ids[0, 8:] = pad
+    ids = torch.randint(5, hc.vocab_size, (2, seq_len), generator=g)
+    ids[0, seq_len - 4:] = pad
     mask = (ids != pad).float()
     ids, mask = ids.to(device), mask.to(device)
     with torch.no_grad():
@@ -128,12 +145,12 @@ def compare(family: str, head: str, device: str = "cpu", seed: int = 0) -> Tuple
     return worst, None
 
 
-def run(families, heads, device: str, tol: float) -> Dict[Tuple[str, str], Tuple[Optional[float], Optional[str]]]:
+def run(families, heads, device: str, tol: float, stress: bool = False, seq_len: int = 12) -> Dict[Tuple[str, str], Tuple[Optional[float], Optional[str]]]:
     res = {}
     for f in families:
         for h in heads:
             try:
-                res[(f, h)] = compare(f, h, device)
+                res[(f, h)] = compare(f, h, device, 0, stress, seq_len)
             except ImportError:
                 raise
             except Exception as e:  # noqa: BLE001  (a cell that cannot be built is reported, the matrix goes on)
@@ -159,10 +176,12 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", default=",".join(HEADS))
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--tol", type=float, default=2e-4)
+    ap.add_argument("--stress", action="store_true", help="weights of trained size (std 0.3) instead of the initialiser's 0.02")
+    ap.add_argument("--seq-len", type=int, default=12, help="sequence length of the probe batch")
     a = ap.parse_args(argv)
     heads = [h for h in a.heads.split(",") if h]
     try:
-        res = run(a.families, heads, a.device, a.tol)
+        res = run(a.families, heads, a.device, a.tol, a.stress, a.seq_len)
     except ImportError as e:
         print(f"parity: the `transformers` package is required ({e})", file=sys.stderr)
         return 2

@@ -169,6 +169,16 @@ if __name__ == "__main__":
     name = sys.argv[1]
     comm.init_process_group("gloo", timeout_s=20 if name == "run_worker_failure" else 120)
     SCENARIOS[name]()
-    comm.barrier()
-    comm.destroy_process_group()
+    try:
+        comm.barrier()
+    except RuntimeError:
+        # the survivor of `run_worker_failure` may have been inside an averaging collective when its peer raised; that
+        # collective ends with the group's timeout and gloo then closes the pair, so no further collective can run
+        if name != "run_worker_failure":
+            raise
+    try:
+        comm.destroy_process_group()
+    except RuntimeError:
+        if name != "run_worker_failure":
+            raise
     print(f"OK {name}")

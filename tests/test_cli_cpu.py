@@ -406,6 +406,8 @@ def test_the_repositorys_own_manifests_resolve(capsys):
             assert line.startswith("PYTHONPATH=.. python -m ")
     assert compose(resolve(root, ["ddp-bench", "quick"])).endswith("--epochs 1 --seed 42 --output runs/ --model mlp --mode solo-0 --tiny")
     assert "--output" not in compose(resolve(root, ["ddp-bench", "report"]))
+    assert compose(resolve(root, ["flodl-hf", "verify-export", "--", "out", "--no-hub-source"])).endswith("flodl_b200.hf.verify_export out --no-hub-source")
+    assert compose(resolve(root, ["flodl-hf", "export", "--", "--hub", "bert-base-uncased", "--out", "x"])).endswith("export_tool --hub bert-base-uncased --out x")
 
 
 def test_init_modes_and_add_flodl_hf(tmp_path, monkeypatch, capsys):

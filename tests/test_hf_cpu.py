@@ -1,6 +1,7 @@
 """HF encoder families on CPU: numerical parity with the `transformers` implementations (tiny random
 configs, weights moved through safetensors), key maps, config round trips, safetensors validation."""
 import json
+import os
 
 import pytest
 import torch
@@ -538,3 +539,89 @@ def test_deberta_stage_modules_match_the_fused_layer():
     assert out.forward_pair(up, x).t.shape == (2, 5, 16)
     assert [p.name for p in so.parameters()] == ["dense.weight", "dense.bias", "LayerNorm.weight", "LayerNorm.bias"]
     assert [p.name for p in it.parameters()] == ["dense.weight", "dense.bias"] and out.dense.weight.t.shape == (16, 32)
+
+
+# ---- export tool, export verification, stress parity ---------------------------------------------------------------
+def test_deberta_log_buckets_match_transformers_inside_and_beyond_the_relative_range():
+    from transformers.models.deberta_v2.modeling_deberta_v2 import make_log_bucket_position as theirs
+    for bucket, maxp, seq in ((4, 8, 12), (8, 16, 40), (32, 64, 64), (256, 512, 512), (256, 512, 700)):
+        ids = torch.arange(seq)
+        rel = ids[:, None] - ids[None, :]
+        mine = deberta_v2.make_log_bucket_position(rel, bucket, maxp)
+        assert torch.equal(mine, theirs(rel, bucket, maxp).long()), (bucket, maxp, seq)
+
+
+@pytest.mark.parametrize("family", ["bert", "albert", "deberta-v2"])
+def test_parity_holds_with_weights_of_trained_size_and_long_sequences(family):
+    """Initialiser-sized weights (std 0.02) keep every attention score near zero and can hide a wrong term; std 0.3 cannot."""
+    from flodl_b200.hf import parity
+    for head in ("base", "mlm"):
+        worst, note = parity.compare(family, head, stress=True, seq_len=20)
+        assert note is None and worst < 1e-3, (family, head, worst, note)
+
+
+def test_deberta_config_emits_and_checks_legacy():
+    cfg = deberta_v2.DebertaV2Config(vocab_size=40, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32,
+                                     max_position_embeddings=16, position_buckets=4, max_relative_positions=8)
+    emitted = json.loads(cfg.to_json_str())
+    assert emitted["legacy"] is False
+    assert deberta_v2.DebertaV2Config.from_json_str(cfg.to_json_str()).hidden_size == 16
+    emitted["legacy"] = True
+    with pytest.raises(Exception, match="legacy = true is not supported"):
+        deberta_v2.DebertaV2Config.from_json_str(json.dumps(emitted))
+
+
+def test_export_tool_hub_and_checkpoint_modes_and_verify_export(tmp_path, capsys):
+    from flodl_b200.hf import export_tool, verify_export
+    repo = tmp_path / "src"
+    _tiny_repo(repo, transformers.BertForSequenceClassification, "BertForSequenceClassification", num_labels=3)
+    out = str(tmp_path / "exp")
+    assert export_tool.main(["--hub", str(repo), "--out", out]) == 0
+    cfg = json.loads(open(os.path.join(out, "config.json")).read())
+    assert cfg["flodl_source_repo"] == str(repo) and cfg["architectures"] == ["BertForSequenceClassification"]
+    rep = verify_export.verify(out)                                   # the stamped source is found and compared bit for bit
+    assert rep["ok"] and rep["loadable"] and rep["source_parity"] and rep["max_abs_diff_vs_source"] == 0.0 and rep["hub_source"] == str(repo)
+    assert rep["auto_class"] == "AutoModelForSequenceClassification" and rep["max_abs_diff_vs_transformers"] < 1e-4
+    base = str(tmp_path / "exp_base")
+    assert export_tool.main(["--hub", str(repo), "--out", base, "--head", "base"]) == 0     # a head checkpoint re-exported as an encoder
+    assert json.loads(open(os.path.join(base, "config.json")).read())["architectures"] == ["BertModel"]
+    assert verify_export.main([base, "--no-hub-source"]) == 0
+    capsys.readouterr()
+    # checkpoint mode: a graph saved as .fdl with its config sidecar
+    head = bert.BertForTokenClassification.on_device(bert.BertConfig.from_json_str((repo / "config.json").read_text()), 3)
+    ck = str(tmp_path / "m.fdl")
+    head.graph().save_checkpoint(ck)
+    out2 = str(tmp_path / "exp2")
+    assert export_tool.main(["--checkpoint", ck, "--out", out2]) == 0
+    assert verify_export.main([out2]) == 2 and "no upstream to compare with" in capsys.readouterr().err
+    assert verify_export.main([out2, "--no-hub-source"]) == 0
+    assert json.loads(capsys.readouterr().out)["architecture"] == "BertForTokenClassification"
+    assert export_tool.main(["--out", out2]) == 2 and "exactly one of" in capsys.readouterr().err
+    assert export_tool.main(["--checkpoint", ck, "--head", "qa", "--out", out2]) == 2
+    assert verify_export.auto_class_for("XLMRobertaForQuestionAnswering") == ("AutoModelForQuestionAnswering", "qa")
+    assert verify_export.auto_class_for("AlbertModel") == ("AutoModel", "base")
+    with pytest.raises(Exception, match="unsupported architecture"):
+        verify_export.auto_class_for("BertForPreTraining")
+
+
+def test_verify_export_flags_a_damaged_export(tmp_path):
+    from flodl_b200.hf import export_tool, verify_export
+    repo = tmp_path / "src"
+    _tiny_repo(repo, transformers.BertModel, "BertModel")
+    out = str(tmp_path / "exp")
+    export_tool.export_from_hub(str(repo), out)
+    tensors = st.read_safetensors(open(os.path.join(out, "model.safetensors"), "rb").read())
+    key = next(k for k in tensors if k.endswith("attention.self.query.weight"))
+    tensors["encoder.layer.0.attention.self.queri.weight"] = tensors.pop(key)          # a renamed key: one missing, one unexpected
+    open(os.path.join(out, "model.safetensors"), "wb").write(st.write_safetensors(tensors))
+    rep_keys = verify_export._load_with_transformers(transformers, "AutoModel", out)
+    assert any("query.weight" in k for k in rep_keys[1]) and any("queri" in k for k in rep_keys[2])
+
+
+def test_export_verification_matrix_cells(tmp_path):
+    from flodl_b200.hf import verify_export
+    res = verify_export.verify_matrix(["distilbert", "deberta-v2"], ["base", "qa", "mlm"], str(tmp_path / "stage"), keep=True)
+    assert all(not isinstance(r, str) and r["ok"] for r in res.values()), res
+    assert os.path.isfile(tmp_path / "stage" / "deberta-v2-mlm" / "model.safetensors")
+    grid = verify_export.render_matrix(res, ["distilbert", "deberta-v2"], ["base", "qa", "mlm"])
+    assert grid.count("PASS") == 6 and "FAIL" not in grid
