@@ -625,3 +625,48 @@ def test_export_verification_matrix_cells(tmp_path):
     assert os.path.isfile(tmp_path / "stage" / "deberta-v2-mlm" / "model.safetensors")
     grid = verify_export.render_matrix(res, ["distilbert", "deberta-v2"], ["base", "qa", "mlm"])
     assert grid.count("PASS") == 6 and "FAIL" not in grid
+
+
+# ---- runnable demos, on local tiny repos --------------------------------------------------------------------------------
+def test_examples_list_and_run_on_local_repos(tmp_path, capsys):
+    from flodl_b200.hf import examples
+    assert examples.main([]) == 0
+    listing = capsys.readouterr().out
+    for name in ("auto-classify", "bert-embed", "bert-classify", "bert-ner", "bert-qa", "roberta-embed", "roberta-qa", "distilbert-classify",
+                 "distilbert-ner", "distilbert-finetune"):
+        assert name in listing
+    assert len(examples.EXAMPLES) == 14
+    assert examples.main(["nope"]) == 2
+    lines = []
+    base = tmp_path / "base"
+    _tiny_repo(base, transformers.BertModel, "BertModel")
+    emb = examples.embed(str(base), ["paris is the capital", "berlin", "paris is the capital"], lines.append)
+    assert emb.shape == (3, 32) and torch.allclose(emb[0], emb[2], atol=1e-5) and abs(float(emb[0] @ emb[0]) - 1.0) < 1e-5
+    cls = tmp_path / "cls"
+    _tiny_repo(cls, transformers.BertForSequenceClassification, "BertForSequenceClassification", num_labels=2, id2label={0: "neg", 1: "pos"},
+               label2id={"neg": 0, "pos": 1})
+    assert examples.main(["auto-classify", "--repo", str(cls), "paris is the capital", "berlin"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("\n") == 2 and ("neg" in out or "pos" in out)
+    tok = tmp_path / "tok"
+    _tiny_repo(tok, transformers.BertForTokenClassification, "BertForTokenClassification", num_labels=3)
+    assert len(examples.ner(str(tok), ["paris is the capital of france"], lines.append)[0]) == 8
+    qa_repo = tmp_path / "qa"
+    _tiny_repo(qa_repo, transformers.BertForQuestionAnswering, "BertForQuestionAnswering")
+    assert examples.main(["bert-qa", "--repo", str(qa_repo), "where is paris", "paris is the capital of france"]) == 0
+    assert "Q: where is paris" in capsys.readouterr().out
+    assert examples.main(["bert-qa", "--repo", str(tmp_path / "missing")]) == 1
+
+
+def test_finetune_example_lowers_the_loss_and_exports(tmp_path):
+    from flodl_b200.hf import examples, verify_export
+    cls = tmp_path / "cls"
+    _tiny_repo(cls, transformers.BertForSequenceClassification, "BertForSequenceClassification", num_labels=2, id2label={0: "neg", 1: "pos"},
+               label2id={"neg": 0, "pos": 1}, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    lines = []
+    out_dir = str(tmp_path / "tuned")
+    curve, preds = examples.finetune(str(cls), ["paris is the capital", "berlin germany", "france", "where what"], [1, 0, 1, 0], steps=30, lr=5e-3,
+                                     out=lines.append, export_dir=out_dir)
+    assert curve[-1] < 0.5 * curve[0] and preds == ["pos", "neg", "pos", "neg"]
+    rep = verify_export.verify(out_dir, no_hub_source=True)
+    assert rep["ok"] and rep["architecture"] == "BertForSequenceClassification"
