@@ -163,7 +163,7 @@ from flodl_b200.graph import FlowBuilder
 
 g = (FlowBuilder.from_(nn.Linear(8, 16)).tag("stem").through(nn.GELU())
      .also(nn.Linear(16, 16)).tag("residual").through(nn.LayerNorm(16)).through(nn.Linear(16, 4)).build())
-print(g.to_dot())
+print(g.dot())
 print(g.forward(Variable.wrap(torch.randn(3, 8))).t.shape)
 '''
 

@@ -204,15 +204,27 @@ def _pick_dw_plan(m_out: int, n_out: int, k_red: int):
 _SIDE = {"on": os.environ.get("FLODL_B200_SIDE_DW", "1") not in ("0", "false", "off"), "streams": {}}
 
 
+# Outside a capture a step of small layers is bound by the host's launch rate, not by the GPU: there the two extra
+# stream switches, two waits and the event of a fork (measured on B200: 40..70 us of host time per linear backward,
+# 1.5 ms of a 9 ms eager BERT-base step) cost more than the overlap returns. So an eager backward forks only for
+# products large enough to keep the GPU busy longer than the host needs to issue them (`work`, in multiply-adds, at least
+# FLODL_B200_EAGER_FORK_MACS, default 2^35); a capture always forks (replay pays no host time).
+_EAGER_FORK_MACS = int(os.environ.get("FLODL_B200_EAGER_FORK_MACS", str(1 << 35)))
+
+
 class _Fork:
     """`with fork: ...` runs the body on the side stream (after everything issued so far on the
     current stream); `fork.join()` makes the current stream wait for it."""
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, work: int = 0):
         self.active = _SIDE["on"] and device.type == "cuda"
         if self.active:
+            capturing = torch.cuda.is_current_stream_capturing()
+            if not capturing and work < _EAGER_FORK_MACS:
+                self.active = False
+                return
             self.main = torch.cuda.current_stream(device)
-            key = (device.index, torch.cuda.is_current_stream_capturing())
+            key = (device.index, capturing)
             side = _SIDE["streams"].get(key)
             if side is None:
                 side = _SIDE["streams"][key] = torch.cuda.Stream(device)
@@ -222,14 +234,13 @@ class _Fork:
     def __enter__(self):
         if self.active:
             self.side.wait_stream(self.main)
-            self.ctx = torch.cuda.stream(self.side)
-            self.ctx.__enter__()
+            torch.cuda.set_stream(self.side)          # the plain call: the `torch.cuda.stream()` context manager costs several times as much
             self.used = True
         return self
 
     def __exit__(self, *exc):
         if self.active:
-            self.ctx.__exit__(*exc)
+            torch.cuda.set_stream(self.main)
         return False
 
     def join(self) -> None:
@@ -312,7 +323,7 @@ class _LinearFn(torch.autograd.Function):
             _launched()
         dy2 = _as_operand(dy2)
         dx = dw = db = None
-        fork = _Fork(dy.device)
+        fork = _Fork(dy.device, dy2.shape[0] * dy2.shape[1] * x2.shape[1])
         with fork:
             if ctx.needs_input_grad[1]:
                 dw = _weight_grad(dy2, x2, w)
@@ -385,7 +396,7 @@ class _FeedForwardFn(torch.autograd.Function):
         dy2 = _as_operand(dy.reshape(-1, N))
         M, F1 = a.shape
         dpre = _new_rows(M, F1, BF16, dy.device)
-        fork = _Fork(dy.device)
+        fork = _Fork(dy.device, M * F1 * N)
         with fork:       # the second layer's parameter gradients need only dy: beside the d(pre-activation) GEMM
             dw2 = _weight_grad(dy2, a, w2) if ctx.needs_input_grad[3] else None
             db2 = _bias_grad(dy2, b2) if (b2 is not None and ctx.needs_input_grad[4]) else None
@@ -607,7 +618,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         alpha = g.detach().float().reshape(1)
         n_dyn = None if counts is None else counts[0:1]
         dx = dw = db = None
-        fork = _Fork(dl.device)
+        fork = _Fork(dl.device, dl.shape[0] * dl.shape[1] * x2.shape[1])
         with fork:
             if ctx.needs_input_grad[1]:
                 dw = _weight_grad(dl, x2, w, alpha=alpha, k_dyn=n_dyn, k_hint=None if counts is None else max(64, x2.shape[0] // 6))
