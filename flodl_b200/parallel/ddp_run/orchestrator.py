@@ -98,18 +98,21 @@ class DdpHandle:
                 return out
 
     def next_metrics(self, timeout: Optional[float] = None) -> Optional[EpochMetrics]:
-        """Blocks until the next epoch has been aggregated; None once the job is over."""
+        """Blocks until the next epoch has been aggregated. None once the job is over (the coordinator has finished and
+        nothing is queued), or when `timeout` seconds pass without a new epoch."""
+        import time
+        deadline = None if timeout is None else time.monotonic() + float(timeout)
         while True:
             try:
-                return self._metrics.get(timeout=0.1 if timeout is None else timeout)
+                return self._metrics.get(timeout=0.1)
             except queue.Empty:
-                if timeout is not None:
-                    return None
                 if self._coordinator is None or not self._coordinator.is_alive():
                     try:
                         return self._metrics.get_nowait()
                     except queue.Empty:
                         return None
+                if deadline is not None and time.monotonic() >= deadline:
+                    return None
 
     def _abort_collectives(self) -> None:
         for w in self._gpu_workers:
