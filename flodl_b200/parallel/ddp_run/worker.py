@@ -93,6 +93,7 @@ class GpuWorker:
         self._loss_sum = 0.0
         self._loss_n = 0
         self._shutdown_seen = False
+        self._averaging_broken = False       # set when an averaging collective failed because a peer was gone
 
     @classmethod
     def new(cls, config: WorkerConfig, model_factory: Callable, optim_factory: Callable, dataset, transport, **kw) -> "GpuWorker":
@@ -248,9 +249,18 @@ class GpuWorker:
             self.load_averaged(msg.payload)
             self.steps_since_avg = 0
         elif k == "SyncNow":
-            if self.fixed_cadence is None:
+            if self.fixed_cadence is None and not self._averaging_broken:
                 log.debug(f"  ddp-worker: rank {self.rank_} SyncNow (step={self.local_step_}, epoch={self.current_epoch_})")
-                self.sync_now()
+                try:
+                    self.sync_now()
+                except RuntimeError as e:
+                    # A peer left between the coordinator's decision and this collective (its `Exiting` and our `SyncNow` crossed).
+                    # The weights are this rank's own again; it trains on alone, answers the coordinator so that nobody waits for
+                    # an acknowledgement, and takes part in no further averaging (the group is no longer whole).
+                    log.msg(f"  ddp: rank {self.rank_}: averaging failed ({type(e).__name__}: {str(e)[:120]}); continuing without it")
+                    self._averaging_broken = True
+                    self.steps_since_avg = 0
+                    self.tim.send(TimingSyncAck(self.rank_, self.local_step_, None))
         elif k == "StartEpoch":
             self.pending_plan = msg.payload
         elif k == "Throttle":
@@ -314,8 +324,13 @@ class GpuWorker:
             if self.cuda:
                 batch = [t.to(self.device_, non_blocking=True) for t in batch]
             self.train_step(batch, train_fn)
-            if self.fixed_cadence is not None and self.steps_since_avg >= self.fixed_cadence:
-                self.sync_now()
+            if self.fixed_cadence is not None and self.steps_since_avg >= self.fixed_cadence and not self._averaging_broken:
+                try:
+                    self.sync_now()
+                except RuntimeError as e:       # a peer is gone (see `dispatch_control`): train on alone
+                    log.msg(f"  ddp: rank {self.rank_}: averaging failed ({type(e).__name__}: {str(e)[:120]}); continuing without it")
+                    self._averaging_broken = True
+                    self.steps_since_avg = 0
             if self.handle_control():
                 return True
         if self.cuda:

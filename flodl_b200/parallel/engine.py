@@ -148,12 +148,16 @@ class TrainEngine:
         p = self.flat.params
         with torch.no_grad():
             pre = p.clone()
-            if weights is not None:
-                p.mul_(float(weights[self.rank]))
-                torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
-            else:
-                torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
-                p.div_(self.world)
+            try:
+                if weights is not None:
+                    p.mul_(float(weights[self.rank]))
+                    torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
+                else:
+                    torch.distributed.all_reduce(p, torch.distributed.ReduceOp.SUM)
+                    p.div_(self.world)
+            except RuntimeError:
+                p.copy_(pre)            # a peer left in the middle: keep this rank's own weights, whole
+                raise
             if alpha != 1.0:
                 p.copy_(torch.lerp(pre, p, float(alpha)))
             out = torch.stack([(p - pre).pow(2).sum(), p.pow(2).sum()])

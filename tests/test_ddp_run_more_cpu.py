@@ -340,3 +340,49 @@ def test_lr_is_the_same_whether_a_scheduler_runs_solo_or_inside_a_worker():
         w.train_step([x, y], _train_fn)
         got.append(w.current_lr())
     assert got == pytest.approx(solo)
+
+
+def test_worker_survives_an_averaging_collective_that_fails_because_a_peer_left():
+    """The coordinator's `SyncNow` and a peer's exit can cross: the collective then ends with an error on the survivor. It
+    keeps its own weights, acknowledges so that nobody waits, skips later averaging and goes on training."""
+    from flodl_b200.parallel.ddp_run.messages import EpochPlan, TimingSyncAck
+    w, t = _worker(total=64, batch=8)
+    calls = {"n": 0}
+
+    def broken(*a, **k):
+        calls["n"] += 1
+        raise RuntimeError("Connection closed by peer")
+    w.engine.average_params = broken
+    before = [p.t.detach().clone() for p in w.model().parameters()]
+    assert w.dispatch_control(ControlMsg.SyncNow()) is False
+    assert calls["n"] == 1 and w._averaging_broken
+    assert all(torch.equal(a, p.t) for a, p in zip(before, w.model().parameters()))
+    acks = []
+    while True:
+        m = t.box("tim0").try_recv()
+        if m is None:
+            break
+        acks.append(m)
+    assert any(isinstance(m, TimingSyncAck) for m in acks)
+    assert w.dispatch_control(ControlMsg.SyncNow()) is False and calls["n"] == 1          # no second attempt
+    assert w.run_epoch_plan(EpochPlan(0, 0, 64), _train_fn) is False and w.local_step() == 8
+
+
+def test_engine_average_restores_the_weights_when_the_collective_fails(monkeypatch):
+    from flodl_b200.parallel.engine import TrainEngine
+    m = nn.Linear(4, 2)
+    eng = TrainEngine(m, lambda ps: nn.SGD(ps, 0.1), grad_sync=False)
+    eng.world, eng.rank = 2, 0                                  # pretend a second rank exists; the collective below fails
+    eng.symm_stage = eng.symm_params = None
+    before = eng.flat.params.clone()
+
+    def boom(tensor, op=None):
+        tensor.mul_(3.0)                                        # a half-done reduction
+        raise RuntimeError("peer gone")
+    monkeypatch.setattr(torch.distributed, "all_reduce", boom)
+    with pytest.raises(RuntimeError, match="peer gone"):
+        eng.average_params()
+    assert torch.equal(eng.flat.params, before)
+    with pytest.raises(RuntimeError):
+        eng.average_params([0.5, 0.5])
+    assert torch.equal(eng.flat.params, before)
