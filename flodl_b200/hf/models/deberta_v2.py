@@ -74,7 +74,10 @@ class DebertaV2Config:
             kinds = sorted(pat.split("|") if isinstance(pat, str) else list(pat))
             if kinds != ["c2p", "p2c"]:
                 raise TensorError(f"DebertaV2Config: pos_att_type {pat!r} is not supported — expected c2p|p2c")
-        if cj.optional_bool(v, "legacy", False):
+        archs = v.get("architectures") or []
+        if cj.optional_bool(v, "legacy", False) and archs and str(archs[0]).endswith("ForMaskedLM"):
+            # `legacy` only selects the masked-LM head's layout; Transformers writes `legacy: true` into every config it
+            # saves, so for the encoder and the other heads the key is ignored
             raise TensorError("DebertaV2Config: legacy = true is not supported: the masked-LM head here is the non-legacy one "
                               "(`lm_predictions.lm_head`: dense(H, H), GELU, LayerNorm, tied decoder), not `cls.predictions`.")
         if str(v.get("norm_rel_ebd", "layer_norm")) != "layer_norm":

@@ -567,6 +567,8 @@ def test_deberta_config_emits_and_checks_legacy():
     assert emitted["legacy"] is False
     assert deberta_v2.DebertaV2Config.from_json_str(cfg.to_json_str()).hidden_size == 16
     emitted["legacy"] = True
+    assert deberta_v2.DebertaV2Config.from_json_str(json.dumps(emitted)).hidden_size == 16     # irrelevant for the encoder: ignored
+    emitted["architectures"] = ["DebertaV2ForMaskedLM"]
     with pytest.raises(Exception, match="legacy = true is not supported"):
         deberta_v2.DebertaV2Config.from_json_str(json.dumps(emitted))
 
