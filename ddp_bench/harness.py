@@ -47,6 +47,24 @@ class RunResult:
         return json.dumps(asdict(self))
 
 
+_TIMELINES: dict = {}       # (model, mode) -> the finished run's timeline, until `run()` has written it next to the result
+
+
+def _timeline(opts: RunOptions) -> Timeline:
+    """Events always; the background sampler (CPU, RAM, GPU utilisation and memory every 100 ms) only for runs whose
+    results are kept, since only those are analysed."""
+    tl = Timeline.new(100)
+    if opts.output_dir:
+        tl.start()
+    return tl
+
+
+def _keep_timeline(res: "RunResult", tl: Timeline) -> None:
+    tl.stop()
+    res.timeline_events = len(tl.events())
+    _TIMELINES[(res.model, res.mode)] = tl
+
+
 def _device(opts: RunOptions, index: int) -> torch.device:
     if opts.device == "cpu" or (opts.device == "auto" and not torch.cuda.is_available()):
         return torch.device("cpu")
@@ -85,11 +103,11 @@ def run_solo(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
     model = _factory(md, opts)(device)
     opt = md.optimizer(lr)(model.parameters())
     res = RunResult(md.name, mode.name(), 1, str(device), epochs, bpe, bs)
-    tl = Timeline()
+    tl = _timeline(opts)
     t_all = time.perf_counter()
     for e in range(epochs):
         t0 = time.perf_counter()
-        tl.event("epoch_start", epoch=e)
+        tl.event("EpochStart", epoch=e)
         perm = torch.randperm(x.shape[0], generator=torch.Generator().manual_seed(opts.seed + e))
         total = 0.0
         for b in range(bpe):
@@ -101,12 +119,12 @@ def run_solo(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
             total += loss.item()
         if device.type == "cuda":
             torch.cuda.synchronize(device)
-        tl.event("epoch_end", epoch=e)
+        tl.event("EpochEnd", epoch=e, loss=total / bpe)
         res.epoch_losses.append(total / bpe)
         res.epoch_ms.append((time.perf_counter() - t0) * 1e3)
     res.total_ms = (time.perf_counter() - t_all) * 1e3
     res.final_eval = _evaluate(md, model, x, y, device)
-    res.timeline_events = len(tl._events)
+    _keep_timeline(res, tl)
     return res
 
 
@@ -121,11 +139,11 @@ def run_sync(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
     model = _factory(md, opts)(device)
     Trainer.setup(model, None, md.optimizer(lr))
     res = RunResult(md.name, mode.name(), world, str(device), epochs, bpe, bs)
-    tl = Timeline()
+    tl = _timeline(opts)
     t_all = time.perf_counter()
     for e in range(epochs):
         t0 = time.perf_counter()
-        tl.event("epoch_start", epoch=e)
+        tl.event("EpochStart", epoch=e)
         perm = torch.randperm(x.shape[0], generator=torch.Generator().manual_seed(opts.seed + e))
         total = 0.0
         for b in range(bpe):
@@ -139,7 +157,7 @@ def run_sync(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
             loss.backward()
             model.step()
             total += loss.item()
-        tl.event("epoch_end", epoch=e)
+        tl.event("EpochEnd", epoch=e, loss=total / bpe)
         res.epoch_losses.append(total / bpe)
         res.epoch_ms.append((time.perf_counter() - t0) * 1e3)
     res.total_ms = (time.perf_counter() - t_all) * 1e3
@@ -151,7 +169,7 @@ def run_sync(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
         for dst, src in zip(plain.buffers(), model.buffers()):
             dst.get().copy_(src.get())
     res.final_eval = _evaluate(md, plain, x, y, device)
-    res.timeline_events = len(tl._events)
+    _keep_timeline(res, tl)
     return res
 
 
@@ -160,7 +178,7 @@ def run_builder(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
     world = comm.world_size() if comm.is_initialized() else 1
     device = _device(opts, comm.local_rank() if comm.is_initialized() else 0)
     x, y = md.dataset(bpe * bs, opts.seed, opts.tiny)
-    tl = Timeline()
+    tl = _timeline(opts)
     b = (Trainer.builder(_factory(md, opts), md.optimizer(lr), md.train_fn).dataset(TensorDataSet(x, y)).batch_size(bs).num_epochs(epochs)
          .policy(mode.policy).backend(mode.backend).timeline(tl))
     res = RunResult(md.name, mode.name(), world, str(device), epochs, bpe, bs)
@@ -187,7 +205,7 @@ def run_builder(md: ModelDef, mode: DdpMode, opts: RunOptions) -> RunResult:
     errs = handle.errors()
     if errs:
         res.error = "; ".join(str(e) for e in errs)
-    res.timeline_events = len(tl._events)
+    _keep_timeline(res, tl)
     if monitor is not None:
         monitor.finish()
     return res
@@ -209,4 +227,8 @@ def run(md: ModelDef, mode: DdpMode, opts: RunOptions) -> Optional[RunResult]:
         os.makedirs(opts.output_dir, exist_ok=True)
         with open(os.path.join(opts.output_dir, f"{md.name}__{mode.name()}.json"), "w") as f:
             f.write(res.json() + "\n")
+        tl = _TIMELINES.pop((res.model, res.mode), None)
+        if tl is not None:
+            tl.save_json(os.path.join(opts.output_dir, f"{md.name}__{mode.name()}.timeline.json"))
+    _TIMELINES.pop((res.model, res.mode), None)
     return res

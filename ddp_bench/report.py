@@ -16,6 +16,8 @@ from .models import all_models
 def load_results(directory: str) -> Dict[str, Dict[str, dict]]:
     out: Dict[str, Dict[str, dict]] = {}
     for path in sorted(glob.glob(os.path.join(directory, "*__*.json"))):
+        if path.endswith(".timeline.json"):
+            continue
         with open(path) as f:
             r = json.loads(f.readline())
         out.setdefault(r["model"], {})[r["mode"]] = r
@@ -65,8 +67,86 @@ def render(rows: List[dict]) -> str:
     return "\n".join(lines)
 
 
+def render_summary(results: Dict[str, Dict[str, dict]], rows: List[dict], timelines=None) -> str:
+    """The cross-model sections (ddp-bench/src/report.rs:196-260): best mode per model, loss ratio and speed-up against
+    solo-0 as model x mode grids, per-epoch loss trajectories, and what the timelines recorded (synchronisations, El Che
+    anchor, GPU utilisation, idle stretches by cause)."""
+    timelines = timelines or {}
+    models = list(results)
+    modes = [m for m in ALL_MODES if any(m in results[x] for x in models)]
+    by = {(r["model"], r["mode"]): r for r in rows}
+    lines = ["## Best mode per model", "", "| model | best loss | mode | fastest (loss within tolerance of solo-0) | mode |", "|---|---|---|---|---|"]
+    for model in models:
+        ok = [r for r in rows if r["model"] == model and r["final_loss"] is not None and not r["error"]]
+        if not ok:
+            lines.append(f"| {model} | - | - | - | - |")
+            continue
+        best = min(ok, key=lambda r: r["final_loss"])
+        fast_pool = [r for r in ok if r.get("converged", True)]
+        fast = min(fast_pool, key=lambda r: r["total_ms"]) if fast_pool else None
+        lines.append(f"| {model} | {best['final_loss']:.4f} | {best['mode']} | " + (f"{fast['total_ms'] / 1e3:.2f} s | {fast['mode']} |" if fast else "- | - |"))
+
+    def grid(title: str, note: str, cell) -> List[str]:
+        out = ["", f"## {title}", "", note, "", "| model | " + " | ".join(modes) + " |", "|---|" + "---|" * len(modes)]
+        for model in models:
+            out.append(f"| {model} | " + " | ".join(cell(by.get((model, m))) for m in modes) + " |")
+        return out
+
+    def ratio(r):
+        if r is None or r["final_loss"] is None:
+            return "-"
+        base = by.get((r["model"], "solo-0"))
+        if base is None or not base["final_loss"]:
+            return "-"
+        return f"{r['final_loss'] / base['final_loss']:.2f}"
+    lines += grid("Convergence quality (loss ratio vs solo-0)", "1.00 = the solo run's final loss; below 1 is better.", ratio)
+    lines += grid("Speed-up vs solo-0", "Wall time of the solo run divided by the run's.",
+                  lambda r: "-" if r is None or r.get("speedup_vs_solo") is None else f"{r['speedup_vs_solo']:.2f}x")
+    lines += ["", "## Per-epoch loss trajectory", ""]
+    for model in models:
+        n = max((len(r["epoch_losses"]) for r in results[model].values()), default=0)
+        if n == 0:
+            continue
+        step = max(1, n // 10)                                  # at most about ten columns
+        cols = list(range(0, n, step))
+        lines += [f"### {model}" + (f" (every {step}th of {n} epochs)" if step > 1 else ""), "", "| mode | " + " | ".join(f"e{c}" for c in cols) + " |",
+                  "|---|" + "---|" * len(cols)]
+        for m in modes:
+            r = results[model].get(m)
+            if r is not None:
+                lines.append(f"| {m} | " + " | ".join(f"{r['epoch_losses'][c]:.4f}" if c < len(r["epoch_losses"]) else "-" for c in cols) + " |")
+        lines.append("")
+    if any(a.sample_count or a.sync_count for a in timelines.values()):
+        gpus = sorted({g for a in timelines.values() for g in a.gpu_mean_util})
+        lines += ["## Timeline", "", "GPUn = mean compute utilisation in %; idle = total time below 5 % utilisation in stretches of at least 500 ms.", "",
+                  "| model | mode | syncs | avg sync ms | sync interval p50 / p95 ms | CPU avgs | avg CPU ms | anchors | throttles | "
+                  + " | ".join(f"GPU{g}" for g in gpus) + " | idle s |", "|---|---|---|---|---|---|---|---|---|" + "---|" * len(gpus) + "---|"]
+        for (model, mode), a in timelines.items():
+            anchors = "-" if not a.anchor_changes else f"{a.anchor_changes[0][0]} -> {a.final_anchor} ({len(a.anchor_changes)} changes)"
+            lines.append(f"| {model} | {mode} | {a.sync_count} | {a.avg_sync_ms:.2f} | {a.sync_interval_p50_ms:.0f} / {a.sync_interval_p95_ms:.0f} | {a.cpu_avg_count} | "
+                         f"{a.avg_cpu_avg_ms:.2f} | {anchors} | {a.throttle_count} | "
+                         + " | ".join(f"{a.gpu_mean_util[g]:.0f}" if g in a.gpu_mean_util else "-" for g in gpus) + f" | {a.idle_ms() / 1e3:.1f} |")
+        gaps = [(k, g) for k, a in timelines.items() for g in a.idle_gaps]
+        if gaps:
+            lines += ["", "## GPU idle analysis", "", "Idle stretches of at least 500 ms, classified by the nearest event.", "",
+                      "| model | mode | GPU | start s | duration s | cause |", "|---|---|---|---|---|---|"]
+            lines += [f"| {k[0]} | {k[1]} | {g.gpu} | {g.start_ms / 1e3:.1f} | {g.duration_ms / 1e3:.1f} | {g.cause} |" for k, g in gaps]
+            lines += ["", "### Idle time by cause", "", "| model | mode | GPU | epoch boundary s | sync s | CPU avg s | unexplained s |", "|---|---|---|---|---|---|---|"]
+            for k, a in timelines.items():
+                for g in sorted({x.gpu for x in a.idle_gaps}):
+                    c = a.idle_by_cause(g)
+                    lines.append(f"| {k[0]} | {k[1]} | {g} | {c['epoch boundary'] / 1e3:.1f} | {c['sync'] / 1e3:.1f} | {c['cpu avg'] / 1e3:.1f} | {c['unexplained'] / 1e3:.1f} |")
+    missing = [f"{m} / {mode}" for m in models for mode in modes if mode not in results[m]]
+    if missing:
+        lines += ["", "## Runs not present", ""] + [f"- {x}" for x in missing]
+    return "\n".join(lines) + "\n"
+
+
 def write_report(directory: str, out_path: Optional[str] = None) -> str:
-    text = render(analyze(load_results(directory)))
+    from .analyze import analyze_dir
+    results = load_results(directory)
+    rows = analyze(results)
+    text = render(rows) + "\n" + render_summary(results, rows, analyze_dir(directory))
     if out_path:
         with open(out_path, "w") as f:
             f.write(text)

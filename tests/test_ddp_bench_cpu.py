@@ -108,3 +108,60 @@ def test_cli_saves_and_validates_baselines_and_answers_the_schema_probe(tmp_path
     schema = json.loads(capsys.readouterr().out)
     assert schema["options"]["model"]["short"] == "m" and "all" in schema["options"]["mode"]["choices"] and schema["options"]["validate"]["type"] == "bool"
     assert schema["options"]["tolerance"]["default"] == 0.15 and schema["strict"] is True
+
+
+# ---- timelines: saved with the results, analysed into the report -------------------------------------------------------
+def _fake_timeline():
+    samples = []
+    for t in range(0, 6000, 100):
+        busy0 = not (2000 <= t <= 3000)                        # GPU 0 idles for a second around a sync
+        busy1 = not (4500 <= t <= 5300)                        # GPU 1 idles with nothing nearby
+        samples.append({"t_ms": t, "cpu_percent": 10.0, "ram_used_bytes": 1 << 30,
+                        "gpus": [{"index": 0, "util": 90.0 if busy0 else 1.0, "vram_used": 2 << 30}, {"index": 1, "util": 80.0 if busy1 else 0.0, "vram_used": 1 << 30}]})
+    events = [{"t_ms": 0, "kind": "EpochStart", "epoch": 0}, {"t_ms": 1000, "kind": "SyncStart"}, {"t_ms": 1010, "kind": "SyncEnd", "duration_ms": 10.0},
+              {"t_ms": 2100, "kind": "SyncStart"}, {"t_ms": 2130, "kind": "SyncEnd", "duration_ms": 30.0}, {"t_ms": 2200, "kind": "AnchorChanged", "from": 10, "to": 14},
+              {"t_ms": 3500, "kind": "SyncStart"}, {"t_ms": 3520, "kind": "SyncEnd", "duration_ms": 20.0}, {"t_ms": 3600, "kind": "Throttle", "rank": 1},
+              {"t_ms": 3700, "kind": "CpuAvgStart"}, {"t_ms": 3750, "kind": "CpuAvgEnd", "duration_ms": 50.0}, {"t_ms": 5900, "kind": "EpochEnd", "epoch": 0, "loss": 0.25}]
+    return {"samples": samples, "events": events}
+
+
+def test_timeline_analysis_counts_syncs_anchor_moves_and_classifies_idle_gaps(tmp_path):
+    from ddp_bench import analyze as A
+    a = A.analyze("mlp", "nccl-cadence", _fake_timeline())
+    assert (a.sync_count, a.cpu_avg_count, a.throttle_count) == (3, 1, 1) and abs(a.avg_sync_ms - 20.0) < 1e-9 and a.avg_cpu_avg_ms == 50.0
+    assert a.anchor_changes == [(10, 14)] and a.final_anchor == 14 and a.epoch_losses == [0.25]
+    assert a.sync_interval_p50_ms == 1250.0 and 1385 <= a.sync_interval_p95_ms <= 1400
+    assert 70 < a.gpu_mean_util[0] < 80 and a.gpu_peak_vram_mb[0] == 2048.0 and a.gpu_mean_vram_mb[1] == 1024.0
+    gaps = {(g.gpu, g.start_ms, g.duration_ms, g.cause) for g in a.idle_gaps}
+    assert gaps == {(0, 2000, 1000, "sync"), (1, 4500, 800, "unexplained")}
+    assert a.idle_ms() == 1800 and a.idle_ms(0) == 1000 and a.idle_by_cause(0)["sync"] == 1000
+    assert A.classify_gap(5500, 6200, _fake_timeline()["events"]) == "epoch boundary"
+    assert A.classify_gap(3300, 3400, [{"t_ms": 3700, "kind": "CpuAvgStart"}]) == "cpu avg"
+    short = {"samples": [{"t_ms": t, "gpus": [{"index": 0, "util": 0.0}]} for t in range(0, 400, 100)], "events": []}
+    assert A.analyze("m", "solo-0", short).idle_gaps == []                  # shorter than half a second: not reported
+    (tmp_path / "bad.json").write_text("[1, 2]")
+    with pytest.raises(ValueError, match="not a timeline"):
+        A.load_timeline(str(tmp_path / "bad.json"))
+    assert A.empty_analysis("m", "x").sync_count == 0
+
+
+def test_runs_save_timelines_and_the_report_has_the_summary_sections(tmp_path):
+    from ddp_bench import analyze as A
+    from ddp_bench.report import write_report
+    out = str(tmp_path / "runs")
+    opts = RunOptions(epochs=2, device="cpu", output_dir=out, tiny=True)
+    for name in ("mlp", "logistic"):
+        assert run(find_model(name), DdpMode.parse("solo-0"), opts) is not None
+    assert A.discover_runs(out) == [("logistic", "solo-0"), ("mlp", "solo-0")]
+    tl = A.load_timeline(os.path.join(out, "mlp__solo-0.timeline.json"))
+    kinds = [e["kind"] for e in tl["events"]]
+    assert kinds.count("EpochStart") == 2 and kinds.count("EpochEnd") == 2 and "loss" in tl["events"][-1]
+    analysis = A.analyze_dir(out)[("mlp", "solo-0")]
+    assert len(analysis.epoch_losses) == 2
+    json.dump(_fake_timeline(), open(os.path.join(out, "mlp__solo-0.timeline.json"), "w"))       # a multi-GPU run's timeline in its place
+    text = write_report(out)
+    for heading in ("## Best mode per model", "## Convergence quality (loss ratio vs solo-0)", "## Speed-up vs solo-0", "## Per-epoch loss trajectory",
+                    "## Timeline", "## GPU idle analysis", "### Idle time by cause"):
+        assert heading in text, heading
+    assert "| mlp | solo-0 | 3 | 20.00 | 1250 / " in text and "10 -> 14 (1 changes)" in text and "| mlp | solo-0 | 0 | 2.0 | 1.0 | sync |" in text
+    assert "| mlp | 1.00 |" in text and "| logistic | 1.00x |" in text
