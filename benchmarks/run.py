@@ -155,14 +155,29 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=-1, help="warm-up epochs per pass (default 3)")
     ap.add_argument("--mode", default="captured", choices=["captured", "eager"],
                     help="flodl arm on CUDA: whole-step CUDA graph through TrainEngine (default) or the op-by-op loop")
+    ap.add_argument("--warmup-secs", type=float, default=0.0, help="GPU warm-up before the first model (matrix products; 0 = none)")
+    ap.add_argument("--lock-clocks", type=int, default=None, metavar="MHZ",
+                    help="lock the SM clocks for the run and reset them afterwards (0 = the device's base clock). OFF unless given: "
+                         "a GPU setting outlives the process, do not use it on a machine you share")
     answer_schema_probe(ap, argv)
     args = ap.parse_args(argv)
+    if args.lock_clocks is not None and args.device.startswith("cuda"):
+        from .clocks import ClockLock, NvmlBackend
+        with ClockLock(NvmlBackend(), args.lock_clocks or None):
+            return _run(args)
+    return _run(args)
+
+
+def _run(args) -> int:
     names = {"all": TIER1 + TIER2, "tier1": TIER1, "tier2": TIER2}.get(args.models) or [m for m in args.models.split(",") if m]
     impls = [i for i in args.impl.split(",") if i]
     for n in names:
         if n not in MODELS:
             print(f"unknown model {n!r}; known: {', '.join(MODELS)}", file=sys.stderr)
             return 2
+    if args.warmup_secs > 0:
+        from .clocks import gpu_warmup
+        print(f"=== GPU warm-up: {gpu_warmup(args.warmup_secs, args.device)} products in {args.warmup_secs:.0f} s ===", flush=True)
     best: Dict[str, Dict[str, BenchResult]] = {n: {} for n in names}
     for _round in range(max(1, args.rounds)):
         for n in names:

@@ -37,3 +37,43 @@ def test_cli_writes_report(tmp_path, capsys):
     text = out.read_text()
     assert "| mlp |" in text and "speed-up" in text
     assert bench_run.main(["--models", "nope"]) == 2
+
+
+# ---- optional clock lock: logic only, against a stand-in for NVML (never the real one) ---------------------------------
+class FakeNvml:
+    def __init__(self, n=2, base=(1500, None), refuse=()):
+        self.n, self.base, self.refuse, self.calls = n, base, set(refuse), []
+    def device_count(self): return self.n
+    def default_graphics_clock(self, i): return self.base[i]
+    def lock(self, i, mhz):
+        if i in self.refuse:
+            raise PermissionError("insufficient permissions")
+        self.calls.append(("lock", i, mhz))
+    def reset(self, i): self.calls.append(("reset", i))
+
+
+def test_clock_lock_locks_resets_and_reports_refusals():
+    from benchmarks.clocks import ClockLock, detect_base_clock
+    nv, lines = FakeNvml(), []
+    assert detect_base_clock(nv, 0) == 1500 and detect_base_clock(nv, 1) is None
+    with ClockLock(nv, None, None, lines.append) as lock:
+        assert lock.locked == [0] and lock.failed == [1]                  # device 1 reports no base clock: left alone
+        assert nv.calls == [("lock", 0, 1500)]
+    assert nv.calls[-1] == ("reset", 0) and lock.locked == []
+    nv = FakeNvml(base=(1500, 1400), refuse=[1])
+    with pytest.raises(RuntimeError):
+        with ClockLock(nv, 1800, [0, 1], lines.append) as lock:
+            assert lock.locked == [0] and lock.failed == [1] and ("lock", 0, 1800) in nv.calls
+            raise RuntimeError("benchmark failed")
+    assert ("reset", 0) in nv.calls and ("reset", 1) not in nv.calls      # reset also after an exception; only what was locked
+    assert any("could not lock" in ln for ln in lines)
+
+
+def test_lock_is_off_unless_asked_for_and_warmup_is_a_no_op_without_a_gpu(monkeypatch):
+    import benchmarks.clocks as clocks
+    from benchmarks import run as bench_run
+    made = []
+    monkeypatch.setattr(clocks, "NvmlBackend", lambda: made.append(1) or FakeNvml())
+    assert bench_run.main(["--models", "mlp", "--impl", "torch", "--device", "cpu", "--quick", "--runs", "1", "--epochs", "1", "--warmup", "0"]) == 0
+    assert made == []                                                      # no NVML object without --lock-clocks
+    assert clocks.gpu_warmup(5.0, "cpu") == 0 and clocks.gpu_warmup(0.0, "cuda") == 0
