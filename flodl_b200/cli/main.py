@@ -1,6 +1,7 @@
 from __future__ import annotations
 
 import inspect
+import re
 import json
 import os
 import subprocess
@@ -62,26 +63,107 @@ def diagnose(as_json: bool = False) -> int:
 
 
 # ---- api-ref ----------------------------------------------------------------------------------------
+_API_SECTIONS = (("Tensors and devices", "flodl_b200.tensor"), ("Tensor operations", "flodl_b200.tensor_ops"), ("Tensor operations (nn, conversion, optimizer primitives)", "flodl_b200.tensor_nn_ops"),
+                 ("Autograd", "flodl_b200.autograd"), ("Modules (nn)", "flodl_b200.nn"), ("Graph builder", "flodl_b200.graph"), ("Data", "flodl_b200.data"),
+                 ("Monitor", "flodl_b200.monitor"), ("Synchronous DDP", "flodl_b200.parallel.ddp"), ("Training engine", "flodl_b200.parallel.engine"),
+                 ("Collectives and streams", "flodl_b200.parallel.comm"), ("Asynchronous DDP", "flodl_b200.parallel.ddp_run"),
+                 ("Hugging Face", "flodl_b200.hf"), ("Command line helpers", "flodl_b200.cli"), ("Other names of the package root", "flodl_b200"))
+_CTOR_NAMES = ("new", "on_device", "configure", "builder", "with_groups", "no_bias", "from_shared_weight", "from_pretrained", "from_pretrained_on_device",
+               "from_dataset", "from_batch_dataset", "from_json_str", "from_file", "from_config", "seed")
+
+
+def _sig(obj) -> str:
+    try:
+        return str(inspect.signature(obj))
+    except (TypeError, ValueError):
+        return "(...)"
+
+
+def _first_line(obj) -> str:
+    doc = (getattr(obj, "__doc__", None) or "").strip().splitlines()          # the object's own text, not an inherited one
+    return doc[0].strip() if doc else ""
+
+
+def api_entries() -> List[dict]:
+    """The public surface, section by section: every class with the file it lives in, its constructors (`X(...)` and the
+    floDl spellings `new`, `on_device`, `configure`, ...), its builder-style methods (those that return the object they are
+    called on) and its other public methods; every public function with its signature."""
+    import importlib
+    out, seen = [], set()
+    for title, modname in _API_SECTIONS:
+        mod = importlib.import_module(modname)
+        names = sorted(n for n in dir(mod) if not n.startswith("_"))
+        for name in names:
+            obj = getattr(mod, name)
+            if inspect.ismodule(obj) or id(obj) in seen or not callable(obj):
+                continue
+            if not str(getattr(obj, "__module__", "")).startswith("flodl_b200"):
+                continue
+            seen.add(id(obj))
+            try:
+                file = os.path.relpath(inspect.getsourcefile(obj), _repo_root())
+            except (TypeError, ValueError):
+                file = ""
+            if not inspect.isclass(obj):
+                out.append({"section": title, "kind": "function", "name": name, "signature": _sig(obj), "doc": _first_line(obj), "file": file})
+                continue
+            ctors, builders, methods = [f"{name}{_sig(obj)}"], [], []
+            members = {}
+            for klass in reversed([k for k in obj.__mro__ if k.__module__.startswith("flodl_b200") and k.__name__ != "Module"] or [obj]):
+                members.update(vars(klass))                  # own definitions win over the intermediate bases'
+            for m, fn in sorted(members.items()):
+                if m.startswith("_"):
+                    continue
+                raw = fn.__func__ if isinstance(fn, (classmethod, staticmethod)) else fn
+                if not callable(raw):
+                    continue
+                sig = _sig(getattr(obj, m))
+                if isinstance(fn, (classmethod, staticmethod)) and (m in _CTOR_NAMES or m.startswith(("with_", "from_"))):
+                    ctors.append(f"{name}.{m}{sig}")
+                    continue
+                try:
+                    src = inspect.getsource(raw)
+                except (OSError, TypeError):
+                    src = ""
+                returns = re.findall(r"\breturn\b[^\n]*", src)
+                fluent = bool(returns) and all(re.fullmatch(r"return self\s*(#.*)?", r.strip()) for r in returns)
+                (builders if fluent else methods).append(f".{m}{sig}")
+            bases = [b.__name__ for b in obj.__mro__[1:] if b.__module__.startswith("flodl_b200")]
+            out.append({"section": title, "kind": "class", "name": name, "doc": _first_line(obj), "file": file, "implements": bases,
+                        "constructors": ctors, "builder": builders, "methods": methods})
+    return out
+
+
 def api_ref(as_json: bool = False) -> int:
-    """The public names of the package root with their signatures."""
+    """`api-ref [--json]`: the structured API reference (for people and for porting tools)."""
     import flodl_b200 as pkg
-    rows = []
-    for name in sorted(n for n in dir(pkg) if not n.startswith("_")):
-        obj = getattr(pkg, name)
-        if inspect.ismodule(obj):
-            continue
-        kind = "class" if inspect.isclass(obj) else "function" if callable(obj) else "value"
-        try:
-            sig = str(inspect.signature(obj)) if callable(obj) else ""
-        except (TypeError, ValueError):
-            sig = "(...)"
-        doc = (inspect.getdoc(obj) or "").strip().splitlines()
-        rows.append({"name": name, "kind": kind, "signature": sig, "doc": doc[0] if doc else ""})
+    rows = api_entries()
     if as_json:
         print(json.dumps(rows, indent=1))
-    else:
-        for r in rows:
-            print(f"{r['kind']:8} {r['name']}{r['signature']}")
+        return 0
+    print(f"flodl_b200 API reference v{pkg.__version__}\n" + "=" * 40)
+    section = None
+    for r in rows:
+        if r["section"] != section:
+            section = r["section"]
+            print(f"\n## {section}\n")
+        if r["kind"] == "function":
+            print(f"  {r['name']}{r['signature']}" + (f"    # {r['doc']}" if r["doc"] else ""))
+            continue
+        impl = f"  (implements: {', '.join(r['implements'])})" if r["implements"] else ""
+        print(f"### {r['name']}{impl}")
+        if r["doc"]:
+            print(f"  {r['doc']}")
+        print(f"  file: {r['file']}")
+        print("  constructors:")
+        for c in r["constructors"]:
+            print(f"    {c}")
+        if r["builder"]:
+            print("  builder:\n    " + "  ".join(b.split("(")[0] + "()" for b in r["builder"]))
+        if r["methods"]:
+            print("  methods:")
+            for m in r["methods"]:
+                print(f"    {m}")
     return 0
 
 

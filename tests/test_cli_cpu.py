@@ -449,3 +449,21 @@ def test_scaffolded_training_script_runs(tmp_path):
     out = subprocess.run([sys.executable, str(script)], cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert os.path.isfile(tmp_path / "model.fdl") and out.stdout.startswith("0 ")
+
+
+def test_api_ref_is_structured_by_section_with_constructors_and_builder_methods(capsys):
+    from flodl_b200.cli.main import api_entries
+    rows = {r["name"]: r for r in api_entries()}
+    conv = rows["Conv2d"]
+    assert conv["kind"] == "class" and conv["file"].endswith("nn/layers.py") and "Module" in conv["implements"]
+    assert any(c.startswith("Conv2d.configure(") for c in conv["constructors"]) and conv["constructors"][0].startswith("Conv2d(in_channels")
+    pool = rows["AvgPool2d"]
+    assert {b.split("(")[0] for b in pool["builder"]} >= {".padding", ".ceil_mode", ".count_include_pad"} and ".name" not in {b.split("(")[0] for b in pool["builder"]}
+    assert any(c.startswith("AvgPool2d.with_stride(") for c in pool["constructors"])
+    fb = rows["FlowBuilder"]
+    assert {".through", ".also", ".tag", ".using"} <= {b.split("(")[0] for b in fb["builder"]} and any(m.startswith(".build(") for m in fb["methods"])
+    assert rows["gt_scalar"]["kind"] == "function" and rows["gt_scalar"]["section"] == "Tensor operations"
+    assert rows["AutoModelForQuestionAnswering"]["section"] == "Hugging Face"
+    assert main(["api-ref"]) == 0
+    text = capsys.readouterr().out
+    assert text.startswith("flodl_b200 API reference v") and "## Modules (nn)" in text and "### Linear" in text and "  constructors:" in text and "  builder:" in text
