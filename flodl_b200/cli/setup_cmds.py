@@ -248,19 +248,125 @@ Errors are `TensorError` exceptions instead of `Result`.
 '''
 
 
+PORT_SKILL = '''# Port a PyTorch training script to flodl_b200
+
+Use when asked to port, convert or migrate PyTorch code to flodl_b200.
+
+## Steps
+1. Read the source: find the model (modules, forward), the loss, the optimizer, the data pipeline, the loop.
+2. Run `python -m flodl_b200.cli api-ref --json` and match every PyTorch construct to an entry (constructors, builder
+   methods); do not guess names.
+3. Write the model with `FlowBuilder`: a chain is `.through(m)`, `x + f(x)` is `.also(f)`, parallel branches are
+   `.split([...]).merge(MergeOp.Add)`, reused values are `.tag("n")` / `.using("n")`, repeated blocks are
+   `.loop_body(b).for_n(k)`. A forward with Python control flow over tensors becomes a custom `nn.Module`.
+4. Keep tensors as `torch.Tensor`; wrap model inputs with `Variable.wrap(t)`, read results with `.t`.
+5. Training: `Trainer.setup(model, None, lambda ps: nn.AdamW(ps, lr, wd))`, then `loss.backward(); model.step()`. For the
+   fast path on a GPU use `TrainEngine(model, optimizer_factory)` + `capture(step_fn, example)` + `replay(batch)` inside
+   `nn.AutocastGuard(torch.bfloat16)`.
+6. Data: `DataLoader.from_batch_dataset(TensorDataSet(x, y)).batch_size(b).device(dev).build()`; `loader.epoch(e)`.
+7. Validate: run a few steps on CPU, compare the first losses with the PyTorch script under the same seed and
+   initial weights (`load_state_dict` values copied into `model.named_parameters()`), then run on the GPU.
+
+## Mapping
+| PyTorch | flodl_b200 |
+|---|---|
+| `nn.Sequential(a, b)` | `FlowBuilder.from_(a).through(b).build()` |
+| `x + self.block(x)` | `.also(block)` |
+| `torch.cat([f(x), g(x)], -1)` | custom module, or `.split([f, g])` + a merge module |
+| `nn.Linear(i, o)` / `nn.Conv2d(i, o, k, s, p)` | `nn.Linear(i, o)` / `nn.Conv2d.configure(i, o, k).with_stride(s).with_padding(p).done()` |
+| `F.cross_entropy(logits, y)` | `nn.cross_entropy_loss(logits_var, y_var)` (2-D logits, ignore_index -100) |
+| `optim.AdamW(ps, lr, weight_decay=wd)` | `nn.AdamW(ps, lr, wd)` |
+| `clip_grad_norm_(ps, 1.0)` | `nn.clip_grad_norm(ps, 1.0)` |
+| `torch.autocast("cuda", torch.bfloat16)` | `nn.AutocastGuard(torch.bfloat16)` |
+| `DistributedDataParallel(m)` | `Trainer.setup(model, None, optimizer_factory)` under `torchrun` |
+| `torch.save(m.state_dict(), p)` | `model.save_checkpoint("m.fdl")` |
+| `AutoModel.from_pretrained(r)` | `flodl_b200.hf.AutoModel.from_pretrained(r)` |
+'''
+
+SKILLS = {"guide": ("The condensed API and porting reference of flodl_b200", None),
+          "port": ("Port PyTorch scripts to flodl_b200: read the source, map the patterns, write the project, validate", PORT_SKILL)}
+TOOLS = {"claude": "Claude Code (.claude/ directory): .claude/skills/<skill>/SKILL.md",
+         "cursor": "Cursor (.cursor/ or .cursorrules): appended to .cursorrules",
+         "generic": "no assistant detected: .fdl/skills/<skill>/SKILL.md"}
+
+
+def detect_tools(root: str) -> List[str]:
+    out = []
+    if os.path.isdir(os.path.join(root, ".claude")):
+        out.append("claude")
+    if os.path.isdir(os.path.join(root, ".cursor")) or os.path.isfile(os.path.join(root, ".cursorrules")):
+        out.append("cursor")
+    return out
+
+
+def skill_text(name: str) -> str:
+    return SKILL if name == "guide" else SKILLS[name][1]
+
+
+def install_skill(root: str, tool: str, name: str) -> str:
+    text = skill_text(name)
+    if tool == "cursor":
+        path = os.path.join(root, ".cursorrules")
+        marker = f"# --- flodl_b200 skill: {name} ---"
+        old = open(path).read() if os.path.isfile(path) else ""
+        if marker in old:                                   # installed before: replace that block, keep the user's own rules
+            head, _, rest = old.partition(marker)
+            tail = rest.partition("# --- end flodl_b200 skill ---")[2]
+            old = head.rstrip("\n") + ("\n" if head.strip() else "") + tail.lstrip("\n")
+        with open(path, "w") as f:
+            f.write((old.rstrip("\n") + "\n\n" if old.strip() else "") + f"{marker}\n{text.rstrip()}\n# --- end flodl_b200 skill ---\n")
+        return path
+    d = os.path.join(root, ".claude", "skills", name) if tool == "claude" else os.path.join(root, ".fdl", "skills", name)
+    os.makedirs(d, exist_ok=True)
+    path = os.path.join(d, "SKILL.md")
+    with open(path, "w") as f:
+        f.write(text)
+    return path
+
+
 def skill(argv: List[str]) -> int:
+    """`skill list | show [name] | install [--tool claude|cursor|generic] [--skill NAME] [dir]`."""
     sub = argv[0] if argv else "show"
+    rest = argv[1:]
+
+    def opt(flag):
+        if flag in rest:
+            i = rest.index(flag)
+            if i + 1 < len(rest):
+                v = rest[i + 1]
+                del rest[i:i + 2]
+                return v
+            del rest[i]
+        return None
     if sub == "show":
-        print(SKILL)
+        name = rest[0] if rest else "guide"
+        if name not in SKILLS:
+            print(f"unknown skill {name!r}; one of: {', '.join(SKILLS)}", file=sys.stderr)
+            return 2
+        print(skill_text(name))
+        return 0
+    if sub == "list":
+        print("skills:")
+        for n, (doc, _t) in SKILLS.items():
+            print(f"  {n:<8} {doc}")
+        found = detect_tools(os.getcwd())
+        print("tools detected here: " + (", ".join(found) if found else "none (install goes to .fdl/skills/)"))
+        for t, doc in TOOLS.items():
+            print(f"  {t:<8} {doc}")
         return 0
     if sub == "install":
-        root = os.path.abspath(argv[1] if len(argv) > 1 else ".")
-        d = os.path.join(root, ".fdl", "skills", "flodl_b200")
-        os.makedirs(d, exist_ok=True)
-        path = os.path.join(d, "SKILL.md")
-        with open(path, "w") as f:
-            f.write(SKILL)
-        print(f"installed {path}")
+        tool, only = opt("--tool"), opt("--skill")
+        root = os.path.abspath(rest[0] if rest else ".")
+        if tool is not None and tool not in TOOLS:
+            print(f"unknown tool {tool!r}; one of: {', '.join(TOOLS)}", file=sys.stderr)
+            return 2
+        if only is not None and only not in SKILLS:
+            print(f"unknown skill {only!r}; one of: {', '.join(SKILLS)}", file=sys.stderr)
+            return 2
+        tools = [tool] if tool else (detect_tools(root) or ["generic"])
+        for t in tools:
+            for n in ([only] if only else list(SKILLS)):
+                print(f"installed {install_skill(root, t, n)}")
         return 0
-    print("usage: skill [show | install [dir]]", file=sys.stderr)
+    print("usage: skill [list | show [name] | install [--tool claude|cursor|generic] [--skill NAME] [dir]]", file=sys.stderr)
     return 2

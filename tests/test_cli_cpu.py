@@ -140,7 +140,7 @@ def test_setup_install_add_libtorch_skill(tmp_path, capsys):
     assert main(["add", str(tmp_path)]) == 0                      # existing files are kept
     assert (tmp_path / "train.py").read_text() == "# mine"
     assert main(["skill", "install", str(tmp_path)]) == 0
-    assert "Porting from floDl" in (tmp_path / ".fdl" / "skills" / "flodl_b200" / "SKILL.md").read_text()
+    assert "Porting from floDl" in (tmp_path / ".fdl" / "skills" / "guide" / "SKILL.md").read_text()
     assert main(["libtorch", "info", "--json"]) == 0
     assert main(["libtorch", "path"]) == 0
     assert main(["install", "--check"]) == 0
@@ -467,3 +467,26 @@ def test_api_ref_is_structured_by_section_with_constructors_and_builder_methods(
     assert main(["api-ref"]) == 0
     text = capsys.readouterr().out
     assert text.startswith("flodl_b200 API reference v") and "## Modules (nn)" in text and "### Linear" in text and "  constructors:" in text and "  builder:" in text
+
+
+def test_skill_list_show_and_install_per_tool(tmp_path, monkeypatch, capsys):
+    monkeypatch.chdir(tmp_path)
+    assert main(["skill", "list"]) == 0
+    out = capsys.readouterr().out
+    assert "port" in out and "guide" in out and "tools detected here: none" in out
+    assert main(["skill", "show", "port"]) == 0 and "FlowBuilder" in capsys.readouterr().out
+    assert main(["skill", "show", "nope"]) == 2
+    (tmp_path / ".claude").mkdir()
+    (tmp_path / ".cursorrules").write_text("my own rule\n")
+    capsys.readouterr()
+    assert main(["skill", "install", "--skill", "port"]) == 0            # both tools detected: both get it
+    assert "Port a PyTorch training script" in (tmp_path / ".claude" / "skills" / "port" / "SKILL.md").read_text()
+    rules = (tmp_path / ".cursorrules").read_text()
+    assert rules.startswith("my own rule") and rules.count("# --- flodl_b200 skill: port ---") == 1
+    assert main(["skill", "install", "--tool", "cursor", "--skill", "port"]) == 0
+    rules = (tmp_path / ".cursorrules").read_text()
+    assert rules.count("# --- flodl_b200 skill: port ---") == 1 and rules.startswith("my own rule")      # replaced, not duplicated
+    assert main(["skill", "install", "--tool", "generic"]) == 0
+    assert (tmp_path / ".fdl" / "skills" / "port" / "SKILL.md").is_file() and (tmp_path / ".fdl" / "skills" / "guide" / "SKILL.md").is_file()
+    assert main(["skill", "install", "--tool", "emacs"]) == 2 and main(["skill", "install", "--skill", "x"]) == 2
+    assert main(["skill", "list"]) == 0 and "claude, cursor" in capsys.readouterr().out
