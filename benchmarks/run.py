@@ -9,6 +9,7 @@ reads and reports them instead)."""
 from __future__ import annotations
 
 import argparse
+import os
 import json
 import subprocess
 import sys
@@ -29,8 +30,8 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
     """`mode` (flodl arm, CUDA only): "captured" runs the framework's standard training path, a
     `TrainEngine` whose whole step (forward, backward, fused optimizer over the flat parameter
     buffer) is one CUDA-graph launch; a model whose forward reads values on the host (data-dependent
-    loops) cannot be captured and runs the same engine step by step. "eager" is the plain
-    op-by-op loop with a per-tensor optimizer, the shape of the reference's benchmark loop."""
+    loops) cannot be captured and trains through the plain loop. "eager" is that plain op-by-op loop
+    with a per-tensor optimizer for every model, the shape of the reference's benchmark loop."""
     build, cfg = MODELS[name]
     if quick:
         cfg = cfg.quick()
@@ -43,11 +44,9 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
     gen = torch.Generator().manual_seed(seed + 1)
     batches = [make_batch(dev, gen) for _ in range(cfg.batches_per_epoch)]
     impl_label = impl
+    capturable = False
     if impl == "flodl" and mode == "captured" and dev.type == "cuda":
-        from flodl_b200.parallel.engine import TrainEngine
         model.train()
-        count = sum(p.t.numel() for p in model.parameters())
-        eng = TrainEngine(model, lambda ps: nn.Adam(ps, lr))
 
         def step_fn(x, y):
             pred = model.forward(Variable.wrap(x))
@@ -56,7 +55,9 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
             return nn.mse_loss(pred, Variable.wrap(y))
         # A forward that reads device values on the host (a data-dependent loop count, an early exit)
         # cannot be recorded into a graph. Find out with one eager forward + backward under PyTorch's
-        # sync detector rather than by letting a capture fail half-way.
+        # sync detector rather than by letting a capture fail half-way. Such a model trains through the
+        # plain op-by-op loop below (measured on B200, feedback_loop: 78 ms per epoch that way, 96 ms
+        # stepping the flat-buffer engine without a capture, 94 ms PyTorch).
         capturable = True
         torch.cuda.synchronize()
         torch.cuda.set_sync_debug_mode("error")
@@ -67,21 +68,27 @@ def run_model(name: str, impl: str, device: str, quick: bool, seed: int = 0, run
         finally:
             torch.cuda.set_sync_debug_mode("default")
         torch.cuda.synchronize()
-        eng.flat.zero_grad()
-        if capturable:
-            eng.capture(step_fn, list(batches[0]), warmup=2)
-            one = lambda x, y: eng.replay([x, y])
-            impl_label = "flodl (one CUDA graph per step)"
-        else:
-            one = lambda x, y: eng.step(lambda: step_fn(x, y))
-            impl_label = "flodl (engine, step by step)"
+        for p in model.parameters():
+            p.t.grad = None
+    if capturable:
+        from flodl_b200.parallel.engine import TrainEngine
+        count = sum(p.t.numel() for p in model.parameters())
+        eng = TrainEngine(model, lambda ps: nn.Adam(ps, lr))
+        eng.capture(step_fn, list(batches[0]), warmup=2)
+        impl_label = "flodl (one CUDA graph per step)"
 
         def epoch(_i, _warm):
             total = 0.0
             for x, y in batches:
-                total += one(x, y).item()
+                total += eng.replay([x, y]).item()
             return total / len(batches)
     elif impl == "flodl":
+        if mode == "captured" and dev.type == "cuda":
+            impl_label = "flodl (op by op: the forward reads device values on the host)"
+        # an engine built for an earlier model of this process switched every size to the native kernels; the plain
+        # loop wants the default again (small tensors through ATen: their cost is host time)
+        from flodl_b200.ops import core as _core
+        _core.set_eager_min_numel(int(os.environ.get("FLODL_B200_EAGER_MIN_NUMEL", str(1 << 20))))
         model.train()
         params = model.parameters()
         count = sum(p.t.numel() for p in params)
