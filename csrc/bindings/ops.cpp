@@ -603,6 +603,7 @@ Tensor attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
 
 void bind_comm(py::module_& m);     // comm.cpp
 void bind_runtime(py::module_& m);  // runtime.cpp
+void bind_graph_exec(py::module_& m);  // graph_exec.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
@@ -654,4 +655,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale"), py::arg("causal"), py::arg("p_drop") = 0.0, py::arg("seed") = 0, py::arg("seed_dev") = py::none());
   bind_comm(m);
   bind_runtime(m);
+  bind_graph_exec(m);
 }

@@ -203,6 +203,21 @@ class Graph(Module, TreeMixin, ObserveMixin, ProfileMixin, RenderMixin, Distribu
         if self.training_start == 0.0:
             self.training_start = time.time()
         profiling = self._profiling
+        if not profiling:
+            ex = self._native_exec()
+            if ex is not None:
+                try:
+                    final, tagged, state = ex.forward(list(graph_inputs))
+                except RuntimeError as e:
+                    if type(e) is RuntimeError and str(e).startswith(("node '", "expected ", "graph produced")):
+                        raise TensorError(str(e)) from None          # the walk's own complaints keep the framework's error type
+                    raise
+                if self.tag_capture:
+                    self.tagged_outputs.clear()
+                    self.tagged_outputs.update(tagged)
+                for si, v in state:
+                    self.state[si]["value"] = v
+                return final
         t_fwd = time.perf_counter() if profiling else 0.0
         prof_nodes, prof_levels = [], []
         slots: List[List[Optional[Variable]]] = [[None] * c for c in self.node_input_count]
@@ -256,6 +271,26 @@ class Graph(Module, TreeMixin, ObserveMixin, ProfileMixin, RenderMixin, Distribu
         if final is None or self.output_port_idx >= len(final):
             raise TensorError("graph produced no output")
         return final[self.output_port_idx]
+
+    def _native_exec(self):
+        """The C++ walk over this graph's precomputed tables (`csrc/runtime/graph_exec.cpp`), built at the first call;
+        None when the native library is not there (the Python walk below does the same) or `FLODL_B200_NATIVE_GRAPH=0`."""
+        ex = self.__dict__.get("_exec")
+        if ex is not None or self.__dict__.get("_exec_unavailable"):
+            return ex
+        from .. import _ext
+        if os.environ.get("FLODL_B200_NATIVE_GRAPH", "1") in ("0", "false", "off") or not _ext.available() or not hasattr(_ext.require(), "GraphExec"):
+            self._exec_unavailable = True
+            return None
+        n = len(self.nodes)
+        self._exec = _ext.require().GraphExec(
+            [list(level) for level in self.levels], [int(c) for c in self.node_input_count], [len(nd.input_ports) for nd in self.nodes],
+            [(int(ni), int(pi)) for ni, pi in self.input_routes], [[(int(fp), int(tn), int(tp)) for fp, tn, tp in self.routes_from[i]] for i in range(n)],
+            [[(int(si), int(pi)) for si, pi in self.state_writers.get(i, ())] for i in range(n)],
+            [[(str(tag), int(pi)) for tag, pi in self.tag_capture.get(i, ())] for i in range(n)],
+            int(self.output_node_idx), int(self.output_port_idx), [nd.run for nd in self.nodes], [str(nd.id) for nd in self.nodes],
+            lambda v: Variable.wrap(torch.zeros_like(v.t)))
+        return self._exec
 
     def _first_tag(self, ni: int) -> str:
         caps = self.tag_capture.get(ni)

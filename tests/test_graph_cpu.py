@@ -342,3 +342,59 @@ def test_native_topological_levels_match_python_rule():
         topological_levels(2, [(0, 1), (1, 0)])
     C = _ext.load()
     assert C is None or hasattr(C, "topo_levels")
+
+
+# ---- the native (C++) walk and the Python walk are the same function --------------------------------------------------
+def _both_walks(build, inputs, calls=2):
+    """Outputs, tagged values and state after `calls` forwards, once through the C++ executor and once through the Python loop."""
+    import os
+    out = {}
+    for native in ("1", "0"):
+        os.environ["FLODL_B200_NATIVE_GRAPH"] = native
+        try:
+            torch.manual_seed(7)
+            g = build()
+            ys = [g.forward_multi(inputs).t.clone() for _ in range(calls)]
+            assert (g._native_exec() is not None) == (native == "1")
+            out[native] = (ys, {k: v.t.clone() for k, v in g.tagged_outputs.items()}, [s["value"].t.clone() for s in g.state if s["value"] is not None])
+        finally:
+            os.environ.pop("FLODL_B200_NATIVE_GRAPH", None)
+    return out["1"], out["0"]
+
+
+def test_native_walk_matches_python_walk_on_tags_state_refs_and_composites():
+    from flodl_b200.graph import MergeOp, SoftmaxRouter, StateAdd
+
+    def build():
+        return (FlowBuilder.from_(nn.Linear(4, 8)).tag("stem").input(["extra"])
+                .through(StateAdd()).using("memory")                     # forward reference: last call's value
+                .split([nn.Linear(8, 8), nn.Linear(8, 8)]).tag_group("b").merge(MergeOp.Mean)
+                .through(StateAdd()).using("extra")                      # a graph input used as a ref
+                .gate(SoftmaxRouter(8, 2), [nn.Linear(8, 8), nn.Linear(8, 8)])
+                .loop_body(FlowBuilder.new().also(nn.Linear(8, 8)).build()).for_n(2)
+                .through(nn.Tanh()).tag("memory").through(nn.Linear(8, 2)).tag("out").build())
+    x, extra = Variable.wrap(torch.randn(3, 4)), Variable.wrap(torch.randn(3, 8))
+    (ya, ta, sa), (yb, tb, sb) = _both_walks(build, [x, extra], calls=3)
+    assert all(torch.equal(a, b) for a, b in zip(ya, yb)) and not torch.equal(ya[0], ya[1])       # state moved between calls, identically
+    assert ta.keys() == tb.keys() and set(ta) >= {"stem", "b_0", "b_1", "memory", "out"} and all(torch.equal(ta[k], tb[k]) for k in ta)
+    assert len(sa) == len(sb) == 1 and torch.equal(sa[0], sb[0])
+
+
+def test_native_walk_keeps_gradients_and_error_types():
+    from flodl_b200.tensor import TensorError
+    g = FlowBuilder.from_(nn.Linear(4, 4)).also(nn.Linear(4, 4)).through(nn.Linear(4, 1)).build()
+    assert g._native_exec() is not None and g._native_exec().node_count() == len(g.nodes) and g._native_exec().level_count() == len(g.levels)
+    x = Variable(torch.randn(5, 4), requires_grad=True)
+    g.forward(x).sum().backward()
+    assert x.grad() is not None and all(p.t.grad is not None for p in g.parameters())
+    with pytest.raises(TensorError, match="expected 1 inputs, got 2"):
+        g.forward_multi([x, x])
+
+    class Boom(nn.Module):
+        def forward(self, v): raise ValueError("inside a node")
+    bad = FlowBuilder.from_(nn.Linear(4, 4)).through(Boom()).build()
+    with pytest.raises(ValueError, match="inside a node"):                # a node's own exception passes through unchanged
+        bad.forward(x)
+    g.enable_profiling()                                                   # profiling uses the Python walk and still works
+    g.forward(x)
+    assert g.profile() is not None and len(g.profile().nodes) == len(g.nodes)
