@@ -383,6 +383,18 @@ def usage(manifest: Optional[str]) -> str:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
+    rc = _main(argv)
+    try:                                              # after the command's own output; never in its way
+        import flodl_b200
+        from .update_check import check
+        for line in check(flodl_b200.__version__):
+            print(line, file=sys.stderr)
+    except Exception:  # noqa: BLE001
+        pass
+    return rc
+
+
+def _main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     env = None
     dry = False

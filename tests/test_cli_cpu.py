@@ -490,3 +490,59 @@ def test_skill_list_show_and_install_per_tool(tmp_path, monkeypatch, capsys):
     assert (tmp_path / ".fdl" / "skills" / "port" / "SKILL.md").is_file() and (tmp_path / ".fdl" / "skills" / "guide" / "SKILL.md").is_file()
     assert main(["skill", "install", "--tool", "emacs"]) == 2 and main(["skill", "install", "--skill", "x"]) == 2
     assert main(["skill", "list"]) == 0 and "claude, cursor" in capsys.readouterr().out
+
+
+# ---- update check: inert without a feed, daily, silent on failure ------------------------------------------------------
+def test_update_check_switches_versions_and_daily_cache(tmp_path):
+    from flodl_b200.cli import update_check as U
+    cfgp = str(tmp_path / "flodl" / "config.json")
+    feed = {"FLODL_B200_UPDATE_URL": "http://feed.invalid/latest.json"}
+    calls = []
+
+    def fetch(url):
+        calls.append(url)
+        return "0.3.0"
+    none = str(tmp_path / "no-dockerenv")
+    assert U.check("0.1.0", 1e9, cfgp, fetch, {}, none) == [] and calls == []                          # no feed configured: nothing fetched
+    for env in ({**feed, "FDL_NO_UPDATE_CHECK": "1"}, {**feed, "CI": "true"}):
+        assert U.check("0.1.0", 1e9, cfgp, fetch, env, none) == [] and calls == []
+    (tmp_path / "dockerenv").write_text("")
+    assert U.check("0.1.0", 1e9, cfgp, fetch, feed, str(tmp_path / "dockerenv")) == [] and calls == []
+    lines = U.check("0.1.0", 1e9, cfgp, fetch, feed, none)
+    assert len(calls) == 1 and "once a day" in lines[0] and "0.3.0 is available (this is 0.1.0)" in lines[1]
+    lines = U.check("0.1.0", 1e9 + 3600, cfgp, fetch, feed, none)                                        # an hour later: remembered, no probe, no note
+    assert len(calls) == 1 and len(lines) == 1 and "0.3.0" in lines[0]
+    assert U.check("0.3.0", 1e9 + 7200, cfgp, fetch, feed, none) == []                                   # up to date: silent
+    U.check("0.1.0", 1e9 + U.DAY_S + 1, cfgp, lambda url: calls.append(url), feed, none)                 # a day later: probes again; a failed probe is silent
+    assert len(calls) == 2 and U.load_config(cfgp)["update_check"]["latest_known"]["flodl_b200"] == "0.3.0"
+    cfg = U.load_config(cfgp)
+    cfg["update_check"]["enabled"] = False
+    U.save_config(cfg, cfgp)
+    assert U.check("0.1.0", 1e9 + 3 * U.DAY_S, cfgp, fetch, feed, none) == [] and len(calls) == 2
+    assert U.max_stable(["0.5.2", "0.6.0-rc1", "v0.5.10", "junk"]) == "0.5.10" and U.parse_version("1.2.0b1") is None and U.parse_version("1.2") == (1, 2, 0)
+
+
+def test_update_check_reads_a_feed_and_never_disturbs_the_command(tmp_path, monkeypatch, capsys):
+    import functools, http.server, threading
+    from flodl_b200.cli import update_check as U
+    (tmp_path / "www").mkdir()
+    (tmp_path / "www" / "latest.json").write_text(json.dumps({"versions": ["9.0.0", "9.1.0-beta", "8.4.1"]}))
+
+    class Quiet(http.server.SimpleHTTPRequestHandler):
+        def log_message(self, *a): pass
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), functools.partial(Quiet, directory=str(tmp_path / "www")))
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        url = f"http://127.0.0.1:{srv.server_address[1]}/latest.json"
+        assert U.fetch_latest(url) == "9.0.0" and U.fetch_latest(url.replace("latest", "missing")) is None
+        monkeypatch.setenv("XDG_CONFIG_HOME", str(tmp_path / "cfg"))
+        monkeypatch.setenv("FLODL_B200_UPDATE_URL", url)
+        monkeypatch.delenv("CI", raising=False)
+        monkeypatch.delenv("FDL_NO_UPDATE_CHECK", raising=False)
+        monkeypatch.setattr(U.os.path, "exists", lambda p, _e=os.path.exists: False if p == "/.dockerenv" else _e(p))
+        monkeypatch.chdir(tmp_path)
+        assert main(["skill", "list"]) == 0
+        err = capsys.readouterr().err
+        assert "9.0.0 is available" in err and os.path.isfile(tmp_path / "cfg" / "flodl" / "config.json")
+    finally:
+        srv.shutdown()

@@ -153,6 +153,45 @@ def test_prefetch_worker_python_path_for_generic_datasets():
     assert got == list(range(12))
 
 
+def test_native_prefetch_ring_survives_many_epochs_early_stops_and_a_slow_consumer():
+    """The C++ ring (producer thread + bounded queue + two condition variables) under the patterns that would show a
+    lost wake-up, a stale batch from a previous epoch, or a join that never returns."""
+    import threading, time
+    from flodl_b200 import _ext
+    if not _ext.available():
+        pytest.skip("native extension not built")
+    n = 257
+    x = torch.arange(n * 3, dtype=torch.float32).view(n, 3)
+    y = torch.arange(n)
+    for depth in (1, 2, 7):
+        w = PrefetchWorker(TensorDataSet(x, y), "cpu", depth)
+        assert w.is_native()
+        g = torch.Generator().manual_seed(depth)
+        for epoch in range(30):
+            order = torch.randperm(n, generator=g).tolist()
+            drop_last = epoch % 2 == 0
+            w.start_epoch(order, 16, drop_last)
+            take = None if epoch % 3 else 1 + epoch % 5            # every third epoch is abandoned after a few batches
+            seen = []
+            while take is None or len(seen) < take * 16:
+                if epoch % 7 == 0:
+                    time.sleep(0.001)                              # a consumer slower than the producer: the ring fills up
+                b = w.next()
+                if b is None:
+                    break
+                assert torch.equal(b[0], x[b[1]])                  # rows of one batch belong together
+                seen += b[1].tolist()
+            want = order[:n // 16 * 16] if drop_last else order
+            assert seen == (want if take is None else want[:take * 16]), (depth, epoch)
+            if take is not None:
+                w.stop()                                           # producer blocked on a full ring must wake up and leave
+        assert w.next() is None                                    # after the last epoch: empty, not blocked
+        done = threading.Event()
+        w.start_epoch(list(range(n)), 4)
+        threading.Thread(target=lambda: (w.stop(), done.set()), daemon=True).start()     # stop from another thread, nothing consumed
+        assert done.wait(10), "stop() did not return with a full ring"
+
+
 def test_prefetch_depth_on_cpu_is_double_buffering():
     assert prefetch_depth_from_vram(1024, 32, "cpu") == 2
 
