@@ -604,6 +604,7 @@ Tensor attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
 void bind_comm(py::module_& m);     // comm.cpp
 void bind_runtime(py::module_& m);  // runtime.cpp
 void bind_graph_exec(py::module_& m);  // graph_exec.cpp
+void bind_cpu_avg(py::module_& m);     // cpu_avg.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "flodl_b200 native kernels (sm_100a) and runtime";
@@ -656,4 +657,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_comm(m);
   bind_runtime(m);
   bind_graph_exec(m);
+  bind_cpu_avg(m);
 }

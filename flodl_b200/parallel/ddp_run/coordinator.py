@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import threading
 import time
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -90,20 +90,14 @@ def aggregate_epoch_metrics(epoch: int, msgs: Sequence[MetricsMsg], device_indic
         per_rank_batch_share=[samples[r] / total_s if total_s else 0.0 for r in range(w)], device_indices=list(device_indices))
 
 
-def average_params(snapshots: Sequence[ParamSnapshot], version: int) -> AveragedParams:
-    """Batch-count-weighted mean of parameters, equal-weight mean of buffers, on the host
-    (coordinator/cpu_avg.rs:540-599)."""
-    if not snapshots:
-        raise ValueError("average_params: no snapshots")
+def _weights(snapshots: Sequence[ParamSnapshot]) -> List[float]:
     total = float(sum(s.batch_count for s in snapshots))
     n = len(snapshots)
-    weights = [s.batch_count / total for s in snapshots] if total > 0 else [1.0 / n] * n
-    params = []
-    for i in range(len(snapshots[0].params)):
-        acc = snapshots[0].params[i].detach().to("cpu", torch.float32) * weights[0]
-        for s, w in zip(snapshots[1:], weights[1:]):
-            acc.add_(s.params[i].detach().to("cpu", torch.float32), alpha=w)
-        params.append(acc.to(snapshots[0].params[i].dtype))
+    return [s.batch_count / total for s in snapshots] if total > 0 else [1.0 / n] * n
+
+
+def _average_buffers(snapshots: Sequence[ParamSnapshot]) -> List[torch.Tensor]:
+    n = len(snapshots)
     buffers = []
     for i in range(len(snapshots[0].buffers)):
         b0 = snapshots[0].buffers[i].detach().cpu()
@@ -114,24 +108,62 @@ def average_params(snapshots: Sequence[ParamSnapshot], version: int) -> Averaged
             buffers.append(acc.to(b0.dtype))
         else:
             buffers.append(b0.clone())
-    return AveragedParams(params, buffers, version)
+    return buffers
+
+
+def average_params(snapshots: Sequence[ParamSnapshot], version: int) -> AveragedParams:
+    """Batch-count-weighted mean of parameters, equal-weight mean of buffers, on the host
+    (coordinator/cpu_avg.rs:540-599). Tensor operations only; `average_and_divergence` is what the coordinator runs."""
+    if not snapshots:
+        raise ValueError("average_params: no snapshots")
+    weights = _weights(snapshots)
+    params = []
+    for i in range(len(snapshots[0].params)):
+        acc = snapshots[0].params[i].detach().to("cpu", torch.float32) * weights[0]
+        for s, w in zip(snapshots[1:], weights[1:]):
+            acc.add_(s.params[i].detach().to("cpu", torch.float32), alpha=w)
+        params.append(acc.to(snapshots[0].params[i].dtype))
+    return AveragedParams(params, _average_buffers(snapshots), version)
 
 
 def divergence_of(snapshots: Sequence[ParamSnapshot], averaged: AveragedParams) -> DivergenceReport:
     """||pre - post|| / ||post|| per rank, plus the norms for the cosine decomposition."""
     post_sq = sum(float(p.double().pow(2).sum()) for p in averaged.params)
-    post = post_sq ** 0.5
-    deltas, pre = [0.0] * len(snapshots), [0.0] * len(snapshots)
+    deltas_sq, pre_sq = [], []
     for s in snapshots:
         d2 = p2 = 0.0
         for a, b in zip(s.params, averaged.params):
             a64 = a.detach().to("cpu", torch.float64)
             d2 += float((a64 - b.double()).pow(2).sum())
             p2 += float(a64.pow(2).sum())
+        deltas_sq.append(d2)
+        pre_sq.append(p2)
+    return _report(snapshots, deltas_sq, pre_sq, post_sq)
+
+
+def _report(snapshots: Sequence[ParamSnapshot], deltas_sq: Sequence[float], pre_sq: Sequence[float], post_sq: float) -> DivergenceReport:
+    post = post_sq ** 0.5
+    deltas, pre = [0.0] * len(snapshots), [0.0] * len(snapshots)
+    for s, d2, p2 in zip(snapshots, deltas_sq, pre_sq):
         r = min(s.rank, len(snapshots) - 1)
         deltas[r] = (d2 ** 0.5) / post if post > 1e-10 else 0.0
         pre[r] = p2 ** 0.5
     return DivergenceReport(deltas, pre, post)
+
+
+def average_and_divergence(snapshots: Sequence[ParamSnapshot], version: int) -> Tuple[AveragedParams, DivergenceReport]:
+    """The mean and the divergence report of one averaging round. With the native library this is a single threaded pass
+    over the snapshots (`cpu_weighted_average`, csrc/runtime/cpu_avg.cpp): every element is read once, the mean written
+    once, the norms accumulated on the way, with the interpreter lock released. Without it, the two functions above."""
+    if not snapshots:
+        raise ValueError("average_and_divergence: no snapshots")
+    from ... import _ext
+    if _ext.available() and hasattr(_ext.require(), "cpu_weighted_average"):
+        per_rank = [[p.detach() if p.device.type == "cpu" else p.detach().cpu() for p in s.params] for s in snapshots]
+        params, d2, p2, post2 = _ext.require().cpu_weighted_average(per_rank, _weights(snapshots), True)
+        return AveragedParams(list(params), _average_buffers(snapshots), version), _report(snapshots, d2, p2, post2)
+    avg = average_params(snapshots, version)
+    return avg, divergence_of(snapshots, avg)
 
 
 class CoordinatorBuilder:
@@ -704,9 +736,7 @@ class Coordinator:
 
                 def work():
                     try:
-                        avg = average_params(snaps, version)
-                        result["avg"] = avg
-                        result["div"] = divergence_of(snaps, avg)
+                        result["avg"], result["div"] = average_and_divergence(snaps, version)
                     except BaseException as e:  # surfaced by the poll below
                         result["err"] = e
 

@@ -519,3 +519,44 @@ def test_builder_requires_dataset_batch_size_epochs():
 @pytest.mark.parametrize("scenario", ["run_fixed", "run_cadence", "run_sync", "run_cpu_backend", "run_worker_failure"])
 def test_processes_over_gloo(scenario):
     run_ranks(scenario)
+
+
+def test_native_average_and_divergence_matches_the_tensor_op_path():
+    """One pass in C++ against the reference arithmetic with tensor operations: fp32 fast path across block and thread
+    boundaries, a non-contiguous and a bf16 tensor through the generic path, rank order, weights, buffers."""
+    from flodl_b200 import _ext
+    from flodl_b200.parallel.ddp_run import average_and_divergence
+    if not _ext.available():
+        pytest.skip("native extension not built")
+    g = torch.Generator().manual_seed(3)
+    shapes = [(16384 * 3 + 17,), (129, 65), (1,), (7, 5, 3), (40000,)]
+
+    def snap(rank, count):
+        ps = [torch.randn(s, generator=g) * (1 + rank) for s in shapes]
+        ps[1] = ps[1].t().contiguous().t()                          # same shape, not contiguous
+        ps[3] = ps[3].to(torch.bfloat16)
+        bufs = [torch.randn(9, generator=g), torch.tensor(rank + 4)]
+        return ParamSnapshot(rank, ps, bufs, count)
+    snaps = [snap(2, 5), snap(0, 1), snap(1, 10)]                   # arrival order differs from rank order
+    ref = average_params(snaps, 4)
+    ref_div = divergence_of(snaps, ref)
+    avg, div = average_and_divergence(snaps, 4)
+    assert avg.version == 4 and len(avg.params) == len(shapes)
+    for a, b in zip(avg.params, ref.params):
+        assert a.dtype == b.dtype and a.shape == b.shape
+        torch.testing.assert_close(a.float(), b.float(), rtol=1e-6, atol=1e-6)
+    for a, b in zip(avg.buffers, ref.buffers):
+        assert torch.equal(a, b)
+    assert div.deltas == pytest.approx(ref_div.deltas, rel=1e-5) and div.pre_norms == pytest.approx(ref_div.pre_norms, rel=1e-6)
+    assert div.post_norm == pytest.approx(ref_div.post_norm, rel=1e-6)
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)                                        # the sums do not depend on the number of threads
+    try:
+        _, div1 = average_and_divergence(snaps, 4)
+    finally:
+        torch.set_num_threads(threads)
+    assert div1.deltas == div.deltas and div1.post_norm == div.post_norm
+    with pytest.raises(RuntimeError, match="shape"):
+        _ext.require().cpu_weighted_average([[torch.zeros(3)], [torch.zeros(4)]], [0.5, 0.5], True)
+    with pytest.raises(RuntimeError, match="weights"):
+        _ext.require().cpu_weighted_average([[torch.zeros(3)]], [0.5, 0.5], True)
