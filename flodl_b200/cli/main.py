@@ -10,7 +10,7 @@ from dataclasses import dataclass
 from typing import List, Optional
 
 from .args import ArgError, FdlArgs, arg
-from .manifest import ManifestError, adopt_template, env_from_first_word, find_manifest, load_manifest, run_command
+from .manifest import ManifestError, adopt_template, command_kind, env_from_first_word, find_manifest, load_manifest, manifest_in, run_command
 
 BUILTINS = ["diagnose", "setup", "install", "libtorch", "build", "bench", "export-hf", "api-ref", "schema", "completions", "autocomplete", "config", "init",
             "add", "skill", "help"]
@@ -367,15 +367,22 @@ def usage(manifest: Optional[str]) -> str:
              "  add [dir]               add a training scaffold to an existing directory",
              "  setup [--force]         check the machine and build the native library",
              "  install [--check|--dev] build and verify the native library",
-             "  libtorch info|list|path which libtorch this process uses",
+             "  libtorch <verb>         info | list | path | activate | download | build | remove: the libtorch variants under libtorch/",
              "  skill show|install      the assistant guide (condensed API and porting reference)"]
     if manifest:
         try:
             cmds = load_manifest(manifest)[0].get("commands") or {}
             if cmds:
                 lines += ["", f"commands from {manifest}:"]
+                here = os.path.dirname(os.path.abspath(manifest))
                 for k, v in cmds.items():
                     desc = (v or {}).get("description", "") if isinstance(v, dict) or v is None else ""
+                    if not desc and command_kind(k, v, here) == "path":       # a sub-project: its own manifest describes it
+                        child = manifest_in(os.path.join(here, (v or {}).get("path", k)))
+                        try:
+                            desc = (load_manifest(child)[0].get("description") or "") if child else ""
+                        except ManifestError:
+                            desc = ""
                     lines.append(f"  {k:<23} {desc}")
         except ManifestError as e:
             lines += ["", f"(manifest error: {e})"]

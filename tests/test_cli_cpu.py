@@ -546,3 +546,16 @@ def test_update_check_reads_a_feed_and_never_disturbs_the_command(tmp_path, monk
         assert "9.0.0 is available" in err and os.path.isfile(tmp_path / "cfg" / "flodl" / "config.json")
     finally:
         srv.shutdown()
+
+
+def test_help_describes_a_sub_project_by_its_own_manifest(tmp_path, monkeypatch, capsys):
+    (tmp_path / "fdl.yml").write_text("commands:\n  tools:\n  other:\n    path: elsewhere\n  hello:\n    run: echo hi\n    description: says hi\n")
+    (tmp_path / "tools").mkdir()
+    (tmp_path / "tools" / "fdl.yml").write_text("description: the tool box\nentry: python tool.py\n")
+    (tmp_path / "elsewhere").mkdir()
+    (tmp_path / "elsewhere" / "fdl.yml").write_text("description: lives elsewhere\nentry: python x.py\n")
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("FDL_NO_UPDATE_CHECK", "1")
+    assert main(["--help"]) == 0
+    out = capsys.readouterr().out
+    assert "the tool box" in out and "lives elsewhere" in out and "says hi" in out
