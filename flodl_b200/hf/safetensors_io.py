@@ -35,11 +35,19 @@ def parse_header(data: bytes) -> Tuple[Dict[str, dict], int]:
         header = json.loads(data[8:8 + n].decode("utf-8"))
     except Exception as e:
         raise TensorError(f"safetensors parse error: {e}")
+    if not isinstance(header, dict):
+        raise TensorError("safetensors parse error: the header is not a JSON object")
     header.pop("__metadata__", None)
     base = 8 + n
     for name, info in header.items():
-        a, b = info["data_offsets"]
-        if a > b or base + b > len(data):
+        offs = info.get("data_offsets") if isinstance(info, dict) else None
+        shape = info.get("shape") if isinstance(info, dict) else None
+        if (not isinstance(info.get("dtype") if isinstance(info, dict) else None, str) or not isinstance(offs, list) or len(offs) != 2
+                or not all(isinstance(x, int) and not isinstance(x, bool) for x in offs) or not isinstance(shape, list)
+                or not all(isinstance(x, int) and not isinstance(x, bool) and x >= 0 for x in shape)):
+            raise TensorError(f"safetensors parse error: entry {name!r} needs a string `dtype`, a `shape` of non-negative integers and two integer `data_offsets`")
+        a, b = offs
+        if a < 0 or a > b or base + b > len(data):
             raise TensorError(f"safetensors parse error: tensor {name!r} data range [{a}, {b}) is outside the file")
     return header, base
 
@@ -78,7 +86,7 @@ def write_safetensors(tensors: Dict[str, torch.Tensor], metadata: Optional[Dict[
         t = tensors[k].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise TensorError(f"save_safetensors: dtype {t.dtype} of {k!r} not supported — only floating-point parameters / buffers can be serialised")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # reshape: a 0-dim tensor cannot be viewed as bytes
         header[k] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)

@@ -185,3 +185,49 @@ def test_corrupt_headers_are_rejected_before_anything_is_allocated():
             C.fdl_load_bytes(bad, False)
     # key listings skip the payloads instead of reading them
     assert [k for k, _ in C.fdl_load_bytes(ok, True)[2]] == ["w"]
+
+
+def test_reader_survives_random_damage():
+    """Property test of the native reader: a valid file with bytes flipped, cut short, or with a stretch overwritten by
+    random data either loads (same number of records, sane shapes) or is refused with an ordinary error. It never takes
+    the process down and never allocates more than the file could hold."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    from flodl_b200 import _ext
+    C = _ext.require()
+
+    def record(name, shape, tag, payload):
+        out = struct.pack("<I", len(name)) + name + struct.pack("<I", len(shape)) + b"".join(struct.pack("<q", d) for d in shape)
+        return out + struct.pack("<BQ", tag, len(payload)) + payload
+    good = (b"FDLC" + struct.pack("<I", 2) + b"\0" * 32 + struct.pack("<I", 3) + record(b"a.weight", [3, 4], 3, bytes(range(48)))
+            + record(b"a.bias", [4], 3, bytes(16)) + record(b"steps", [], 3, bytes(4)))
+    assert len(C.fdl_load_bytes(good, False)[2]) == 3
+
+    damage = st.one_of(
+        st.tuples(st.just("flip"), st.integers(0, len(good) - 1), st.integers(1, 255)),
+        st.tuples(st.just("cut"), st.integers(0, len(good) - 1), st.just(0)),
+        st.tuples(st.just("noise"), st.integers(0, len(good) - 1), st.binary(min_size=1, max_size=24)))
+
+    @settings(max_examples=400, deadline=None, derandomize=True, database=None)
+    @given(st.lists(damage, min_size=1, max_size=3))
+    def run(edits):
+        data = bytearray(good)
+        for kind, at, arg in edits:
+            at = min(at, max(len(data) - 1, 0))
+            if not data:
+                break
+            if kind == "flip":
+                data[at] ^= arg
+            elif kind == "cut":
+                del data[at:]
+            else:
+                data[at:at + len(arg)] = arg
+        for keys_only in (False, True):
+            try:
+                recs = C.fdl_load_bytes(bytes(data), keys_only)[2]
+            except (RuntimeError, ValueError, UnicodeDecodeError, OverflowError):
+                continue
+            for _, t in recs:
+                assert t is None or t.numel() * t.element_size() <= len(data)
+    run()

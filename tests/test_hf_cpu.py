@@ -672,3 +672,44 @@ def test_finetune_example_lowers_the_loss_and_exports(tmp_path):
     assert curve[-1] < 0.5 * curve[0] and preds == ["pos", "neg", "pos", "neg"]
     rep = verify_export.verify(out_dir, no_hub_source=True)
     assert rep["ok"] and rep["architecture"] == "BertForSequenceClassification"
+
+
+def test_safetensors_reader_refuses_damaged_files_cleanly():
+    """Random damage to a valid file, and hand-made hostile headers: the reader loads or raises TensorError, nothing else."""
+    import json as _json, struct as _struct
+    pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    from flodl_b200.hf.safetensors_io import read_safetensors, write_safetensors
+    from flodl_b200.tensor import TensorError
+    good = write_safetensors({"a.weight": torch.arange(12.0).view(3, 4), "a.bias": torch.zeros(4, dtype=torch.bfloat16), "s": torch.tensor(2.0)})
+    assert set(read_safetensors(good)) == {"a.weight", "a.bias", "s"}
+
+    def with_header(h, payload=b"\\0" * 64):
+        raw = _json.dumps(h).encode()
+        return _struct.pack("<Q", len(raw)) + raw + payload
+    for hostile in ([1, 2], {"w": 3}, {"w": {"dtype": "F32", "shape": [2], "data_offsets": [-8, 0]}}, {"w": {"dtype": "F32", "shape": [-2, -4], "data_offsets": [0, 32]}},
+                    {"w": {"dtype": "F32", "shape": [2]}}, {"w": {"dtype": 7, "shape": [2], "data_offsets": [0, 8]}}, {"w": {"dtype": "F32", "shape": [1 << 62, 4], "data_offsets": [0, 8]}},
+                    {"w": {"dtype": "F32", "shape": "2", "data_offsets": [0, 8]}}, {"w": {"dtype": "F32", "shape": [2], "data_offsets": [0, 1 << 40]}}):
+        with pytest.raises(TensorError):
+            read_safetensors(with_header(hostile))
+
+    @settings(max_examples=300, deadline=None, derandomize=True, database=None)
+    @given(st.lists(st.tuples(st.sampled_from(["flip", "cut", "noise"]), st.integers(0, len(good) - 1), st.binary(min_size=1, max_size=16)), min_size=1, max_size=3))
+    def run(edits):
+        data = bytearray(good)
+        for kind, at, arg in edits:
+            if not data:
+                break
+            at = min(at, len(data) - 1)
+            if kind == "flip":
+                data[at] ^= arg[0] or 1
+            elif kind == "cut":
+                del data[at:]
+            else:
+                data[at:at + len(arg)] = arg
+        try:
+            out = read_safetensors(bytes(data))
+        except TensorError:
+            return
+        assert all(t.numel() * t.element_size() <= len(data) for t in out.values())
+    run()
